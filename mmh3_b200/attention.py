@@ -1,0 +1,354 @@
+"""Attention over the DiT's fused qkv projection output, through the library's C ABI.
+
+The functions and workspaces here mirror the safe wrappers of niw/mmh3's CUDA crate
+(crates/mmh3-cuda/src/attention.rs): the same names, argument meaning, buffer sizes and bounds
+checks, with `torch` tensors standing where the crate has `DeviceBuffer`s. Every call goes through
+`extern "C"` entry points with raw device pointers; torch only owns the memory and the stream.
+A failing call raises `CudaError` with the cudaError_t the entry point returned.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import enum
+
+import torch
+
+from . import _lib
+from .vsa import VSA_TILE, VsaPlan
+
+HEAD_DIM = 128
+SPARSE_BLOCK = 64
+
+
+class CudaError(RuntimeError):
+    def __init__(self, code: int, call: str):
+        super().__init__(f"{call} returned cudaError {code}")
+        self.code = code
+
+
+def check(code: int, call: str) -> None:
+    if code != 0:
+        raise CudaError(code, call)
+
+
+class AttentionInputs(enum.IntEnum):
+    """Where the attention finds its per-block inputs (attention.rs:495-514)."""
+
+    RAW = 0
+    PREPARED = 1
+    PREPARED_WITH_VALUES = 2
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _pointer(tensor: torch.Tensor | None, offset_elements: int = 0) -> ctypes.c_void_p:
+    if tensor is None:
+        return ctypes.c_void_p(0)
+    assert tensor.is_cuda and tensor.is_contiguous()
+    return ctypes.c_void_p(tensor.data_ptr() + offset_elements * tensor.element_size())
+
+
+def make_layout(token_stride, head_stride=(HEAD_DIM,) * 4, batch_stride=(0,) * 4,
+                heads_per_key_value: int = 0, causal: int = 0) -> _lib.AttentionLayout:
+    layout = _lib.AttentionLayout()
+    for index in range(4):
+        layout.token_stride[index] = token_stride[index]
+        layout.head_stride[index] = head_stride[index]
+        layout.batch_stride[index] = batch_stride[index]
+    layout.heads_per_key_value = heads_per_key_value
+    layout.causal = causal
+    return layout
+
+
+def qkv_layout(heads: int) -> _lib.AttentionLayout:
+    """The DiT's layout: qkv [tokens, 3, heads, 128] and output [tokens, heads, 128]."""
+    inner = heads * HEAD_DIM
+    return make_layout((3 * inner, 3 * inner, 3 * inner, inner))
+
+
+def take_status() -> int:
+    """Synchronizes and returns the kernels' status word: 0 unless a bounded wait ran out."""
+    return _lib.library().mmh3_b200_take_status()
+
+
+# -------------------------------------------------------------------------------------------------
+# Dense BF16
+
+
+def attention(element_type: int, head_dim: int, query: torch.Tensor, key: torch.Tensor,
+              value: torch.Tensor, output: torch.Tensor, tokens: int, heads: int, batch: int,
+              layout: _lib.AttentionLayout, scale: float, offsets=(0, 0, 0, 0)) -> None:
+    """Softmax attention over tensors described by `layout` (attention.rs:371-435).
+
+    `query`, `key`, `value` and `output` are the buffers the operands live in, each starting
+    `offsets[i]` elements in. Every addressed element must lie inside its buffer.
+    """
+    group = max(layout.heads_per_key_value, 1)
+    if heads % group != 0:
+        raise ValueError("heads must be a multiple of the heads per key and value head")
+    buffers = (query, key, value, output)
+    for operand in range(4):
+        operand_heads = heads // group if operand in (1, 2) else heads
+        last = (offsets[operand] + (batch - 1) * layout.batch_stride[operand]
+                + (tokens - 1) * layout.token_stride[operand]
+                + (operand_heads - 1) * layout.head_stride[operand] + head_dim)
+        if last > buffers[operand].numel():
+            raise ValueError(f"operand {operand} reaches past its buffer")
+    check(
+        _lib.library().mmh3_attention(
+            element_type, head_dim, _pointer(query, offsets[0]), _pointer(key, offsets[1]),
+            _pointer(value, offsets[2]), _pointer(output, offsets[3]), tokens, heads, batch,
+            ctypes.byref(layout), scale, _stream()),
+        "mmh3_attention",
+    )
+
+
+def dense_bf16(qkv: torch.Tensor, output: torch.Tensor, tokens: int, heads: int,
+               scale: float) -> None:
+    """Dense bidirectional attention with head dimension 128 (attention.rs:469-493).
+
+    `qkv` is BF16 [tokens, 3, heads, 128] as the fused projection leaves it and `output` receives
+    BF16 [tokens, heads, 128].
+    """
+    inner = heads * HEAD_DIM
+    if qkv.numel() < tokens * 3 * inner:
+        raise ValueError("qkv is smaller than tokens x 3 x heads x 128")
+    if output.numel() < tokens * inner:
+        raise ValueError("output is smaller than tokens x heads x 128")
+    assert qkv.dtype == torch.bfloat16 and output.dtype == torch.bfloat16
+    check(
+        _lib.library().mmh3_attention_bf16(
+            _pointer(qkv), _pointer(qkv, inner), _pointer(qkv, 2 * inner), _pointer(output),
+            tokens, heads, 3 * inner, 3 * inner, 3 * inner, inner, scale, _stream()),
+        "mmh3_attention_bf16",
+    )
+
+
+# -------------------------------------------------------------------------------------------------
+# Quantized
+
+
+class QuantizedWorkspace:
+    """Scratch for one sequence of INT8/FP8 attention, reused across layers (attention.rs:61-140)."""
+
+    def __init__(self, tokens: int, heads: int, blocks: int | None = None, device="cuda"):
+        if not (0 < tokens <= 2**31 - 64 and 0 < heads <= 65535):
+            raise ValueError("invalid attention shape")
+        self.tokens, self.heads = tokens, heads
+        self.blocks = blocks if blocks is not None else -(-tokens // SPARSE_BLOCK)
+        rows = tokens * heads * HEAD_DIM
+        byte = dict(dtype=torch.uint8, device=device)
+        real = dict(dtype=torch.float32, device=device)
+        self.query = torch.empty(rows, **byte)
+        self.key = torch.empty(rows, **byte)
+        self.value = torch.empty(self.blocks * SPARSE_BLOCK * heads * HEAD_DIM, **byte)
+        self.query_scales = torch.empty(heads * self.blocks, **real)
+        self.key_scales = torch.empty(heads * self.blocks, **real)
+        self.value_scales = torch.empty(heads, **real)
+        self.value_maxima = torch.empty(heads * self.blocks, **real)
+        self.value_head_maxima = torch.zeros(heads, **real)
+
+    def raw(self) -> _lib.QuantizedWorkspaceStruct:
+        return _lib.QuantizedWorkspaceStruct(
+            self.query.data_ptr(), self.key.data_ptr(), self.value.data_ptr(),
+            self.query_scales.data_ptr(), self.key_scales.data_ptr(),
+            self.value_scales.data_ptr(), self.value_maxima.data_ptr())
+
+
+def dense_quantized(qkv: torch.Tensor, output: torch.Tensor, scale: float,
+                    workspace: QuantizedWorkspace,
+                    inputs: AttentionInputs = AttentionInputs.RAW) -> None:
+    """Dense attention with INT8 QK and FP8 PV (attention.rs:778-817)."""
+    tokens, heads = workspace.tokens, workspace.heads
+    inner = heads * HEAD_DIM
+    if qkv.numel() < tokens * 3 * inner or output.numel() < tokens * inner:
+        raise ValueError("qkv or output is smaller than the workspace's sequence")
+    layout = qkv_layout(heads)
+    raw = workspace.raw()
+    check(
+        _lib.library().mmh3_attention_quantized(
+            _pointer(qkv), _pointer(qkv, inner), _pointer(qkv, 2 * inner), _pointer(output),
+            tokens, heads, ctypes.byref(layout), scale, None, ctypes.byref(raw), int(inputs),
+            _stream()),
+        "mmh3_attention_quantized",
+    )
+
+
+class HeadNorm:
+    """Per-head RMSNorm weights of q and k and the rotary angles of every token."""
+
+    def __init__(self, query_weight: torch.Tensor, key_weight: torch.Tensor,
+                 angles: torch.Tensor | None, pairs: int, epsilon: float):
+        if query_weight.numel() < HEAD_DIM or key_weight.numel() < HEAD_DIM:
+            raise ValueError("the norm weights hold 128 BF16 values")
+        if 2 * pairs > HEAD_DIM:
+            raise ValueError("the rotary pairs exceed the head")
+        self.query_weight, self.key_weight = query_weight, key_weight
+        self.angles, self.pairs, self.epsilon = angles, pairs, epsilon
+
+    def check(self, qkv: torch.Tensor, tokens: int, heads: int) -> None:
+        if qkv.numel() < tokens * 3 * heads * HEAD_DIM:
+            raise ValueError("qkv is smaller than tokens x 3 x heads x 128")
+        if self.angles is not None and self.angles.numel() < tokens * self.pairs:
+            raise ValueError("the angles do not cover every token")
+
+
+def qk_norm_rope(qkv: torch.Tensor, norm: HeadNorm, tokens: int, heads: int) -> None:
+    """Per-head RMSNorm of q and k in [tokens, 3, heads, 128] rows, then RoPE, in place."""
+    norm.check(qkv, tokens, heads)
+    check(
+        _lib.library().mmh3_qk_norm_rope(
+            _pointer(qkv), _pointer(norm.query_weight), _pointer(norm.key_weight),
+            _pointer(norm.angles), norm.pairs, tokens, heads, heads, norm.epsilon, _stream()),
+        "mmh3_qk_norm_rope",
+    )
+
+
+# -------------------------------------------------------------------------------------------------
+# Video sparse attention
+
+
+class VsaWorkspace:
+    """The tiles of one VSA plan and scratch for its sequence and heads (attention.rs:975-1110)."""
+
+    def __init__(self, plan: VsaPlan, tokens: int, heads: int, quantized: bool = False,
+                 device="cuda"):
+        tiles = plan.tiles
+        if not 0 < tiles <= 65536:
+            raise ValueError(f"invalid tile count {tiles}")
+        if not all(1 <= length <= VSA_TILE for length in plan.tile_lengths) or not all(
+                start + length <= tokens
+                for start, length in zip(plan.tile_starts, plan.tile_lengths)):
+            raise ValueError("the plan's tiles do not fit the sequence")
+        self.tokens, self.heads, self.tiles = tokens, heads, tiles
+        self.prefix_tiles = plan.prefix_tiles
+        self.quantized = (QuantizedWorkspace(tokens, heads, blocks=tiles, device=device)
+                          if quantized else None)
+        self.tile_starts = torch.tensor(plan.tile_starts, dtype=torch.int32, device=device)
+        self.tile_lengths = torch.tensor(plan.tile_lengths, dtype=torch.int32, device=device)
+        per_tile = heads * tiles * HEAD_DIM
+        real = dict(dtype=torch.float32, device=device)
+        self.pooled_query = torch.empty(per_tile, **real)
+        self.pooled_key = torch.empty(per_tile, **real)
+        self.pooled_value = torch.empty(per_tile, **real)
+        self.routes = torch.empty(heads * tiles * tiles, dtype=torch.int16, device=device)
+        self.route_counts = torch.zeros(heads * tiles, dtype=torch.int32, device=device)
+        self.coarse = torch.empty(per_tile, **real)
+
+    def raw(self) -> _lib.VsaWorkspaceStruct:
+        return _lib.VsaWorkspaceStruct(
+            self.tile_starts.data_ptr(), self.tile_lengths.data_ptr(),
+            self.pooled_query.data_ptr(), self.pooled_key.data_ptr(),
+            self.pooled_value.data_ptr(), self.routes.data_ptr(), self.route_counts.data_ptr(),
+            self.coarse.data_ptr())
+
+    def sparse_raw(self) -> _lib.SparseWorkspace:
+        """The pooled buffers under the names the fused input pass writes them by."""
+        workspace = _lib.SparseWorkspace()
+        workspace.centroids = self.pooled_query.data_ptr()
+        workspace.block_keys = self.pooled_key.data_ptr()
+        workspace.value_sums = self.pooled_value.data_ptr()
+        return workspace
+
+    def selected_fraction(self) -> float:
+        """Mean fraction of the tiles the query tiles of the last call attended token by token."""
+        selected = int(self.route_counts.to(torch.int64).sum().item())
+        return selected / (self.heads * self.tiles * self.tiles)
+
+    def routes_host(self):
+        """Routes [heads, tiles, tiles] as uint16 and counts [heads, tiles], on the host."""
+        routes = self.routes.cpu().numpy().view("uint16").reshape(self.heads, self.tiles,
+                                                                 self.tiles)
+        counts = self.route_counts.cpu().numpy().reshape(self.heads, self.tiles)
+        return routes, counts
+
+
+def prepare_inputs(qkv: torch.Tensor, norm: HeadNorm, tokens: int, heads: int,
+                   quantized: QuantizedWorkspace | None = None, vsa: VsaWorkspace | None = None,
+                   value_head_maxima: torch.Tensor | None = None) -> None:
+    """qk_norm_rope fused with the attention's per-block work (attention.rs:670-760).
+
+    With `vsa`, the blocks are its tiles, its pooled buffers are filled, and its own quantized
+    workspace (if any) is used.
+    """
+    norm.check(qkv, tokens, heads)
+    if vsa is not None and vsa.quantized is not None:
+        quantized = vsa.quantized
+    sparse = vsa.sparse_raw() if vsa is not None else None
+    raw = quantized.raw() if quantized is not None else None
+    check(
+        _lib.library().mmh3_attention_inputs(
+            _pointer(qkv), _pointer(norm.query_weight), _pointer(norm.key_weight),
+            _pointer(norm.angles), norm.pairs, tokens, heads, norm.epsilon,
+            ctypes.byref(sparse) if sparse is not None else None,
+            ctypes.byref(raw) if raw is not None else None,
+            _pointer(vsa.tile_starts) if vsa is not None else None,
+            _pointer(vsa.tile_lengths) if vsa is not None else None,
+            vsa.tiles if vsa is not None else 0, _pointer(value_head_maxima), _stream()),
+        "mmh3_attention_inputs",
+    )
+
+
+def vsa(qkv: torch.Tensor, gate: torch.Tensor | None, output: torch.Tensor,
+        layout: _lib.AttentionLayout, scale: float, kept: int, workspace: VsaWorkspace,
+        inputs: AttentionInputs = AttentionInputs.RAW, offsets=None) -> None:
+    """VSA over BF16 heads of 128 in the workspace's tile order (attention.rs:1189-1250).
+
+    `gate`, BF16 [tokens, heads, 128], adds the coarse branch.
+    """
+    tokens, heads = workspace.tokens, workspace.heads
+    inner = heads * HEAD_DIM
+    if offsets is None:
+        offsets = (0, inner, 2 * inner, 0)
+    for operand in range(4):
+        buffer = output if operand == 3 else qkv
+        last = (offsets[operand] + (tokens - 1) * layout.token_stride[operand]
+                + (heads - 1) * layout.head_stride[operand] + HEAD_DIM)
+        if last > buffer.numel():
+            raise ValueError(f"operand {operand} reaches past its buffer")
+    if gate is not None and gate.numel() < tokens * inner:
+        raise ValueError("the gate is smaller than tokens x heads x 128")
+    if workspace.quantized is not None and inputs == AttentionInputs.RAW:
+        raise ValueError("quantized VSA needs prepared inputs")
+    raw = workspace.raw()
+    quantized = workspace.quantized.raw() if workspace.quantized is not None else None
+    check(
+        _lib.library().mmh3_vsa_attention(
+            _pointer(qkv, offsets[0]), _pointer(qkv, offsets[1]), _pointer(qkv, offsets[2]),
+            _pointer(gate), inner, _pointer(output, offsets[3]), tokens, heads,
+            ctypes.byref(layout), scale, workspace.tiles, workspace.prefix_tiles, kept,
+            ctypes.byref(raw), ctypes.byref(quantized) if quantized is not None else None,
+            int(inputs), _stream()),
+        "mmh3_vsa_attention",
+    )
+
+
+# -------------------------------------------------------------------------------------------------
+# Ulysses layout changes
+
+
+def shard_pack(source: torch.Tensor, packed: torch.Tensor, tokens: int, tensors: int, heads: int,
+               first_head: int, span: int, dim: int = HEAD_DIM) -> None:
+    """[tokens][tensors][heads][dim] -> [tokens][tensors][span][dim] at `first_head`."""
+    if source.numel() < tokens * tensors * heads * dim or packed.numel() < tokens * tensors * span * dim:
+        raise ValueError("a buffer is smaller than its shape")
+    check(
+        _lib.library().mmh3_dit_shard_pack(_pointer(source), _pointer(packed), tokens, tensors,
+                                           heads, dim, first_head, span, _stream()),
+        "mmh3_dit_shard_pack",
+    )
+
+
+def shard_unpack(part: torch.Tensor, output: torch.Tensor, tokens: int, heads: int,
+                 first_head: int, span: int, dim: int = HEAD_DIM) -> None:
+    """[tokens][span][dim] -> [tokens][heads][dim] at `first_head`."""
+    if part.numel() < tokens * span * dim or output.numel() < tokens * heads * dim:
+        raise ValueError("a buffer is smaller than its shape")
+    check(
+        _lib.library().mmh3_dit_shard_unpack(_pointer(part), _pointer(output), tokens, heads, dim,
+                                             first_head, span, _stream()),
+        "mmh3_dit_shard_unpack",
+    )

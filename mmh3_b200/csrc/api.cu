@@ -1,0 +1,184 @@
+// The extern "C" entry points of libmmh3_attn_b200.so: argument checks in the reference's terms,
+// then the launchers. Declarations and the reference function each one replaces are in
+// include/mmh3_attention.h.
+#include "common.cuh"
+
+using namespace mmh3;
+
+extern "C" int mmh3_attention_roped(int element_type, int head_dim, const void *query,
+                                    const void *key, const void *value, void *output, int tokens,
+                                    int heads, int batch, const Mmh3AttentionLayout *layout,
+                                    float scale, const float *angles, int pairs, float epsilon,
+                                    mmh3_stream_t stream) {
+    (void)pairs;
+    (void)epsilon;
+    // crates/mmh3-cuda/kernels/attention.cu:507-510
+    if (layout == nullptr || tokens <= 0 || heads <= 0 || batch <= 0 ||
+        (layout->heads_per_key_value > 0 && heads % layout->heads_per_key_value != 0)) {
+        return INVALID_VALUE;
+    }
+    if ((element_type != 0 && element_type != 1) || (head_dim != 64 && head_dim != 128)) {
+        return INVALID_VALUE;
+    }
+    if (element_type != 0 || head_dim != 128 || layout->causal != 0 || angles != nullptr) {
+        return NOT_SUPPORTED;
+    }
+    return launch_dense_bf16(query, key, value, output, tokens, heads, batch, *layout, scale,
+                             as_stream(stream));
+}
+
+extern "C" int mmh3_attention(int element_type, int head_dim, const void *query, const void *key,
+                              const void *value, void *output, int tokens, int heads, int batch,
+                              const Mmh3AttentionLayout *layout, float scale,
+                              mmh3_stream_t stream) {
+    return mmh3_attention_roped(element_type, head_dim, query, key, value, output, tokens, heads,
+                                batch, layout, scale, nullptr, 0, 0.0f, stream);
+}
+
+extern "C" int mmh3_attention_bf16(const void *query, const void *key, const void *value,
+                                   void *output, int tokens, int heads, int64_t query_stride,
+                                   int64_t key_stride, int64_t value_stride, int64_t output_stride,
+                                   float scale, mmh3_stream_t stream) {
+    const Mmh3AttentionLayout layout = {{query_stride, key_stride, value_stride, output_stride},
+                                        {128, 128, 128, 128},
+                                        {0, 0, 0, 0},
+                                        1,
+                                        0};
+    return mmh3_attention(0, 128, query, key, value, output, tokens, heads, 1, &layout, scale,
+                          stream);
+}
+
+extern "C" int mmh3_qk_norm_rope(void *qkv, const void *query_weight, const void *key_weight,
+                                 const float *angles, int pairs, int tokens, int query_heads,
+                                 int key_heads, float epsilon, mmh3_stream_t stream) {
+    if (tokens <= 0 || query_heads < 0 || key_heads < 0 || pairs < 0 || 2 * pairs > HEAD_DIM) {
+        return INVALID_VALUE;
+    }
+    return launch_qk_norm_rope(static_cast<__nv_bfloat16 *>(qkv),
+                               static_cast<const __nv_bfloat16 *>(query_weight),
+                               static_cast<const __nv_bfloat16 *>(key_weight), angles, pairs,
+                               tokens, query_heads, key_heads, epsilon, as_stream(stream));
+}
+
+extern "C" int mmh3_attention_inputs(void *qkv, const void *query_weight, const void *key_weight,
+                                     const float *angles, int pairs, int tokens, int heads,
+                                     float epsilon, const Mmh3SparseWorkspace *sparse,
+                                     const Mmh3QuantizedWorkspace *quantized,
+                                     const int32_t *tile_starts, const int32_t *tile_lengths,
+                                     int tiles, const float *value_head_maxima,
+                                     mmh3_stream_t stream) {
+    // crates/mmh3-cuda/kernels/dit.cu:786-790
+    if (tokens <= 0 || heads <= 0 || (sparse == nullptr && quantized == nullptr) ||
+        (tile_starts != nullptr && (tile_lengths == nullptr || tiles <= 0)) ||
+        (value_head_maxima != nullptr && quantized == nullptr) || pairs < 0 ||
+        2 * pairs > HEAD_DIM) {
+        return INVALID_VALUE;
+    }
+    return launch_attention_inputs(static_cast<__nv_bfloat16 *>(qkv),
+                                   static_cast<const __nv_bfloat16 *>(query_weight),
+                                   static_cast<const __nv_bfloat16 *>(key_weight), angles, pairs,
+                                   tokens, heads, epsilon, sparse, quantized, tile_starts,
+                                   tile_lengths, tiles, value_head_maxima, as_stream(stream));
+}
+
+extern "C" int mmh3_attention_quantized(const void *query, const void *key, const void *value,
+                                        void *output, int tokens, int heads,
+                                        const Mmh3AttentionLayout *layout, float scale,
+                                        const Mmh3SparseWorkspace *sparse,
+                                        const Mmh3QuantizedWorkspace *workspace, int inputs_ready,
+                                        mmh3_stream_t stream) {
+    // crates/mmh3-cuda/kernels/quantized_attention.cu:581-583
+    if (layout == nullptr || workspace == nullptr || tokens <= 0 || heads <= 0 ||
+        layout->causal != 0 || layout->heads_per_key_value > 1 || inputs_ready < 0 ||
+        inputs_ready > 2) {
+        return INVALID_VALUE;
+    }
+    if (sparse != nullptr) {
+        return NOT_SUPPORTED;
+    }
+    const int prepared = launch_quantize(query, key, value, tokens, heads, *layout, *workspace,
+                                         nullptr, nullptr, 0, inputs_ready, as_stream(stream));
+    if (prepared != 0) {
+        return prepared;
+    }
+    return launch_quantized_attention(*workspace, output, tokens, heads, *layout, scale, nullptr,
+                                      0, nullptr, 0, as_stream(stream));
+}
+
+extern "C" int mmh3_vsa_attention_quantized(const void *value, const void *gate,
+                                            int64_t gate_stride, void *output, int tokens,
+                                            int heads, const Mmh3AttentionLayout *layout,
+                                            float scale, int tiles, const Mmh3VsaWorkspace *vsa,
+                                            const Mmh3QuantizedWorkspace *workspace,
+                                            int inputs_ready, mmh3_stream_t stream) {
+    // crates/mmh3-cuda/kernels/quantized_attention.cu:619-622
+    if (layout == nullptr || vsa == nullptr || workspace == nullptr || tokens <= 0 || heads <= 0 ||
+        tiles <= 0 || layout->causal != 0 || layout->heads_per_key_value > 1) {
+        return INVALID_VALUE;
+    }
+    if (inputs_ready != 2) {
+        // INT8 q and k and the |v| maxima are there; FP8 V is still to be made.
+        const int prepared =
+            launch_quantize(nullptr, nullptr, value, tokens, heads, *layout, *workspace,
+                            vsa->tile_starts, vsa->tile_lengths, tiles, 1, as_stream(stream));
+        if (prepared != 0) {
+            return prepared;
+        }
+    }
+    return launch_quantized_attention(*workspace, output, tokens, heads, *layout, scale, vsa,
+                                      tiles, gate, gate_stride, as_stream(stream));
+}
+
+extern "C" int mmh3_vsa_attention(const void *query, const void *key, const void *value,
+                                  const void *gate, int64_t gate_stride, void *output, int tokens,
+                                  int heads, const Mmh3AttentionLayout *layout, float scale,
+                                  int tiles, int prefix_tiles, int kept,
+                                  const Mmh3VsaWorkspace *workspace,
+                                  const Mmh3QuantizedWorkspace *quantized, int inputs_ready,
+                                  mmh3_stream_t stream) {
+    // crates/mmh3-cuda/kernels/vsa_attention.cu:510-513
+    if (layout == nullptr || workspace == nullptr || tokens <= 0 || heads <= 0 || tiles <= 0 ||
+        tiles > 65536 || prefix_tiles < 0 || prefix_tiles > tiles || kept < 1 ||
+        (quantized != nullptr && !inputs_ready)) {
+        return INVALID_VALUE;
+    }
+    if (!inputs_ready) {
+        const int pooled =
+            launch_pool(query, key, value, heads, *layout, tiles, *workspace, as_stream(stream));
+        if (pooled != 0) {
+            return pooled;
+        }
+    }
+    const int selected = launch_select(*workspace, tiles, heads, prefix_tiles, kept, scale,
+                                       gate != nullptr, as_stream(stream));
+    if (selected != 0) {
+        return selected;
+    }
+    if (quantized != nullptr) {
+        return mmh3_vsa_attention_quantized(value, gate, gate_stride, output, tokens, heads, layout,
+                                            scale, tiles, workspace, quantized, inputs_ready,
+                                            stream);
+    }
+    return launch_vsa_attention(query, key, value, gate, gate_stride, output, tokens, heads,
+                                *layout, scale, tiles, *workspace, as_stream(stream));
+}
+
+extern "C" int mmh3_sparse_attention(const void *, const void *, const void *, void *, int, int,
+                                     const Mmh3AttentionLayout *, float, float, int, int, int, int,
+                                     const Mmh3SparseWorkspace *, const Mmh3QuantizedWorkspace *,
+                                     int, mmh3_stream_t) {
+    return NOT_SUPPORTED;
+}
+
+extern "C" int mmh3_dit_shard_pack(const void *source, void *packed, int tokens, int tensors,
+                                   int heads, int dim, int first_head, int span,
+                                   mmh3_stream_t stream) {
+    return launch_shard_pack(source, packed, tokens, tensors, heads, dim, first_head, span,
+                             as_stream(stream));
+}
+
+extern "C" int mmh3_dit_shard_unpack(const void *part, void *output, int tokens, int heads,
+                                     int dim, int first_head, int span, mmh3_stream_t stream) {
+    return launch_shard_unpack(part, output, tokens, heads, dim, first_head, span,
+                               as_stream(stream));
+}

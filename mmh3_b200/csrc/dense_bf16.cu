@@ -1,0 +1,470 @@
+// Dense non-causal BF16 attention for heads of 128 on sm_100a: softmax(Q K^T * scale) V with FP32
+// accumulation and softmax and BF16 output. Computes what the reference's attention_kernel
+// (crates/mmh3-cuda/kernels/attention.cu:122-381) computes, with another design:
+//
+// A CTA owns two tiles of 128 query rows of one head and walks the keys in blocks of 128.
+//
+// - Warp 8 (one thread) streams the tiles with TMA into 128-byte-swizzled shared memory: the two
+//   query tiles once, then K0, V0, K1, V1, ... through a ring of five 32 KiB stages.
+// - Warp 9 (one thread) issues the tcgen05 MMAs. S = Q K^T (128 x 128, FP32) of each query tile
+//   lands in tensor memory; O += P V accumulates there too, with P read from tensor memory. The
+//   two query tiles alternate, so the tensor cores work on one while the softmax of the other runs.
+// - Warps 0-3 and 4-7 are the softmax of tile 0 and tile 1, one thread per query row (a row is one
+//   TMEM lane, so no reduction crosses threads). A thread reads its row of S, keeps the running
+//   maximum and sum, writes P as BF16 over the first half of the S columns it has just read, and
+//   rescales its row of O only when the maximum has grown by more than 2^8, which the final
+//   division by the row sum makes exact again.
+//
+// Tensor memory: S0 | S1 | O0 | O1, 128 columns each, all 512 columns of the SM.
+#include <cfloat>
+#include <cmath>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace mmh3 {
+
+namespace {
+
+using namespace sm100;
+
+constexpr int TILE_M = 128;                   // query rows per tile, one per TMEM lane
+constexpr int QUERY_TILES = 2;                // query tiles per CTA
+constexpr int TILE_N = 128;                   // keys per block
+constexpr int STAGES = 5;                     // ring of K and V tiles
+constexpr int SLAB_BYTES = 128 * 128;         // 128 rows of 64 BF16
+constexpr int TILE_BYTES = 2 * SLAB_BYTES;    // a 128 x 128 BF16 tile as two slabs of 64 columns
+constexpr int SOFTMAX_WARPS = 4 * QUERY_TILES;
+constexpr int LOAD_WARP = SOFTMAX_WARPS;
+constexpr int MMA_WARP = SOFTMAX_WARPS + 1;
+// Warps 10 and 11 only fill the third warpgroup, whose registers go to the softmax warps.
+constexpr int THREADS = (SOFTMAX_WARPS + 4) * 32;
+constexpr int SOFTMAX_REGISTERS = 216;
+constexpr int OTHER_REGISTERS = 80;
+static_assert(SOFTMAX_WARPS * 32 * SOFTMAX_REGISTERS + 128 * OTHER_REGISTERS <= 65536,
+              "the register file is 64 Ki registers");
+
+constexpr int SMEM_QUERY = 0;
+constexpr int SMEM_RING = QUERY_TILES * TILE_BYTES;
+constexpr int SMEM_BARRIERS = SMEM_RING + STAGES * TILE_BYTES;
+// Barriers, then the TMEM base address and the abort flag. The extra 1024 bytes align the tiles.
+constexpr int SMEM_BYTES = SMEM_BARRIERS + 256 + 1024;
+
+enum Barrier {
+    QUERY_FULL = 0,
+    RING_FULL = 1,
+    RING_EMPTY = RING_FULL + STAGES,
+    SCORES_FULL = RING_EMPTY + STAGES,               // one per query tile
+    PROBABILITIES_FULL = SCORES_FULL + QUERY_TILES,  // one per query tile
+    OUTPUT_FULL = PROBABILITIES_FULL + QUERY_TILES,
+    BARRIERS = OUTPUT_FULL + 1,
+};
+static_assert(BARRIERS * 8 + 8 <= 256, "the barriers outgrew their corner of shared memory");
+
+constexpr uint32_t TMEM_COLUMNS = 512;
+constexpr uint32_t TMEM_SCORES = 0;    // + tile * 128
+constexpr uint32_t TMEM_OUTPUT = 256;  // + tile * 128
+
+constexpr uint32_t SCORE_MMA = instruction_descriptor(ACCUMULATE_F32, FORMAT_BF16, FORMAT_BF16, 0,
+                                                      0, TILE_M, TILE_N);
+constexpr uint32_t OUTPUT_MMA = instruction_descriptor(ACCUMULATE_F32, FORMAT_BF16, FORMAT_BF16, 0,
+                                                       1, TILE_M, HEAD_DIM);
+
+// The maximum may lag the true row maximum by this much (in log2 units) before O is rescaled.
+constexpr float RESCALE_THRESHOLD = 8.0f;
+
+struct DenseMaps {
+    CUtensorMap query;
+    CUtensorMap key;
+    CUtensorMap value;
+};
+
+// K-major descriptor of contraction step `step` (16 of the 128 dimensions) of a Q or K tile.
+__device__ __forceinline__ uint64_t row_operand(uint32_t tile, int step) {
+    return smem_descriptor(tile + (step / 4) * SLAB_BYTES + (step % 4) * 32, 16, 1024);
+}
+
+// MN-major descriptor of contraction step `step` (16 of the 128 keys) of a V tile: N runs along
+// the rows of both slabs.
+__device__ __forceinline__ uint64_t value_operand(uint32_t tile, int step) {
+    return smem_descriptor(tile + step * 16 * 128, SLAB_BYTES, 1024);
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+    dense_bf16_kernel(const __grid_constant__ DenseMaps maps, __nv_bfloat16 *__restrict__ output,
+                      int tokens, int heads_per_key_value, int64_t output_token_stride,
+                      int64_t output_head_stride, int vector_stores, float scale_log2,
+                      unsigned int *status) {
+    extern __shared__ uint8_t shared_memory[];
+    const uint32_t base = (smem_u32(shared_memory) + 1023u) & ~1023u;
+    uint8_t *aligned = shared_memory + (base - smem_u32(shared_memory));
+    const uint32_t barriers = base + SMEM_BARRIERS;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(aligned + SMEM_BARRIERS +
+                                                                         BARRIERS * 8);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+    const Watchdog watchdog = {abort_flag, status};
+    auto barrier = [&](int index) { return barriers + index * 8; };
+
+    // Once a wait has run out anywhere, the rest of the grid drains instead of waiting too.
+    if (*reinterpret_cast<volatile unsigned int *>(status) != 0) {
+        return;
+    }
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    const int head = blockIdx.y;
+    const int first_query = blockIdx.x * (QUERY_TILES * TILE_M);
+    const int blocks = (tokens + TILE_N - 1) / TILE_N;
+
+    if (threadIdx.x == 0) {
+        mbar_init(barrier(QUERY_FULL), 1);
+        for (int stage = 0; stage < STAGES; stage++) {
+            mbar_init(barrier(RING_FULL + stage), 1);
+            mbar_init(barrier(RING_EMPTY + stage), 1);
+        }
+        for (int tile = 0; tile < QUERY_TILES; tile++) {
+            mbar_init(barrier(SCORES_FULL + tile), 1);
+            mbar_init(barrier(PROBABILITIES_FULL + tile), TILE_M);
+        }
+        mbar_init(barrier(OUTPUT_FULL), 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), TMEM_COLUMNS);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp >= SOFTMAX_WARPS) {
+        register_decrease<OTHER_REGISTERS>();
+    }
+    if (warp == LOAD_WARP) {
+        if (lane == 0) {
+            tma_prefetch_descriptor(&maps.query);
+            tma_prefetch_descriptor(&maps.key);
+            tma_prefetch_descriptor(&maps.value);
+            const int key_value_head = head / heads_per_key_value;
+            mbar_expect_tx(barrier(QUERY_FULL), QUERY_TILES * TILE_BYTES);
+            for (int tile = 0; tile < QUERY_TILES; tile++) {
+                for (int slab = 0; slab < 2; slab++) {
+                    tma_load_3d(base + SMEM_QUERY + tile * TILE_BYTES + slab * SLAB_BYTES,
+                                &maps.query, barrier(QUERY_FULL), slab * 64,
+                                first_query + tile * TILE_M, head);
+                }
+            }
+            // K0, V0, K1, V1, ... in the order the MMA warp consumes and releases them.
+            for (int item = 0; item < 2 * blocks; item++) {
+                const int stage = item % STAGES;
+                const int use = item / STAGES;
+                if (use > 0 && !mbar_wait(barrier(RING_EMPTY + stage), (use - 1) & 1, watchdog,
+                                          STATUS_DENSE | 1)) {
+                    break;
+                }
+                mbar_expect_tx(barrier(RING_FULL + stage), TILE_BYTES);
+                const CUtensorMap *map = (item & 1) ? &maps.value : &maps.key;
+                for (int slab = 0; slab < 2; slab++) {
+                    tma_load_3d(base + SMEM_RING + stage * TILE_BYTES + slab * SLAB_BYTES, map,
+                                barrier(RING_FULL + stage), slab * 64, (item / 2) * TILE_N,
+                                key_value_head);
+                }
+            }
+        }
+    } else if (warp == MMA_WARP) {
+        if (lane == 0) {
+            const uint32_t query_tiles = base + SMEM_QUERY;
+            const uint32_t ring = base + SMEM_RING;
+            auto score = [&](int tile, uint32_t key_tile) {
+                #pragma unroll
+                for (int step = 0; step < HEAD_DIM / 16; step++) {
+                    mma_f16_ss(tmem + TMEM_SCORES + tile * TILE_N,
+                               row_operand(query_tiles + tile * TILE_BYTES, step),
+                               row_operand(key_tile, step), SCORE_MMA, step > 0);
+                }
+                tcgen05_commit(barrier(SCORES_FULL + tile));
+            };
+            auto accumulate = [&](int tile, uint32_t value_tile, bool first) {
+                #pragma unroll
+                for (int step = 0; step < TILE_N / 16; step++) {
+                    // P is BF16, two to a column: 16 keys are 8 columns.
+                    mma_f16_ts(tmem + TMEM_OUTPUT + tile * HEAD_DIM,
+                               tmem + TMEM_SCORES + tile * TILE_N + step * 8,
+                               value_operand(value_tile, step), OUTPUT_MMA, !first || step > 0);
+                }
+            };
+            bool alive = mbar_wait(barrier(QUERY_FULL), 0, watchdog, STATUS_DENSE | 2) &&
+                         mbar_wait(barrier(RING_FULL + 0), 0, watchdog, STATUS_DENSE | 3);
+            if (alive) {
+                tcgen05_fence_after();
+                score(0, ring);
+                score(1, ring);
+                tcgen05_commit(barrier(RING_EMPTY + 0));
+            }
+            int item = 1; // ring position of V of the current block; K of the next follows it
+            for (int block = 0; alive && block < blocks; block++, item += 2) {
+                const int value_stage = item % STAGES;
+                const int key_stage = (item + 1) % STAGES;
+                const bool more = block + 1 < blocks;
+                alive = mbar_wait(barrier(RING_FULL + value_stage), (item / STAGES) & 1, watchdog,
+                                  STATUS_DENSE | 4) &&
+                        (!more || mbar_wait(barrier(RING_FULL + key_stage),
+                                            ((item + 1) / STAGES) & 1, watchdog,
+                                            STATUS_DENSE | 5));
+                if (!alive) {
+                    break;
+                }
+                const uint32_t value_tile = ring + value_stage * TILE_BYTES;
+                const uint32_t key_tile = ring + key_stage * TILE_BYTES;
+                #pragma unroll
+                for (int tile = 0; tile < QUERY_TILES; tile++) {
+                    alive = mbar_wait(barrier(PROBABILITIES_FULL + tile), block & 1, watchdog,
+                                      STATUS_DENSE | 6);
+                    if (!alive) {
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    accumulate(tile, value_tile, block == 0);
+                    if (tile == QUERY_TILES - 1) {
+                        tcgen05_commit(barrier(RING_EMPTY + value_stage));
+                    }
+                    if (more) {
+                        // Issued after the P V that reads the columns it overwrites.
+                        score(tile, key_tile);
+                        if (tile == QUERY_TILES - 1) {
+                            tcgen05_commit(barrier(RING_EMPTY + key_stage));
+                        }
+                    }
+                }
+            }
+            if (alive) {
+                tcgen05_commit(barrier(OUTPUT_FULL));
+            }
+        }
+    } else if (warp < SOFTMAX_WARPS) {
+        // Softmax of query tile `tile`; this thread owns row `row`, TMEM lane `row`.
+        register_increase<SOFTMAX_REGISTERS>();
+        const int tile = warp / 4;
+        const int row = (warp % 4) * 32 + lane;
+        const uint32_t lane_base = static_cast<uint32_t>((warp % 4) * 32) << 16;
+        const uint32_t scores = tmem + lane_base + TMEM_SCORES + tile * TILE_N;
+        const uint32_t accumulator = tmem + lane_base + TMEM_OUTPUT + tile * HEAD_DIM;
+        float maximum = -INFINITY; // of the raw scores, before the scale
+        float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        bool alive = true;
+        for (int block = 0; block < blocks; block++) {
+            alive = mbar_wait(barrier(SCORES_FULL + tile), block & 1, watchdog, STATUS_DENSE | 7);
+            // The tensor memory accesses below are warp-wide: the warp goes on or leaves as one.
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) {
+                break;
+            }
+            tcgen05_fence_after();
+            uint32_t raw[4][32];
+            #pragma unroll
+            for (int chunk = 0; chunk < 4; chunk++) {
+                tmem_load_32(scores + chunk * 32, raw[chunk]);
+            }
+            tmem_wait_load();
+            float s[TILE_N];
+            #pragma unroll
+            for (int index = 0; index < TILE_N; index++) {
+                s[index] = __uint_as_float(raw[index / 32][index % 32]);
+            }
+            const int valid = tokens - block * TILE_N;
+            if (valid < TILE_N) {
+                // Keys past the last token arrive as zeroes and are masked.
+                #pragma unroll
+                for (int index = 0; index < TILE_N; index++) {
+                    if (index >= valid) {
+                        s[index] = -INFINITY;
+                    }
+                }
+            }
+            float partial[4] = {s[0], s[1], s[2], s[3]};
+            #pragma unroll
+            for (int index = 4; index < TILE_N; index++) {
+                partial[index % 4] = fmaxf(partial[index % 4], s[index]);
+            }
+            const float block_maximum =
+                fmaxf(fmaxf(partial[0], partial[1]), fmaxf(partial[2], partial[3]));
+            if (block == 0) {
+                maximum = block_maximum;
+            } else {
+                const bool grown = (block_maximum - maximum) * scale_log2 > RESCALE_THRESHOLD;
+                if (__any_sync(0xffffffffu, grown)) {
+                    // S(block) being complete means P V of the block before is too, so O is
+                    // at rest until this thread hands over P.
+                    const float raised = fmaxf(maximum, block_maximum);
+                    const float correction = exp2_approx((maximum - raised) * scale_log2);
+                    maximum = raised;
+                    #pragma unroll
+                    for (int index = 0; index < 4; index++) {
+                        sums[index] *= correction;
+                    }
+                    #pragma unroll
+                    for (int chunk = 0; chunk < 4; chunk++) {
+                        uint32_t values[32];
+                        tmem_load_32(accumulator + chunk * 32, values);
+                        tmem_wait_load();
+                        #pragma unroll
+                        for (int index = 0; index < 32; index++) {
+                            values[index] =
+                                __float_as_uint(__uint_as_float(values[index]) * correction);
+                        }
+                        tmem_store_32(accumulator + chunk * 32, values);
+                    }
+                }
+            }
+            const float offset = maximum * scale_log2;
+            #pragma unroll
+            for (int chunk = 0; chunk < 2; chunk++) {
+                uint32_t packed[32];
+                #pragma unroll
+                for (int pair = 0; pair < 32; pair++) {
+                    const int index = chunk * 64 + pair * 2;
+                    const float low = exp2_approx(fmaf(s[index], scale_log2, -offset));
+                    const float high = exp2_approx(fmaf(s[index + 1], scale_log2, -offset));
+                    sums[pair % 2 * 2] += low;
+                    sums[pair % 2 * 2 + 1] += high;
+                    packed[pair] = pack_bf16(low, high);
+                }
+                tmem_store_32(scores + chunk * 32, packed);
+            }
+            tmem_wait_store();
+            tcgen05_fence_before();
+            mbar_arrive(barrier(PROBABILITIES_FULL + tile));
+        }
+        if (alive) {
+            alive = mbar_wait(barrier(OUTPUT_FULL), 0, watchdog, STATUS_DENSE | 8);
+            alive = __all_sync(0xffffffffu, alive);
+        }
+        if (alive) {
+            tcgen05_fence_after();
+            const float inverse = 1.0f / ((sums[0] + sums[1]) + (sums[2] + sums[3]));
+            const int token = first_query + tile * TILE_M + row;
+            __nv_bfloat16 *output_row =
+                output + static_cast<int64_t>(token) * output_token_stride +
+                static_cast<int64_t>(head) * output_head_stride;
+            #pragma unroll
+            for (int chunk = 0; chunk < 4; chunk++) {
+                uint32_t values[32];
+                tmem_load_32(accumulator + chunk * 32, values);
+                tmem_wait_load();
+                if (token < tokens) {
+                    uint32_t packed[16];
+                    #pragma unroll
+                    for (int pair = 0; pair < 16; pair++) {
+                        packed[pair] = pack_bf16(__uint_as_float(values[pair * 2]) * inverse,
+                                                 __uint_as_float(values[pair * 2 + 1]) * inverse);
+                    }
+                    if (vector_stores) {
+                        uint4 *destination = reinterpret_cast<uint4 *>(output_row + chunk * 32);
+                        #pragma unroll
+                        for (int part = 0; part < 4; part++) {
+                            destination[part] =
+                                make_uint4(packed[part * 4], packed[part * 4 + 1],
+                                           packed[part * 4 + 2], packed[part * 4 + 3]);
+                        }
+                    } else {
+                        uint16_t *destination =
+                            reinterpret_cast<uint16_t *>(output_row + chunk * 32);
+                        #pragma unroll
+                        for (int pair = 0; pair < 16; pair++) {
+                            destination[pair * 2] = static_cast<uint16_t>(packed[pair] & 0xffffu);
+                            destination[pair * 2 + 1] = static_cast<uint16_t>(packed[pair] >> 16);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        if (*abort_flag != 0) {
+            // Give what is still in flight time to land before the columns go back.
+            for (int spin = 0; spin < 64; spin++) {
+                __nanosleep(1000);
+            }
+        }
+        tcgen05_fence_after();
+        tmem_dealloc(tmem, TMEM_COLUMNS);
+    }
+}
+
+bool encode_operand(CUtensorMap *map, const void *base, int tokens, int heads, int64_t token_stride,
+                    int64_t head_stride) {
+    const uint64_t dimensions[3] = {static_cast<uint64_t>(HEAD_DIM), static_cast<uint64_t>(tokens),
+                                    static_cast<uint64_t>(heads)};
+    uint64_t strides[2] = {static_cast<uint64_t>(token_stride) * 2,
+                           static_cast<uint64_t>(head_stride) * 2};
+    if (heads == 1 && strides[1] == 0) {
+        // A dimension of one never uses its stride, but the encoder rejects zero.
+        strides[1] = strides[0] * static_cast<uint64_t>(tokens);
+    }
+    const uint32_t box[3] = {64, TILE_M, 1};
+    return encode_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dimensions, strides,
+                             box);
+}
+
+} // namespace
+
+int launch_dense_bf16(const void *query, const void *key, const void *value, void *output,
+                      int tokens, int heads, int batch, const Mmh3AttentionLayout &layout,
+                      float scale, cudaStream_t stream) {
+    const int group = layout.heads_per_key_value > 0 ? layout.heads_per_key_value : 1;
+    if (!(scale > 0.0f) || !std::isfinite(scale)) {
+        return INVALID_VALUE;
+    }
+    for (int operand = 0; operand < 4; operand++) {
+        if (layout.token_stride[operand] <= 0 || layout.head_stride[operand] < 0) {
+            return INVALID_VALUE;
+        }
+    }
+    unsigned int *status = status_pointer();
+    if (status == nullptr) {
+        return static_cast<int>(cudaErrorInvalidDevice);
+    }
+    static SharedMemoryOptIn shared_memory;
+    const cudaError_t configured = shared_memory.ensure(dense_bf16_kernel, SMEM_BYTES);
+    if (configured != cudaSuccess) {
+        return static_cast<int>(configured);
+    }
+    const auto *q = static_cast<const __nv_bfloat16 *>(query);
+    const auto *k = static_cast<const __nv_bfloat16 *>(key);
+    const auto *v = static_cast<const __nv_bfloat16 *>(value);
+    auto *out = static_cast<__nv_bfloat16 *>(output);
+    for (int item = 0; item < batch; item++) {
+        const __nv_bfloat16 *batch_query = q + item * layout.batch_stride[QUERY];
+        const __nv_bfloat16 *batch_key = k + item * layout.batch_stride[KEY];
+        const __nv_bfloat16 *batch_value = v + item * layout.batch_stride[VALUE];
+        __nv_bfloat16 *batch_output = out + item * layout.batch_stride[OUTPUT];
+        DenseMaps maps;
+        if (!encode_operand(&maps.query, batch_query, tokens, heads, layout.token_stride[QUERY],
+                            layout.head_stride[QUERY]) ||
+            !encode_operand(&maps.key, batch_key, tokens, heads / group, layout.token_stride[KEY],
+                            layout.head_stride[KEY]) ||
+            !encode_operand(&maps.value, batch_value, tokens, heads / group,
+                            layout.token_stride[VALUE], layout.head_stride[VALUE])) {
+            // TMA wants 16-byte aligned bases and strides.
+            return NOT_SUPPORTED;
+        }
+        const int vector_stores = reinterpret_cast<uintptr_t>(batch_output) % 16 == 0 &&
+                                  layout.token_stride[OUTPUT] % 8 == 0 &&
+                                  layout.head_stride[OUTPUT] % 8 == 0;
+        const dim3 grid((tokens + QUERY_TILES * TILE_M - 1) / (QUERY_TILES * TILE_M), heads);
+        dense_bf16_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(
+            maps, batch_output, tokens, group, layout.token_stride[OUTPUT],
+            layout.head_stride[OUTPUT], vector_stores, scale * LOG2_E, status);
+        const cudaError_t launched = cudaGetLastError();
+        if (launched != cudaSuccess) {
+            return static_cast<int>(launched);
+        }
+    }
+    return 0;
+}
+
+} // namespace mmh3

@@ -1,0 +1,181 @@
+"""Parity of the dense BF16 attention kernel, through the C ABI, on a B200.
+
+Mirrors crates/mmh3-cuda/tests/attention.rs: the same generator, seeds, shapes and tolerance against
+an f64 softmax attention, plus ragged sizes around the kernel's 128/256-row tiles, the benchmark's
+value distribution, and the reference's own CUDA kernel on the same device buffers.
+"""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib
+from mmh3_b200 import _lib, attention, synthetic
+
+pytestmark = pytest.mark.gpu
+
+SCALE = synthetic.softmax_scale()
+
+
+def lcg_qkv(oracle, tokens, heads, seed):
+    values, _ = oracle_lib.lcg(oracle, seed, tokens * 3 * heads * 128, -2.0, 2.0)
+    return synthetic.to_bf16_bits(values).reshape(tokens, 3, heads, 128)
+
+
+def run_dense(bits, tokens, heads):
+    qkv = synthetic.bf16_tensor(bits, "cuda")
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    attention.dense_bf16(qkv, output, tokens, heads, SCALE)
+    assert attention.take_status() == 0
+    return output.float().cpu().numpy()
+
+
+def cosine(a, b):
+    a, b = a.astype(np.float64).ravel(), b.astype(np.float64).ravel()
+    return float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-300))
+
+
+def load_selftest():
+    library = ctypes.CDLL(str(_lib.SELFTEST_LIBRARY))
+    library.mmh3_b200_umma_selftest.argtypes = [ctypes.c_int] + [ctypes.c_void_p] * 6
+    library.mmh3_b200_umma_selftest.restype = ctypes.c_int
+    return library
+
+
+def test_umma_bf16_building_blocks():
+    """scores = A.B^T from shared memory and output = P.V with P in tensor memory, BF16."""
+    library = load_selftest()
+    generator = torch.Generator().manual_seed(11)
+    a = torch.randn((128, 128), generator=generator).bfloat16().cuda()
+    b = torch.randn((128, 128), generator=generator).bfloat16().cuda()
+    v = torch.randn((128, 128), generator=generator).bfloat16().cuda()
+    p = torch.rand((128, 128), generator=generator).bfloat16().cuda()
+    scores = torch.zeros((128, 128), dtype=torch.float32, device="cuda")
+    output = torch.zeros((128, 128), dtype=torch.float32, device="cuda")
+    code = library.mmh3_b200_umma_selftest(0, a.data_ptr(), b.data_ptr(), v.data_ptr(),
+                                           p.data_ptr(), scores.data_ptr(), output.data_ptr())
+    assert code == 0
+    assert attention.take_status() == 0
+    expected_scores = a.float().cpu() @ b.float().cpu().t()
+    expected_output = p.float().cpu() @ v.float().cpu()
+    assert torch.allclose(scores.cpu(), expected_scores, atol=1e-3, rtol=1e-4)
+    assert torch.allclose(output.cpu(), expected_output, atol=1e-3, rtol=1e-4)
+
+
+def test_umma_int8_fp8_building_blocks(oracle):
+    """INT8 A.B^T with INT32 accumulators (exact) and E4M3 P.V^T with P in tensor memory."""
+    library = load_selftest()
+    rng = np.random.default_rng(12)
+    a = rng.integers(-127, 128, size=(128, 128), dtype=np.int8)
+    b = rng.integers(-127, 128, size=(128, 128), dtype=np.int8)
+    p = rng.integers(0, 0x7F, size=(128, 128), dtype=np.uint8)  # positive finite E4M3
+    v = rng.integers(0, 0x7F, size=(128, 128), dtype=np.uint8)
+    v |= (rng.integers(0, 2, size=(128, 128), dtype=np.uint8) << 7)
+    table = np.array([oracle.oracle_e4m3_to_f32(code) for code in range(256)], dtype=np.float64)
+    device = [torch.from_numpy(x.view(np.uint8).copy()).cuda() for x in (a, b, v, p)]
+    scores = torch.zeros((128, 128), dtype=torch.int32, device="cuda")
+    output = torch.zeros((128, 128), dtype=torch.float32, device="cuda")
+    code = library.mmh3_b200_umma_selftest(1, *(x.data_ptr() for x in device), scores.data_ptr(),
+                                           output.data_ptr())
+    assert code == 0
+    assert attention.take_status() == 0
+    expected_scores = a.astype(np.int32) @ b.astype(np.int32).T
+    assert np.array_equal(scores.cpu().numpy(), expected_scores)
+    # v is V^T [dims][keys]: output[m][d] = sum_k p[m][k] v[d][k]
+    expected_output = table[p] @ table[v].T
+    assert np.allclose(output.cpu().numpy(), expected_output, rtol=2e-3, atol=1e-2)
+
+
+@pytest.mark.parametrize("tokens,heads", [(1, 1), (64, 2), (200, 3)])
+def test_matches_cpu_reference(oracle, tokens, heads):
+    """attention.rs:27-90: LCG data uniform in [-2, 2), seed tokens * 31 + heads."""
+    bits = lcg_qkv(oracle, tokens, heads, tokens * 31 + heads)
+    actual = run_dense(bits, tokens, heads)
+    expected = oracle_lib.attention_bf16(oracle, bits, tokens, heads, SCALE)
+    assert np.all(np.abs(actual - expected) <= 0.02 + 0.01 * np.abs(expected))
+
+
+@pytest.mark.parametrize("tokens", [127, 128, 129, 255, 256, 257, 384, 1000])
+def test_ragged_sizes(oracle, tokens):
+    heads = 2
+    bits = synthetic.dense_qkv(tokens, heads, seed=tokens).view(torch.int16).numpy().view(np.uint16)
+    actual = run_dense(bits, tokens, heads)
+    expected = oracle_lib.attention_bf16(oracle, bits, tokens, heads, SCALE)
+    assert np.max(np.abs(actual - expected)) <= 2e-2
+    assert cosine(actual, expected) >= 0.9995
+
+
+def test_cpu_workload_sampled(oracle):
+    """B=1, H=8, L=4096 with the benchmark's distribution, every 29th query row on the CPU."""
+    tokens, heads = synthetic.CONFIGS["C0"]
+    bits = synthetic.dense_qkv(tokens, heads, seed=0).view(torch.int16).numpy().view(np.uint16)
+    actual = run_dense(bits, tokens, heads)
+    rows = list(range(0, tokens, 29))
+    for row in rows:
+        expected = oracle_lib.attention_bf16(oracle, bits, tokens, heads, SCALE, row, row + 1)
+        assert np.max(np.abs(actual[row] - expected[0])) <= 2e-2
+    expected = np.concatenate([
+        oracle_lib.attention_bf16(oracle, bits, tokens, heads, SCALE, row, row + 1) for row in rows[:32]
+    ])
+    assert cosine(actual[rows[:32]], expected) >= 0.9995
+
+
+def test_agrees_with_the_reference_kernel(reference_kernels):
+    """The reference's mma.sync kernel and this one on the same device buffers."""
+    tokens, heads = 1000, 3
+    inner = heads * 128
+    qkv = synthetic.dense_qkv(tokens, heads, seed=5).cuda()
+    ours = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    theirs = torch.zeros_like(ours)
+    attention.dense_bf16(qkv, ours, tokens, heads, SCALE)
+    base = qkv.data_ptr()
+    code = reference_kernels.mmh3_attention_bf16(base, base + 2 * inner, base + 4 * inner,
+                                                 theirs.data_ptr(), tokens, heads, 3 * inner,
+                                                 3 * inner, 3 * inner, inner, SCALE, None)
+    assert code == 0
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    a, b = ours.float().cpu().numpy(), theirs.float().cpu().numpy()
+    assert np.max(np.abs(a - b)) <= 2e-2
+    assert cosine(a, b) >= 0.9995
+
+
+def test_grouped_heads_and_batches(oracle):
+    """mmh3_attention with two query heads per key/value head and a batch of two."""
+    tokens, heads, group, batch = 130, 4, 2, 2
+    generator = torch.Generator().manual_seed(3)
+    q = torch.randn((batch, tokens, heads, 128), generator=generator).bfloat16()
+    k = torch.randn((batch, tokens, heads // group, 128), generator=generator).bfloat16()
+    v = torch.randn((batch, tokens, heads // group, 128), generator=generator).bfloat16()
+    output = torch.zeros((batch, tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    kv_inner = heads // group * 128
+    layout = attention.make_layout(
+        (heads * 128, kv_inner, kv_inner, heads * 128),
+        batch_stride=(tokens * heads * 128, tokens * kv_inner, tokens * kv_inner,
+                      tokens * heads * 128),
+        heads_per_key_value=group)
+    attention.attention(0, 128, q.cuda(), k.cuda(), v.cuda(), output, tokens, heads, batch, layout,
+                        SCALE)
+    assert attention.take_status() == 0
+    scores = torch.einsum("bqhd,bkhd->bhqk", q.double(),
+                          k.double().repeat_interleave(group, dim=2)) * SCALE
+    expected = torch.einsum("bhqk,bkhd->bqhd", scores.softmax(-1),
+                            v.double().repeat_interleave(group, dim=2))
+    assert torch.max(torch.abs(output.cpu().double() - expected)) <= 2e-2
+
+
+def test_unsupported_combinations_report_an_error():
+    tokens, heads = 64, 1
+    qkv = torch.zeros((tokens, 3, heads, 128), dtype=torch.bfloat16, device="cuda")
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    layout = attention.qkv_layout(heads)
+    library = _lib.library()
+    arguments = (qkv.data_ptr(), qkv.data_ptr() + 256, qkv.data_ptr() + 512, output.data_ptr(),
+                 tokens, heads, 1, ctypes.byref(layout), SCALE, None)
+    assert library.mmh3_attention(1, 128, *arguments) == _lib.CUDA_ERROR_NOT_SUPPORTED
+    assert library.mmh3_attention(0, 64, *arguments) == _lib.CUDA_ERROR_NOT_SUPPORTED
+    assert library.mmh3_attention(2, 128, *arguments) == _lib.CUDA_ERROR_INVALID_VALUE
+    layout.causal = 1
+    assert library.mmh3_attention(0, 128, *arguments) == _lib.CUDA_ERROR_NOT_SUPPORTED
