@@ -1,0 +1,409 @@
+"""Benchmark of the attention hot path: `python bench.py --gpus N --steps K --warmup W`.
+
+Metric: attention throughput in TFLOP/s (and ms per layer), FLOPs = 4 * L^2 * 128 * H as the
+reference counts them (src/bin/mmh3-tools/bench.rs:141). A step is one attention layer over one
+batch of seeded synthetic activations.
+
+- N = 1: dense BF16 attention at L = 65,536 + 512 text tokens, H = 32, D = 128 (the configuration the
+  metric is quoted on). The same line carries the INT8/FP8 kernel, the fused quantize pass and the
+  video-sparse path as extra keys.
+- N > 1 (launched by torch.distributed.run, one rank per GPU): the head-sharded (Ulysses) video
+  attention layer, L = 124,992 + 512, H = 32, sequence-sharded inputs, NCCL all-to-all both ways,
+  dense attention on 32 / N heads per rank. The total work is fixed, so scaling is strong.
+- `--impl reference`: the reference's CPU attention path (the f64 oracle restating
+  crates/mmh3-cpu/src/dit.rs:79-118; Rust is not installed here) on all host threads, each step a
+  bounded sample of query rows of the same workload.
+
+Rank 0 prints one JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import pathlib
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+REPO = pathlib.Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO))
+sys.path.insert(0, str(REPO / "tests"))
+
+HEAD_DIM = 128
+HEADS = 32
+DENSE_TOKENS = 65536 + 512
+VIDEO_TOKENS = 124992 + 512
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def attention_flops(tokens: int, heads: int) -> float:
+    return 4.0 * tokens * tokens * HEAD_DIM * heads
+
+
+def measured_peaks() -> tuple[dict, str]:
+    path = REPO / "MEASURED_PEAKS.json"
+    if path.exists():
+        return json.loads(path.read_text()), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.process = None
+        self.lines: list[str] = []
+
+    def __enter__(self):
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.process = None
+        return self
+
+    def _read(self):
+        for line in self.process.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *_):
+        if self.process is not None:
+            self.process.terminate()
+            self.process.wait(timeout=5)
+            self.thread.join(timeout=5)
+
+    def summary(self) -> dict:
+        clocks, maxima, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            fields = [field.strip() for field in line.split(",")]
+            if len(fields) != 7:
+                continue
+            try:
+                clocks.append(float(fields[0]))
+                maxima.append(float(fields[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, fields[3:]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not clocks:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        busy = sorted(clocks)[len(clocks) // 4:]  # drop the idle samples around the region
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(maxima),
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def cpu_attention_sampler(tokens: int, heads: int, seed: int, rows: int, qkv=None,
+                          threads: int = 0):
+    """A function that times the CPU oracle on `rows` query rows of every head against all keys of
+    the workload and returns (seconds, flops, threads used)."""
+    import numpy as np
+    import torch
+
+    import oracle_lib
+    from mmh3_b200 import synthetic
+
+    oracle = oracle_lib.load()
+    used = threads or oracle.oracle_max_threads()
+    if qkv is None:
+        qkv = synthetic.dense_qkv(tokens, heads, seed)
+    bits = qkv.view(torch.int16).numpy().view(np.uint16)
+    first = (tokens // 2 // 64) * 64
+
+    def sample():
+        start = time.perf_counter()
+        oracle_lib.attention_bf16(oracle, bits, tokens, heads, synthetic.softmax_scale(), first,
+                                  first + rows, 0, heads, used)
+        seconds = time.perf_counter() - start
+        return seconds, 4.0 * rows * tokens * HEAD_DIM * heads, used
+
+    return sample
+
+
+def run_reference(args) -> None:
+    """The reference arm: the CPU path on the box's host cores, rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    tokens = DENSE_TOKENS if args.gpus == 1 else VIDEO_TOKENS
+    rows = args.cpu_rows
+    times = []
+    flops = used = 0
+    sample = cpu_attention_sampler(tokens, HEADS, 1, rows)
+    for step in range(args.warmup + args.steps):
+        seconds, flops, used = sample()
+        if step >= args.warmup:
+            times.append(seconds)
+    mean = sum(times) / len(times)
+    value = flops / mean / 1e12
+    described = (f"{rows} query rows x {HEADS} heads against all {tokens} keys per step "
+                 f"({flops / 1e9:.1f} GFLOP of the layer's "
+                 f"{attention_flops(tokens, HEADS) / 1e12:.1f} TFLOP)")
+    line = {
+        "impl": "reference", "metric": "attention_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": mean * 1e3 * attention_flops(tokens, HEADS) / flops,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64",
+        "data": "synthetic",
+        "config": {"workload": workload_name(args.gpus), "tokens": tokens, "heads": HEADS,
+                   "head_dim": HEAD_DIM, "ms_per_step": "extrapolated from the sample to a layer"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": used, "kind": "port",
+                         "sample": described},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_name(gpus: int) -> str:
+    if gpus == 1:
+        return "dense BF16 attention, L=65536+512, H=32, D=128 (BASELINE configs[1])"
+    return (f"Ulysses head-sharded dense BF16 video attention layer, L=124992+512, H=32, D=128, "
+            f"{gpus} ranks (BASELINE configs[4])")
+
+
+def time_region(torch, stream_fn, steps: int, barrier=None) -> float:
+    """Milliseconds per step of `stream_fn` over `steps` calls, CUDA events on the current stream,
+    synchronized on both sides."""
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if barrier is not None:
+        barrier()
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(steps):
+        stream_fn()
+    end.record()
+    if barrier is not None:
+        barrier()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / steps
+
+
+def run_single(args) -> None:
+    import torch
+
+    from mmh3_b200 import attention, synthetic
+
+    torch.cuda.set_device(0)
+    tokens, heads = DENSE_TOKENS, HEADS
+    scale = synthetic.softmax_scale()
+    flops = attention_flops(tokens, heads)
+    host_qkv = synthetic.dense_qkv(tokens, heads, seed=1, pinned=True)
+    qkv = host_qkv.cuda()
+    output = torch.zeros((tokens, heads, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
+    host_output = torch.empty((tokens, heads, HEAD_DIM), dtype=torch.bfloat16, pin_memory=True)
+
+    def dense():
+        attention.dense_bf16(qkv, output, tokens, heads, scale)
+
+    def end_to_end():
+        # Host buffers in, host buffers out, through the C ABI call the reference's wrapper makes.
+        qkv.copy_(host_qkv, non_blocking=True)
+        attention.dense_bf16(qkv, output, tokens, heads, scale)
+        host_output.copy_(output, non_blocking=True)
+
+    for _ in range(args.warmup):
+        dense()
+    status = attention.take_status()
+    with ClockSampler(0) as sampler:
+        dense_ms = time_region(torch, dense, args.steps)
+    clocks = sampler.summary()
+    for _ in range(max(1, args.warmup // 2)):
+        end_to_end()
+    e2e_ms = time_region(torch, end_to_end, args.steps)
+    status = status or attention.take_status()
+
+    extras = {}
+    launches = args.steps
+    if not args.dense_only:
+        extras = run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, args)
+
+    peaks, source = measured_peaks()
+    achieved = flops / dense_ms / 1e9
+    peak = peaks["bf16_tflops"]
+    cpu = None
+    if not args.no_cpu:
+        seconds, sample_flops, used = cpu_attention_sampler(tokens, heads, 1, args.cpu_rows,
+                                                            qkv=host_qkv)()
+        cpu = {"value": sample_flops / seconds / 1e12, "unit": "TFLOP/s", "cores": used,
+               "kind": "port",
+               "sample": (f"{args.cpu_rows} query rows x {heads} heads against all {tokens} keys "
+                          f"({sample_flops / 1e9:.1f} GFLOP, {seconds:.1f} s)")}
+    line = {
+        "metric": "attention_tflops", "value": achieved, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dense_ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": workload_name(1), "tokens": tokens, "heads": heads,
+                   "head_dim": HEAD_DIM, "flops_per_step": flops,
+                   "l2": "inputs (1.6 GB) exceed L2 (126 MB)", "kernel_status": status},
+        "e2e": {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": host_qkv.numel() * 2,
+                "d2h_bytes_per_step": host_output.numel() * 2},
+        "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak, "traffic": None,
+                     "peak_source": f"{source} bf16_tflops (burst)",
+                     "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"]},
+        "cpu_baseline": cpu,
+        "clocks": clocks,
+        "extra": extras,
+    }
+    print(json.dumps(line))
+
+
+def run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, args) -> dict:
+    """The other kernels of the path at the same shape, each timed with CUDA events."""
+    extras = {}
+    peaks, source = measured_peaks()
+    flops = attention_flops(tokens, heads)
+    steps = max(2, args.steps // 2)
+    try:
+        workspace = attention.QuantizedWorkspace(tokens, heads)
+        generator = torch.Generator(device="cpu").manual_seed(2)
+        norm = attention.HeadNorm(
+            (torch.rand(HEAD_DIM, generator=generator) + 0.5).bfloat16().cuda(),
+            (torch.rand(HEAD_DIM, generator=generator) + 0.5).bfloat16().cuda(),
+            ((torch.rand((tokens, 48), generator=generator) - 0.5) * 80.0).cuda(), 48, 1e-6)
+        prepared = qkv.clone()
+        maxima = prepared[:, 2].float().abs().amax(dim=(0, 2)).contiguous()
+
+        def quantize():
+            attention.prepare_inputs(prepared, norm, tokens, heads, quantized=workspace,
+                                     value_head_maxima=maxima)
+
+        quantize()
+        ms = time_region(torch, quantize, steps)
+        moved = 3.0 * tokens * heads * HEAD_DIM * 3  # 2 bytes read + 1 byte written per element
+        extras["fused_quantize"] = {
+            "ms": ms, "gbs": moved / ms / 1e6, "algorithmic_bytes": moved,
+            "frac_of_hbm": moved / ms / 1e6 / peaks["hbm_gbs"], "peak_source": source}
+
+        def quantized():
+            attention.dense_quantized(prepared, output, scale, workspace,
+                                      attention.AttentionInputs.PREPARED_WITH_VALUES)
+
+        quantized()
+        ms = time_region(torch, quantized, steps)
+        extras["int8_fp8_attention"] = {"ms": ms, "tflops": flops / ms / 1e9}
+        extras["kernel_status"] = attention.take_status()
+    except attention.CudaError as error:
+        extras["int8_fp8_error"] = str(error)
+    return extras
+
+
+def run_sharded(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    from mmh3_b200 import attention, synthetic
+    from mmh3_b200.shard import Shard, UlyssesAttention
+
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    tokens, heads = VIDEO_TOKENS, HEADS
+    scale = synthetic.softmax_scale()
+    shard = Shard.even(rank, world, tokens, heads, 1)
+    own = shard.own_tokens
+
+    def dense(qkv, output, count, span):
+        attention.dense_bf16(qkv, output, count, span, scale)
+
+    layer = UlyssesAttention(shard, tokens, heads, dense, "cuda", torch.bfloat16,
+                             pack=attention.shard_pack, unpack=attention.shard_unpack)
+    # Every rank draws the same stream and keeps its own rows, so the data does not depend on N.
+    generator_rows = synthetic.dense_qkv(len(own), heads, seed=3 + own.start, pinned=True)
+    qkv = generator_rows.cuda()
+    output = torch.zeros((len(own), heads, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
+    host_output = torch.empty((len(own), heads, HEAD_DIM), dtype=torch.bfloat16, pin_memory=True)
+
+    def step():
+        layer.run(qkv, output)
+
+    def end_to_end():
+        qkv.copy_(generator_rows, non_blocking=True)
+        layer.run(qkv, output)
+        host_output.copy_(output, non_blocking=True)
+
+    for _ in range(args.warmup):
+        step()
+    with ClockSampler(local) as sampler:
+        ms = time_region(torch, step, args.steps, barrier=dist.barrier)
+    for _ in range(max(1, args.warmup // 2)):
+        end_to_end()
+    e2e_ms = time_region(torch, end_to_end, args.steps, barrier=dist.barrier)
+    status = attention.take_status()
+    times = torch.tensor([ms, e2e_ms, float(status)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, e2e_ms, status = times.tolist()
+    if rank == 0:
+        flops = attention_flops(tokens, heads)
+        peaks, source = measured_peaks()
+        value = flops / ms / 1e9
+        line = {
+            "metric": "attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": workload_name(world), "tokens": tokens, "heads": heads,
+                       "head_dim": HEAD_DIM, "flops_per_step": flops,
+                       "parallelism": f"ulysses{world}", "kernel_status": int(status),
+                       "exchange_bytes_per_rank": layer.exchange_bytes(),
+                       "l2": "inputs exceed L2 (126 MB)"},
+            "e2e": {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": generator_rows.numel() * 2 * world,
+                    "d2h_bytes_per_step": host_output.numel() * 2 * world},
+            # per rank and step: N packs, the attention kernel, N unpacks (NCCL's kernels aside)
+            "gpu_launches": args.steps * (2 * world + 1),
+            "roofline": {"bound": "tensor", "achieved": value, "peak": peaks["bf16_tflops"] * world,
+                         "unit": "TFLOP/s", "frac": value / (peaks["bf16_tflops"] * world),
+                         "traffic": None, "peak_source": f"{source} bf16_tflops (burst) x {world}"},
+            "cpu_baseline": None,
+            "clocks": sampler.summary(),
+        }
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=5)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--cpu-rows", type=int, default=32,
+                        help="query rows per head of the CPU baseline's sample")
+    parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--dense-only", action="store_true",
+                        help="time only the dense BF16 kernel (for profiler captures)")
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 0)
+    if args.impl == "reference":
+        run_reference(args)
+    elif args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        run_sharded(args)
+    else:
+        run_single(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -111,6 +111,12 @@ int launch_vsa_attention(const void *query, const void *key, const void *value, 
                          const Mmh3AttentionLayout &layout, float scale, int tiles,
                          const Mmh3VsaWorkspace &workspace, cudaStream_t stream);
 
+// The INT8/FP8 token attention over the routes of `vsa`.
+int launch_vsa_attention_quantized(const Mmh3QuantizedWorkspace &workspace, void *output,
+                                   int tokens, int heads, const Mmh3AttentionLayout &layout,
+                                   float scale, const Mmh3VsaWorkspace &vsa, int tiles,
+                                   const void *gate, int64_t gate_stride, cudaStream_t stream);
+
 // shard.cu
 int launch_shard_pack(const void *source, void *packed, int tokens, int tensors, int heads, int dim,
                       int first_head, int span, cudaStream_t stream);

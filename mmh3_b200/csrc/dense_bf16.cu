@@ -39,10 +39,16 @@ constexpr int LOAD_WARP = SOFTMAX_WARPS;
 constexpr int MMA_WARP = SOFTMAX_WARPS + 1;
 // Warps 10 and 11 only fill the third warpgroup, whose registers go to the softmax warps.
 constexpr int THREADS = (SOFTMAX_WARPS + 4) * 32;
-constexpr int SOFTMAX_REGISTERS = 216;
-constexpr int OTHER_REGISTERS = 80;
-static_assert(SOFTMAX_WARPS * 32 * SOFTMAX_REGISTERS + 128 * OTHER_REGISTERS <= 65536,
-              "the register file is 64 Ki registers");
+constexpr int SOFTMAX_REGISTERS = 208;
+constexpr int OTHER_REGISTERS = 88;
+// setmaxnreg.inc blocks until the CTA's own pool holds the registers it asks for, and only what the
+// CTA's warps have given back with setmaxnreg.dec goes into that pool: what the third warpgroup
+// releases from the 168 registers per thread the kernel launches with must cover what the two
+// softmax warpgroups take, or the kernel never gets past the increase.
+constexpr int LAUNCH_REGISTERS = 168;
+static_assert((LAUNCH_REGISTERS - OTHER_REGISTERS) * 128 >=
+                  (SOFTMAX_REGISTERS - LAUNCH_REGISTERS) * SOFTMAX_WARPS * 32,
+              "the softmax warps ask for more registers than the other warps release");
 
 constexpr int SMEM_QUERY = 0;
 constexpr int SMEM_RING = QUERY_TILES * TILE_BYTES;

@@ -1,0 +1,137 @@
+"""Head-sharded (Ulysses) attention across the GPUs of one box.
+
+Every rank carries a contiguous run of the sequence and every head outside the attention, and every
+token and a contiguous run of heads inside it, as niw/mmh3 splits a DiT step
+(crates/mmh3-core/src/shard.rs:1-11, 155-188; crates/mmh3-cuda/src/dit.rs:1416-1604, 1713-1800).
+The reference moves the data with its own socket/RDMA/peer-copy exchange; here the two exchanges are
+NCCL all-to-alls over NVLink through `torch.distributed`, one process per GPU. On CPU ranks (gloo)
+the same code runs with the attention itself supplied by the caller, which is how the partitioning
+and the exchange are tested without a GPU.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+from typing import Callable
+
+import torch
+import torch.distributed as dist
+
+HEAD_DIM = 128
+
+
+@dataclasses.dataclass(frozen=True)
+class Shard:
+    """Which tokens and which heads each rank owns; both cuts are contiguous."""
+
+    rank: int
+    tokens: tuple[range, ...]
+    heads: tuple[range, ...]
+
+    @staticmethod
+    def even(rank: int, ranks: int, tokens: int, heads: int, alignment: int = 1) -> "Shard":
+        """Cuts `tokens` and `heads` into `ranks` shares. Tokens divide on a multiple of
+        `alignment` (VSA needs whole tiles), and the remainder of either cut goes to the last rank
+        (shard.rs:168-188)."""
+
+        def cut(total: int, step: int) -> tuple[range, ...]:
+            step = max(step, 1)
+            each = (total // ranks // step) * step
+            return tuple(
+                range(index * each, total if index + 1 == ranks else (index + 1) * each)
+                for index in range(ranks))
+
+        return Shard(rank, cut(tokens, alignment), cut(heads, 1))
+
+    @property
+    def ranks(self) -> int:
+        return len(self.tokens)
+
+    @property
+    def own_tokens(self) -> range:
+        return self.tokens[self.rank]
+
+    @property
+    def own_heads(self) -> range:
+        return self.heads[self.rank]
+
+    @property
+    def is_whole(self) -> bool:
+        return self.ranks == 1
+
+
+# attention(qkv [tokens, 3, heads, 128], output [tokens, heads, 128], tokens, heads)
+AttentionFn = Callable[[torch.Tensor, torch.Tensor, int, int], None]
+# pack(source, packed, tokens, tensors, heads, first_head, span); unpack(part, output, tokens, heads,
+# first_head, span)
+PackFn = Callable[..., None]
+
+
+def _torch_pack(source, packed, tokens, tensors, heads, first_head, span):
+    view = source.view(tokens, tensors, heads, HEAD_DIM)
+    packed.view(tokens, tensors, span, HEAD_DIM).copy_(view[:, :, first_head:first_head + span])
+
+
+def _torch_unpack(part, output, tokens, heads, first_head, span):
+    output.view(tokens, heads, HEAD_DIM)[:, first_head:first_head + span].copy_(
+        part.view(tokens, span, HEAD_DIM))
+
+
+class UlyssesAttention:
+    """One attention layer over a sequence-sharded qkv, with persistent exchange buffers.
+
+    `run(qkv_own, output_own)` takes this rank's rows of the fused projection,
+    [own tokens, 3, heads, 128], and fills this rank's rows of the output, [own tokens, heads, 128].
+    """
+
+    def __init__(self, shard: Shard, total_tokens: int, heads: int, attention: AttentionFn,
+                 device, dtype=torch.bfloat16, pack: PackFn | None = None,
+                 unpack: PackFn | None = None, group=None):
+        self.shard, self.tokens, self.heads = shard, total_tokens, heads
+        self.attention = attention
+        self.group = group
+        self.pack = pack or _torch_pack
+        self.unpack = unpack or _torch_unpack
+        own_tokens, own_heads = len(shard.own_tokens), len(shard.own_heads)
+        self.own_tokens, self.own_heads = own_tokens, own_heads
+        make = dict(dtype=dtype, device=device)
+        # Sent: for each peer, its heads of my tokens. Received: my heads of every rank's tokens,
+        # which is already [all tokens, 3, own heads, 128] because tokens are outermost.
+        self.send_inputs = torch.empty(own_tokens * 3 * heads * HEAD_DIM, **make)
+        self.inputs = torch.empty(total_tokens * 3 * own_heads * HEAD_DIM, **make)
+        self.attended = torch.empty(total_tokens * own_heads * HEAD_DIM, **make)
+        self.received = torch.empty(own_tokens * heads * HEAD_DIM, **make)
+        self.input_send_splits = [own_tokens * 3 * len(peer) * HEAD_DIM for peer in shard.heads]
+        self.input_recv_splits = [len(peer) * 3 * own_heads * HEAD_DIM for peer in shard.tokens]
+        self.output_send_splits = [len(peer) * own_heads * HEAD_DIM for peer in shard.tokens]
+        self.output_recv_splits = [own_tokens * len(peer) * HEAD_DIM for peer in shard.heads]
+
+    def exchange_bytes(self) -> int:
+        """Bytes this rank sends to other ranks per layer."""
+        rank = self.shard.rank
+        elements = (sum(self.input_send_splits) - self.input_send_splits[rank]
+                    + sum(self.output_send_splits) - self.output_send_splits[rank])
+        return elements * self.send_inputs.element_size()
+
+    def run(self, qkv_own: torch.Tensor, output_own: torch.Tensor) -> None:
+        shard = self.shard
+        if shard.is_whole:
+            self.attention(qkv_own, output_own, self.tokens, self.heads)
+            return
+        offset = 0
+        for peer, heads in enumerate(shard.heads):
+            count = self.input_send_splits[peer]
+            self.pack(qkv_own, self.send_inputs[offset:offset + count], self.own_tokens, 3,
+                      self.heads, heads.start, len(heads))
+            offset += count
+        dist.all_to_all_single(self.inputs, self.send_inputs, self.input_recv_splits,
+                               self.input_send_splits, group=self.group)
+        self.attention(self.inputs, self.attended, self.tokens, self.own_heads)
+        dist.all_to_all_single(self.received, self.attended, self.output_recv_splits,
+                               self.output_send_splits, group=self.group)
+        offset = 0
+        for peer, heads in enumerate(shard.heads):
+            count = self.output_recv_splits[peer]
+            self.unpack(self.received[offset:offset + count], output_own, self.own_tokens,
+                        self.heads, heads.start, len(heads))
+            offset += count

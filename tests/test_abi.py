@@ -1,0 +1,95 @@
+"""The C-ABI library loads without a GPU, exports every symbol include/mmh3_attention.h declares,
+lays its structs out as the reference's #[repr(C)] mirrors do, and rejects bad arguments with the
+reference's error codes before touching a device. No kernel runs here."""
+
+import ctypes
+import pathlib
+import re
+import subprocess
+
+import pytest
+
+from mmh3_b200 import _lib
+
+REPO = pathlib.Path(__file__).resolve().parent.parent
+HEADER = REPO / "include" / "mmh3_attention.h"
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"^int\s+(mmh3_\w+)\s*\(", text, flags=re.M)))
+
+
+def test_header_compiles_as_c():
+    subprocess.run(["gcc", "-std=c99", "-fsyntax-only", "-x", "c", str(HEADER)], check=True)
+
+
+def test_every_declared_symbol_is_exported():
+    library = _lib.library()
+    names = declared_functions()
+    assert len(names) == 12
+    assert sorted(_lib.SIGNATURES) == names
+    for name in names:
+        assert getattr(library, name) is not None
+
+
+def test_struct_layouts():
+    # crates/mmh3-cuda/src/attention.rs:13-23, 49-58, 143-156, 962-972
+    assert ctypes.sizeof(_lib.AttentionLayout) == 104
+    assert _lib.AttentionLayout.head_stride.offset == 32
+    assert _lib.AttentionLayout.batch_stride.offset == 64
+    assert _lib.AttentionLayout.heads_per_key_value.offset == 96
+    assert _lib.AttentionLayout.causal.offset == 100
+    assert ctypes.sizeof(_lib.QuantizedWorkspaceStruct) == 7 * 8
+    assert ctypes.sizeof(_lib.SparseWorkspace) == 11 * 8
+    assert ctypes.sizeof(_lib.VsaWorkspaceStruct) == 8 * 8
+
+
+def test_bad_arguments_are_rejected_before_any_launch():
+    library = _lib.library()
+    layout = _lib.AttentionLayout()
+    for index in range(4):
+        layout.token_stride[index] = 384
+        layout.head_stride[index] = 128
+    invalid = _lib.CUDA_ERROR_INVALID_VALUE
+    assert library.mmh3_attention(0, 128, None, None, None, None, 0, 1, 1, ctypes.byref(layout),
+                                  0.1, None) == invalid
+    assert library.mmh3_attention(0, 128, None, None, None, None, 8, 0, 1, ctypes.byref(layout),
+                                  0.1, None) == invalid
+    layout.heads_per_key_value = 3
+    assert library.mmh3_attention(0, 128, None, None, None, None, 8, 4, 1, ctypes.byref(layout),
+                                  0.1, None) == invalid
+    layout.heads_per_key_value = 0
+    assert library.mmh3_attention(0, 96, None, None, None, None, 8, 4, 1, ctypes.byref(layout),
+                                  0.1, None) == invalid
+    assert library.mmh3_attention(1, 64, None, None, None, None, 8, 4, 1, ctypes.byref(layout),
+                                  0.1, None) == _lib.CUDA_ERROR_NOT_SUPPORTED
+    workspace = _lib.QuantizedWorkspaceStruct()
+    layout.causal = 1
+    assert library.mmh3_attention_quantized(None, None, None, None, 8, 1, ctypes.byref(layout),
+                                            0.1, None, ctypes.byref(workspace), 0, None) == invalid
+    layout.causal = 0
+    assert library.mmh3_attention_quantized(None, None, None, None, -1, 1, ctypes.byref(layout),
+                                            0.1, None, ctypes.byref(workspace), 0, None) == invalid
+    vsa = _lib.VsaWorkspaceStruct()
+    # kept < 1, prefix_tiles > tiles, quantized without prepared inputs
+    assert library.mmh3_vsa_attention(None, None, None, None, 0, None, 8, 1, ctypes.byref(layout),
+                                      0.1, 4, 1, 0, ctypes.byref(vsa), None, 0, None) == invalid
+    assert library.mmh3_vsa_attention(None, None, None, None, 0, None, 8, 1, ctypes.byref(layout),
+                                      0.1, 4, 5, 1, ctypes.byref(vsa), None, 0, None) == invalid
+    assert library.mmh3_vsa_attention(None, None, None, None, 0, None, 8, 1, ctypes.byref(layout),
+                                      0.1, 4, 1, 1, ctypes.byref(vsa), ctypes.byref(workspace), 0,
+                                      None) == invalid
+    assert library.mmh3_attention_inputs(None, None, None, None, 0, 8, 1, 1e-6, None, None, None,
+                                         None, 0, None, None) == invalid
+    assert library.mmh3_dit_shard_pack(None, None, 8, 3, 4, 100, 0, 2, None) == invalid
+    assert library.mmh3_sparse_attention(None, None, None, None, 8, 1, ctypes.byref(layout), 0.1,
+                                         0.5, 0, 0, 0, 0, None, None, 0,
+                                         None) == _lib.CUDA_ERROR_NOT_SUPPORTED
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_library", None)
+    monkeypatch.setattr(_lib, "LIBRARY", tmp_path / "absent.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.library()
