@@ -62,7 +62,8 @@ int multiprocessor_count() {
 }
 
 bool encode_tensor_map(CUtensorMap *map, CUtensorMapDataType type, int rank, const void *base,
-                       const uint64_t *dimensions, const uint64_t *strides, const uint32_t *box) {
+                       const uint64_t *dimensions, const uint64_t *strides, const uint32_t *box,
+                       CUtensorMapSwizzle swizzle) {
     PFN_cuTensorMapEncodeTiled_v12000 encoder = tensor_map_encoder();
     if (encoder == nullptr || reinterpret_cast<uintptr_t>(base) % 16 != 0 || rank < 2 ||
         rank > 5) {
@@ -85,7 +86,7 @@ bool encode_tensor_map(CUtensorMap *map, CUtensorMapDataType type, int rank, con
     }
     return encoder(map, type, static_cast<cuuint32_t>(rank), const_cast<void *>(base),
                    global_dimensions, global_strides, box_dimensions, element_strides,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }

@@ -44,11 +44,12 @@ unsigned int *status_pointer();
 // Multiprocessors of the current device, or 0.
 int multiprocessor_count();
 
-// Encodes a tiled tensor map of up to five dimensions with the 128-byte swizzle and zero fill of
+// Encodes a tiled tensor map of up to five dimensions with a swizzle (128 bytes unless told) and zero fill of
 // out-of-range boxes. `strides` are in bytes for dimensions 1 and up. Returns false when the
 // driver refuses, e.g. for a base or a stride that is not a multiple of 16 bytes.
 bool encode_tensor_map(CUtensorMap *map, CUtensorMapDataType type, int rank, const void *base,
-                       const uint64_t *dimensions, const uint64_t *strides, const uint32_t *box);
+                       const uint64_t *dimensions, const uint64_t *strides, const uint32_t *box,
+                       CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B);
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per device and kernel. A launcher keeps
 // one of these per kernel as a function-local static.

@@ -215,14 +215,20 @@ __device__ __forceinline__ void tmem_store_8(uint32_t address, const uint32_t (&
 // - MN-major operand (the contraction runs down the rows): `stride` is the distance between
 //   groups of eight rows of the contraction, and `leading` the distance between slabs of 128
 //   bytes (64 16-bit elements) along M or N.
+//
+// `swizzle` is the layout code of the descriptor: SWIZZLE_128B for rows of 128 bytes, SWIZZLE_64B
+// for rows of 64 bytes (eight rows to a 512-byte atom).
+constexpr uint64_t SWIZZLE_128B = 2, SWIZZLE_64B = 4;
+
 __device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t leading,
-                                                    uint32_t stride) {
+                                                    uint32_t stride,
+                                                    uint64_t swizzle = SWIZZLE_128B) {
     uint64_t descriptor = 0;
     descriptor |= static_cast<uint64_t>((address >> 4) & 0x3fffu);
     descriptor |= static_cast<uint64_t>((leading >> 4) & 0x3fffu) << 16;
     descriptor |= static_cast<uint64_t>((stride >> 4) & 0x3fffu) << 32;
     descriptor |= 1ull << 46; // descriptor version of sm_100
-    descriptor |= 2ull << 61; // 128-byte swizzle
+    descriptor |= swizzle << 61;
     return descriptor;
 }
 

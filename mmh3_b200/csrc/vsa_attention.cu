@@ -1,17 +1,617 @@
+// VSA's token attention on sm_100a: every query tile (a run of up to 64 tokens) attends, token by
+// token, to the tiles its route lists, plus gate * coarse when a gate is given. BF16 or INT8/FP8
+// operands, FP32 softmax and accumulation, BF16 output. It computes what the reference's VSA
+// attention kernels compute (crates/mmh3-cuda/kernels/vsa_attention.cu:304-493 and the VSA pattern
+// of quantized_attention.cu:247-549) with another design.
+//
+// The tcgen05 MMA works on 128 rows, a tile has at most 64, so a CTA takes TWO query tiles of one
+// head, A in rows 0-63 and B in rows 64-127, and walks their two route lists in step. At step i
+// the key block is the i-th routed tile of A (keys 0-63) next to the i-th routed tile of B (keys
+// 64-127), fetched by TMA as two boxes of 64 rows. S = Q K^T then holds the wanted scores on its
+// diagonal blocks: a softmax thread (one per row) reads only the 64 columns of its own tile's
+// keys, and writes P with zeroes in the other tile's columns, so that O += P V adds nothing across
+// the pair. Half of each MMA is spent on the off-diagonal blocks; in exchange every row and every
+// softmax thread has work, and the tiles keep their own routes.
+//
+// Rows of a box past a tile's length belong to the next tile (or are zero past the sequence):
+// their scores are masked and their probabilities are zero. A list that ends before its
+// partner's loads zero tiles from past the end of the sequence.
+//
+// Two CTAs share an SM (256 TMEM columns and under 100 KiB of shared memory each): while one
+// waits for its softmax, the MMAs of the other run.
+#include <cfloat>
+#include <cmath>
+
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace mmh3 {
 
-int launch_vsa_attention(const void *, const void *, const void *, const void *, int64_t, void *,
-                         int, int, const Mmh3AttentionLayout &, float, int,
-                         const Mmh3VsaWorkspace &, cudaStream_t) {
-    return NOT_SUPPORTED;
+namespace {
+
+using namespace sm100;
+
+constexpr int TILE = 64;              // rows of a VSA tile
+constexpr int PAIR = 2 * TILE;        // rows and keys of one MMA
+constexpr int SOFTMAX_WARPS = 4;
+constexpr int LOAD_WARP = SOFTMAX_WARPS;
+constexpr int MMA_WARP = SOFTMAX_WARPS + 1;
+constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
+constexpr uint32_t TMEM_COLUMNS = 256;
+constexpr uint32_t TMEM_SCORES = 0;
+constexpr uint32_t TMEM_OUTPUT = 128;
+constexpr float RESCALE_THRESHOLD = 8.0f;
+constexpr float LOG2_448 = 8.807354922057604f;
+
+template <bool QUANTIZED> struct Shape {
+    // Bytes of a 128-row operand tile and of the half of it one VSA tile fills.
+    static constexpr int TILE_BYTES = QUANTIZED ? PAIR * 128 : 2 * PAIR * 128;
+    static constexpr int STAGES = QUANTIZED ? 4 : 2;
+    static constexpr int SMEM_QUERY = 0;
+    static constexpr int SMEM_RING = TILE_BYTES;
+    static constexpr int SMEM_BARRIERS = SMEM_RING + STAGES * TILE_BYTES;
+    static constexpr int SMEM_BYTES = SMEM_BARRIERS + 256 + 1024;
+    static constexpr int QUERY_FULL = 0;
+    static constexpr int RING_FULL = 1;
+    static constexpr int RING_EMPTY = RING_FULL + STAGES;
+    static constexpr int SCORES_FULL = RING_EMPTY + STAGES;
+    static constexpr int PROBABILITIES_FULL = SCORES_FULL + 1;
+    static constexpr int OUTPUT_FULL = PROBABILITIES_FULL + 1;
+    static constexpr int BARRIERS = OUTPUT_FULL + 1;
+    static_assert(BARRIERS * 8 + 8 <= 256, "the barriers outgrew their corner of shared memory");
+};
+
+struct VsaMaps {
+    // BF16: [128, tokens, heads] each, boxes of 64 columns x 64 rows.
+    // INT8/FP8: query and key [128, tokens, heads] INT8 in boxes of 128 x 64; value
+    // [tiles * 64, 128, heads] E4M3 in boxes of 64 keys x 128 dimensions with the 64-byte swizzle.
+    CUtensorMap query;
+    CUtensorMap key;
+    CUtensorMap value;
+};
+
+struct VsaParams {
+    __nv_bfloat16 *output;
+    int64_t output_token_stride;
+    int64_t output_head_stride;
+    const __nv_bfloat16 *gate;
+    int64_t gate_stride;
+    const float *coarse;
+    const int32_t *tile_starts;
+    const int32_t *tile_lengths;
+    const uint16_t *routes;
+    const int32_t *route_counts;
+    const float *query_scales;
+    const float *key_scales;
+    const float *value_scales;
+    int tokens;
+    int tiles;
+    float scale_log2;
+    int vector_stores;
+    unsigned int *status;
+};
+
+__device__ __forceinline__ uint32_t pack_e4m3(float a, float b, float c, float d) {
+    uint16_t low, high;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(low) : "f"(b), "f"(a));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(high) : "f"(d), "f"(c));
+    return static_cast<uint32_t>(low) | (static_cast<uint32_t>(high) << 16);
 }
 
-int launch_vsa_attention_quantized(const Mmh3QuantizedWorkspace &, void *, int, int,
-                                   const Mmh3AttentionLayout &, float, const Mmh3VsaWorkspace &,
-                                   int, const void *, int64_t, cudaStream_t) {
-    return NOT_SUPPORTED;
+template <bool QUANTIZED>
+__global__ void __launch_bounds__(THREADS, 2)
+    vsa_attention_kernel(const __grid_constant__ VsaMaps maps, const VsaParams p) {
+    using S = Shape<QUANTIZED>;
+    extern __shared__ uint8_t shared_memory[];
+    const uint32_t base = (smem_u32(shared_memory) + 1023u) & ~1023u;
+    uint8_t *aligned = shared_memory + (base - smem_u32(shared_memory));
+    const uint32_t barriers = base + S::SMEM_BARRIERS;
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(
+        aligned + S::SMEM_BARRIERS + S::BARRIERS * 8);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+    const Watchdog watchdog = {abort_flag, p.status};
+    auto barrier = [&](int index) { return barriers + index * 8; };
+
+    if (*reinterpret_cast<volatile unsigned int *>(p.status) != 0) {
+        return;
+    }
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    const int head = blockIdx.y;
+    // The two query tiles of this CTA; the second may not exist.
+    const int query_tiles[2] = {static_cast<int>(blockIdx.x) * 2,
+                                static_cast<int>(blockIdx.x) * 2 + 1};
+    const bool exists[2] = {true, query_tiles[1] < p.tiles};
+    const size_t route_rows[2] = {static_cast<size_t>(head) * p.tiles + query_tiles[0],
+                                  static_cast<size_t>(head) * p.tiles + query_tiles[1]};
+    const int counts[2] = {p.route_counts[route_rows[0]],
+                           exists[1] ? p.route_counts[route_rows[1]] : 0};
+    const int steps = max(counts[0], counts[1]);
+
+    if (threadIdx.x == 0) {
+        mbar_init(barrier(S::QUERY_FULL), 1);
+        for (int stage = 0; stage < S::STAGES; stage++) {
+            mbar_init(barrier(S::RING_FULL + stage), 1);
+            mbar_init(barrier(S::RING_EMPTY + stage), 1);
+        }
+        mbar_init(barrier(S::SCORES_FULL), 1);
+        mbar_init(barrier(S::PROBABILITIES_FULL), PAIR);
+        mbar_init(barrier(S::OUTPUT_FULL), 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), TMEM_COLUMNS);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == LOAD_WARP) {
+        if (lane == 0) {
+            tma_prefetch_descriptor(&maps.query);
+            tma_prefetch_descriptor(&maps.key);
+            tma_prefetch_descriptor(&maps.value);
+            // A box that starts at row `tokens` lies past the tensor and arrives as zeroes.
+            auto load_rows = [&](const CUtensorMap *map, uint32_t destination, uint32_t bar,
+                                 int row) {
+                if constexpr (QUANTIZED) {
+                    tma_load_3d(destination, map, bar, 0, row, head);
+                } else {
+                    tma_load_3d(destination, map, bar, 0, row, head);
+                    tma_load_3d(destination + PAIR * 128, map, bar, 64, row, head);
+                }
+            };
+            mbar_expect_tx(barrier(S::QUERY_FULL), S::TILE_BYTES);
+            for (int half = 0; half < 2; half++) {
+                load_rows(&maps.query, base + S::SMEM_QUERY + half * TILE * 128,
+                          barrier(S::QUERY_FULL),
+                          exists[half] ? p.tile_starts[query_tiles[half]] : p.tokens);
+            }
+            // The tiles of step 0, then one step ahead of the loads.
+            int tiles_now[2], tiles_next[2];
+            for (int half = 0; half < 2; half++) {
+                tiles_now[half] =
+                    counts[half] > 0 ? p.routes[route_rows[half] * p.tiles] : -1;
+            }
+            for (int step = 0; step < steps; step++) {
+                for (int half = 0; half < 2; half++) {
+                    tiles_next[half] = step + 1 < counts[half]
+                                           ? p.routes[route_rows[half] * p.tiles + step + 1]
+                                           : -1;
+                }
+                int rows[2];
+                for (int half = 0; half < 2; half++) {
+                    rows[half] = tiles_now[half] >= 0 ? p.tile_starts[tiles_now[half]] : p.tokens;
+                }
+                bool alive = true;
+                for (int part = 0; part < 2 && alive; part++) { // K, then V
+                    const int item = 2 * step + part;
+                    const int stage = item % S::STAGES;
+                    const int use = item / S::STAGES;
+                    if (use > 0 && !mbar_wait(barrier(S::RING_EMPTY + stage), (use - 1) & 1,
+                                              watchdog, STATUS_VSA | 1)) {
+                        alive = false;
+                        break;
+                    }
+                    const uint32_t bar = barrier(S::RING_FULL + stage);
+                    const uint32_t destination = base + S::SMEM_RING + stage * S::TILE_BYTES;
+                    mbar_expect_tx(bar, S::TILE_BYTES);
+                    for (int half = 0; half < 2; half++) {
+                        if (QUANTIZED && part == 1) {
+                            // FP8 V: 64 keys of tile t are columns t * 64 of [128 dims] rows; each
+                            // half is its own tile of 64-byte rows.
+                            const int column =
+                                tiles_now[half] >= 0 ? tiles_now[half] * TILE : p.tiles * TILE;
+                            tma_load_3d(destination + half * (HEAD_DIM * TILE), &maps.value, bar,
+                                        column, 0, head);
+                        } else {
+                            load_rows(part ? &maps.value : &maps.key,
+                                      destination + half * TILE * 128, bar, rows[half]);
+                        }
+                    }
+                }
+                if (!alive) {
+                    break;
+                }
+                tiles_now[0] = tiles_next[0];
+                tiles_now[1] = tiles_next[1];
+            }
+        }
+    } else if (warp == MMA_WARP) {
+        if (lane == 0) {
+            const uint32_t query_tile = base + S::SMEM_QUERY;
+            const uint32_t ring = base + S::SMEM_RING;
+            constexpr uint32_t SCORE_MMA =
+                QUANTIZED ? instruction_descriptor(ACCUMULATE_S32, FORMAT_S8, FORMAT_S8, 0, 0,
+                                                   PAIR, PAIR)
+                          : instruction_descriptor(ACCUMULATE_F32, FORMAT_BF16, FORMAT_BF16, 0, 0,
+                                                   PAIR, PAIR);
+            constexpr uint32_t OUTPUT_MMA =
+                QUANTIZED ? instruction_descriptor(ACCUMULATE_F32, FORMAT_E4M3, FORMAT_E4M3, 0, 0,
+                                                   PAIR, HEAD_DIM)
+                          : instruction_descriptor(ACCUMULATE_F32, FORMAT_BF16, FORMAT_BF16, 0, 1,
+                                                   PAIR, HEAD_DIM);
+            auto score = [&](uint32_t key_tile) {
+                if constexpr (QUANTIZED) {
+                    #pragma unroll
+                    for (int step = 0; step < HEAD_DIM / 32; step++) {
+                        mma_i8_ss(tmem + TMEM_SCORES,
+                                  smem_descriptor(query_tile + step * 32, 16, 1024),
+                                  smem_descriptor(key_tile + step * 32, 16, 1024), SCORE_MMA,
+                                  step > 0);
+                    }
+                } else {
+                    #pragma unroll
+                    for (int step = 0; step < HEAD_DIM / 16; step++) {
+                        const uint32_t offset = (step / 4) * (PAIR * 128) + (step % 4) * 32;
+                        mma_f16_ss(tmem + TMEM_SCORES,
+                                   smem_descriptor(query_tile + offset, 16, 1024),
+                                   smem_descriptor(key_tile + offset, 16, 1024), SCORE_MMA,
+                                   step > 0);
+                    }
+                }
+                tcgen05_commit(barrier(S::SCORES_FULL));
+            };
+            auto accumulate = [&](uint32_t value_tile, bool first) {
+                if constexpr (QUANTIZED) {
+                    #pragma unroll
+                    for (int step = 0; step < PAIR / 32; step++) {
+                        // Two tiles of [128 dims][64 keys] in the 64-byte swizzle.
+                        const uint32_t address =
+                            value_tile + (step / 2) * (HEAD_DIM * TILE) + (step % 2) * 32;
+                        mma_f8_ts(tmem + TMEM_OUTPUT, tmem + TMEM_SCORES + step * 8,
+                                  smem_descriptor(address, 16, 512, SWIZZLE_64B), OUTPUT_MMA,
+                                  !first || step > 0);
+                    }
+                } else {
+                    #pragma unroll
+                    for (int step = 0; step < PAIR / 16; step++) {
+                        mma_f16_ts(tmem + TMEM_OUTPUT, tmem + TMEM_SCORES + step * 8,
+                                   smem_descriptor(value_tile + step * 16 * 128, PAIR * 128, 1024),
+                                   OUTPUT_MMA, !first || step > 0);
+                    }
+                }
+            };
+            bool alive = steps == 0 ||
+                         (mbar_wait(barrier(S::QUERY_FULL), 0, watchdog, STATUS_VSA | 2) &&
+                          mbar_wait(barrier(S::RING_FULL + 0), 0, watchdog, STATUS_VSA | 3));
+            if (alive && steps > 0) {
+                tcgen05_fence_after();
+                score(ring);
+                tcgen05_commit(barrier(S::RING_EMPTY + 0));
+            }
+            int item = 1;
+            for (int step = 0; alive && step < steps; step++, item += 2) {
+                const int value_stage = item % S::STAGES;
+                const int key_stage = (item + 1) % S::STAGES;
+                const bool more = step + 1 < steps;
+                alive = mbar_wait(barrier(S::RING_FULL + value_stage), (item / S::STAGES) & 1,
+                                  watchdog, STATUS_VSA | 4) &&
+                        (!more || mbar_wait(barrier(S::RING_FULL + key_stage),
+                                            ((item + 1) / S::STAGES) & 1, watchdog,
+                                            STATUS_VSA | 5)) &&
+                        mbar_wait(barrier(S::PROBABILITIES_FULL), step & 1, watchdog,
+                                  STATUS_VSA | 6);
+                if (!alive) {
+                    break;
+                }
+                tcgen05_fence_after();
+                accumulate(ring + value_stage * S::TILE_BYTES, step == 0);
+                tcgen05_commit(barrier(S::RING_EMPTY + value_stage));
+                if (more) {
+                    score(ring + key_stage * S::TILE_BYTES);
+                    tcgen05_commit(barrier(S::RING_EMPTY + key_stage));
+                }
+            }
+            if (alive) {
+                tcgen05_commit(barrier(S::OUTPUT_FULL));
+            }
+        }
+    } else {
+        // Softmax: this thread owns row `row` of the pair, which is row `row % 64` of tile `half`.
+        const int row = warp * 32 + lane;
+        const int half = row / TILE;
+        const int count = counts[half];
+        const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+        // The 64 columns of S that hold this tile's keys, and where its P goes: BF16 P packs two
+        // keys to a column (own keys in 32 columns), E4M3 P four (16 columns).
+        const uint32_t scores = tmem + lane_base + TMEM_SCORES + half * TILE;
+        constexpr int P_COLUMNS = QUANTIZED ? TILE / 4 : TILE / 2;
+        const uint32_t own_p = tmem + lane_base + TMEM_SCORES + half * P_COLUMNS;
+        const uint32_t other_p = tmem + lane_base + TMEM_SCORES + (1 - half) * P_COLUMNS;
+        const uint32_t accumulator = tmem + lane_base + TMEM_OUTPUT;
+        const uint16_t *route = p.routes + route_rows[half] * p.tiles;
+        float query_factor = p.scale_log2;
+        const float *head_key_scales = nullptr;
+        if constexpr (QUANTIZED) {
+            query_factor *= exists[half] ? p.query_scales[route_rows[half]] : 0.0f;
+            head_key_scales = p.key_scales + static_cast<size_t>(head) * p.tiles;
+        }
+        float maximum = -INFINITY;
+        float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        int key_tile = count > 0 ? route[0] : 0;
+        bool alive = true;
+        for (int step = 0; step < steps; step++) {
+            const bool active = step < count;
+            const int valid = active ? p.tile_lengths[key_tile] : 0;
+            float factor = query_factor;
+            if constexpr (QUANTIZED) {
+                factor *= active ? __ldg(head_key_scales + key_tile) : 0.0f;
+            }
+            key_tile = step + 1 < count ? route[step + 1] : 0;
+            alive = mbar_wait(barrier(S::SCORES_FULL), step & 1, watchdog, STATUS_VSA | 7);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) {
+                break;
+            }
+            tcgen05_fence_after();
+            uint32_t raw[2][32];
+            tmem_load_32(scores, raw[0]);
+            tmem_load_32(scores + 32, raw[1]);
+            tmem_wait_load();
+            float s[TILE];
+            #pragma unroll
+            for (int index = 0; index < TILE; index++) {
+                const uint32_t word = raw[index / 32][index % 32];
+                s[index] = QUANTIZED ? static_cast<float>(static_cast<int32_t>(word)) * factor
+                                     : __uint_as_float(word) * factor;
+                if (index >= valid) {
+                    s[index] = -INFINITY;
+                }
+            }
+            float partial[4] = {s[0], s[1], s[2], s[3]};
+            #pragma unroll
+            for (int index = 4; index < TILE; index++) {
+                partial[index % 4] = fmaxf(partial[index % 4], s[index]);
+            }
+            const float block_maximum =
+                fmaxf(fmaxf(partial[0], partial[1]), fmaxf(partial[2], partial[3]));
+            // The first step of a list always has keys, so the maximum is finite from then on.
+            const float threshold = QUANTIZED ? 0.0f : RESCALE_THRESHOLD;
+            const bool grown = active && block_maximum - maximum > threshold;
+            if (step == 0) {
+                maximum = active ? block_maximum : 0.0f;
+            } else if (__any_sync(0xffffffffu, grown)) {
+                const float raised = fmaxf(maximum, block_maximum);
+                const float correction = exp2_approx(maximum - raised);
+                maximum = raised;
+                #pragma unroll
+                for (int index = 0; index < 4; index++) {
+                    sums[index] *= correction;
+                }
+                #pragma unroll
+                for (int chunk = 0; chunk < 4; chunk++) {
+                    uint32_t values[32];
+                    tmem_load_32(accumulator + chunk * 32, values);
+                    tmem_wait_load();
+                    #pragma unroll
+                    for (int index = 0; index < 32; index++) {
+                        values[index] =
+                            __float_as_uint(__uint_as_float(values[index]) * correction);
+                    }
+                    tmem_store_32(accumulator + chunk * 32, values);
+                }
+            }
+            if constexpr (QUANTIZED) {
+                const float offset = maximum - LOG2_448;
+                uint32_t packed[16], zeroes[16];
+                #pragma unroll
+                for (int quad = 0; quad < 16; quad++) {
+                    float q[4];
+                    #pragma unroll
+                    for (int element = 0; element < 4; element++) {
+                        q[element] = exp2_approx(s[quad * 4 + element] - offset);
+                        sums[element] += q[element];
+                    }
+                    packed[quad] = pack_e4m3(q[0], q[1], q[2], q[3]);
+                    zeroes[quad] = 0;
+                }
+                tmem_store_16(own_p, packed);
+                tmem_store_16(other_p, zeroes);
+            } else {
+                uint32_t packed[32], zeroes[32];
+                #pragma unroll
+                for (int pair = 0; pair < 32; pair++) {
+                    const float low = exp2_approx(s[pair * 2] - maximum);
+                    const float high = exp2_approx(s[pair * 2 + 1] - maximum);
+                    sums[pair % 2 * 2] += low;
+                    sums[pair % 2 * 2 + 1] += high;
+                    packed[pair] = pack_bf16(low, high);
+                    zeroes[pair] = 0;
+                }
+                tmem_store_32(own_p, packed);
+                tmem_store_32(other_p, zeroes);
+            }
+            tmem_wait_store();
+            tcgen05_fence_before();
+            mbar_arrive(barrier(S::PROBABILITIES_FULL));
+        }
+        if (alive && steps > 0) {
+            alive = mbar_wait(barrier(S::OUTPUT_FULL), 0, watchdog, STATUS_VSA | 8);
+            alive = __all_sync(0xffffffffu, alive);
+        }
+        if (alive && steps > 0) {
+            tcgen05_fence_after();
+            const int tile_row = row % TILE;
+            const bool stored =
+                exists[half] && tile_row < p.tile_lengths[query_tiles[half]] && count > 0;
+            const int64_t token = stored ? p.tile_starts[query_tiles[half]] + tile_row : 0;
+            float inverse = 1.0f / ((sums[0] + sums[1]) + (sums[2] + sums[3]));
+            if constexpr (QUANTIZED) {
+                inverse *= p.value_scales[head];
+            }
+            __nv_bfloat16 *output_row = p.output + token * p.output_token_stride +
+                                        static_cast<int64_t>(head) * p.output_head_stride;
+            const bool gated = p.gate != nullptr;
+            const __nv_bfloat16 *gate_row =
+                gated ? p.gate + token * p.gate_stride + static_cast<int64_t>(head) * HEAD_DIM
+                      : nullptr;
+            const float *coarse = gated ? p.coarse + route_rows[half] * HEAD_DIM : nullptr;
+            #pragma unroll
+            for (int chunk = 0; chunk < 4; chunk++) {
+                uint32_t values[32];
+                tmem_load_32(accumulator + chunk * 32, values);
+                tmem_wait_load();
+                if (stored) {
+                    float results[32];
+                    #pragma unroll
+                    for (int index = 0; index < 32; index++) {
+                        results[index] = __uint_as_float(values[index]) * inverse;
+                    }
+                    if (gated) {
+                        #pragma unroll
+                        for (int index = 0; index < 32; index++) {
+                            results[index] =
+                                fmaf(__bfloat162float(gate_row[chunk * 32 + index]),
+                                     __ldg(coarse + chunk * 32 + index), results[index]);
+                        }
+                    }
+                    uint32_t packed[16];
+                    #pragma unroll
+                    for (int pair = 0; pair < 16; pair++) {
+                        packed[pair] = pack_bf16(results[pair * 2], results[pair * 2 + 1]);
+                    }
+                    if (p.vector_stores) {
+                        uint4 *destination = reinterpret_cast<uint4 *>(output_row + chunk * 32);
+                        #pragma unroll
+                        for (int part = 0; part < 4; part++) {
+                            destination[part] =
+                                make_uint4(packed[part * 4], packed[part * 4 + 1],
+                                           packed[part * 4 + 2], packed[part * 4 + 3]);
+                        }
+                    } else {
+                        uint16_t *destination =
+                            reinterpret_cast<uint16_t *>(output_row + chunk * 32);
+                        #pragma unroll
+                        for (int pair = 0; pair < 16; pair++) {
+                            destination[pair * 2] = static_cast<uint16_t>(packed[pair] & 0xffffu);
+                            destination[pair * 2 + 1] = static_cast<uint16_t>(packed[pair] >> 16);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        if (*abort_flag != 0) {
+            for (int spin = 0; spin < 64; spin++) {
+                __nanosleep(1000);
+            }
+        }
+        tcgen05_fence_after();
+        tmem_dealloc(tmem, TMEM_COLUMNS);
+    }
+}
+
+template <bool QUANTIZED>
+int launch(const VsaMaps &maps, const VsaParams &params, int heads, cudaStream_t stream) {
+    using S = Shape<QUANTIZED>;
+    static SharedMemoryOptIn shared_memory;
+    const cudaError_t configured =
+        shared_memory.ensure(vsa_attention_kernel<QUANTIZED>, S::SMEM_BYTES);
+    if (configured != cudaSuccess) {
+        return static_cast<int>(configured);
+    }
+    const dim3 grid((params.tiles + 1) / 2, heads);
+    vsa_attention_kernel<QUANTIZED><<<grid, THREADS, S::SMEM_BYTES, stream>>>(maps, params);
+    return static_cast<int>(cudaGetLastError());
+}
+
+bool fill_params(VsaParams &params, void *output, int tokens, const Mmh3AttentionLayout &layout,
+                 float scale, const Mmh3VsaWorkspace &workspace, int tiles, const void *gate,
+                 int64_t gate_stride) {
+    params.output = static_cast<__nv_bfloat16 *>(output);
+    params.output_token_stride = layout.token_stride[OUTPUT];
+    params.output_head_stride = layout.head_stride[OUTPUT];
+    params.gate = static_cast<const __nv_bfloat16 *>(gate);
+    params.gate_stride = gate_stride;
+    params.coarse = workspace.coarse;
+    params.tile_starts = workspace.tile_starts;
+    params.tile_lengths = workspace.tile_lengths;
+    params.routes = workspace.routes;
+    params.route_counts = workspace.route_counts;
+    params.tokens = tokens;
+    params.tiles = tiles;
+    params.scale_log2 = scale * LOG2_E;
+    params.vector_stores = reinterpret_cast<uintptr_t>(output) % 16 == 0 &&
+                           layout.token_stride[OUTPUT] % 8 == 0 &&
+                           layout.head_stride[OUTPUT] % 8 == 0;
+    params.status = status_pointer();
+    return params.status != nullptr;
+}
+
+} // namespace
+
+int launch_vsa_attention(const void *query, const void *key, const void *value, const void *gate,
+                         int64_t gate_stride, void *output, int tokens, int heads,
+                         const Mmh3AttentionLayout &layout, float scale, int tiles,
+                         const Mmh3VsaWorkspace &workspace, cudaStream_t stream) {
+    if (!(scale > 0.0f) || !std::isfinite(scale)) {
+        return INVALID_VALUE;
+    }
+    VsaParams params = {};
+    if (!fill_params(params, output, tokens, layout, scale, workspace, tiles, gate, gate_stride)) {
+        return static_cast<int>(cudaErrorInvalidDevice);
+    }
+    VsaMaps maps;
+    const void *bases[3] = {query, key, value};
+    CUtensorMap *targets[3] = {&maps.query, &maps.key, &maps.value};
+    for (int operand = 0; operand < 3; operand++) {
+        const uint64_t dimensions[3] = {HEAD_DIM, static_cast<uint64_t>(tokens),
+                                        static_cast<uint64_t>(heads)};
+        uint64_t strides[2] = {static_cast<uint64_t>(layout.token_stride[operand]) * 2,
+                               static_cast<uint64_t>(layout.head_stride[operand]) * 2};
+        if (heads == 1 && strides[1] == 0) {
+            strides[1] = strides[0] * static_cast<uint64_t>(tokens);
+        }
+        const uint32_t box[3] = {64, TILE, 1};
+        if (!encode_tensor_map(targets[operand], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                               bases[operand], dimensions, strides, box)) {
+            return NOT_SUPPORTED;
+        }
+    }
+    return launch<false>(maps, params, heads, stream);
+}
+
+int launch_vsa_attention_quantized(const Mmh3QuantizedWorkspace &quantized, void *output,
+                                   int tokens, int heads, const Mmh3AttentionLayout &layout,
+                                   float scale, const Mmh3VsaWorkspace &workspace, int tiles,
+                                   const void *gate, int64_t gate_stride, cudaStream_t stream) {
+    if (!(scale > 0.0f) || !std::isfinite(scale)) {
+        return INVALID_VALUE;
+    }
+    VsaParams params = {};
+    if (!fill_params(params, output, tokens, layout, scale, workspace, tiles, gate, gate_stride)) {
+        return static_cast<int>(cudaErrorInvalidDevice);
+    }
+    params.query_scales = quantized.query_scales;
+    params.key_scales = quantized.key_scales;
+    params.value_scales = quantized.value_scales;
+    VsaMaps maps;
+    const uint64_t row_dimensions[3] = {HEAD_DIM, static_cast<uint64_t>(tokens),
+                                        static_cast<uint64_t>(heads)};
+    const uint64_t row_strides[2] = {static_cast<uint64_t>(heads) * HEAD_DIM, HEAD_DIM};
+    const uint32_t row_box[3] = {HEAD_DIM, TILE, 1};
+    const uint64_t padded = static_cast<uint64_t>(tiles) * TILE;
+    const uint64_t value_dimensions[3] = {padded, HEAD_DIM, static_cast<uint64_t>(heads)};
+    const uint64_t value_strides[2] = {padded, padded * HEAD_DIM};
+    const uint32_t value_box[3] = {TILE, HEAD_DIM, 1};
+    if (!encode_tensor_map(&maps.query, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, quantized.query,
+                           row_dimensions, row_strides, row_box) ||
+        !encode_tensor_map(&maps.key, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, quantized.key,
+                           row_dimensions, row_strides, row_box) ||
+        !encode_tensor_map(&maps.value, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, quantized.value,
+                           value_dimensions, value_strides, value_box,
+                           CU_TENSOR_MAP_SWIZZLE_64B)) {
+        return NOT_SUPPORTED;
+    }
+    return launch<true>(maps, params, heads, stream);
 }
 
 } // namespace mmh3

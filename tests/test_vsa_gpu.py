@@ -136,3 +136,103 @@ def test_matches_the_reference(oracle, reference_kernels, heads, sparsity, gated
     assert np.max(np.abs(actual - expected)) < 0.05
     other = reference_output.float().cpu().numpy()
     assert np.max(np.abs(actual - other)) < 0.05
+
+
+def prepared_case(oracle, layout, heads):
+    """Inputs with norm weights and angles, and the normalized rows the attention then sees."""
+    from test_inputs_gpu import EPSILON, make_inputs, norm_for
+
+    tokens = len(layout)
+    bits, query_weight, key_weight, angles = make_inputs(oracle, tokens, heads)
+    norm = norm_for(query_weight, key_weight, angles)
+    normalized = synthetic.bf16_tensor(bits, "cuda")
+    attention.qk_norm_rope(normalized, norm, tokens, heads)
+    normalized_bits = normalized.view(torch.int16).cpu().numpy().view(np.uint16)
+    return bits, norm, normalized_bits, EPSILON
+
+
+@pytest.mark.parametrize("with_values", [False, True])
+@pytest.mark.parametrize("gated", [False, True])
+def test_quantized_vsa_matches_the_reference(oracle, reference_kernels, with_values, gated):
+    """crates/mmh3-cuda/tests/attention_inputs.rs:423-572: INT8/FP8 VSA over prepared inputs against
+    the f64 reference (relative L2 < 0.02, max error < 0.1), and against the reference's kernel."""
+    layout = PackedLayout.text_to_video(70, 9, 16, 24, 40)
+    plan = VsaPlan.for_layout(layout)
+    tokens, heads = len(layout), 2
+    inner = heads * 128
+    kept = plan.kept_video_tiles(0.7)
+    bits, norm, normalized_bits, epsilon = prepared_case(oracle, layout, heads)
+    gate_values, _ = oracle_lib.lcg(oracle, 99, tokens * inner, -2.0, 2.0)
+    gate_bits = synthetic.to_bf16_bits(gate_values).reshape(tokens, heads, 128)
+    gate = synthetic.bf16_tensor(gate_bits, "cuda") if gated else None
+    vsa_layout = attention.qkv_layout(heads)
+    inputs = (attention.AttentionInputs.PREPARED_WITH_VALUES if with_values
+              else attention.AttentionInputs.PREPARED)
+
+    ours_qkv = synthetic.bf16_tensor(bits, "cuda")
+    maxima = ours_qkv[:, 2].float().abs().amax(dim=(0, 2)).contiguous() if with_values else None
+    ours = attention.VsaWorkspace(plan, tokens, heads, quantized=True)
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    attention.prepare_inputs(ours_qkv, norm, tokens, heads, vsa=ours, value_head_maxima=maxima)
+    attention.vsa(ours_qkv, gate, output, vsa_layout, SCALE, kept, ours, inputs)
+    assert attention.take_status() == 0
+
+    theirs_qkv = synthetic.bf16_tensor(bits, "cuda")
+    theirs = attention.VsaWorkspace(plan, tokens, heads, quantized=True)
+    reference_output = torch.zeros_like(output)
+    sparse, quantized, raw = theirs.sparse_raw(), theirs.quantized.raw(), theirs.raw()
+    assert reference_kernels.mmh3_attention_inputs(
+        theirs_qkv.data_ptr(), norm.query_weight.data_ptr(), norm.key_weight.data_ptr(),
+        norm.angles.data_ptr(), norm.pairs, tokens, heads, epsilon, ctypes.byref(sparse),
+        ctypes.byref(quantized), theirs.tile_starts.data_ptr(), theirs.tile_lengths.data_ptr(),
+        theirs.tiles, maxima.data_ptr() if with_values else None, None) == 0
+    base = theirs_qkv.data_ptr()
+    assert reference_kernels.mmh3_vsa_attention(
+        base, base + 2 * inner, base + 4 * inner, gate.data_ptr() if gated else None, inner,
+        reference_output.data_ptr(), tokens, heads, ctypes.byref(vsa_layout), SCALE, plan.tiles,
+        plan.prefix_tiles, kept, ctypes.byref(raw), ctypes.byref(quantized), int(inputs),
+        None) == 0
+    torch.cuda.synchronize()
+    assert_routes_equal(*ours.routes_host(), *theirs.routes_host())
+    assert torch.equal(ours.quantized.value, theirs.quantized.value)
+
+    expected = oracle_reference(oracle, plan, normalized_bits, gate_bits if gated else None, heads,
+                                kept)
+    actual = output.float().cpu().numpy()
+    difference = np.linalg.norm((actual - expected).astype(np.float64))
+    assert difference / np.linalg.norm(expected.astype(np.float64)) < 0.02
+    assert np.max(np.abs(actual - expected)) < 0.1
+    other = reference_output.float().cpu().numpy()
+    a, b = actual.astype(np.float64).ravel(), other.astype(np.float64).ravel()
+    assert a @ b / (np.linalg.norm(a) * np.linalg.norm(b)) >= 0.9995
+
+
+def test_larger_plan_with_an_odd_tile_count(oracle, reference_kernels):
+    """More tiles than one CTA pair, an odd tile count, and routes that differ between neighbours."""
+    layout = PackedLayout.text_to_video(130, 9, 32, 48, 0)
+    plan, bits, gate_bits = make_case(oracle, layout, 2)
+    assert plan.tiles % 2 == 1
+    tokens, heads = len(layout), 2
+    inner = heads * 128
+    kept = plan.kept_video_tiles(0.8)
+    qkv = synthetic.bf16_tensor(bits, "cuda")
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    reference_output = torch.zeros_like(output)
+    workspace = attention.VsaWorkspace(plan, tokens, heads)
+    theirs = attention.VsaWorkspace(plan, tokens, heads)
+    vsa_layout = attention.qkv_layout(heads)
+    attention.vsa(qkv, None, output, vsa_layout, SCALE, kept, workspace)
+    raw = theirs.raw()
+    base = qkv.data_ptr()
+    assert reference_kernels.mmh3_vsa_attention(
+        base, base + 2 * inner, base + 4 * inner, None, inner, reference_output.data_ptr(), tokens,
+        heads, ctypes.byref(vsa_layout), SCALE, plan.tiles, plan.prefix_tiles, kept,
+        ctypes.byref(raw), None, 0, None) == 0
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    assert abs(workspace.selected_fraction() - plan.expected_selected_fraction(kept)) < 1e-9
+    assert_routes_equal(*workspace.routes_host(), *theirs.routes_host())
+    a = output.float().cpu().numpy().astype(np.float64).ravel()
+    b = reference_output.float().cpu().numpy().astype(np.float64).ravel()
+    assert np.max(np.abs(a - b)) < 0.05
+    assert a @ b / (np.linalg.norm(a) * np.linalg.norm(b)) >= 0.9995
