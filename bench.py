@@ -200,7 +200,7 @@ def run_single(args) -> None:
     from mmh3_b200 import attention, synthetic
 
     torch.cuda.set_device(0)
-    tokens, heads = DENSE_TOKENS, HEADS
+    tokens, heads = args.tokens or DENSE_TOKENS, args.heads or HEADS
     scale = synthetic.softmax_scale()
     flops = attention_flops(tokens, heads)
     host_qkv = synthetic.dense_qkv(tokens, heads, seed=1, pinned=True)
@@ -249,9 +249,13 @@ def run_single(args) -> None:
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dense_ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": workload_name(1), "tokens": tokens, "heads": heads,
-                   "head_dim": HEAD_DIM, "flops_per_step": flops,
-                   "l2": "inputs (1.6 GB) exceed L2 (126 MB)", "kernel_status": status},
+        "config": {"workload": workload_name(1) if (tokens, heads) == (DENSE_TOKENS, HEADS)
+                   else f"dense BF16 attention, reduced case L={tokens}, H={heads} (not the "
+                        "benchmark configuration)",
+                   "tokens": tokens, "heads": heads, "head_dim": HEAD_DIM,
+                   "flops_per_step": flops,
+                   "l2": f"inputs ({host_qkv.numel() * 2 / 1e9:.2f} GB) exceed L2 (126 MB)",
+                   "kernel_status": status},
         "e2e": {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": host_qkv.numel() * 2,
                 "d2h_bytes_per_step": host_output.numel() * 2},
@@ -393,6 +397,10 @@ def main() -> None:
     parser.add_argument("--cpu-rows", type=int, default=32,
                         help="query rows per head of the CPU baseline's sample")
     parser.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    parser.add_argument("--tokens", type=int, default=0,
+                        help="a reduced sequence length for profiler captures (N = 1 only)")
+    parser.add_argument("--heads", type=int, default=0,
+                        help="a reduced head count for profiler captures (N = 1 only)")
     parser.add_argument("--dense-only", action="store_true",
                         help="time only the dense BF16 kernel (for profiler captures)")
     args = parser.parse_args()
