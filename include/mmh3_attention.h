@@ -167,6 +167,27 @@ int mmh3_dit_shard_pack(const void *source, void *packed, int tokens, int tensor
 int mmh3_dit_shard_unpack(const void *part, void *output, int tokens, int heads, int dim,
                           int first_head, int span, mmh3_stream_t stream);
 
+/* No counterpart in the reference. mmh3_attention_quantized with inputs_ready = 0, for callers that
+ * cannot allocate its workspace: a host that accounts for the whole device itself and has given
+ * what is left to something else (mmh3 sizes its weight streaming that way), or a loop that cannot
+ * take the device-wide stall of a cudaMalloc. The INT8 q and k, the FP8 V and their scales live in a
+ * fixed array inside the library's device image (about 12 MiB on every GPU that loads the library,
+ * until the process exits), and this call allocates and frees nothing.
+ *
+ * Limits: heads <= 64 and (tokens rounded up to a multiple of 64) * heads <= 32,768, e.g. 4,096
+ * tokens of 8 heads. Anything larger returns cudaErrorInvalidValue and names the limit on stderr.
+ * The layout must not be causal nor share key/value heads, as for mmh3_attention_quantized.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
+ * that first call outside any stream capture. All calls on a device share the one array, which
+ * keeps what the last call left in it; every byte a call reads it has written first, so results do
+ * not depend on earlier calls, but two calls whose kernels overlap on the GPU (different streams)
+ * race and must be ordered by the caller. */
+int mmh3_b200_attention_quantized_static(const void *query, const void *key, const void *value,
+                                         void *output, int tokens, int heads,
+                                         const Mmh3AttentionLayout *layout, float scale,
+                                         mmh3_stream_t stream);
+
 /* Not in the reference. The kernels bound every wait on a barrier; one that runs out stores a
  * nonzero code in a per-device status word and the CTA returns without finishing its tile. This
  * synchronizes the current device and returns the word (0 = every kernel ran to completion),

@@ -114,6 +114,8 @@ SIGNATURES = {
     "mmh3_dit_shard_pack": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_void_p],
     "mmh3_dit_shard_unpack": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "mmh3_b200_attention_quantized_static": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                             P(AttentionLayout), c_float, c_void_p],
     "mmh3_b200_take_status": [],
 }
 

@@ -177,6 +177,24 @@ def dense_quantized(qkv: torch.Tensor, output: torch.Tensor, scale: float,
     )
 
 
+def dense_quantized_static(qkv: torch.Tensor, output: torch.Tensor, tokens: int, heads: int,
+                           scale: float) -> None:
+    """`dense_quantized` from raw BF16 inputs without a workspace: the scratch is a fixed array
+    inside the library, for callers that cannot allocate device memory. Shapes past the array's
+    size (tokens rounded up to 64, times heads, at most 32,768; at most 64 heads) are refused.
+    Calls on one device share the array, so overlapping calls on different streams race."""
+    inner = heads * HEAD_DIM
+    if qkv.numel() < tokens * 3 * inner or output.numel() < tokens * inner:
+        raise ValueError("qkv or output is smaller than tokens x heads x 128")
+    layout = qkv_layout(heads)
+    check(
+        _lib.library().mmh3_b200_attention_quantized_static(
+            _pointer(qkv), _pointer(qkv, inner), _pointer(qkv, 2 * inner), _pointer(output),
+            tokens, heads, ctypes.byref(layout), scale, _stream()),
+        "mmh3_b200_attention_quantized_static",
+    )
+
+
 class HeadNorm:
     """Per-head RMSNorm weights of q and k and the rotary angles of every token."""
 
