@@ -62,7 +62,8 @@ class ClockSampler:
     def __init__(self, index: int):
         self.index = index
         self.process = None
-        self.lines: list[str] = []
+        self.lines: list[tuple[float, str]] = []
+        self.window = (0.0, float("inf"))
 
     def __enter__(self):
         try:
@@ -78,7 +79,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.process.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def mark(self, start: float, end: float) -> None:
+        """Only samples taken between `start` and `end` (host clock) count."""
+        self.window = (start, end)
 
     def __exit__(self, *_):
         if self.process is not None:
@@ -89,7 +94,9 @@ class ClockSampler:
     def summary(self) -> dict:
         clocks, maxima, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for stamp, line in self.lines:
+            if not self.window[0] <= stamp <= self.window[1]:
+                continue
             fields = [field.strip() for field in line.split(",")]
             if len(fields) != 7:
                 continue
@@ -103,8 +110,7 @@ class ClockSampler:
                     reasons.add(name)
         if not clocks:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        busy = sorted(clocks)[len(clocks) // 4:]  # drop the idle samples around the region
-        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(maxima),
+        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(maxima),
                 "reasons": sorted(reasons), "samples": len(clocks)}
 
 
@@ -177,13 +183,14 @@ def workload_name(gpus: int) -> str:
             f"{gpus} ranks (BASELINE configs[4])")
 
 
-def time_region(torch, stream_fn, steps: int, barrier=None) -> float:
+def time_region(torch, stream_fn, steps: int, barrier=None, sampler=None) -> float:
     """Milliseconds per step of `stream_fn` over `steps` calls, CUDA events on the current stream,
     synchronized on both sides."""
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if barrier is not None:
         barrier()
     torch.cuda.synchronize()
+    began = time.time()
     start.record()
     for _ in range(steps):
         stream_fn()
@@ -191,6 +198,8 @@ def time_region(torch, stream_fn, steps: int, barrier=None) -> float:
     if barrier is not None:
         barrier()
     torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.mark(began, time.time())
     return start.elapsed_time(end) / steps
 
 
@@ -217,11 +226,14 @@ def run_single(args) -> None:
         attention.dense_bf16(qkv, output, tokens, heads, scale)
         host_output.copy_(output, non_blocking=True)
 
-    for _ in range(args.warmup):
-        dense()
-    status = attention.take_status()
+    # The sampler starts before the warm-up (nvidia-smi takes a moment to deliver its first line);
+    # only what it reads during the timed steps is kept.
     with ClockSampler(0) as sampler:
-        dense_ms = time_region(torch, dense, args.steps)
+        for _ in range(args.warmup):
+            dense()
+        status = attention.take_status()
+        dense_ms = time_region(torch, dense, args.steps, sampler=sampler)
+        time.sleep(0.2)
     clocks = sampler.summary()
     for _ in range(max(1, args.warmup // 2)):
         end_to_end()
@@ -308,7 +320,61 @@ def run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, a
         extras["kernel_status"] = attention.take_status()
     except attention.CudaError as error:
         extras["int8_fp8_error"] = str(error)
+    del workspace, prepared
+    torch.cuda.empty_cache()
+    try:
+        extras["vsa"] = run_vsa(torch, attention, synthetic, heads, scale, steps)
+    except attention.CudaError as error:
+        extras["vsa_error"] = str(error)
     return extras
+
+
+def run_vsa(torch, attention, synthetic, heads, scale, steps) -> dict:
+    """Video sparse attention on the 31 x 48 x 84 grid + 512 text tokens (BASELINE configs[3]):
+    pool, select and token attention timed apart. Inputs are drawn on the device: N(0, 1) plus 0.5 x
+    a trilinearly upsampled low-resolution field per head and channel, in the plan's cube order."""
+    layout, plan = synthetic.video_plan()
+    tokens = len(layout)
+    kept = plan.kept_video_tiles(0.875)
+    generator = torch.Generator(device="cuda").manual_seed(3)
+    qkv = torch.randn((tokens, 3, heads, HEAD_DIM), generator=generator, device="cuda",
+                      dtype=torch.float32).bfloat16()
+    grid = (layout.latent_frames, layout.latent_height // 2, layout.latent_width // 2)
+    order = torch.tensor(plan.video_order, dtype=torch.int64, device="cuda")
+    video = slice(plan.video_start, plan.video_start + len(plan.video_order))
+    for head in range(heads):
+        low = torch.randn((1, 3 * HEAD_DIM, 4, 6, 11), generator=generator, device="cuda")
+        smooth = torch.nn.functional.interpolate(low, size=grid, mode="trilinear",
+                                                 align_corners=True)
+        smooth = smooth.reshape(3 * HEAD_DIM, -1).t().reshape(-1, 3, HEAD_DIM)[order]
+        qkv[video, :, head, :] = (qkv[video, :, head, :].float() + 0.5 * smooth).bfloat16()
+    output = torch.zeros((tokens, heads, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
+    workspace = attention.VsaWorkspace(plan, tokens, heads)
+    vsa_layout = attention.qkv_layout(heads)
+
+    def whole():
+        attention.vsa(qkv, None, output, vsa_layout, scale, kept, workspace)
+
+    whole()
+    ms = time_region(torch, whole, steps)
+    lengths = torch.tensor(plan.tile_lengths, dtype=torch.float64, device="cuda")
+    counts = workspace.route_counts.view(heads, plan.tiles).to(torch.int64)
+    # Keys each query tile attends: the sum of the lengths of its routed tiles.
+    routed_keys = torch.zeros((heads, plan.tiles), dtype=torch.float64, device="cuda")
+    routes = workspace.routes.view(heads, plan.tiles, plan.tiles)
+    for head in range(heads):
+        table = lengths[routes[head].to(torch.int64) & 0xFFFF]
+        mask = torch.arange(plan.tiles, device="cuda")[None, :] < counts[head][:, None]
+        routed_keys[head] = (table * mask).sum(dim=1)
+    sparse_flops = float((routed_keys * lengths[None, :]).sum().item()) * 4.0 * HEAD_DIM
+    return {
+        "workload": f"VSA L={tokens} (8 prefix + 2016 video tiles), H={heads}, kept {kept}",
+        "ms": ms, "sparse_flops": sparse_flops, "sparse_tflops": sparse_flops / ms / 1e9,
+        "dense_equivalent_tflops": attention_flops(tokens, heads) / ms / 1e9,
+        "selected_fraction": workspace.selected_fraction(),
+        "expected_selected_fraction": plan.expected_selected_fraction(kept),
+        "kernel_status": attention.take_status(),
+    }
 
 
 def run_sharded(args) -> None:
@@ -347,10 +413,11 @@ def run_sharded(args) -> None:
         layer.run(qkv, output)
         host_output.copy_(output, non_blocking=True)
 
-    for _ in range(args.warmup):
-        step()
     with ClockSampler(local) as sampler:
-        ms = time_region(torch, step, args.steps, barrier=dist.barrier)
+        for _ in range(args.warmup):
+            step()
+        ms = time_region(torch, step, args.steps, barrier=dist.barrier, sampler=sampler)
+        time.sleep(0.2)
     for _ in range(max(1, args.warmup // 2)):
         end_to_end()
     e2e_ms = time_region(torch, end_to_end, args.steps, barrier=dist.barrier)
