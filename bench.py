@@ -289,7 +289,11 @@ def run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, a
     peaks, source = measured_peaks()
     flops = attention_flops(tokens, heads)
     steps = max(2, args.steps // 2)
+    if args.skip_quantized:
+        workspace = prepared = None
     try:
+        if args.skip_quantized:
+            raise StopIteration
         workspace = attention.QuantizedWorkspace(tokens, heads)
         generator = torch.Generator(device="cpu").manual_seed(2)
         norm = attention.HeadNorm(
@@ -318,14 +322,17 @@ def run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, a
         ms = time_region(torch, quantized, steps)
         extras["int8_fp8_attention"] = {"ms": ms, "tflops": flops / ms / 1e9}
         extras["kernel_status"] = attention.take_status()
+    except StopIteration:
+        pass
     except attention.CudaError as error:
         extras["int8_fp8_error"] = str(error)
     del workspace, prepared
     torch.cuda.empty_cache()
-    try:
-        extras["vsa"] = run_vsa(torch, attention, synthetic, heads, scale, steps)
-    except attention.CudaError as error:
-        extras["vsa_error"] = str(error)
+    if not args.skip_vsa:
+        try:
+            extras["vsa"] = run_vsa(torch, attention, synthetic, heads, scale, steps)
+        except attention.CudaError as error:
+            extras["vsa_error"] = str(error)
     return extras
 
 
@@ -363,8 +370,10 @@ def run_vsa(torch, attention, synthetic, heads, scale, steps) -> dict:
     routed_keys = torch.zeros((heads, plan.tiles), dtype=torch.float64, device="cuda")
     routes = workspace.routes.view(heads, plan.tiles, plan.tiles)
     for head in range(heads):
-        table = lengths[routes[head].to(torch.int64) & 0xFFFF]
+        # Entries past a row's count are whatever the buffer held: clamp them before they index.
         mask = torch.arange(plan.tiles, device="cuda")[None, :] < counts[head][:, None]
+        entries = ((routes[head].to(torch.int64) & 0xFFFF) * mask).clamp_(0, plan.tiles - 1)
+        table = lengths[entries]
         routed_keys[head] = (table * mask).sum(dim=1)
     sparse_flops = float((routed_keys * lengths[None, :]).sum().item()) * 4.0 * HEAD_DIM
     return {
@@ -468,6 +477,10 @@ def main() -> None:
                         help="a reduced sequence length for profiler captures (N = 1 only)")
     parser.add_argument("--heads", type=int, default=0,
                         help="a reduced head count for profiler captures (N = 1 only)")
+    parser.add_argument("--skip-quantized", action="store_true",
+                        help="leave the fused quantize pass and the INT8/FP8 kernel out")
+    parser.add_argument("--skip-vsa", action="store_true",
+                        help="leave the video sparse attention out")
     parser.add_argument("--dense-only", action="store_true",
                         help="time only the dense BF16 kernel (for profiler captures)")
     args = parser.parse_args()

@@ -24,6 +24,7 @@ constexpr int THREADS = 256;
 constexpr int WARPS = THREADS / 32;
 // A row of 128 BF16 values is 16 chunks of 16 bytes.
 constexpr int CHUNKS_PER_THREAD = BLOCK_ROWS * 16 / THREADS;
+constexpr int HEADS_PER_CTA = 4;
 
 struct InputsParams {
     const __nv_bfloat16 *source[3];
@@ -54,6 +55,8 @@ struct InputsParams {
     int last_part;
     // Whether rows can be read in 16-byte chunks.
     int vector_loads;
+    // Heads one CTA walks, sharing the cosines and sines of its block's angles.
+    int heads_per_cta;
 };
 
 __device__ __forceinline__ float warp_max(float value) {
@@ -64,14 +67,39 @@ __device__ __forceinline__ float warp_max(float value) {
     return value;
 }
 
+// x / scale, rounded to nearest as IEEE division rounds it, for many x and one scale: with
+// y = RN(1 / scale), q = RN(x * y) and the exact residual r = x - q * scale, RN(q + r * y) is the
+// correctly rounded quotient (Markstein) unless the significand of the scale is all ones or the
+// residual could underflow; `exact` says whether the scale is one of those, and then the division
+// itself is used. The quotient's bits decide an INT8 or FP8 code, so "almost" would not do.
+struct Divider {
+    float scale;
+    float reciprocal;
+    bool exact;
+    __device__ __forceinline__ explicit Divider(float divisor) : scale(divisor) {
+        reciprocal = __frcp_rn(divisor);
+        const uint32_t bits = __float_as_uint(divisor);
+        exact = (bits & 0x007fffffu) != 0x007fffffu && divisor >= 1e-24f && divisor <= 1e24f;
+    }
+    __device__ __forceinline__ float operator()(float x) const {
+        if (exact) {
+            const float quotient = __fmul_rn(x, reciprocal);
+            const float residual = __fmaf_rn(-quotient, scale, x);
+            return __fmaf_rn(residual, reciprocal, quotient);
+        }
+        return __fdiv_rn(x, scale);
+    }
+};
+
 // RMSNorm of the row `row` of the tile with `weight`, then the split-half rotary embedding of its
-// first 2 * pairs dimensions, written back to the tile in BF16. One warp works on the row; lane l
-// holds dimensions l, l + 32, l + 64 and l + 96, which is what the order of the additions in the
-// sum of squares depends on.
-__device__ __forceinline__ void normalize_row(__nv_bfloat16 *row, float *scratch,
-                                              const __nv_bfloat16 *__restrict__ weight,
-                                              const float *__restrict__ token_angles, int pairs,
-                                              float epsilon) {
+// first 2 * pairs dimensions from the cosines and sines of the row's angles, written back to the
+// tile in BF16. One warp works on the row; lane l holds dimensions l, l + 32, l + 64 and l + 96,
+// which is what the order of the additions in the sum of squares depends on. Returns the largest
+// magnitude this lane wrote.
+__device__ __forceinline__ float normalize_row(__nv_bfloat16 *row, float *scratch,
+                                               const __nv_bfloat16 *__restrict__ weight,
+                                               const float2 *__restrict__ row_trig, int pairs,
+                                               float epsilon) {
     const int lane = threadIdx.x % 32;
     float values[4];
     float squares = 0.0f;
@@ -90,19 +118,18 @@ __device__ __forceinline__ void normalize_row(__nv_bfloat16 *row, float *scratch
         values[part] = __fmul_rn(
             values[part], __fmul_rn(inverse, __bfloat162float(weight[lane + part * 32])));
     }
-    if (token_angles != nullptr) {
+    if (row_trig != nullptr) {
         #pragma unroll
         for (int part = 0; part < 4; part++) {
             scratch[lane + part * 32] = values[part];
         }
         __syncwarp();
         for (int pair = lane; pair < pairs; pair += 32) {
-            float sine, cosine;
-            sincosf(token_angles[pair], &sine, &cosine);
+            const float2 trig = row_trig[pair]; // (cosine, sine)
             const float first = scratch[pair];
             const float second = scratch[pair + pairs];
-            scratch[pair] = __fmaf_rn(cosine, first, -__fmul_rn(sine, second));
-            scratch[pair + pairs] = __fmaf_rn(sine, first, __fmul_rn(cosine, second));
+            scratch[pair] = __fmaf_rn(trig.x, first, -__fmul_rn(trig.y, second));
+            scratch[pair + pairs] = __fmaf_rn(trig.y, first, __fmul_rn(trig.x, second));
         }
         __syncwarp();
         #pragma unroll
@@ -111,20 +138,39 @@ __device__ __forceinline__ void normalize_row(__nv_bfloat16 *row, float *scratch
         }
         __syncwarp();
     }
+    float maximum = 0.0f;
     #pragma unroll
     for (int part = 0; part < 4; part++) {
-        row[lane + part * 32] = __float2bfloat16_rn(values[part]);
+        const __nv_bfloat16 rounded = __float2bfloat16_rn(values[part]);
+        row[lane + part * 32] = rounded;
+        maximum = fmaxf(maximum, fabsf(__bfloat162float(rounded)));
     }
+    return maximum;
 }
 
+__device__ __forceinline__ float chunk_max(const uint4 &chunk) {
+    const uint32_t words[4] = {chunk.x, chunk.y, chunk.z, chunk.w};
+    float maximum = 0.0f;
+    #pragma unroll
+    for (int word = 0; word < 4; word++) {
+        maximum = fmaxf(maximum, fabsf(__uint_as_float(words[word] << 16)));
+        maximum = fmaxf(maximum, fabsf(__uint_as_float(words[word] & 0xffff0000u)));
+    }
+    return maximum;
+}
+
+// Dynamic shared memory: the cosines and sines of the block's angles, [rows][pairs] float2, computed
+// once per CTA and used by q and k of every head the CTA takes.
 template <bool NORMALIZE, bool STATS, bool QUANTIZE>
 __global__ void __launch_bounds__(THREADS, 4) inputs_kernel(const InputsParams p) {
+    extern __shared__ __align__(16) float2 trig[];
     __shared__ __align__(16) __nv_bfloat16 tile[BLOCK_ROWS][HEAD_DIM];
     __shared__ float scratch[WARPS][HEAD_DIM];
-    __shared__ float maxima[HEAD_DIM / 32];
+    __shared__ float maxima[WARPS];
     const int block = blockIdx.x;
-    const int head = blockIdx.y;
     const int blocks = gridDim.x;
+    const int first_head = blockIdx.y * p.heads_per_cta;
+    const int head_count = min(p.heads_per_cta, p.heads - first_head);
     const int64_t first_token =
         p.tile_starts != nullptr ? p.tile_starts[block] : static_cast<int64_t>(block) * BLOCK_ROWS;
     const int rows = p.tile_lengths != nullptr
@@ -132,10 +178,16 @@ __global__ void __launch_bounds__(THREADS, 4) inputs_kernel(const InputsParams p
                          : min(BLOCK_ROWS, p.tokens - block * BLOCK_ROWS);
     const int lane = threadIdx.x % 32;
     const int warp = threadIdx.x / 32;
-    const size_t statistic = (static_cast<size_t>(head) * blocks + block) * HEAD_DIM;
+    const bool rotate = NORMALIZE && p.angles != nullptr;
+    const bool values_here =
+        QUANTIZE && (p.value_head_maxima != nullptr || p.value_scales_ready != 0);
+    const int parts = p.last_part - p.first_part + 1;
+    const int items = head_count * parts;
 
     uint4 chunks[CHUNKS_PER_THREAD];
-    auto load = [&](int part) {
+    auto load = [&](int item) {
+        const int part = p.first_part + item % parts;
+        const int head = first_head + item / parts;
         const __nv_bfloat16 *rows_base =
             p.source[part] + first_token * p.token_stride[part] + head * p.head_stride[part];
         #pragma unroll
@@ -161,51 +213,76 @@ __global__ void __launch_bounds__(THREADS, 4) inputs_kernel(const InputsParams p
         }
     };
 
-    const bool values_here =
-        QUANTIZE && (p.value_head_maxima != nullptr || p.value_scales_ready != 0);
-    const int last_part = p.last_part;
-    load(p.first_part);
-    for (int part = p.first_part; part <= last_part; part++) {
+    load(0);
+    if (rotate) {
+        for (int index = threadIdx.x; index < rows * p.pairs; index += THREADS) {
+            float sine, cosine;
+            sincosf(p.angles[first_token * p.pairs + index], &sine, &cosine);
+            trig[index] = make_float2(cosine, sine);
+        }
+    }
+    for (int item = 0; item < items; item++) {
+        const int part = p.first_part + item % parts;
+        const int head = first_head + item / parts;
+        const size_t statistic = (static_cast<size_t>(head) * blocks + block) * HEAD_DIM;
+        // The rows go to the tile; the largest magnitude is taken on the way where nothing
+        // changes the rows before it is needed.
+        float maximum = 0.0f;
         #pragma unroll
         for (int index = 0; index < CHUNKS_PER_THREAD; index++) {
             const int chunk = threadIdx.x + index * THREADS;
             if (chunk / 16 < rows) {
                 *reinterpret_cast<uint4 *>(&tile[chunk / 16][(chunk % 16) * 8]) = chunks[index];
+                if (QUANTIZE && (!NORMALIZE || part == 2)) {
+                    maximum = fmaxf(maximum, chunk_max(chunks[index]));
+                }
             }
         }
         __syncthreads();
-        if (part < last_part) {
-            load(part + 1);
+        if (item + 1 < items) {
+            load(item + 1);
+        }
+        if (NORMALIZE && part < 2) {
+            for (int row = warp; row < rows; row += WARPS) {
+                maximum = fmaxf(maximum,
+                                normalize_row(tile[row], scratch[warp], p.weight[part],
+                                              rotate ? trig + row * p.pairs : nullptr, p.pairs,
+                                              p.epsilon));
+            }
+        }
+        const bool needs_maximum = QUANTIZE && (part < 2 || !values_here);
+        if (needs_maximum) {
+            maximum = warp_max(maximum);
+            if (lane == 0) {
+                maxima[warp] = maximum;
+            }
+        }
+        if (NORMALIZE || needs_maximum) {
+            __syncthreads();
+        }
+        if (needs_maximum) {
+            maximum = maxima[0];
+            #pragma unroll
+            for (int index = 1; index < WARPS; index++) {
+                maximum = fmaxf(maximum, maxima[index]);
+            }
+        }
+
+        if constexpr (STATS) {
+            // The sums over the rows in row order, one thread per dimension.
+            if (threadIdx.x < HEAD_DIM) {
+                const int dimension = threadIdx.x;
+                float sum = 0.0f;
+                for (int row = 0; row < rows; row++) {
+                    sum += __bfloat162float(tile[row][dimension]);
+                }
+                p.pooled[part][statistic + dimension] = part == 2 ? sum : sum / rows;
+            }
         }
 
         if (part == 2) {
-            const int dimension = threadIdx.x % HEAD_DIM;
-            if (threadIdx.x < HEAD_DIM && (STATS || (QUANTIZE && !values_here))) {
-                float sum = 0.0f, maximum = 0.0f;
-                for (int row = 0; row < rows; row++) {
-                    const float value = __bfloat162float(tile[row][dimension]);
-                    sum += value;
-                    maximum = fmaxf(maximum, fabsf(value));
-                }
-                if constexpr (STATS) {
-                    p.pooled[2][statistic + dimension] = sum;
-                }
-                if (QUANTIZE && !values_here) {
-                    maximum = warp_max(maximum);
-                    if (lane == 0) {
-                        maxima[warp] = maximum;
-                    }
-                }
-            }
-            if (QUANTIZE && !values_here) {
-                __syncthreads();
-                if (threadIdx.x == 0) {
-                    float maximum = maxima[0];
-                    for (int index = 1; index < HEAD_DIM / 32; index++) {
-                        maximum = fmaxf(maximum, maxima[index]);
-                    }
-                    p.value_maxima[head * blocks + block] = maximum;
-                }
+            if (QUANTIZE && !values_here && threadIdx.x == 0) {
+                p.value_maxima[head * blocks + block] = maximum;
             }
             if (values_here) {
                 // FP8 V transposed into 64 columns per block, zero past the block's rows. Each
@@ -219,6 +296,8 @@ __global__ void __launch_bounds__(THREADS, 4) inputs_kernel(const InputsParams p
                 } else {
                     scale = p.value_scales[head];
                 }
+                const Divider divide(scale);
+                const int dimension = threadIdx.x % HEAD_DIM;
                 const int first_row = threadIdx.x / HEAD_DIM * 32;
                 uint32_t words[8];
                 #pragma unroll
@@ -230,7 +309,7 @@ __global__ void __launch_bounds__(THREADS, 4) inputs_kernel(const InputsParams p
                         const float element =
                             row < rows ? __bfloat162float(tile[row][dimension]) : 0.0f;
                         packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(
-                                      element / scale, __NV_SATFINITE, __NV_E4M3))
+                                      divide(element), __NV_SATFINITE, __NV_E4M3))
                                   << (8 * byte);
                     }
                     words[word] = packed;
@@ -242,83 +321,49 @@ __global__ void __launch_bounds__(THREADS, 4) inputs_kernel(const InputsParams p
                 destination[0] = make_uint4(words[0], words[1], words[2], words[3]);
                 destination[1] = make_uint4(words[4], words[5], words[6], words[7]);
             }
-            break;
-        }
-
-        if constexpr (NORMALIZE) {
-            for (int row = warp; row < rows; row += WARPS) {
-                normalize_row(tile[row], scratch[warp], p.weight[part],
-                              p.angles != nullptr ? p.angles + (first_token + row) * p.pairs
-                                                  : nullptr,
-                              p.pairs, p.epsilon);
-            }
-            __syncthreads();
-        }
-
-        // The sum and the maximum over the rows of the block, one thread per dimension.
-        if (threadIdx.x < HEAD_DIM) {
-            const int dimension = threadIdx.x;
-            float sum = 0.0f, maximum = 0.0f;
-            for (int row = 0; row < rows; row++) {
-                const float value = __bfloat162float(tile[row][dimension]);
-                sum += value;
-                maximum = fmaxf(maximum, fabsf(value));
-            }
-            if constexpr (STATS) {
-                p.pooled[part][statistic + dimension] = sum / rows;
-            }
+        } else {
             if constexpr (QUANTIZE) {
-                maximum = warp_max(maximum);
-                if (lane == 0) {
-                    maxima[warp] = maximum;
+                const float scale = fmaxf(maximum / 127.0f, 1e-30f);
+                if (threadIdx.x == 0) {
+                    p.scales[part][head * blocks + block] = scale;
                 }
-            }
-        }
-
-        if constexpr (QUANTIZE) {
-            __syncthreads();
-            float maximum = maxima[0];
-            #pragma unroll
-            for (int index = 1; index < HEAD_DIM / 32; index++) {
-                maximum = fmaxf(maximum, maxima[index]);
-            }
-            const float scale = fmaxf(maximum / 127.0f, 1e-30f);
-            if (threadIdx.x == 0) {
-                p.scales[part][head * blocks + block] = scale;
-            }
-            // A row of 128 INT8 values is 8 chunks of 16 bytes, each from 16 BF16 values.
-            uint8_t *destination = p.quantized[part] + (first_token * p.heads + head) * HEAD_DIM;
-            for (int chunk = threadIdx.x; chunk < rows * 8; chunk += THREADS) {
-                const uint4 *source =
-                    reinterpret_cast<const uint4 *>(&tile[chunk / 8][(chunk % 8) * 16]);
-                const uint4 halves[2] = {source[0], source[1]};
-                const __nv_bfloat16 *elements = reinterpret_cast<const __nv_bfloat16 *>(halves);
-                uint32_t words[4];
-                #pragma unroll
-                for (int word = 0; word < 4; word++) {
-                    uint32_t packed = 0;
+                const Divider divide(scale);
+                // A row of 128 INT8 values is 8 chunks of 16 bytes, each from 16 BF16 values.
+                uint8_t *destination =
+                    p.quantized[part] + (first_token * p.heads + head) * HEAD_DIM;
+                for (int chunk = threadIdx.x; chunk < rows * 8; chunk += THREADS) {
+                    const uint4 *source =
+                        reinterpret_cast<const uint4 *>(&tile[chunk / 8][(chunk % 8) * 16]);
+                    const uint4 halves[2] = {source[0], source[1]};
+                    const __nv_bfloat16 *elements =
+                        reinterpret_cast<const __nv_bfloat16 *>(halves);
+                    uint32_t words[4];
                     #pragma unroll
-                    for (int byte = 0; byte < 4; byte++) {
-                        const int8_t value = static_cast<int8_t>(__float2int_rn(
-                            __bfloat162float(elements[word * 4 + byte]) / scale));
-                        packed |= static_cast<uint32_t>(static_cast<uint8_t>(value)) << (8 * byte);
+                    for (int word = 0; word < 4; word++) {
+                        uint32_t packed = 0;
+                        #pragma unroll
+                        for (int byte = 0; byte < 4; byte++) {
+                            const int8_t value = static_cast<int8_t>(__float2int_rn(
+                                divide(__bfloat162float(elements[word * 4 + byte]))));
+                            packed |= static_cast<uint32_t>(static_cast<uint8_t>(value))
+                                      << (8 * byte);
+                        }
+                        words[word] = packed;
                     }
-                    words[word] = packed;
+                    *reinterpret_cast<uint4 *>(
+                        destination + static_cast<int64_t>(chunk / 8) * p.heads * HEAD_DIM +
+                        (chunk % 8) * 16) = make_uint4(words[0], words[1], words[2], words[3]);
                 }
-                *reinterpret_cast<uint4 *>(destination +
-                                           static_cast<int64_t>(chunk / 8) * p.heads * HEAD_DIM +
-                                           (chunk % 8) * 16) =
-                    make_uint4(words[0], words[1], words[2], words[3]);
             }
-        }
-
-        if (NORMALIZE && p.normalized[part] != nullptr) {
-            __nv_bfloat16 *rows_base = p.normalized[part] + first_token * p.token_stride[part] +
-                                       head * p.head_stride[part];
-            for (int chunk = threadIdx.x; chunk < rows * 16; chunk += THREADS) {
-                *reinterpret_cast<uint4 *>(rows_base + (chunk / 16) * p.token_stride[part] +
-                                           (chunk % 16) * 8) =
-                    *reinterpret_cast<const uint4 *>(&tile[chunk / 16][(chunk % 16) * 8]);
+            if (NORMALIZE && p.normalized[part] != nullptr) {
+                __nv_bfloat16 *rows_base = p.normalized[part] +
+                                           first_token * p.token_stride[part] +
+                                           head * p.head_stride[part];
+                for (int chunk = threadIdx.x; chunk < rows * 16; chunk += THREADS) {
+                    *reinterpret_cast<uint4 *>(rows_base + (chunk / 16) * p.token_stride[part] +
+                                               (chunk % 16) * 8) =
+                        *reinterpret_cast<const uint4 *>(&tile[chunk / 16][(chunk % 16) * 8]);
+                }
             }
         }
         __syncthreads();
@@ -353,9 +398,25 @@ bool aligned_rows(const void *base, int64_t token_stride, int64_t head_stride) {
 }
 
 template <bool NORMALIZE, bool STATS, bool QUANTIZE>
-int launch(const InputsParams &params, int blocks, cudaStream_t stream) {
+int launch(InputsParams params, int blocks, cudaStream_t stream) {
+    const bool rotate = NORMALIZE && params.angles != nullptr;
+    // With angles a CTA takes several heads so that their sincosf is paid once; the grid still
+    // holds several CTAs per SM slot.
+    params.heads_per_cta = rotate ? HEADS_PER_CTA : 1;
+    const int groups = (params.heads + params.heads_per_cta - 1) / params.heads_per_cta;
+    const size_t shared = rotate ? static_cast<size_t>(BLOCK_ROWS) * params.pairs * sizeof(float2)
+                                 : 0;
+    if (rotate) {
+        // Up to 64 pairs: 32 KiB of cosines and sines beside the 20 KiB of static shared memory.
+        static SharedMemoryOptIn shared_memory;
+        const cudaError_t configured = shared_memory.ensure(
+            inputs_kernel<NORMALIZE, STATS, QUANTIZE>, BLOCK_ROWS * (HEAD_DIM / 2) * 8);
+        if (configured != cudaSuccess) {
+            return static_cast<int>(configured);
+        }
+    }
     inputs_kernel<NORMALIZE, STATS, QUANTIZE>
-        <<<dim3(blocks, params.heads), THREADS, 0, stream>>>(params);
+        <<<dim3(blocks, groups), THREADS, shared, stream>>>(params);
     return static_cast<int>(cudaGetLastError());
 }
 

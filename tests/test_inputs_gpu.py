@@ -226,3 +226,29 @@ def test_fused_pass_agrees_with_separate_passes(oracle):
     attention.dense_quantized(separate_qkv, output, SCALE, separate, attention.AttentionInputs.RAW)
     assert attention.take_status() == 0
     assert_workspaces_equal(fused, separate)
+
+
+def test_quantization_is_bit_exact_over_many_scales(oracle, reference_kernels):
+    """Many blocks whose magnitudes span forty binades, so that the per-block scales take many
+    different significands: the quotients must still round exactly as the reference's divisions."""
+    tokens, heads = 8192, 4
+    inner = heads * 128
+    generator = torch.Generator().manual_seed(77)
+    values = torch.randn((tokens, 3, heads, 128), generator=generator)
+    binades = torch.randint(-20, 21, (tokens // 64, 1, 3, heads, 1), generator=generator).float()
+    values = (values.view(tokens // 64, 64, 3, heads, 128) * torch.exp2(binades)).view(
+        tokens, 3, heads, 128)
+    qkv = values.bfloat16().cuda()
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    ours = attention.QuantizedWorkspace(tokens, heads)
+    theirs = attention.QuantizedWorkspace(tokens, heads)
+    attention.dense_quantized(qkv, output, SCALE, ours, attention.AttentionInputs.RAW)
+    layout = attention.qkv_layout(heads)
+    raw = theirs.raw()
+    base = qkv.data_ptr()
+    assert reference_kernels.mmh3_attention_quantized(
+        base, base + 2 * inner, base + 4 * inner, output.data_ptr(), tokens, heads,
+        ctypes.byref(layout), SCALE, None, ctypes.byref(raw), 0, None) == 0
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    assert_workspaces_equal(ours, theirs)
