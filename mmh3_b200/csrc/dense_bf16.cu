@@ -78,6 +78,8 @@ constexpr uint32_t OUTPUT_MMA = instruction_descriptor(ACCUMULATE_F32, FORMAT_BF
 
 // The maximum may lag the true row maximum by this much (in log2 units) before O is rescaled.
 constexpr float RESCALE_THRESHOLD = 8.0f;
+// Of every four pairs of probabilities, how many take the polynomial exp2 instead of the MUFU.
+constexpr int POLYNOMIAL_PAIRS_OF_4 = 1;
 
 struct DenseMaps {
     CUtensorMap query;
@@ -85,16 +87,19 @@ struct DenseMaps {
     CUtensorMap value;
 };
 
-// K-major descriptor of contraction step `step` (16 of the 128 dimensions) of a Q or K tile.
-__device__ __forceinline__ uint64_t row_operand(uint32_t tile, int step) {
-    return smem_descriptor(tile + (step / 4) * SLAB_BYTES + (step % 4) * 32, 16, 1024);
+// K-major descriptor of a Q or K tile, and the byte offset of contraction step `step` (16 of the
+// 128 dimensions) in it.
+__device__ __forceinline__ uint64_t row_operand(uint32_t tile) {
+    return smem_descriptor(tile, 16, 1024);
 }
+__host__ __device__ constexpr uint32_t row_step(int step) { return (step / 4) * SLAB_BYTES + (step % 4) * 32; }
 
-// MN-major descriptor of contraction step `step` (16 of the 128 keys) of a V tile: N runs along
-// the rows of both slabs.
-__device__ __forceinline__ uint64_t value_operand(uint32_t tile, int step) {
-    return smem_descriptor(tile + step * 16 * 128, SLAB_BYTES, 1024);
+// MN-major descriptor of a V tile (N runs along the rows of both slabs), and the byte offset of
+// contraction step `step` (16 of the 128 keys) in it.
+__device__ __forceinline__ uint64_t value_operand(uint32_t tile) {
+    return smem_descriptor(tile, SLAB_BYTES, 1024);
 }
+__host__ __device__ constexpr uint32_t value_step(int step) { return step * 16 * 128; }
 
 __global__ void __launch_bounds__(THREADS, 1)
     dense_bf16_kernel(const __grid_constant__ DenseMaps maps, __nv_bfloat16 *__restrict__ output,
@@ -182,22 +187,28 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (lane == 0) {
             const uint32_t query_tiles = base + SMEM_QUERY;
             const uint32_t ring = base + SMEM_RING;
+            const uint64_t query_operands[QUERY_TILES] = {row_operand(query_tiles),
+                                                          row_operand(query_tiles + TILE_BYTES)};
             auto score = [&](int tile, uint32_t key_tile) {
+                const uint64_t key_operand = row_operand(key_tile);
                 #pragma unroll
                 for (int step = 0; step < HEAD_DIM / 16; step++) {
                     mma_f16_ss(tmem + TMEM_SCORES + tile * TILE_N,
-                               row_operand(query_tiles + tile * TILE_BYTES, step),
-                               row_operand(key_tile, step), SCORE_MMA, step > 0);
+                               advance_descriptor(query_operands[tile], row_step(step)),
+                               advance_descriptor(key_operand, row_step(step)), SCORE_MMA,
+                               step > 0);
                 }
                 tcgen05_commit(barrier(SCORES_FULL + tile));
             };
             auto accumulate = [&](int tile, uint32_t value_tile, bool first) {
+                const uint64_t operand = value_operand(value_tile);
                 #pragma unroll
                 for (int step = 0; step < TILE_N / 16; step++) {
                     // P is BF16, two to a column: 16 keys are 8 columns.
                     mma_f16_ts(tmem + TMEM_OUTPUT + tile * HEAD_DIM,
                                tmem + TMEM_SCORES + tile * TILE_N + step * 8,
-                               value_operand(value_tile, step), OUTPUT_MMA, !first || step > 0);
+                               advance_descriptor(operand, value_step(step)), OUTPUT_MMA,
+                               !first || step > 0);
                 }
             };
             bool alive = mbar_wait(barrier(QUERY_FULL), 0, watchdog, STATUS_DENSE | 2) &&
@@ -257,7 +268,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         const uint32_t scores = tmem + lane_base + TMEM_SCORES + tile * TILE_N;
         const uint32_t accumulator = tmem + lane_base + TMEM_OUTPUT + tile * HEAD_DIM;
         float maximum = -INFINITY; // of the raw scores, before the scale
-        float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float2 sums[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
         bool alive = true;
         for (int block = 0; block < blocks; block++) {
             alive = mbar_wait(barrier(SCORES_FULL + tile), block & 1, watchdog, STATUS_DENSE | 7);
@@ -305,10 +316,9 @@ __global__ void __launch_bounds__(THREADS, 1)
                     const float raised = fmaxf(maximum, block_maximum);
                     const float correction = exp2_approx((maximum - raised) * scale_log2);
                     maximum = raised;
-                    #pragma unroll
-                    for (int index = 0; index < 4; index++) {
-                        sums[index] *= correction;
-                    }
+                    const float2 correction2 = make_float2(correction, correction);
+                    sums[0] = __fmul2_rn(sums[0], correction2);
+                    sums[1] = __fmul2_rn(sums[1], correction2);
                     #pragma unroll
                     for (int chunk = 0; chunk < 4; chunk++) {
                         uint32_t values[32];
@@ -323,18 +333,28 @@ __global__ void __launch_bounds__(THREADS, 1)
                     }
                 }
             }
+            // p = 2^(s * scale - maximum * scale), two elements at a time. One pair in four takes
+            // the polynomial on the FMA pipe: the MUFU alone would need as long for a tile's
+            // exponentials as the tensor pipe needs for its two MMAs.
             const float offset = maximum * scale_log2;
+            const float2 scale2 = make_float2(scale_log2, scale_log2);
+            const float2 offset2 = make_float2(-offset, -offset);
             #pragma unroll
             for (int chunk = 0; chunk < 2; chunk++) {
                 uint32_t packed[32];
                 #pragma unroll
                 for (int pair = 0; pair < 32; pair++) {
                     const int index = chunk * 64 + pair * 2;
-                    const float low = exp2_approx(fmaf(s[index], scale_log2, -offset));
-                    const float high = exp2_approx(fmaf(s[index + 1], scale_log2, -offset));
-                    sums[pair % 2 * 2] += low;
-                    sums[pair % 2 * 2 + 1] += high;
-                    packed[pair] = pack_bf16(low, high);
+                    const float2 x =
+                        __ffma2_rn(make_float2(s[index], s[index + 1]), scale2, offset2);
+                    float2 probability;
+                    if (pair % 4 < POLYNOMIAL_PAIRS_OF_4) {
+                        probability = exp2_polynomial(x);
+                    } else {
+                        probability = make_float2(exp2_approx(x.x), exp2_approx(x.y));
+                    }
+                    sums[pair % 2] = __fadd2_rn(sums[pair % 2], probability);
+                    packed[pair] = pack_bf16(probability.x, probability.y);
                 }
                 tmem_store_32(scores + chunk * 32, packed);
             }
@@ -348,7 +368,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         }
         if (alive) {
             tcgen05_fence_after();
-            const float inverse = 1.0f / ((sums[0] + sums[1]) + (sums[2] + sums[3]));
+            const float inverse = 1.0f / ((sums[0].x + sums[0].y) + (sums[1].x + sums[1].y));
             const int token = first_query + tile * TILE_M + row;
             __nv_bfloat16 *output_row =
                 output + static_cast<int64_t>(token) * output_token_stride +

@@ -232,6 +232,14 @@ __device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t l
     return descriptor;
 }
 
+// The same descriptor `bytes` further on in shared memory: the address field is the low 14 bits, in
+// units of 16 bytes, and shared memory is smaller than the field, so the addition never carries
+// into the next field. The MMA-issuing thread builds each tile's descriptor once and steps through
+// it with this, which keeps its instruction stream short.
+__device__ __forceinline__ uint64_t advance_descriptor(uint64_t descriptor, uint32_t bytes) {
+    return descriptor + (bytes >> 4);
+}
+
 // Operand formats of the instruction descriptor.
 constexpr uint32_t FORMAT_F16 = 0, FORMAT_BF16 = 1;   // kind::f16
 constexpr uint32_t FORMAT_U8 = 0, FORMAT_S8 = 1;      // kind::i8
@@ -289,6 +297,26 @@ __device__ __forceinline__ float exp2_approx(float value) {
     float result;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(result) : "f"(value));
     return result;
+}
+
+// 2^x for both halves of a pair on the FMA pipe instead of the MUFU: x is split into its nearest
+// integer n (the low mantissa bits after adding 1.5 * 2^23) and a fraction f in [-0.5, 0.5], 2^f is
+// a cubic (relative error under 8e-5, far below what BF16 or E4M3 keep), and n goes into the
+// exponent field. x must not be far above zero; anything below -127 gives 2^-127.
+__device__ __forceinline__ float2 exp2_polynomial(float2 x) {
+    constexpr float MAGIC = 12582912.0f;
+    x.x = fmaxf(x.x, -127.0f);
+    x.y = fmaxf(x.y, -127.0f);
+    const float2 shifted = __fadd2_rn(x, make_float2(MAGIC, MAGIC));
+    const float2 whole = __fadd2_rn(shifted, make_float2(-MAGIC, -MAGIC));
+    const float2 fraction = __ffma2_rn(whole, make_float2(-1.0f, -1.0f), x);
+    float2 power = __ffma2_rn(fraction, make_float2(0.05520550534129143f, 0.05520550534129143f),
+                              make_float2(0.24261397123336792f, 0.24261397123336792f));
+    power = __ffma2_rn(power, fraction, make_float2(0.6932547688484192f, 0.6932547688484192f));
+    power = __ffma2_rn(power, fraction, make_float2(0.9999276995658875f, 0.9999276995658875f));
+    power.x = __int_as_float(__float_as_int(power.x) + (__float_as_int(shifted.x) << 23));
+    power.y = __int_as_float(__float_as_int(power.y) + (__float_as_int(shifted.y) << 23));
+    return power;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
