@@ -302,11 +302,12 @@ __device__ __forceinline__ float exp2_approx(float value) {
 // 2^x for both halves of a pair on the FMA pipe instead of the MUFU: x is split into its nearest
 // integer n (the low mantissa bits after adding 1.5 * 2^23) and a fraction f in [-0.5, 0.5], 2^f is
 // a cubic (relative error under 8e-5, far below what BF16 or E4M3 keep), and n goes into the
-// exponent field. x must not be far above zero; anything below -127 gives 2^-127.
+// exponent field. x must not be far above zero. Anything below -125 gives 2^-125: the cubic lies in
+// [0.7, 1.42], so its exponent field is 126 or 127 and n = -125 still leaves a positive one.
 __device__ __forceinline__ float2 exp2_polynomial(float2 x) {
     constexpr float MAGIC = 12582912.0f;
-    x.x = fmaxf(x.x, -127.0f);
-    x.y = fmaxf(x.y, -127.0f);
+    x.x = fmaxf(x.x, -125.0f);
+    x.y = fmaxf(x.y, -125.0f);
     const float2 shifted = __fadd2_rn(x, make_float2(MAGIC, MAGIC));
     const float2 whole = __fadd2_rn(shifted, make_float2(-MAGIC, -MAGIC));
     const float2 fraction = __ffma2_rn(whole, make_float2(-1.0f, -1.0f), x);
