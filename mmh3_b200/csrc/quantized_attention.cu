@@ -11,14 +11,17 @@
 //   O += P8 V8^T with kind::f8f6f4 into FP32 tensor memory, P8 read from tensor memory;
 // - warps 0-7 are the softmax, one thread per query row: INT32 scores are dequantized with
 //   scale * log2(e) * q_scale[row block] * k_scale[key block] (a 128-key block spans two key
-//   scales), the probabilities are scaled by 448 and rounded to E4M3 as the reference does, and
-//   written over the first 32 columns of S.
+//   scales), the probabilities are scaled and rounded to E4M3 as the reference does, and written
+//   over the first 32 columns of S. Maxima are taken on the integers, the FP32 arithmetic runs on
+//   pairs (fma.rn.f32x2), and a quarter of the exponentials on a polynomial instead of the MUFU:
+//   with MMAs twice as fast as BF16's, this kernel is bound by its softmax instruction stream.
 //
-// The running maximum is exact here (no lag as in the BF16 kernel): E4M3 saturates at 448, so a
-// probability may never exceed one.
+// The running maximum may lag the true one by a factor of two before O is rescaled; E4M3
+// saturates at 448, so the probabilities are scaled by 224 instead of the reference's 448.
 #include <cfloat>
 #include <cmath>
 #include <cuda_fp8.h>
+#include <type_traits>
 
 #include "common.cuh"
 #include "sm100.cuh"
@@ -72,8 +75,15 @@ constexpr uint32_t SCORE_MMA =
 constexpr uint32_t OUTPUT_MMA =
     instruction_descriptor(ACCUMULATE_F32, FORMAT_E4M3, FORMAT_E4M3, 0, 0, TILE_M, HEAD_DIM);
 
-// log2(448): folding the reference's factor of 448 into the exponent.
-constexpr float LOG2_448 = 8.807354922057604f;
+// The probabilities go to E4M3 times 224: the reference's factor of 448, halved because the running
+// maximum here may lag the true one by a factor of two. log2(224) folds it into the exponent.
+constexpr float LOG2_224 = 7.807354922057604f;
+constexpr float RESCALE_THRESHOLD = 1.0f;
+// Of every four pairs of probabilities, how many take the polynomial exp2 instead of the MUFU.
+constexpr int POLYNOMIAL_PAIRS_OF_4 = 1;
+// What a key past the last token scores, before the scales: below every real score (at most
+// 128 * 127 * 127 in magnitude) by far, and small enough to stay finite after scaling.
+constexpr int32_t MASKED_SCORE = -(1 << 28);
 
 struct QuantizedMaps {
     CUtensorMap query; // [128, tokens, heads] INT8
@@ -84,14 +94,6 @@ struct QuantizedMaps {
 // K-major descriptor of contraction step `step` (32 bytes of the 128-byte rows) of a tile.
 __device__ __forceinline__ uint64_t row_operand(uint32_t tile, int step) {
     return smem_descriptor(tile + step * 32, 16, 1024);
-}
-
-__device__ __forceinline__ uint32_t pack_e4m3(float a, float b, float c, float d) {
-    // cvt packs its first source into the upper byte.
-    uint16_t low, high;
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(low) : "f"(b), "f"(a));
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(high) : "f"(d), "f"(c));
-    return static_cast<uint32_t>(low) | (static_cast<uint32_t>(high) << 16);
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -260,14 +262,15 @@ __global__ void __launch_bounds__(THREADS, 1)
                                                         token / 64]
                                          : 0.0f);
         float maximum = -FLT_MAX;
-        float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float2 sums[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
         bool alive = true;
         for (int block = 0; block < blocks; block++) {
-            // The scales of the two 64-key halves of this block.
+            // The scales of the two 64-key halves of this block. A half past the last block holds
+            // masked scores only and borrows the other's scale.
             const float factor_low = query_factor * __ldg(head_key_scales + 2 * block);
             const float factor_high =
                 2 * block + 1 < blocks64 ? query_factor * __ldg(head_key_scales + 2 * block + 1)
-                                         : 0.0f;
+                                         : factor_low;
             alive = mbar_wait(barrier(SCORES_FULL + tile), block & 1, watchdog,
                               STATUS_QUANTIZED | 7);
             alive = __all_sync(0xffffffffu, alive);
@@ -281,39 +284,47 @@ __global__ void __launch_bounds__(THREADS, 1)
                 tmem_load_32(scores + chunk * 32, raw[chunk]);
             }
             tmem_wait_load();
-            float s[TILE_N];
-            #pragma unroll
-            for (int index = 0; index < TILE_N; index++) {
-                s[index] = static_cast<float>(static_cast<int32_t>(raw[index / 32][index % 32])) *
-                           (index < 64 ? factor_low : factor_high);
-            }
             const int valid = tokens - block * TILE_N;
             if (valid < TILE_N) {
+                // Keys past the last token: an integer far below any score.
                 #pragma unroll
                 for (int index = 0; index < TILE_N; index++) {
                     if (index >= valid) {
-                        s[index] = -FLT_MAX;
+                        raw[index / 32][index % 32] = static_cast<uint32_t>(MASKED_SCORE);
                     }
                 }
             }
-            float partial[4] = {s[0], s[1], s[2], s[3]};
+            // The maximum of each 64-key half as an integer, three values to an instruction, then
+            // the two candidates in FP32 with their scales.
+            int maxima[2];
             #pragma unroll
-            for (int index = 4; index < TILE_N; index++) {
-                partial[index % 4] = fmaxf(partial[index % 4], s[index]);
+            for (int half = 0; half < 2; half++) {
+                int partial[2] = {static_cast<int>(raw[half * 2][0]),
+                                  static_cast<int>(raw[half * 2][1])};
+                #pragma unroll
+                for (int index = 2; index + 1 < 64; index += 2) {
+                    const int chain = (index / 2) % 2;
+                    partial[chain] = __vimax3_s32(
+                        partial[chain], static_cast<int>(raw[half * 2 + index / 32][index % 32]),
+                        static_cast<int>(raw[half * 2 + (index + 1) / 32][(index + 1) % 32]));
+                }
+                maxima[half] = max(partial[0], partial[1]);
             }
-            const float block_maximum =
-                fmaxf(fmaxf(partial[0], partial[1]), fmaxf(partial[2], partial[3]));
-            const bool grown = block_maximum > maximum;
+            const float block_maximum = fmaxf(static_cast<float>(maxima[0]) * factor_low,
+                                              static_cast<float>(maxima[1]) * factor_high);
+            // The maximum may lag by up to one (a factor of two in the probabilities), which the
+            // factor of 224 instead of 448 leaves room for in E4M3; the division by the row sum
+            // makes the result exact again.
+            const bool grown = block_maximum - maximum > RESCALE_THRESHOLD;
             if (block == 0) {
                 maximum = block_maximum;
             } else if (__any_sync(0xffffffffu, grown)) {
                 const float raised = fmaxf(maximum, block_maximum);
                 const float correction = exp2_approx(maximum - raised);
                 maximum = raised;
-                #pragma unroll
-                for (int index = 0; index < 4; index++) {
-                    sums[index] *= correction;
-                }
+                const float2 correction2 = make_float2(correction, correction);
+                sums[0] = __fmul2_rn(sums[0], correction2);
+                sums[1] = __fmul2_rn(sums[1], correction2);
                 #pragma unroll
                 for (int chunk = 0; chunk < 4; chunk++) {
                     uint32_t values[32];
@@ -327,18 +338,53 @@ __global__ void __launch_bounds__(THREADS, 1)
                     tmem_store_32(accumulator + chunk * 32, values);
                 }
             }
-            // 448 * exp2(s - maximum), at most 448, which E4M3 holds exactly.
-            const float offset = maximum - LOG2_448;
+            // 224 * exp2(score - maximum) as E4M3, two elements at a time; one pair in four takes
+            // the polynomial on the FMA pipe.
+            const float offset = LOG2_224 - maximum;
             uint32_t packed[32];
-            #pragma unroll
-            for (int quad = 0; quad < 32; quad++) {
-                float p[4];
+            // MASKED is set for the last block of a sequence that does not fill it: the keys past
+            // the last token then get an exponent of minus infinity whatever their scale is (a scale
+            // may be zero, which would turn the masked integer into a score of zero).
+            auto exponentials = [&](auto masked) {
+                constexpr bool MASKED = decltype(masked)::value;
                 #pragma unroll
-                for (int element = 0; element < 4; element++) {
-                    p[element] = exp2_approx(s[quad * 4 + element] - offset);
-                    sums[element] += p[element];
+                for (int quad = 0; quad < 32; quad++) {
+                    const float factor = quad < 16 ? factor_low : factor_high;
+                    const float2 factor2 = make_float2(factor, factor);
+                    const float2 offset2 = make_float2(offset, offset);
+                    uint16_t halves[2];
+                    #pragma unroll
+                    for (int pair = 0; pair < 2; pair++) {
+                        const int index = quad * 4 + pair * 2;
+                        const float2 raw_pair = make_float2(
+                            static_cast<float>(static_cast<int32_t>(raw[index / 32][index % 32])),
+                            static_cast<float>(
+                                static_cast<int32_t>(raw[(index + 1) / 32][(index + 1) % 32])));
+                        float2 x = __ffma2_rn(raw_pair, factor2, offset2);
+                        if (MASKED) {
+                            x.x = index < valid ? x.x : -INFINITY;
+                            x.y = index + 1 < valid ? x.y : -INFINITY;
+                        }
+                        float2 probability;
+                        if ((quad * 2 + pair) % 4 < POLYNOMIAL_PAIRS_OF_4) {
+                            probability = exp2_polynomial(x);
+                        } else {
+                            probability = make_float2(exp2_approx(x.x), exp2_approx(x.y));
+                        }
+                        sums[pair] = __fadd2_rn(sums[pair], probability);
+                        // cvt packs its first source into the upper byte.
+                        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;"
+                            : "=h"(halves[pair])
+                            : "f"(probability.y), "f"(probability.x));
+                    }
+                    packed[quad] = static_cast<uint32_t>(halves[0]) |
+                                   (static_cast<uint32_t>(halves[1]) << 16);
                 }
-                packed[quad] = pack_e4m3(p[0], p[1], p[2], p[3]);
+            };
+            if (valid < TILE_N) {
+                exponentials(std::true_type{});
+            } else {
+                exponentials(std::false_type{});
             }
             tmem_store_32(scores, packed);
             tmem_wait_store();
@@ -353,7 +399,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             tcgen05_fence_after();
             // The sums carry the factor of 448 the probabilities do.
             const float inverse =
-                value_scales[head] / ((sums[0] + sums[1]) + (sums[2] + sums[3]));
+                value_scales[head] / ((sums[0].x + sums[0].y) + (sums[1].x + sums[1].y));
             __nv_bfloat16 *output_row =
                 output + static_cast<int64_t>(token) * output_token_stride +
                 static_cast<int64_t>(head) * output_head_stride;
