@@ -336,6 +336,27 @@ def run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, a
     return extras
 
 
+def kernel_times(torch, fn) -> dict:
+    """Device time of each kernel one call of `fn` launches, by name, from the CUPTI activity
+    records torch's profiler collects (milliseconds). Empty when the profiler is unavailable."""
+    try:
+        from torch.profiler import ProfilerActivity, profile
+
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as recorded:
+            fn()
+            torch.cuda.synchronize()
+        times: dict[str, float] = {}
+        for event in recorded.events():
+            if event.device_time_total > 0:
+                name = event.name.replace("(anonymous namespace)::", "").replace("<unnamed>::", "")
+                name = name.split("(")[0].replace("void ", "")
+                times[name] = times.get(name, 0.0) + event.device_time_total / 1e3
+        return {name: round(ms, 4) for name, ms in times.items()}
+    except Exception as error:  # the breakdown is a convenience, never a reason to fail the run
+        return {"unavailable": str(error)[:80]}
+
+
 def run_vsa(torch, attention, synthetic, heads, scale, steps) -> dict:
     """Video sparse attention on the 31 x 48 x 84 grid + 512 text tokens (BASELINE configs[3]):
     pool, select and token attention timed apart. Inputs are drawn on the device: N(0, 1) plus 0.5 x
@@ -380,6 +401,7 @@ def run_vsa(torch, attention, synthetic, heads, scale, steps) -> dict:
         "workload": f"VSA L={tokens} (8 prefix + 2016 video tiles), H={heads}, kept {kept}",
         "ms": ms, "sparse_flops": sparse_flops, "sparse_tflops": sparse_flops / ms / 1e9,
         "dense_equivalent_tflops": attention_flops(tokens, heads) / ms / 1e9,
+        "kernel_ms": kernel_times(torch, whole),
         "selected_fraction": workspace.selected_fraction(),
         "expected_selected_fraction": plan.expected_selected_fraction(kept),
         "kernel_status": attention.take_status(),

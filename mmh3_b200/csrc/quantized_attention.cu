@@ -91,9 +91,9 @@ struct QuantizedMaps {
     CUtensorMap value; // [padded tokens, 128, heads] E4M3
 };
 
-// K-major descriptor of contraction step `step` (32 bytes of the 128-byte rows) of a tile.
-__device__ __forceinline__ uint64_t row_operand(uint32_t tile, int step) {
-    return smem_descriptor(tile + step * 32, 16, 1024);
+// K-major descriptor of a tile of 128-byte rows; contraction step `step` is 32 bytes further on.
+__device__ __forceinline__ uint64_t row_operand(uint32_t tile) {
+    return smem_descriptor(tile, 16, 1024);
 }
 
 __global__ void __launch_bounds__(THREADS, 1)
@@ -182,22 +182,27 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (lane == 0) {
             const uint32_t query_tiles = base + SMEM_QUERY;
             const uint32_t ring = base + SMEM_RING;
+            const uint64_t query_operands[QUERY_TILES] = {row_operand(query_tiles),
+                                                          row_operand(query_tiles + TILE_BYTES)};
             auto score = [&](int tile, uint32_t key_tile) {
+                const uint64_t key_operand = row_operand(key_tile);
                 #pragma unroll
                 for (int step = 0; step < HEAD_DIM / 32; step++) {
                     mma_i8_ss(tmem + TMEM_SCORES + tile * TILE_N,
-                              row_operand(query_tiles + tile * TILE_BYTES, step),
-                              row_operand(key_tile, step), SCORE_MMA, step > 0);
+                              advance_descriptor(query_operands[tile], step * 32),
+                              advance_descriptor(key_operand, step * 32), SCORE_MMA, step > 0);
                 }
                 tcgen05_commit(barrier(SCORES_FULL + tile));
             };
             auto accumulate = [&](int tile, uint32_t value_tile, bool first) {
+                const uint64_t operand = row_operand(value_tile);
                 #pragma unroll
                 for (int step = 0; step < TILE_N / 32; step++) {
                     // P is E4M3, four to a column: 32 keys are 8 columns.
                     mma_f8_ts(tmem + TMEM_OUTPUT + tile * HEAD_DIM,
                               tmem + TMEM_SCORES + tile * TILE_N + step * 8,
-                              row_operand(value_tile, step), OUTPUT_MMA, !first || step > 0);
+                              advance_descriptor(operand, step * 32), OUTPUT_MMA,
+                              !first || step > 0);
                 }
             };
             bool alive = mbar_wait(barrier(QUERY_FULL), 0, watchdog, STATUS_QUANTIZED | 2) &&

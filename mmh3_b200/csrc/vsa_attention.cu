@@ -20,7 +20,9 @@
 // Two CTAs share an SM (256 TMEM columns and under 100 KiB of shared memory each): while one
 // waits for its softmax, the MMAs of the other run.
 #include <cfloat>
+#include <climits>
 #include <cmath>
+#include <type_traits>
 
 #include "common.cuh"
 #include "sm100.cuh"
@@ -40,8 +42,13 @@ constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
 constexpr uint32_t TMEM_COLUMNS = 256;
 constexpr uint32_t TMEM_SCORES = 0;
 constexpr uint32_t TMEM_OUTPUT = 128;
-constexpr float RESCALE_THRESHOLD = 8.0f;
-constexpr float LOG2_448 = 8.807354922057604f;
+// How far (in log2 units) the running maximum may lag before O is rescaled: BF16 probabilities
+// have the range for 2^8; E4M3 saturates at 448, so there the lag is one and the probabilities are
+// scaled by 224 instead of the reference's 448.
+template <bool QUANTIZED> constexpr float RESCALE_LAG = QUANTIZED ? 1.0f : 8.0f;
+constexpr float LOG2_224 = 7.807354922057604f;
+// Of every four pairs of probabilities, how many take the polynomial exp2 instead of the MUFU.
+constexpr int POLYNOMIAL_PAIRS_OF_4 = 1;
 
 template <bool QUANTIZED> struct Shape {
     // Bytes of a 128-row operand tile and of the half of it one VSA tile fills.
@@ -90,13 +97,6 @@ struct VsaParams {
     int vector_stores;
     unsigned int *status;
 };
-
-__device__ __forceinline__ uint32_t pack_e4m3(float a, float b, float c, float d) {
-    uint16_t low, high;
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(low) : "f"(b), "f"(a));
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(high) : "f"(d), "f"(c));
-    return static_cast<uint32_t>(low) | (static_cast<uint32_t>(high) << 16);
-}
 
 template <bool QUANTIZED>
 __global__ void __launch_bounds__(THREADS, 2)
@@ -234,44 +234,43 @@ __global__ void __launch_bounds__(THREADS, 2)
                                                    PAIR, HEAD_DIM)
                           : instruction_descriptor(ACCUMULATE_F32, FORMAT_BF16, FORMAT_BF16, 0, 1,
                                                    PAIR, HEAD_DIM);
+            const uint64_t query_operand = smem_descriptor(query_tile, 16, 1024);
             auto score = [&](uint32_t key_tile) {
+                const uint64_t key_operand = smem_descriptor(key_tile, 16, 1024);
                 if constexpr (QUANTIZED) {
                     #pragma unroll
                     for (int step = 0; step < HEAD_DIM / 32; step++) {
-                        mma_i8_ss(tmem + TMEM_SCORES,
-                                  smem_descriptor(query_tile + step * 32, 16, 1024),
-                                  smem_descriptor(key_tile + step * 32, 16, 1024), SCORE_MMA,
-                                  step > 0);
+                        mma_i8_ss(tmem + TMEM_SCORES, advance_descriptor(query_operand, step * 32),
+                                  advance_descriptor(key_operand, step * 32), SCORE_MMA, step > 0);
                     }
                 } else {
                     #pragma unroll
                     for (int step = 0; step < HEAD_DIM / 16; step++) {
                         const uint32_t offset = (step / 4) * (PAIR * 128) + (step % 4) * 32;
-                        mma_f16_ss(tmem + TMEM_SCORES,
-                                   smem_descriptor(query_tile + offset, 16, 1024),
-                                   smem_descriptor(key_tile + offset, 16, 1024), SCORE_MMA,
-                                   step > 0);
+                        mma_f16_ss(tmem + TMEM_SCORES, advance_descriptor(query_operand, offset),
+                                   advance_descriptor(key_operand, offset), SCORE_MMA, step > 0);
                     }
                 }
                 tcgen05_commit(barrier(S::SCORES_FULL));
             };
             auto accumulate = [&](uint32_t value_tile, bool first) {
                 if constexpr (QUANTIZED) {
+                    // Two tiles of [128 dims][64 keys] in the 64-byte swizzle.
+                    const uint64_t operand = smem_descriptor(value_tile, 16, 512, SWIZZLE_64B);
                     #pragma unroll
                     for (int step = 0; step < PAIR / 32; step++) {
-                        // Two tiles of [128 dims][64 keys] in the 64-byte swizzle.
-                        const uint32_t address =
-                            value_tile + (step / 2) * (HEAD_DIM * TILE) + (step % 2) * 32;
                         mma_f8_ts(tmem + TMEM_OUTPUT, tmem + TMEM_SCORES + step * 8,
-                                  smem_descriptor(address, 16, 512, SWIZZLE_64B), OUTPUT_MMA,
-                                  !first || step > 0);
+                                  advance_descriptor(operand, (step / 2) * (HEAD_DIM * TILE) +
+                                                                  (step % 2) * 32),
+                                  OUTPUT_MMA, !first || step > 0);
                     }
                 } else {
+                    const uint64_t operand = smem_descriptor(value_tile, PAIR * 128, 1024);
                     #pragma unroll
                     for (int step = 0; step < PAIR / 16; step++) {
                         mma_f16_ts(tmem + TMEM_OUTPUT, tmem + TMEM_SCORES + step * 8,
-                                   smem_descriptor(value_tile + step * 16 * 128, PAIR * 128, 1024),
-                                   OUTPUT_MMA, !first || step > 0);
+                                   advance_descriptor(operand, step * 16 * 128), OUTPUT_MMA,
+                                   !first || step > 0);
                     }
                 }
             };
@@ -331,7 +330,7 @@ __global__ void __launch_bounds__(THREADS, 2)
             head_key_scales = p.key_scales + static_cast<size_t>(head) * p.tiles;
         }
         float maximum = -INFINITY;
-        float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float2 sums[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
         int key_tile = count > 0 ? route[0] : 0;
         bool alive = true;
         for (int step = 0; step < steps; step++) {
@@ -352,78 +351,119 @@ __global__ void __launch_bounds__(THREADS, 2)
             tmem_load_32(scores, raw[0]);
             tmem_load_32(scores + 32, raw[1]);
             tmem_wait_load();
-            float s[TILE];
-            #pragma unroll
-            for (int index = 0; index < TILE; index++) {
-                const uint32_t word = raw[index / 32][index % 32];
-                s[index] = QUANTIZED ? static_cast<float>(static_cast<int32_t>(word)) * factor
-                                     : __uint_as_float(word) * factor;
-                if (index >= valid) {
-                    s[index] = -INFINITY;
-                }
-            }
-            float partial[4] = {s[0], s[1], s[2], s[3]};
-            #pragma unroll
-            for (int index = 4; index < TILE; index++) {
-                partial[index % 4] = fmaxf(partial[index % 4], s[index]);
-            }
-            const float block_maximum =
-                fmaxf(fmaxf(partial[0], partial[1]), fmaxf(partial[2], partial[3]));
-            // The first step of a list always has keys, so the maximum is finite from then on.
-            const float threshold = QUANTIZED ? 0.0f : RESCALE_THRESHOLD;
-            const bool grown = active && block_maximum - maximum > threshold;
-            if (step == 0) {
-                maximum = active ? block_maximum : 0.0f;
-            } else if (__any_sync(0xffffffffu, grown)) {
-                const float raised = fmaxf(maximum, block_maximum);
-                const float correction = exp2_approx(maximum - raised);
-                maximum = raised;
-                #pragma unroll
-                for (int index = 0; index < 4; index++) {
-                    sums[index] *= correction;
-                }
-                #pragma unroll
-                for (int chunk = 0; chunk < 4; chunk++) {
-                    uint32_t values[32];
-                    tmem_load_32(accumulator + chunk * 32, values);
-                    tmem_wait_load();
+            // MASKED: the key tile is shorter than 64 (or this list has ended), so the columns
+            // past its length take an exponent of minus infinity. Warps 0-1 and 2-3 serve
+            // different tiles, but a warp serves one, so the choice is uniform across a warp.
+            auto softmax_step = [&](auto masked) {
+                constexpr bool MASKED = decltype(masked)::value;
+                // The block maximum in the units of the exponent: scale * log2(e) times the score.
+                float block_maximum;
+                if constexpr (QUANTIZED) {
+                    int partial[2] = {INT_MIN, INT_MIN};
                     #pragma unroll
-                    for (int index = 0; index < 32; index++) {
-                        values[index] =
-                            __float_as_uint(__uint_as_float(values[index]) * correction);
+                    for (int index = 0; index + 1 < TILE; index += 2) {
+                        const int first = static_cast<int>(raw[index / 32][index % 32]);
+                        const int second = static_cast<int>(raw[(index + 1) / 32][(index + 1) % 32]);
+                        partial[(index / 2) % 2] = __vimax3_s32(
+                            partial[(index / 2) % 2], MASKED && index >= valid ? INT_MIN : first,
+                            MASKED && index + 1 >= valid ? INT_MIN : second);
                     }
-                    tmem_store_32(accumulator + chunk * 32, values);
-                }
-            }
-            if constexpr (QUANTIZED) {
-                const float offset = maximum - LOG2_448;
-                uint32_t packed[16], zeroes[16];
-                #pragma unroll
-                for (int quad = 0; quad < 16; quad++) {
-                    float q[4];
+                    const int largest = max(partial[0], partial[1]);
+                    block_maximum =
+                        largest == INT_MIN ? -INFINITY : static_cast<float>(largest) * factor;
+                } else {
+                    float partial[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                     #pragma unroll
-                    for (int element = 0; element < 4; element++) {
-                        q[element] = exp2_approx(s[quad * 4 + element] - offset);
-                        sums[element] += q[element];
+                    for (int index = 0; index < TILE; index++) {
+                        const float score = __uint_as_float(raw[index / 32][index % 32]);
+                        partial[index % 4] =
+                            fmaxf(partial[index % 4], MASKED && index >= valid ? -INFINITY : score);
                     }
-                    packed[quad] = pack_e4m3(q[0], q[1], q[2], q[3]);
-                    zeroes[quad] = 0;
+                    block_maximum =
+                        fmaxf(fmaxf(partial[0], partial[1]), fmaxf(partial[2], partial[3])) * factor;
                 }
-                tmem_store_16(own_p, packed);
-                tmem_store_16(other_p, zeroes);
+                // The first step of a list always has keys, so the maximum is finite from then on.
+                const bool grown = active && block_maximum - maximum > RESCALE_LAG<QUANTIZED>;
+                if (step == 0) {
+                    maximum = active ? block_maximum : 0.0f;
+                } else if (__any_sync(0xffffffffu, grown)) {
+                    const float raised = fmaxf(maximum, block_maximum);
+                    const float correction = exp2_approx(maximum - raised);
+                    maximum = raised;
+                    const float2 correction2 = make_float2(correction, correction);
+                    sums[0] = __fmul2_rn(sums[0], correction2);
+                    sums[1] = __fmul2_rn(sums[1], correction2);
+                    #pragma unroll
+                    for (int chunk = 0; chunk < 4; chunk++) {
+                        uint32_t values[32];
+                        tmem_load_32(accumulator + chunk * 32, values);
+                        tmem_wait_load();
+                        #pragma unroll
+                        for (int index = 0; index < 32; index++) {
+                            values[index] =
+                                __float_as_uint(__uint_as_float(values[index]) * correction);
+                        }
+                        tmem_store_32(accumulator + chunk * 32, values);
+                    }
+                }
+                // p = 2^(factor * score - maximum), times 224 for E4M3; pairs of elements, one
+                // pair in four on the polynomial.
+                const float offset = QUANTIZED ? LOG2_224 - maximum : -maximum;
+                const float2 factor2 = make_float2(factor, factor);
+                const float2 offset2 = make_float2(offset, offset);
+                constexpr int WORDS = QUANTIZED ? TILE / 4 : TILE / 2;
+                uint32_t packed[WORDS], zeroes[WORDS];
+                #pragma unroll
+                for (int pair = 0; pair < TILE / 2; pair++) {
+                    const uint32_t words[2] = {raw[(pair * 2) / 32][(pair * 2) % 32],
+                                               raw[(pair * 2 + 1) / 32][(pair * 2 + 1) % 32]};
+                    const float2 score =
+                        QUANTIZED ? make_float2(static_cast<float>(static_cast<int32_t>(words[0])),
+                                                static_cast<float>(static_cast<int32_t>(words[1])))
+                                  : make_float2(__uint_as_float(words[0]),
+                                                __uint_as_float(words[1]));
+                    float2 x = __ffma2_rn(score, factor2, offset2);
+                    if (MASKED) {
+                        x.x = pair * 2 < valid ? x.x : -INFINITY;
+                        x.y = pair * 2 + 1 < valid ? x.y : -INFINITY;
+                    }
+                    float2 probability;
+                    if (pair % 4 < POLYNOMIAL_PAIRS_OF_4) {
+                        probability = exp2_polynomial(x);
+                    } else {
+                        probability = make_float2(exp2_approx(x.x), exp2_approx(x.y));
+                    }
+                    sums[pair % 2] = __fadd2_rn(sums[pair % 2], probability);
+                    if constexpr (QUANTIZED) {
+                        uint16_t two;
+                        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;"
+                            : "=h"(two)
+                            : "f"(probability.y), "f"(probability.x));
+                        if (pair % 2 == 0) {
+                            packed[pair / 2] = two;
+                        } else {
+                            packed[pair / 2] |= static_cast<uint32_t>(two) << 16;
+                        }
+                    } else {
+                        packed[pair] = pack_bf16(probability.x, probability.y);
+                    }
+                }
+                #pragma unroll
+                for (int word = 0; word < WORDS; word++) {
+                    zeroes[word] = 0;
+                }
+                if constexpr (QUANTIZED) {
+                    tmem_store_16(own_p, packed);
+                    tmem_store_16(other_p, zeroes);
+                } else {
+                    tmem_store_32(own_p, packed);
+                    tmem_store_32(other_p, zeroes);
+                }
+            };
+            if (valid < TILE) {
+                softmax_step(std::true_type{});
             } else {
-                uint32_t packed[32], zeroes[32];
-                #pragma unroll
-                for (int pair = 0; pair < 32; pair++) {
-                    const float low = exp2_approx(s[pair * 2] - maximum);
-                    const float high = exp2_approx(s[pair * 2 + 1] - maximum);
-                    sums[pair % 2 * 2] += low;
-                    sums[pair % 2 * 2 + 1] += high;
-                    packed[pair] = pack_bf16(low, high);
-                    zeroes[pair] = 0;
-                }
-                tmem_store_32(own_p, packed);
-                tmem_store_32(other_p, zeroes);
+                softmax_step(std::false_type{});
             }
             tmem_wait_store();
             tcgen05_fence_before();
@@ -439,7 +479,7 @@ __global__ void __launch_bounds__(THREADS, 2)
             const bool stored =
                 exists[half] && tile_row < p.tile_lengths[query_tiles[half]] && count > 0;
             const int64_t token = stored ? p.tile_starts[query_tiles[half]] + tile_row : 0;
-            float inverse = 1.0f / ((sums[0] + sums[1]) + (sums[2] + sums[3]));
+            float inverse = 1.0f / ((sums[0].x + sums[0].y) + (sums[1].x + sums[1].y));
             if constexpr (QUANTIZED) {
                 inverse *= p.value_scales[head];
             }

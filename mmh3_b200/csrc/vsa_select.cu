@@ -5,9 +5,9 @@
 // (crates/mmh3-cuda/kernels/vsa_attention.cu:96-273). That fixes the FP32 evaluation order of a
 // score: 32 chains of four fused multiply-adds over dimensions l, l + 32, l + 64, l + 96, summed
 // over a balanced tree that pairs chains by bit 4 of l first and by bit 0 last, then one multiply
-// by the scale. Here one thread evaluates that whole tree for one key tile and four query tiles,
-// with the key tiles staged through shared memory in batches of 128; the reference spreads a score
-// over the lanes of a warp. The selection itself is a function of the scores alone, so it is free
+// by the scale. Here one thread evaluates that whole tree: it holds one pooled key in registers and
+// scores it against each of its CTA's eight query tiles, whose pooled queries sit in shared memory
+// regrouped by chain; the reference spreads a score over the lanes of a warp. The selection itself is a function of the scores alone, so it is free
 // to differ: here a warp finds the kept-th largest video score with a four-pass radix select over
 // order-preserving integer keys (the reference descends one bit at a time), ties go to the lower
 // tile index, and the route is an ascending list of uint16 tile indices.
@@ -21,9 +21,7 @@ namespace {
 
 constexpr int THREADS = 128;
 constexpr int WARPS = THREADS / 32;
-constexpr int KEY_BATCH = 128;
-constexpr int KEY_PITCH = HEAD_DIM + 1; // odd, so that the rows of a batch start in distinct banks
-constexpr int QUERIES = 4;
+constexpr int MAX_QUERIES = 8;
 
 // Maps a float to an unsigned integer with the same order.
 __device__ __forceinline__ uint32_t ordered_bits(float value) {
@@ -31,33 +29,21 @@ __device__ __forceinline__ uint32_t ordered_bits(float value) {
     return (bits & 0x80000000u) ? ~bits : bits | 0x80000000u;
 }
 
-// The sum over the chains l = BASE, BASE + STRIDE, ... of the products of four queries with one
-// key, in the tree order described at the top. `queries` is [128][4], `key` one row of 128.
+// The sum over the chains l = BASE, BASE + STRIDE, ... of the products of one query with one key,
+// in the tree order described at the top. `key` is the key's 128 values in registers; `query` holds
+// the query regrouped by chain: query[l] = (q[l], q[l + 32], q[l + 64], q[l + 96]).
 template <int STRIDE, int BASE>
-__device__ __forceinline__ void score_tree(const float4 *__restrict__ queries,
-                                           const float *__restrict__ key, float (&sums)[QUERIES]) {
+__device__ __forceinline__ float score_tree(const float4 *__restrict__ query,
+                                            const float (&key)[HEAD_DIM]) {
     if constexpr (STRIDE == 32) {
-        #pragma unroll
-        for (int query = 0; query < QUERIES; query++) {
-            sums[query] = 0.0f;
-        }
-        #pragma unroll
-        for (int part = 0; part < HEAD_DIM / 32; part++) {
-            const float4 q = queries[BASE + part * 32];
-            const float k = key[BASE + part * 32];
-            sums[0] = __fmaf_rn(q.x, k, sums[0]);
-            sums[1] = __fmaf_rn(q.y, k, sums[1]);
-            sums[2] = __fmaf_rn(q.z, k, sums[2]);
-            sums[3] = __fmaf_rn(q.w, k, sums[3]);
-        }
+        const float4 q = query[BASE];
+        float sum = __fmaf_rn(q.x, key[BASE], 0.0f);
+        sum = __fmaf_rn(q.y, key[BASE + 32], sum);
+        sum = __fmaf_rn(q.z, key[BASE + 64], sum);
+        return __fmaf_rn(q.w, key[BASE + 96], sum);
     } else {
-        float other[QUERIES];
-        score_tree<STRIDE * 2, BASE>(queries, key, sums);
-        score_tree<STRIDE * 2, BASE + STRIDE>(queries, key, other);
-        #pragma unroll
-        for (int query = 0; query < QUERIES; query++) {
-            sums[query] = __fadd_rn(sums[query], other[query]);
-        }
+        return __fadd_rn(score_tree<STRIDE * 2, BASE>(query, key),
+                         score_tree<STRIDE * 2, BASE + STRIDE>(query, key));
     }
 }
 
@@ -79,13 +65,15 @@ __device__ __forceinline__ float block_reduce(float value, float *scratch, bool 
     return result;
 }
 
-__global__ void __launch_bounds__(THREADS)
+// One CTA takes QUERIES consecutive query tiles of one head. A thread holds one pooled key in
+// registers (read once, straight from L2) and scores it against each of the CTA's queries, which
+// sit in shared memory regrouped by chain; then the next key, 128 tiles further on.
+template <int QUERIES>
+__global__ void __launch_bounds__(THREADS, 3)
     select_kernel(Mmh3VsaWorkspace workspace, int tiles, int prefix_tiles, int kept, float scale,
                   int coarse) {
-    extern __shared__ __align__(16) float dynamic[];
-    float *scores = dynamic;                              // [QUERIES][tiles]
-    float *keys = dynamic + static_cast<size_t>(QUERIES) * tiles; // [KEY_BATCH][KEY_PITCH]
-    __shared__ float4 queries[HEAD_DIM];
+    extern __shared__ __align__(16) float scores[]; // [QUERIES][tiles]
+    __shared__ float4 queries[QUERIES][32];
     __shared__ float sums[QUERIES];
     __shared__ float scratch[WARPS];
     __shared__ int histogram[WARPS][256];
@@ -96,44 +84,35 @@ __global__ void __launch_bounds__(THREADS)
     const int warp = threadIdx.x / 32;
     const size_t first_row = static_cast<size_t>(head) * tiles + first_query;
 
-    {
-        float values[QUERIES];
-        #pragma unroll
-        for (int query = 0; query < QUERIES; query++) {
-            values[query] =
-                query < query_count
-                    ? workspace.pooled_query[(first_row + query) * HEAD_DIM + threadIdx.x]
-                    : 0.0f;
+    for (int index = threadIdx.x; index < QUERIES * 32; index += THREADS) {
+        const int query = index / 32, chain = index % 32;
+        float4 grouped = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (query < query_count) {
+            const float *pooled = workspace.pooled_query + (first_row + query) * HEAD_DIM;
+            grouped = make_float4(pooled[chain], pooled[chain + 32], pooled[chain + 64],
+                                  pooled[chain + 96]);
         }
-        queries[threadIdx.x] = make_float4(values[0], values[1], values[2], values[3]);
+        queries[query][chain] = grouped;
     }
+    __syncthreads();
 
     const float *head_keys = workspace.pooled_key + static_cast<size_t>(head) * tiles * HEAD_DIM;
-    for (int first = 0; first < tiles; first += KEY_BATCH) {
-        __syncthreads();
-        const int batch = min(KEY_BATCH, tiles - first);
-        for (int chunk = threadIdx.x; chunk < batch * (HEAD_DIM / 4); chunk += THREADS) {
-            const int row = chunk / (HEAD_DIM / 4);
-            const int column = chunk % (HEAD_DIM / 4) * 4;
-            const float4 loaded = __ldg(reinterpret_cast<const float4 *>(
-                head_keys + static_cast<size_t>(first + row) * HEAD_DIM + column));
-            float *destination = keys + row * KEY_PITCH + column;
-            destination[0] = loaded.x;
-            destination[1] = loaded.y;
-            destination[2] = loaded.z;
-            destination[3] = loaded.w;
+    for (int tile = threadIdx.x; tile < tiles; tile += THREADS) {
+        float key[HEAD_DIM];
+        const float4 *row = reinterpret_cast<const float4 *>(head_keys +
+                                                             static_cast<size_t>(tile) * HEAD_DIM);
+        #pragma unroll
+        for (int chunk = 0; chunk < HEAD_DIM / 4; chunk++) {
+            const float4 loaded = __ldg(row + chunk);
+            key[chunk * 4] = loaded.x;
+            key[chunk * 4 + 1] = loaded.y;
+            key[chunk * 4 + 2] = loaded.z;
+            key[chunk * 4 + 3] = loaded.w;
         }
-        __syncthreads();
-        if (static_cast<int>(threadIdx.x) < batch) {
-            float totals[QUERIES];
-            score_tree<1, 0>(queries, keys + threadIdx.x * KEY_PITCH, totals);
-            #pragma unroll
-            for (int query = 0; query < QUERIES; query++) {
-                if (query < query_count) {
-                    scores[static_cast<size_t>(query) * tiles + first + threadIdx.x] =
-                        __fmul_rn(totals[query], scale);
-                }
-            }
+        #pragma unroll 1
+        for (int query = 0; query < query_count; query++) {
+            scores[static_cast<size_t>(query) * tiles + tile] =
+                __fmul_rn(score_tree<1, 0>(queries[query], key), scale);
         }
     }
     __syncthreads();
@@ -156,11 +135,17 @@ __global__ void __launch_bounds__(THREADS)
                     bins[bin] = 0;
                 }
                 __syncwarp();
-                for (int tile = prefix_tiles + lane; tile < tiles; tile += 32) {
-                    const uint32_t bits = ordered_bits(query_scores[tile]);
-                    if ((bits & settled) == threshold) {
-                        atomicAdd(&bins[(bits >> shift) & 255u], 1);
+                for (int first = prefix_tiles; first < tiles; first += 32) {
+                    const int tile = first + lane;
+                    const uint32_t bits = tile < tiles ? ordered_bits(query_scores[tile]) : 0;
+                    const bool counted = tile < tiles && (bits & settled) == threshold;
+                    // Scores crowd into a few bins, so the lanes of a bin add their count once.
+                    const uint32_t bin = counted ? (bits >> shift) & 255u : 256u;
+                    const unsigned same = __match_any_sync(0xffffffffu, bin);
+                    if (counted && lane == __ffs(same) - 1) {
+                        bins[bin] += __popc(same);
                     }
+                    __syncwarp();
                 }
                 __syncwarp();
                 // Lane l owns bins 8 l .. 8 l + 7. `above` counts the candidates in higher bins.
@@ -259,7 +244,7 @@ __global__ void __launch_bounds__(THREADS)
     const float *values =
         workspace.pooled_value + static_cast<size_t>(head) * tiles * HEAD_DIM + threadIdx.x;
     float outputs[QUERIES] = {};
-    constexpr int VALUE_BATCH = 16;
+    constexpr int VALUE_BATCH = 8;
     for (int first = 0; first < tiles; first += VALUE_BATCH) {
         float loaded[VALUE_BATCH];
         #pragma unroll
@@ -291,15 +276,10 @@ __global__ void __launch_bounds__(THREADS)
     }
 }
 
-} // namespace
-
-int launch_select(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int prefix_tiles,
-                  int kept, float scale, int coarse, cudaStream_t stream) {
-    const size_t shared =
-        (static_cast<size_t>(QUERIES) * tiles + KEY_BATCH * KEY_PITCH) * sizeof(float);
-    if (shared > 200 * 1024) {
-        return INVALID_VALUE;
-    }
+template <int QUERIES>
+int launch_queries(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int prefix_tiles,
+                   int kept, float scale, int coarse, cudaStream_t stream) {
+    const size_t shared = static_cast<size_t>(QUERIES) * tiles * sizeof(float);
     // The opt-in limit only ever grows, and is per device.
     static std::atomic<size_t> configured[MAX_DEVICES];
     const int device = current_device();
@@ -307,16 +287,41 @@ int launch_select(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int p
         return static_cast<int>(cudaErrorInvalidDevice);
     }
     if (shared > configured[device].load(std::memory_order_relaxed)) {
-        const cudaError_t status = cudaFuncSetAttribute(
-            select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+        const cudaError_t status =
+            cudaFuncSetAttribute(select_kernel<QUERIES>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(shared));
         if (status != cudaSuccess) {
             return static_cast<int>(status);
         }
         configured[device].store(shared, std::memory_order_relaxed);
     }
-    select_kernel<<<dim3((tiles + QUERIES - 1) / QUERIES, heads), THREADS, shared, stream>>>(
-        workspace, tiles, prefix_tiles, kept, scale, coarse);
+    select_kernel<QUERIES><<<dim3((tiles + QUERIES - 1) / QUERIES, heads), THREADS, shared,
+                             stream>>>(workspace, tiles, prefix_tiles, kept, scale, coarse);
     return static_cast<int>(cudaGetLastError());
+}
+
+} // namespace
+
+int launch_select(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int prefix_tiles,
+                  int kept, float scale, int coarse, cudaStream_t stream) {
+    // As many query tiles per CTA as keep its scores within a third of an SM's shared memory
+    // (three CTAs per SM), fewer for very long sequences, down to one.
+    const size_t row = static_cast<size_t>(tiles) * sizeof(float);
+    constexpr size_t SHARE = 66 * 1024, LIMIT = 200 * 1024;
+    if (MAX_QUERIES * row <= SHARE) {
+        return launch_queries<8>(workspace, tiles, heads, prefix_tiles, kept, scale, coarse, stream);
+    }
+    if (4 * row <= SHARE) {
+        return launch_queries<4>(workspace, tiles, heads, prefix_tiles, kept, scale, coarse, stream);
+    }
+    if (2 * row <= SHARE) {
+        return launch_queries<2>(workspace, tiles, heads, prefix_tiles, kept, scale, coarse, stream);
+    }
+    if (row <= LIMIT) {
+        return launch_queries<1>(workspace, tiles, heads, prefix_tiles, kept, scale, coarse, stream);
+    }
+    return INVALID_VALUE;
 }
 
 } // namespace mmh3
