@@ -24,7 +24,7 @@ constexpr int THREADS = 256;
 constexpr int WARPS = THREADS / 32;
 // A row of 128 BF16 values is 16 chunks of 16 bytes.
 constexpr int CHUNKS_PER_THREAD = BLOCK_ROWS * 16 / THREADS;
-constexpr int HEADS_PER_CTA = 4;
+constexpr int HEADS_PER_CTA = 8;
 
 struct InputsParams {
     const __nv_bfloat16 *source[3];

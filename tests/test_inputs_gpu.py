@@ -24,7 +24,7 @@ EPSILON = 1e-6
 SCALE = synthetic.softmax_scale()
 
 
-def make_inputs(oracle, tokens, heads, pairs=PAIRS):
+def make_inputs(oracle, tokens, heads):
     """Blocks of tokens share a direction (attention_inputs.rs:51-98)."""
     inner = heads * 128
     state = tokens * 31 + heads
@@ -35,16 +35,16 @@ def make_inputs(oracle, tokens, heads, pairs=PAIRS):
     qkv = directions[(index // (3 * inner) // 64) * 3 * inner + index % (3 * inner)] + noise
     query_weight, state = oracle_lib.lcg(oracle, state, 128, 0.5, 1.5)
     key_weight, state = oracle_lib.lcg(oracle, state, 128, 0.5, 1.5)
-    angles, state = oracle_lib.lcg(oracle, state, tokens * max(pairs, 1), -40.0, 40.0)
+    angles, state = oracle_lib.lcg(oracle, state, tokens * PAIRS, -40.0, 40.0)
     return (synthetic.to_bf16_bits(qkv.astype(np.float32)).reshape(tokens, 3, heads, 128),
             synthetic.to_bf16_bits(query_weight), synthetic.to_bf16_bits(key_weight), angles)
 
 
-def norm_for(query_weight, key_weight, angles, pairs=PAIRS):
+def norm_for(query_weight, key_weight, angles):
     return attention.HeadNorm(synthetic.bf16_tensor(query_weight, "cuda"),
                               synthetic.bf16_tensor(key_weight, "cuda"),
                               torch.from_numpy(angles).cuda() if angles is not None else None,
-                              pairs if angles is not None else 0, EPSILON)
+                              PAIRS if angles is not None else 0, EPSILON)
 
 
 def valid_value_columns(workspace, lengths):
@@ -252,28 +252,3 @@ def test_quantization_is_bit_exact_over_many_scales(oracle, reference_kernels):
     torch.cuda.synchronize()
     assert attention.take_status() == 0
     assert_workspaces_equal(ours, theirs)
-
-
-@pytest.mark.parametrize("pairs", [0, 16, 20, 32, 64])
-def test_fused_preparation_is_bit_exact_for_other_rotary_widths(oracle, reference_kernels, pairs):
-    """Rotary widths other than the usual 48 pairs: multiples of 16 take the register-resident
-    pass, anything else (20 here) and no rotation at all take their own paths."""
-    tokens, heads = 333, 5
-    bits, query_weight, key_weight, angles = make_inputs(oracle, tokens, heads, pairs)
-    norm = norm_for(query_weight, key_weight, angles if pairs else None, pairs)
-    ours_qkv = synthetic.bf16_tensor(bits, "cuda")
-    theirs_qkv = ours_qkv.clone()
-    ours = attention.QuantizedWorkspace(tokens, heads)
-    theirs = attention.QuantizedWorkspace(tokens, heads)
-    fill(ours, 0x33)
-    fill(theirs, 0x33)
-    maxima = ours_qkv[:, 2].float().abs().amax(dim=(0, 2)).contiguous()
-    attention.prepare_inputs(ours_qkv, norm, tokens, heads, quantized=ours,
-                             value_head_maxima=maxima)
-    raw = theirs.raw()
-    assert reference_kernels.mmh3_attention_inputs(
-        theirs_qkv.data_ptr(), norm.query_weight.data_ptr(), norm.key_weight.data_ptr(),
-        norm.angles.data_ptr() if pairs else None, norm.pairs, tokens, heads, EPSILON, None,
-        ctypes.byref(raw), None, None, 0, maxima.data_ptr(), None) == 0
-    torch.cuda.synchronize()
-    assert_workspaces_equal(ours, theirs, values=True, maxima=False)
