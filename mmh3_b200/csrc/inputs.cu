@@ -370,352 +370,6 @@ __global__ void __launch_bounds__(THREADS, 4) inputs_kernel(const InputsParams p
     }
 }
 
-// The same pass for the common case, with far fewer instructions per element: 16-byte aligned rows,
-// normalization wanted, and rotary pairs that are a multiple of 16 up to 64 (GROUPS = pairs / 8 is
-// 0, 2, 4, 6 or 8). Four threads share a row: thread j of the four holds the 16-byte groups
-// j, j + 4, j + 8 and j + 12 of the row's sixteen, i.e. dimensions 32 k + 8 j + i, in registers, and
-// a row of q or k never goes through shared memory.
-//
-// - The sum of squares keeps the reference's order: chain l = 8 j + i adds its dimensions l, l + 32,
-//   l + 64, l + 96 in turn, and the 32 chains are added pairing l with l ^ 16 (the thread two lanes
-//   over), l ^ 8 (the next lane), then l ^ 4, l ^ 2, l ^ 1 inside the thread.
-// - The rotary partner of group g is group g + GROUPS or g - GROUPS. With GROUPS a multiple of four
-//   it is the thread's own; with GROUPS = 2 or 6 it belongs to the thread two lanes over, and the
-//   two exchange what the other needs with one shuffle per value.
-// - V still takes the tile in shared memory, where it is transposed for the FP8 layout.
-template <int GROUPS> struct Rotary {
-    // Whether group g = 4 k + j is the first or the second half of a pair, and the slot (k) of the
-    // partner group in the thread that holds it.
-    __device__ static bool first(int k, int j) { return 4 * k + j < GROUPS; }
-    __device__ static bool second(int k, int j) {
-        return 4 * k + j >= GROUPS && 4 * k + j < 2 * GROUPS;
-    }
-    __device__ static int partner_slot(int k, int j) {
-        return first(k, j) ? (4 * k + j + GROUPS) / 4 : (4 * k + j - GROUPS) / 4;
-    }
-    // The pair index of dimension i of the group: the first half's dimension.
-    __device__ static int pair_group(int k, int j) {
-        return first(k, j) ? 4 * k + j : 4 * k + j - GROUPS;
-    }
-};
-
-template <bool STATS, bool QUANTIZE, int GROUPS>
-__global__ void __launch_bounds__(THREADS, 2) inputs_rows_kernel(const InputsParams p) {
-    extern __shared__ __align__(16) float2 trig[];
-    __shared__ __align__(16) __nv_bfloat16 tile[BLOCK_ROWS][HEAD_DIM];
-    __shared__ float maxima[2][WARPS];
-    const int block = blockIdx.x;
-    const int blocks = gridDim.x;
-    const int first_head = blockIdx.y * p.heads_per_cta;
-    const int head_count = min(p.heads_per_cta, p.heads - first_head);
-    const int64_t first_token =
-        p.tile_starts != nullptr ? p.tile_starts[block] : static_cast<int64_t>(block) * BLOCK_ROWS;
-    const int rows = p.tile_lengths != nullptr
-                         ? p.tile_lengths[block]
-                         : min(BLOCK_ROWS, p.tokens - block * BLOCK_ROWS);
-    const int lane = threadIdx.x % 32;
-    const int warp = threadIdx.x / 32;
-    const int row = threadIdx.x / 4;
-    const int j = threadIdx.x % 4;
-    const bool live = row < rows;
-    constexpr bool ROTATE = GROUPS > 0;
-    const bool values_here =
-        QUANTIZE && (p.value_head_maxima != nullptr || p.value_scales_ready != 0);
-    const int items = head_count * 3;
-
-    uint4 chunks[4];
-    auto load = [&](int item) {
-        const int part = item % 3;
-        const int head = first_head + item / 3;
-        const __nv_bfloat16 *source = p.source[part] + (first_token + row) * p.token_stride[part] +
-                                      head * p.head_stride[part] + 8 * j;
-        if (live) {
-            #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                chunks[k] = __ldg(reinterpret_cast<const uint4 *>(source + 32 * k));
-            }
-        }
-    };
-
-    load(0);
-    if (ROTATE) {
-        for (int index = threadIdx.x; index < rows * p.pairs; index += THREADS) {
-            float sine, cosine;
-            sincosf(p.angles[first_token * p.pairs + index], &sine, &cosine);
-            trig[index] = make_float2(cosine, sine);
-        }
-    }
-    // The norm weights of this thread's dimensions, q then k, as the BF16 pairs they are stored as.
-    uint4 weights[2][4];
-    #pragma unroll
-    for (int part = 0; part < 2; part++) {
-        #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            weights[part][k] =
-                __ldg(reinterpret_cast<const uint4 *>(p.weight[part] + 32 * k + 8 * j));
-        }
-    }
-    __syncthreads();
-
-    for (int item = 0; item < items; item++) {
-        const int part = item % 3;
-        const int head = first_head + item / 3;
-        const size_t statistic = (static_cast<size_t>(head) * blocks + block) * HEAD_DIM;
-        uint4 held[4] = {chunks[0], chunks[1], chunks[2], chunks[3]};
-        if (item + 1 < items) {
-            load(item + 1);
-        }
-        if (part == 2) {
-            // V: the block maximum, the summed rows, or the transposed FP8 rows, through the tile.
-            float maximum = 0.0f;
-            if (live) {
-                #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    *reinterpret_cast<uint4 *>(&tile[row][32 * k + 8 * j]) = held[k];
-                    if (QUANTIZE && !values_here) {
-                        maximum = fmaxf(maximum, chunk_max(held[k]));
-                    }
-                }
-            }
-            if (QUANTIZE && !values_here) {
-                maximum = warp_max(maximum);
-                if (lane == 0) {
-                    maxima[item % 2][warp] = maximum;
-                }
-            }
-            __syncthreads();
-            if (QUANTIZE && !values_here && threadIdx.x == 0) {
-                maximum = maxima[item % 2][0];
-                for (int index = 1; index < WARPS; index++) {
-                    maximum = fmaxf(maximum, maxima[item % 2][index]);
-                }
-                p.value_maxima[head * blocks + block] = maximum;
-            }
-            if (STATS && threadIdx.x < HEAD_DIM) {
-                float sum = 0.0f;
-                for (int source_row = 0; source_row < rows; source_row++) {
-                    sum += __bfloat162float(tile[source_row][threadIdx.x]);
-                }
-                p.pooled[2][statistic + threadIdx.x] = sum;
-            }
-            if (values_here) {
-                float scale;
-                if (p.value_head_maxima != nullptr) {
-                    scale = fmaxf(p.value_head_maxima[head] / 448.0f, 1e-30f);
-                    if (block == 0 && threadIdx.x == 0) {
-                        p.value_scales[head] = scale;
-                    }
-                } else {
-                    scale = p.value_scales[head];
-                }
-                const Divider divide(scale);
-                const int dimension = threadIdx.x % HEAD_DIM;
-                const int first_row = threadIdx.x / HEAD_DIM * 32;
-                uint32_t words[8];
-                #pragma unroll
-                for (int word = 0; word < 8; word++) {
-                    uint32_t packed = 0;
-                    #pragma unroll
-                    for (int byte = 0; byte < 4; byte++) {
-                        const int source_row = first_row + word * 4 + byte;
-                        const float element = source_row < rows
-                                                  ? __bfloat162float(tile[source_row][dimension])
-                                                  : 0.0f;
-                        packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(
-                                      divide(element), __NV_SATFINITE, __NV_E4M3))
-                                  << (8 * byte);
-                    }
-                    words[word] = packed;
-                }
-                uint4 *destination = reinterpret_cast<uint4 *>(
-                    p.value8 +
-                    (static_cast<int64_t>(head) * HEAD_DIM + dimension) * blocks * BLOCK_ROWS +
-                    static_cast<int64_t>(block) * BLOCK_ROWS + first_row);
-                destination[0] = make_uint4(words[0], words[1], words[2], words[3]);
-                destination[1] = make_uint4(words[4], words[5], words[6], words[7]);
-            }
-            __syncthreads();
-            continue;
-        }
-
-        // q or k: this thread's 32 values of its row.
-        float x[4][8];
-        #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const uint32_t words[4] = {held[k].x, held[k].y, held[k].z, held[k].w};
-            #pragma unroll
-            for (int word = 0; word < 4; word++) {
-                x[k][word * 2] = __uint_as_float(words[word] << 16);
-                x[k][word * 2 + 1] = __uint_as_float(words[word] & 0xffff0000u);
-            }
-        }
-        float chains[8];
-        #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            chains[i] = __fmaf_rn(x[0][i], x[0][i], 0.0f);
-            chains[i] = __fmaf_rn(x[1][i], x[1][i], chains[i]);
-            chains[i] = __fmaf_rn(x[2][i], x[2][i], chains[i]);
-            chains[i] = __fmaf_rn(x[3][i], x[3][i], chains[i]);
-        }
-        #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            chains[i] = __fadd_rn(chains[i], __shfl_xor_sync(0xffffffffu, chains[i], 2));
-        }
-        #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            chains[i] = __fadd_rn(chains[i], __shfl_xor_sync(0xffffffffu, chains[i], 1));
-        }
-        const float fours[4] = {__fadd_rn(chains[0], chains[4]), __fadd_rn(chains[1], chains[5]),
-                                __fadd_rn(chains[2], chains[6]), __fadd_rn(chains[3], chains[7])};
-        const float squares =
-            __fadd_rn(__fadd_rn(fours[0], fours[2]), __fadd_rn(fours[1], fours[3]));
-        const float inverse = rsqrtf(__fmaf_rn(squares, 1.0f / HEAD_DIM, p.epsilon));
-        #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            const uint32_t words[4] = {weights[part][k].x, weights[part][k].y, weights[part][k].z,
-                                       weights[part][k].w};
-            #pragma unroll
-            for (int word = 0; word < 4; word++) {
-                x[k][word * 2] = __fmul_rn(
-                    x[k][word * 2], __fmul_rn(inverse, __uint_as_float(words[word] << 16)));
-                x[k][word * 2 + 1] =
-                    __fmul_rn(x[k][word * 2 + 1],
-                              __fmul_rn(inverse, __uint_as_float(words[word] & 0xffff0000u)));
-            }
-        }
-        if constexpr (ROTATE) {
-            using R = Rotary<GROUPS>;
-            constexpr bool CROSS = GROUPS % 4 != 0; // the partner group is two lanes over
-            constexpr int SLOTS = (2 * GROUPS + 3) / 4;  // slots with a rotating group in some thread
-            // First every exchange, on the values as normalized: a partner must not see a value
-            // this thread has already rotated.
-            float theirs[SLOTS][8];
-            #pragma unroll
-            for (int k = 0; k < SLOTS; k++) {
-                // What the partner thread needs from this one for ITS slot k: its j is this j ^ 2
-                // when the groups cross lanes, else it is this thread itself.
-                const int partner_j = CROSS ? (j ^ 2) : j;
-                const int wanted = R::partner_slot(k, partner_j);
-                #pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    float sent = x[0][i];
-                    sent = wanted == 1 ? x[1][i] : sent;
-                    sent = wanted == 2 ? x[2][i] : sent;
-                    sent = wanted == 3 ? x[3][i] : sent;
-                    theirs[k][i] = CROSS ? __shfl_xor_sync(0xffffffffu, sent, 2) : sent;
-                }
-            }
-            #pragma unroll
-            for (int k = 0; k < SLOTS; k++) {
-                const bool is_first = R::first(k, j), is_second = R::second(k, j);
-                if (is_first || is_second) {
-                    const float2 *row_trig = trig + row * p.pairs + 8 * R::pair_group(k, j);
-                    #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        const float2 angle = row_trig[i]; // (cosine, sine)
-                        const float mine = x[k][i];
-                        x[k][i] = is_first
-                                      ? __fmaf_rn(angle.x, mine, -__fmul_rn(angle.y, theirs[k][i]))
-                                      : __fmaf_rn(angle.y, theirs[k][i], __fmul_rn(angle.x, mine));
-                    }
-                }
-            }
-        }
-        // Round to BF16; the largest magnitude of the rounded values.
-        uint4 rounded[4];
-        float maximum = 0.0f;
-        #pragma unroll
-        for (int k = 0; k < 4; k++) {
-            uint32_t words[4];
-            #pragma unroll
-            for (int word = 0; word < 4; word++) {
-                const __nv_bfloat162 pair =
-                    __floats2bfloat162_rn(x[k][word * 2], x[k][word * 2 + 1]);
-                words[word] = *reinterpret_cast<const uint32_t *>(&pair);
-                x[k][word * 2] = __uint_as_float(words[word] << 16);
-                x[k][word * 2 + 1] = __uint_as_float(words[word] & 0xffff0000u);
-                maximum = fmaxf(maximum, fmaxf(fabsf(x[k][word * 2]), fabsf(x[k][word * 2 + 1])));
-            }
-            rounded[k] = make_uint4(words[0], words[1], words[2], words[3]);
-        }
-        if (!live) {
-            maximum = 0.0f;
-        }
-        if constexpr (STATS) {
-            if (live) {
-                #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    *reinterpret_cast<uint4 *>(&tile[row][32 * k + 8 * j]) = rounded[k];
-                }
-            }
-        }
-        if constexpr (QUANTIZE) {
-            maximum = warp_max(maximum);
-            if (lane == 0) {
-                maxima[item % 2][warp] = maximum;
-            }
-        }
-        if (STATS || QUANTIZE) {
-            __syncthreads();
-        }
-        if constexpr (STATS) {
-            if (threadIdx.x < HEAD_DIM) {
-                float sum = 0.0f;
-                for (int source_row = 0; source_row < rows; source_row++) {
-                    sum += __bfloat162float(tile[source_row][threadIdx.x]);
-                }
-                p.pooled[part][statistic + threadIdx.x] = sum / rows;
-            }
-        }
-        if constexpr (QUANTIZE) {
-            maximum = maxima[item % 2][0];
-            #pragma unroll
-            for (int index = 1; index < WARPS; index++) {
-                maximum = fmaxf(maximum, maxima[item % 2][index]);
-            }
-            const float scale = fmaxf(maximum / 127.0f, 1e-30f);
-            if (threadIdx.x == 0) {
-                p.scales[part][head * blocks + block] = scale;
-            }
-            if (live) {
-                const Divider divide(scale);
-                uint8_t *destination = p.quantized[part] +
-                                       ((first_token + row) * p.heads + head) * HEAD_DIM + 8 * j;
-                #pragma unroll
-                for (int k = 0; k < 4; k++) {
-                    uint32_t words[2];
-                    #pragma unroll
-                    for (int word = 0; word < 2; word++) {
-                        uint32_t packed = 0;
-                        #pragma unroll
-                        for (int byte = 0; byte < 4; byte++) {
-                            const int8_t value = static_cast<int8_t>(
-                                __float2int_rn(divide(x[k][word * 4 + byte])));
-                            packed |= static_cast<uint32_t>(static_cast<uint8_t>(value))
-                                      << (8 * byte);
-                        }
-                        words[word] = packed;
-                    }
-                    *reinterpret_cast<uint2 *>(destination + 32 * k) =
-                        make_uint2(words[0], words[1]);
-                }
-            }
-        }
-        if (p.normalized[part] != nullptr && live) {
-            __nv_bfloat16 *destination = p.normalized[part] +
-                                         (first_token + row) * p.token_stride[part] +
-                                         head * p.head_stride[part] + 8 * j;
-            #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                *reinterpret_cast<uint4 *>(destination + 32 * k) = rounded[k];
-            }
-        }
-        if constexpr (STATS) {
-            __syncthreads(); // the tile is read until here
-        }
-    }
-}
-
 // The FP8 scale of each head from its block maxima of |v|
 // (crates/mmh3-cuda/kernels/quantized_attention.cu:116-127).
 __global__ void value_scales_kernel(const float *__restrict__ maxima, float *__restrict__ scales,
@@ -743,49 +397,9 @@ bool aligned_rows(const void *base, int64_t token_stride, int64_t head_stride) {
            head_stride % 8 == 0;
 }
 
-template <bool STATS, bool QUANTIZE, int GROUPS>
-int launch_rows(InputsParams params, int blocks, cudaStream_t stream) {
-    params.heads_per_cta = GROUPS > 0 ? HEADS_PER_CTA : 1;
-    const int groups = (params.heads + params.heads_per_cta - 1) / params.heads_per_cta;
-    const size_t shared = static_cast<size_t>(BLOCK_ROWS) * params.pairs * sizeof(float2);
-    auto kernel = inputs_rows_kernel<STATS, QUANTIZE, GROUPS>;
-    if (GROUPS > 0) {
-        static SharedMemoryOptIn shared_memory;
-        const cudaError_t configured =
-            shared_memory.ensure(kernel, BLOCK_ROWS * (HEAD_DIM / 2) * 8);
-        if (configured != cudaSuccess) {
-            return static_cast<int>(configured);
-        }
-    }
-    kernel<<<dim3(blocks, groups), THREADS, GROUPS > 0 ? shared : 0, stream>>>(params);
-    return static_cast<int>(cudaGetLastError());
-}
-
 template <bool NORMALIZE, bool STATS, bool QUANTIZE>
 int launch(InputsParams params, int blocks, cudaStream_t stream) {
     const bool rotate = NORMALIZE && params.angles != nullptr;
-    if (NORMALIZE && params.vector_loads && params.first_part == 0 && params.last_part == 2 &&
-        reinterpret_cast<uintptr_t>(params.weight[0]) % 16 == 0 &&
-        reinterpret_cast<uintptr_t>(params.weight[1]) % 16 == 0) {
-        // The register-resident pass takes the common shapes; everything else the general one.
-        const int groups = rotate ? params.pairs / 8 : 0;
-        if (!rotate || params.pairs % 8 == 0) {
-            switch (groups) {
-            case 0:
-                return launch_rows<STATS, QUANTIZE, 0>(params, blocks, stream);
-            case 2:
-                return launch_rows<STATS, QUANTIZE, 2>(params, blocks, stream);
-            case 4:
-                return launch_rows<STATS, QUANTIZE, 4>(params, blocks, stream);
-            case 6:
-                return launch_rows<STATS, QUANTIZE, 6>(params, blocks, stream);
-            case 8:
-                return launch_rows<STATS, QUANTIZE, 8>(params, blocks, stream);
-            default:
-                break;
-            }
-        }
-    }
     // With angles a CTA takes several heads so that their sincosf is paid once; the grid still
     // holds several CTAs per SM slot.
     params.heads_per_cta = rotate ? HEADS_PER_CTA : 1;
