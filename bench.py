@@ -330,7 +330,8 @@ def run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, a
     torch.cuda.empty_cache()
     if not args.skip_vsa:
         try:
-            extras["vsa"] = run_vsa(torch, attention, synthetic, heads, scale, steps)
+            extras["vsa"] = run_vsa(torch, attention, synthetic, heads, scale, steps,
+                                    args.vsa_frames)
         except attention.CudaError as error:
             extras["vsa_error"] = str(error)
     return extras
@@ -357,11 +358,11 @@ def kernel_times(torch, fn) -> dict:
         return {"unavailable": str(error)[:80]}
 
 
-def run_vsa(torch, attention, synthetic, heads, scale, steps) -> dict:
+def run_vsa(torch, attention, synthetic, heads, scale, steps, frames=31) -> dict:
     """Video sparse attention on the 31 x 48 x 84 grid + 512 text tokens (BASELINE configs[3]):
     pool, select and token attention timed apart. Inputs are drawn on the device: N(0, 1) plus 0.5 x
     a trilinearly upsampled low-resolution field per head and channel, in the plan's cube order."""
-    layout, plan = synthetic.video_plan()
+    layout, plan = synthetic.video_plan(frames=frames)
     tokens = len(layout)
     kept = plan.kept_video_tiles(0.875)
     generator = torch.Generator(device="cuda").manual_seed(3)
@@ -398,7 +399,8 @@ def run_vsa(torch, attention, synthetic, heads, scale, steps) -> dict:
         routed_keys[head] = (table * mask).sum(dim=1)
     sparse_flops = float((routed_keys * lengths[None, :]).sum().item()) * 4.0 * HEAD_DIM
     return {
-        "workload": f"VSA L={tokens} (8 prefix + 2016 video tiles), H={heads}, kept {kept}",
+        "workload": (f"VSA L={tokens} ({plan.prefix_tiles} prefix + {plan.video_tiles} video "
+                     f"tiles), H={heads}, kept {kept}"),
         "ms": ms, "sparse_flops": sparse_flops, "sparse_tflops": sparse_flops / ms / 1e9,
         "dense_equivalent_tflops": attention_flops(tokens, heads) / ms / 1e9,
         "kernel_ms": kernel_times(torch, whole),
@@ -503,6 +505,9 @@ def main() -> None:
                         help="leave the fused quantize pass and the INT8/FP8 kernel out")
     parser.add_argument("--skip-vsa", action="store_true",
                         help="leave the video sparse attention out")
+    parser.add_argument("--vsa-frames", type=int, default=31,
+                        help="latent frames of the video sparse attention case (31 is the "
+                             "benchmark configuration; fewer for profiler captures)")
     parser.add_argument("--dense-only", action="store_true",
                         help="time only the dense BF16 kernel (for profiler captures)")
     args = parser.parse_args()
