@@ -38,6 +38,9 @@ HEAD_DIM = 128
 HEADS = 32
 DENSE_TOKENS = 65536 + 512
 VIDEO_TOKENS = 124992 + 512
+# DRAM bytes per token and head of the dense kernel: 404.7 MB read + 116.2 MB written in the ncu
+# capture of one launch at L = 16,384, H = 32 (q, k, v, output once each would be 1,024 B).
+DENSE_TRAFFIC_PER_TOKEN = 520.9e6 / (16384 * 32)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -53,65 +56,113 @@ def measured_peaks() -> tuple[dict, str]:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons through NVML (read-only queries) on a thread while
+    the timed region runs; nvidia-smi in loop mode stands in where NVML cannot be loaded."""
 
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    PERIOD = 0.005
 
     def __init__(self, index: int):
         self.index = index
         self.process = None
-        self.lines: list[tuple[float, str]] = []
+        self.thread = None
+        self.stop = threading.Event()
+        # (host time, SM MHz, max SM MHz, active reasons)
+        self.samples: list[tuple[float, float, float, tuple[str, ...]]] = []
         self.window = (0.0, float("inf"))
+        self.source = None
+
+    def _nvml_handle(self):
+        import pynvml
+        import torch
+
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+        if not uuid.startswith("GPU-"):
+            uuid = "GPU-" + uuid
+        return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid)
 
     def __enter__(self):
+        try:
+            nvml, handle = self._nvml_handle()
+            nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)
+            self.source = "nvml"
+            self.thread = threading.Thread(target=self._poll, args=(nvml, handle), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            self.source = None
         try:
             self.process = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                  "-i", str(self.index), "-lms", "100"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.source = "nvidia-smi"
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
             self.process = None
         return self
 
+    def _poll(self, nvml, handle):
+        masks = {
+            "hw_slowdown": nvml.nvmlClocksThrottleReasonHwSlowdown,
+            "hw_thermal_slowdown": nvml.nvmlClocksThrottleReasonHwThermalSlowdown,
+            "sw_thermal_slowdown": nvml.nvmlClocksThrottleReasonSwThermalSlowdown,
+            "sw_power_cap": nvml.nvmlClocksThrottleReasonSwPowerCap,
+        }
+        try:
+            maximum = float(nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM))
+        except Exception:
+            maximum = float("nan")
+        while not self.stop.is_set():
+            try:
+                clock = float(nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM))
+                bits = nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                active = tuple(name for name, mask in masks.items() if bits & mask)
+                self.samples.append((time.time(), clock, maximum, active))
+            except Exception:
+                pass
+            self.stop.wait(self.PERIOD)
+
     def _read(self):
         for line in self.process.stdout:
-            self.lines.append((time.time(), line.strip()))
+            fields = [field.strip() for field in line.split(",")]
+            if len(fields) != 7:
+                continue
+            try:
+                clock, maximum = float(fields[0]), float(fields[1])
+            except ValueError:
+                continue
+            active = tuple(name for name, flag in zip(self.NAMES, fields[3:])
+                           if flag.lower().startswith("active"))
+            self.samples.append((time.time(), clock, maximum, active))
 
     def mark(self, start: float, end: float) -> None:
         """Only samples taken between `start` and `end` (host clock) count."""
         self.window = (start, end)
 
     def __exit__(self, *_):
+        self.stop.set()
         if self.process is not None:
             self.process.terminate()
             self.process.wait(timeout=5)
+        if self.thread is not None:
             self.thread.join(timeout=5)
 
     def summary(self) -> dict:
-        clocks, maxima, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for stamp, line in self.lines:
-            if not self.window[0] <= stamp <= self.window[1]:
-                continue
-            fields = [field.strip() for field in line.split(",")]
-            if len(fields) != 7:
-                continue
-            try:
-                clocks.append(float(fields[0]))
-                maxima.append(float(fields[1]))
-            except ValueError:
-                continue
-            for name, flag in zip(names, fields[3:]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        if not clocks:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max(maxima),
-                "reasons": sorted(reasons), "samples": len(clocks)}
+        inside = [sample for sample in self.samples
+                  if self.window[0] <= sample[0] <= self.window[1]]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0,
+                    "source": self.source}
+        reasons = sorted({name for sample in inside for name in sample[3]})
+        return {"sm_mhz": statistics.median(sample[1] for sample in inside),
+                "sm_max_mhz": max(sample[2] for sample in inside),
+                "reasons": reasons, "samples": len(inside), "source": self.source}
 
 
 def cpu_attention_sampler(tokens: int, heads: int, seed: int, rows: int, qkv=None,
@@ -273,7 +324,11 @@ def run_single(args) -> None:
                 "d2h_bytes_per_step": host_output.numel() * 2},
         "gpu_launches": launches,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                     "frac": achieved / peak, "traffic": None,
+                     "frac": achieved / peak, "traffic": DENSE_TRAFFIC_PER_TOKEN * tokens * heads,
+                     "traffic_unit": "bytes per launch (dram read + write), scaled in proportion "
+                                     "to L x H from the ncu capture at L=16384, H=32 (520.9 MB "
+                                     "against 536.9 MB algorithmic)",
+                     "algorithmic_bytes": 8.0 * tokens * heads * HEAD_DIM,
                      "peak_source": f"{source} bf16_tflops (burst)",
                      "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"]},
         "cpu_baseline": cpu,
@@ -479,7 +534,10 @@ def run_sharded(args) -> None:
             "gpu_launches": args.steps * (2 * world + 1),
             "roofline": {"bound": "tensor", "achieved": value, "peak": peaks["bf16_tflops"] * world,
                          "unit": "TFLOP/s", "frac": value / (peaks["bf16_tflops"] * world),
-                         "traffic": None, "peak_source": f"{source} bf16_tflops (burst) x {world}"},
+                         "traffic": DENSE_TRAFFIC_PER_TOKEN * tokens * heads / world,
+                         "traffic_unit": "bytes per rank's launch, scaled from the 1-GPU ncu "
+                                         "capture in proportion to L x heads per rank",
+                         "peak_source": f"{source} bf16_tflops (burst) x {world}"},
             "cpu_baseline": None,
             "clocks": sampler.summary(),
         }
