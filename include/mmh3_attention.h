@@ -149,8 +149,13 @@ int mmh3_vsa_attention_quantized(const void *value, const void *gate, int64_t ga
                                  const Mmh3QuantizedWorkspace *workspace, int inputs_ready,
                                  mmh3_stream_t stream);
 
-/* Sol-Attn is outside this library: the symbol exists so that mmh3's Rust crate links, and
- * returns cudaErrorNotSupported. Replaces crates/mmh3-cuda/kernels/sparse_attention.cu:546. */
+/* Sol-Attn over one sequence of BF16 heads of 128: blocks of 64 tokens; a query block attends the
+ * key blocks it routes (pooled score above tau standard deviations, its neighbours, the key sinks
+ * [sink_key_start, sink_key_end), every block for the query sinks) token by token and the rest
+ * through one pooled term each. inputs_ready != 0: the workspace already holds the block statistics
+ * (mmh3_attention_inputs). The routes are bit-identical to the reference's. A non-null `quantized`
+ * (INT8/FP8 token attention over the routes) returns cudaErrorNotSupported.
+ * Replaces crates/mmh3-cuda/kernels/sparse_attention.cu:546-586. */
 int mmh3_sparse_attention(const void *query, const void *key, const void *value, void *output,
                           int tokens, int heads, const Mmh3AttentionLayout *layout, float scale,
                           float tau, int sink_key_start, int sink_key_end, int sink_query_start,

@@ -286,16 +286,17 @@ class VsaWorkspace:
 
 def prepare_inputs(qkv: torch.Tensor, norm: HeadNorm, tokens: int, heads: int,
                    quantized: QuantizedWorkspace | None = None, vsa: VsaWorkspace | None = None,
-                   value_head_maxima: torch.Tensor | None = None) -> None:
+                   value_head_maxima: torch.Tensor | None = None, sol=None) -> None:
     """qk_norm_rope fused with the attention's per-block work (attention.rs:670-760).
 
     With `vsa`, the blocks are its tiles, its pooled buffers are filled, and its own quantized
-    workspace (if any) is used.
+    workspace (if any) is used. With `sol` (a `SparseWorkspace`), the block statistics of Sol-Attn
+    are filled over blocks of 64 tokens.
     """
     norm.check(qkv, tokens, heads)
     if vsa is not None and vsa.quantized is not None:
         quantized = vsa.quantized
-    sparse = vsa.sparse_raw() if vsa is not None else None
+    sparse = vsa.sparse_raw() if vsa is not None else (sol.raw() if sol is not None else None)
     raw = quantized.raw() if quantized is not None else None
     check(
         _lib.library().mmh3_attention_inputs(
@@ -341,6 +342,104 @@ def vsa(qkv: torch.Tensor, gate: torch.Tensor | None, output: torch.Tensor,
             ctypes.byref(raw), ctypes.byref(quantized) if quantized is not None else None,
             int(inputs), _stream()),
         "mmh3_vsa_attention",
+    )
+
+
+# -------------------------------------------------------------------------------------------------
+# Sol-Attn
+
+SPARSE_BLOCK = 64
+
+
+class SparseSinks:
+    """Block ranges [start, end) that are always exact (mmh3-core/src/dit/sparse.rs:79-101):
+    `key_blocks` every query attends token by token, `query_blocks` attend every key so."""
+
+    def __init__(self, key_blocks=(0, 0), query_blocks=(0, 0)):
+        self.key_blocks = tuple(key_blocks)
+        self.query_blocks = tuple(query_blocks)
+
+    @classmethod
+    def for_layout(cls, layout) -> "SparseSinks":
+        """H3's conditioning: every query attends the text and audio prefix exactly, and the audio
+        queries run dense. `layout` is a `vsa.PackedLayout`."""
+        video, audio = layout.segment("video"), layout.segment("audio")
+        prefix_blocks = -(-video.start // SPARSE_BLOCK)
+        return cls((0, prefix_blocks), (audio.start // SPARSE_BLOCK, prefix_blocks))
+
+    def __eq__(self, other):
+        return (self.key_blocks, self.query_blocks) == (other.key_blocks, other.query_blocks)
+
+    def __repr__(self):
+        return f"SparseSinks(key_blocks={self.key_blocks}, query_blocks={self.query_blocks})"
+
+
+class SparseWorkspace:
+    """Scratch buffers of Sol-Attn for one sequence length and head count (attention.rs:818-908).
+    Only BF16 token attention is built: there is no quantized variant of this workspace."""
+
+    def __init__(self, tokens: int, heads: int, device="cuda"):
+        blocks = -(-tokens // SPARSE_BLOCK)
+        if not 0 < blocks <= 65535:
+            raise ValueError(f"invalid block count {blocks}")
+        self.tokens, self.heads, self.blocks = tokens, heads, blocks
+        per_block = heads * blocks * HEAD_DIM
+        real = dict(dtype=torch.float32, device=device)
+        self.centroids = torch.empty(per_block, **real)
+        self.block_keys = torch.empty(per_block, **real)
+        self.value_sums = torch.empty(per_block, **real)
+        self.key_mean = torch.empty(heads * HEAD_DIM, **real)
+        self.key_variance = torch.empty(heads * HEAD_DIM, **real)
+        self.row_offsets = torch.empty(heads * tokens, **real)
+        self.routes = torch.empty(heads * blocks * blocks, dtype=torch.int16, device=device)
+        self.route_counts = torch.zeros(heads * blocks, dtype=torch.int32, device=device)
+        self.tail_max = torch.empty(heads * blocks, **real)
+        self.tail_sum = torch.empty(heads * blocks, **real)
+        self.tail_values = torch.empty(per_block, **real)
+
+    def raw(self) -> _lib.SparseWorkspace:
+        workspace = _lib.SparseWorkspace()
+        for name, _ in _lib.SparseWorkspace._fields_:
+            setattr(workspace, name, getattr(self, name).data_ptr())
+        return workspace
+
+    def routed_fraction(self) -> float:
+        """Fraction of (head, query block, key block) triples the last call routed token by
+        token."""
+        routed = int(self.route_counts.to(torch.int64).sum().item())
+        return routed / (self.heads * self.blocks * self.blocks)
+
+    def routes_host(self):
+        """Routes [heads, blocks, blocks] as uint16 and counts [heads, blocks], on the host."""
+        routes = self.routes.cpu().numpy().view("uint16").reshape(self.heads, self.blocks,
+                                                                 self.blocks)
+        counts = self.route_counts.cpu().numpy().reshape(self.heads, self.blocks)
+        return routes, counts
+
+
+def sparse(qkv: torch.Tensor, output: torch.Tensor, layout: _lib.AttentionLayout, scale: float,
+           tau: float, sinks: SparseSinks, workspace: SparseWorkspace,
+           inputs: AttentionInputs = AttentionInputs.RAW, offsets=None) -> None:
+    """Sol-Attn over BF16 heads of 128 for one sequence (attention.rs:1253-1306). With prepared
+    inputs the workspace already holds the block statistics (`prepare_inputs(..., sol=...)`)."""
+    tokens, heads = workspace.tokens, workspace.heads
+    inner = heads * HEAD_DIM
+    if offsets is None:
+        offsets = (0, inner, 2 * inner, 0)
+    for operand in range(4):
+        buffer = output if operand == 3 else qkv
+        last = (offsets[operand] + (tokens - 1) * layout.token_stride[operand]
+                + (heads - 1) * layout.head_stride[operand] + HEAD_DIM)
+        if last > buffer.numel():
+            raise ValueError(f"operand {operand} reaches past its buffer")
+    raw = workspace.raw()
+    check(
+        _lib.library().mmh3_sparse_attention(
+            _pointer(qkv, offsets[0]), _pointer(qkv, offsets[1]), _pointer(qkv, offsets[2]),
+            _pointer(output, offsets[3]), tokens, heads, ctypes.byref(layout), scale, tau,
+            sinks.key_blocks[0], sinks.key_blocks[1], sinks.query_blocks[0],
+            sinks.query_blocks[1], ctypes.byref(raw), None, int(inputs), _stream()),
+        "mmh3_sparse_attention",
     )
 
 

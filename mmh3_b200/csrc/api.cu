@@ -163,11 +163,27 @@ extern "C" int mmh3_vsa_attention(const void *query, const void *key, const void
                                 *layout, scale, tiles, *workspace, as_stream(stream));
 }
 
-extern "C" int mmh3_sparse_attention(const void *, const void *, const void *, void *, int, int,
-                                     const Mmh3AttentionLayout *, float, float, int, int, int, int,
-                                     const Mmh3SparseWorkspace *, const Mmh3QuantizedWorkspace *,
-                                     int, mmh3_stream_t) {
-    return NOT_SUPPORTED;
+extern "C" int mmh3_sparse_attention(const void *query, const void *key, const void *value,
+                                     void *output, int tokens, int heads,
+                                     const Mmh3AttentionLayout *layout, float scale, float tau,
+                                     int sink_key_start, int sink_key_end, int sink_query_start,
+                                     int sink_query_end, const Mmh3SparseWorkspace *workspace,
+                                     const Mmh3QuantizedWorkspace *quantized, int inputs_ready,
+                                     mmh3_stream_t stream) {
+    if (tokens <= 0 || heads <= 0) {
+        return INVALID_VALUE;
+    }
+    if (layout == nullptr || workspace == nullptr || query == nullptr || key == nullptr ||
+        value == nullptr || output == nullptr) {
+        return INVALID_VALUE;
+    }
+    if (quantized != nullptr) {
+        // The INT8/FP8 token attention over Sol-Attn's routes is not built.
+        return NOT_SUPPORTED;
+    }
+    return launch_sparse_attention(query, key, value, output, tokens, heads, *layout, scale, tau,
+                                   sink_key_start, sink_key_end, sink_query_start, sink_query_end,
+                                   *workspace, inputs_ready, as_stream(stream));
 }
 
 extern "C" int mmh3_dit_shard_pack(const void *source, void *packed, int tokens, int tensors,

@@ -96,6 +96,18 @@ int launch_pool(const void *query, const void *key, const void *value, int heads
                 const Mmh3AttentionLayout &layout, int tiles, const Mmh3VsaWorkspace &workspace,
                 cudaStream_t stream);
 
+int launch_block_statistics(const void *query, const void *key, const void *value, int tokens,
+                            int heads, const Mmh3AttentionLayout &layout,
+                            const Mmh3SparseWorkspace &workspace, cudaStream_t stream);
+
+// sol_attention.cu: Sol-Attn over BF16 q, k, v (block statistics unless inputs_ready, centring,
+// routing, row offsets, token attention merged with the pooled tails).
+int launch_sparse_attention(const void *query, const void *key, const void *value, void *output,
+                            int tokens, int heads, const Mmh3AttentionLayout &layout, float scale,
+                            float tau, int sink_key_start, int sink_key_end, int sink_query_start,
+                            int sink_query_end, const Mmh3SparseWorkspace &workspace,
+                            int inputs_ready, cudaStream_t stream);
+
 // vsa_select.cu
 int launch_select(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int prefix_tiles,
                   int kept, float scale, int coarse, cudaStream_t stream);
@@ -111,6 +123,12 @@ int launch_vsa_attention(const void *query, const void *key, const void *value, 
                          int64_t gate_stride, void *output, int tokens, int heads,
                          const Mmh3AttentionLayout &layout, float scale, int tiles,
                          const Mmh3VsaWorkspace &workspace, cudaStream_t stream);
+
+// Sol-Attn's token attention over the routes in `sparse`, merged with its pooled tails.
+int launch_sol_token_attention(const void *query, const void *key, const void *value, void *output,
+                               int tokens, int heads, const Mmh3AttentionLayout &layout,
+                               float scale, const Mmh3SparseWorkspace &sparse,
+                               cudaStream_t stream);
 
 // The INT8/FP8 token attention over the routes of `vsa`.
 int launch_vsa_attention_quantized(const Mmh3QuantizedWorkspace &workspace, void *output,

@@ -604,4 +604,30 @@ int launch_pool(const void *query, const void *key, const void *value, int heads
     return launch<false, true, false>(params, tiles, stream);
 }
 
+// Sol-Attn's block statistics: the same pooling pass over blocks of 64 tokens (no tile tables),
+// into the mean query, mean key and summed value of the sparse workspace.
+int launch_block_statistics(const void *query, const void *key, const void *value, int tokens,
+                            int heads, const Mmh3AttentionLayout &layout,
+                            const Mmh3SparseWorkspace &workspace, cudaStream_t stream) {
+    InputsParams params = {};
+    const void *sources[3] = {query, key, value};
+    params.vector_loads = 1;
+    for (int part = 0; part < 3; part++) {
+        params.source[part] = static_cast<const __nv_bfloat16 *>(sources[part]);
+        params.token_stride[part] = layout.token_stride[part];
+        params.head_stride[part] = layout.head_stride[part];
+        if (!aligned_rows(sources[part], layout.token_stride[part], layout.head_stride[part])) {
+            params.vector_loads = 0;
+        }
+    }
+    params.heads = heads;
+    params.tokens = tokens;
+    params.pooled[0] = workspace.centroids;
+    params.pooled[1] = workspace.block_keys;
+    params.pooled[2] = workspace.value_sums;
+    params.first_part = 0;
+    params.last_part = 2;
+    return launch<false, true, false>(params, (tokens + BLOCK_ROWS - 1) / BLOCK_ROWS, stream);
+}
+
 } // namespace mmh3

@@ -91,6 +91,12 @@ struct VsaParams {
     const float *query_scales;
     const float *key_scales;
     const float *value_scales;
+    // Sol-Attn: the pooled tail of each query block as an online-softmax state and the centring
+    // offset of each row's scores (see the epilogue); null for VSA.
+    const float *tail_max;
+    const float *tail_sum;
+    const float *tail_values;
+    const float *row_offsets;
     int tokens;
     int tiles;
     float scale_log2;
@@ -118,6 +124,13 @@ __global__ void __launch_bounds__(THREADS, 2)
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
     const int head = blockIdx.y;
+    // Without tile tables the tiles are the blocks of 64 tokens (Sol-Attn).
+    auto tile_start = [&](int tile) {
+        return p.tile_starts != nullptr ? p.tile_starts[tile] : tile * TILE;
+    };
+    auto tile_length = [&](int tile) {
+        return p.tile_lengths != nullptr ? p.tile_lengths[tile] : min(TILE, p.tokens - tile * TILE);
+    };
     // The two query tiles of this CTA; the second may not exist.
     const int query_tiles[2] = {static_cast<int>(blockIdx.x) * 2,
                                 static_cast<int>(blockIdx.x) * 2 + 1};
@@ -168,7 +181,7 @@ __global__ void __launch_bounds__(THREADS, 2)
             for (int half = 0; half < 2; half++) {
                 load_rows(&maps.query, base + S::SMEM_QUERY + half * TILE * 128,
                           barrier(S::QUERY_FULL),
-                          exists[half] ? p.tile_starts[query_tiles[half]] : p.tokens);
+                          exists[half] ? tile_start(query_tiles[half]) : p.tokens);
             }
             // The tiles of step 0, then one step ahead of the loads.
             int tiles_now[2], tiles_next[2];
@@ -184,7 +197,7 @@ __global__ void __launch_bounds__(THREADS, 2)
                 }
                 int rows[2];
                 for (int half = 0; half < 2; half++) {
-                    rows[half] = tiles_now[half] >= 0 ? p.tile_starts[tiles_now[half]] : p.tokens;
+                    rows[half] = tiles_now[half] >= 0 ? tile_start(tiles_now[half]) : p.tokens;
                 }
                 bool alive = true;
                 for (int part = 0; part < 2 && alive; part++) { // K, then V
@@ -335,7 +348,7 @@ __global__ void __launch_bounds__(THREADS, 2)
         bool alive = true;
         for (int step = 0; step < steps; step++) {
             const bool active = step < count;
-            const int valid = active ? p.tile_lengths[key_tile] : 0;
+            const int valid = active ? tile_length(key_tile) : 0;
             float factor = query_factor;
             if constexpr (QUANTIZED) {
                 factor *= active ? __ldg(head_key_scales + key_tile) : 0.0f;
@@ -477,11 +490,28 @@ __global__ void __launch_bounds__(THREADS, 2)
             tcgen05_fence_after();
             const int tile_row = row % TILE;
             const bool stored =
-                exists[half] && tile_row < p.tile_lengths[query_tiles[half]] && count > 0;
-            const int64_t token = stored ? p.tile_starts[query_tiles[half]] + tile_row : 0;
-            float inverse = 1.0f / ((sums[0].x + sums[0].y) + (sums[1].x + sums[1].y));
+                exists[half] && tile_row < tile_length(query_tiles[half]) && count > 0;
+            const int64_t token = stored ? tile_start(query_tiles[half]) + tile_row : 0;
+            const float sum = (sums[0].x + sums[0].y) + (sums[1].x + sums[1].y);
+            float inverse = 1.0f / sum;
             if constexpr (QUANTIZED) {
                 inverse *= p.value_scales[head];
+            }
+            // Sol-Attn: every key block the list leaves out contributes one pooled term; their
+            // sum arrives as a softmax state (maximum, sum of weights, weighted values) in the
+            // units of the centred scores, which this row's scores reach by its offset.
+            const bool tailed = p.tail_max != nullptr;
+            const float *tail_values = tailed ? p.tail_values + route_rows[half] * HEAD_DIM : nullptr;
+            float tail_weight = 0.0f;
+            if (tailed && stored) {
+                const float centred = maximum - p.row_offsets[static_cast<size_t>(head) * p.tokens + token];
+                const float tail_maximum = p.tail_max[route_rows[half]];
+                const float merged = fmaxf(centred, tail_maximum);
+                const float routed_weight = exp2f(centred - merged);
+                tail_weight = exp2f(tail_maximum - merged);
+                inverse = 1.0f / (sum * routed_weight + p.tail_sum[route_rows[half]] * tail_weight);
+                tail_weight *= inverse;
+                inverse *= routed_weight;
             }
             __nv_bfloat16 *output_row = p.output + token * p.output_token_stride +
                                         static_cast<int64_t>(head) * p.output_head_stride;
@@ -507,6 +537,13 @@ __global__ void __launch_bounds__(THREADS, 2)
                             results[index] =
                                 fmaf(__bfloat162float(gate_row[chunk * 32 + index]),
                                      __ldg(coarse + chunk * 32 + index), results[index]);
+                        }
+                    }
+                    if (tailed) {
+                        #pragma unroll
+                        for (int index = 0; index < 32; index++) {
+                            results[index] = fmaf(__ldg(tail_values + chunk * 32 + index),
+                                                  tail_weight, results[index]);
                         }
                     }
                     uint32_t packed[16];
@@ -586,6 +623,28 @@ bool fill_params(VsaParams &params, void *output, int tokens, const Mmh3Attentio
     return params.status != nullptr;
 }
 
+// BF16 q, k, v as [128, tokens, heads] in boxes of 64 columns x 64 rows.
+bool encode_bf16_maps(VsaMaps &maps, const void *query, const void *key, const void *value,
+                      int tokens, int heads, const Mmh3AttentionLayout &layout) {
+    const void *bases[3] = {query, key, value};
+    CUtensorMap *targets[3] = {&maps.query, &maps.key, &maps.value};
+    for (int operand = 0; operand < 3; operand++) {
+        const uint64_t dimensions[3] = {HEAD_DIM, static_cast<uint64_t>(tokens),
+                                        static_cast<uint64_t>(heads)};
+        uint64_t strides[2] = {static_cast<uint64_t>(layout.token_stride[operand]) * 2,
+                               static_cast<uint64_t>(layout.head_stride[operand]) * 2};
+        if (heads == 1 && strides[1] == 0) {
+            strides[1] = strides[0] * static_cast<uint64_t>(tokens);
+        }
+        const uint32_t box[3] = {64, TILE, 1};
+        if (!encode_tensor_map(targets[operand], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                               bases[operand], dimensions, strides, box)) {
+            return false;
+        }
+    }
+    return true;
+}
+
 } // namespace
 
 int launch_vsa_attention(const void *query, const void *key, const void *value, const void *gate,
@@ -600,21 +659,32 @@ int launch_vsa_attention(const void *query, const void *key, const void *value, 
         return static_cast<int>(cudaErrorInvalidDevice);
     }
     VsaMaps maps;
-    const void *bases[3] = {query, key, value};
-    CUtensorMap *targets[3] = {&maps.query, &maps.key, &maps.value};
-    for (int operand = 0; operand < 3; operand++) {
-        const uint64_t dimensions[3] = {HEAD_DIM, static_cast<uint64_t>(tokens),
-                                        static_cast<uint64_t>(heads)};
-        uint64_t strides[2] = {static_cast<uint64_t>(layout.token_stride[operand]) * 2,
-                               static_cast<uint64_t>(layout.head_stride[operand]) * 2};
-        if (heads == 1 && strides[1] == 0) {
-            strides[1] = strides[0] * static_cast<uint64_t>(tokens);
-        }
-        const uint32_t box[3] = {64, TILE, 1};
-        if (!encode_tensor_map(targets[operand], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
-                               bases[operand], dimensions, strides, box)) {
-            return NOT_SUPPORTED;
-        }
+    if (!encode_bf16_maps(maps, query, key, value, tokens, heads, layout)) {
+        return NOT_SUPPORTED;
+    }
+    return launch<false>(maps, params, heads, stream);
+}
+
+int launch_sol_token_attention(const void *query, const void *key, const void *value, void *output,
+                               int tokens, int heads, const Mmh3AttentionLayout &layout,
+                               float scale, const Mmh3SparseWorkspace &sparse,
+                               cudaStream_t stream) {
+    // The routes of Sol-Attn in the form the kernel walks: blocks of 64 tokens for tiles, no gate.
+    Mmh3VsaWorkspace workspace = {};
+    workspace.routes = sparse.routes;
+    workspace.route_counts = sparse.route_counts;
+    VsaParams params = {};
+    const int blocks = (tokens + TILE - 1) / TILE;
+    if (!fill_params(params, output, tokens, layout, scale, workspace, blocks, nullptr, 0)) {
+        return static_cast<int>(cudaErrorInvalidDevice);
+    }
+    params.tail_max = sparse.tail_max;
+    params.tail_sum = sparse.tail_sum;
+    params.tail_values = sparse.tail_values;
+    params.row_offsets = sparse.row_offsets;
+    VsaMaps maps;
+    if (!encode_bf16_maps(maps, query, key, value, tokens, heads, layout)) {
+        return NOT_SUPPORTED;
     }
     return launch<false>(maps, params, heads, stream);
 }

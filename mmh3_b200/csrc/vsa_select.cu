@@ -14,6 +14,7 @@
 #include <cfloat>
 
 #include "common.cuh"
+#include "pooled_score.cuh"
 
 namespace mmh3 {
 
@@ -27,24 +28,6 @@ constexpr int MAX_QUERIES = 8;
 __device__ __forceinline__ uint32_t ordered_bits(float value) {
     const uint32_t bits = __float_as_uint(value);
     return (bits & 0x80000000u) ? ~bits : bits | 0x80000000u;
-}
-
-// The sum over the chains l = BASE, BASE + STRIDE, ... of the products of one query with one key,
-// in the tree order described at the top. `key` is the key's 128 values in registers; `query` holds
-// the query regrouped by chain: query[l] = (q[l], q[l + 32], q[l + 64], q[l + 96]).
-template <int STRIDE, int BASE>
-__device__ __forceinline__ float score_tree(const float4 *__restrict__ query,
-                                            const float (&key)[HEAD_DIM]) {
-    if constexpr (STRIDE == 32) {
-        const float4 q = query[BASE];
-        float sum = __fmaf_rn(q.x, key[BASE], 0.0f);
-        sum = __fmaf_rn(q.y, key[BASE + 32], sum);
-        sum = __fmaf_rn(q.z, key[BASE + 64], sum);
-        return __fmaf_rn(q.w, key[BASE + 96], sum);
-    } else {
-        return __fadd_rn(score_tree<STRIDE * 2, BASE>(query, key),
-                         score_tree<STRIDE * 2, BASE + STRIDE>(query, key));
-    }
 }
 
 __device__ __forceinline__ float block_reduce(float value, float *scratch, bool maximum) {

@@ -695,6 +695,299 @@ void oracle_vsa_reference(const float *query, const float *key, const float *val
 }
 
 // ---------------------------------------------------------------------------------------------
+// Sol-Attn (crates/mmh3-core/src/dit/sparse.rs, crates/mmh3-cuda/kernels/sparse_attention.cu)
+
+// Everything the routing of Sol-Attn leaves in its workspace, in FP32 and in the kernels' order
+// (sparse_attention.cu:72-290, 315-338), from BF16 query, key and value with strides in elements:
+// block_stats (sums down the rows; mean query, mean key, summed value), center_keys (mean and
+// variance down the blocks, the block keys centred in place), route (threshold = tau * sqrt(spread
+// * log2_scale^2 + 1e-6) with the spread summed over a xor butterfly per warp of 32 dimensions and
+// then over the four warps; pooled scores in the order of oracle_vsa_score; a key block is routed
+// if its score clears the threshold, if it neighbours the query block, or by the sinks), the
+// pooled tail of the unrouted blocks as (maximum, sum of weights times block length, weighted value
+// sums), and row_offsets. The tail sums and the offsets are accumulated in FP32 in an order of
+// this function's own; the kernels' differ in the last bits. `sinks` = {key start, key end, query
+// start, query end}. Any output may be null.
+void oracle_sol_route(const uint16_t *query, const uint16_t *key, const uint16_t *value,
+                      const int64_t *token_stride, const int64_t *head_stride, int tokens,
+                      int heads, float tau, float scale, const int32_t *sinks, float *centroids,
+                      float *block_keys, float *value_sums, float *key_mean, float *key_variance,
+                      float *row_offsets, uint16_t *routes, int32_t *route_counts,
+                      float *tail_max, float *tail_sum, float *tail_values) {
+    const int blocks = (tokens + 63) / 64;
+    const float log2_scale = scale * 1.4426950408889634f;
+    std::vector<int32_t> starts(blocks), lengths(blocks);
+    for (int block = 0; block < blocks; block++) {
+        starts[block] = block * 64;
+        lengths[block] = std::min(64, tokens - block * 64);
+    }
+    const size_t per_block = static_cast<size_t>(heads) * blocks * 128;
+    std::vector<float> mean_query(per_block), mean_key(per_block), sums(per_block);
+    oracle_vsa_pool(query, key, value, token_stride, head_stride, heads, starts.data(),
+                    lengths.data(), blocks, mean_query.data(), mean_key.data(), sums.data());
+    std::vector<float> means(heads * 128), variances(heads * 128);
+    for (int head = 0; head < heads; head++) {
+        for (int index = 0; index < 128; index++) {
+            float *column = mean_key.data() + static_cast<size_t>(head) * blocks * 128 + index;
+            float total = 0.0f;
+            for (int block = 0; block < blocks; block++) {
+                total += column[static_cast<size_t>(block) * 128];
+            }
+            const float mean = total / blocks;
+            float squares = 0.0f;
+            for (int block = 0; block < blocks; block++) {
+                const float centred = column[static_cast<size_t>(block) * 128] - mean;
+                column[static_cast<size_t>(block) * 128] = centred;
+                squares = std::fma(centred, centred, squares);
+            }
+            means[head * 128 + index] = mean;
+            variances[head * 128 + index] = squares / blocks;
+        }
+    }
+#pragma omp parallel
+    {
+        std::vector<float> scores(blocks);
+        std::vector<uint8_t> routed(blocks);
+#pragma omp for collapse(2)
+        for (int head = 0; head < heads; head++) {
+            for (int query_block = 0; query_block < blocks; query_block++) {
+                const size_t row = static_cast<size_t>(head) * blocks + query_block;
+                const float *centroid = mean_query.data() + row * 128;
+                float warps[4];
+                for (int warp = 0; warp < 4; warp++) {
+                    float lanes[32];
+                    for (int lane = 0; lane < 32; lane++) {
+                        const int index = warp * 32 + lane;
+                        lanes[lane] = (centroid[index] * centroid[index]) *
+                                      variances[head * 128 + index];
+                    }
+                    for (int offset = 16; offset > 0; offset /= 2) {
+                        float next[32];
+                        for (int lane = 0; lane < 32; lane++) {
+                            next[lane] = lanes[lane] + lanes[lane ^ offset];
+                        }
+                        std::memcpy(lanes, next, sizeof(next));
+                    }
+                    warps[warp] = lanes[0];
+                }
+                const float spread = ((warps[0] + warps[1]) + warps[2]) + warps[3];
+                const float threshold =
+                    tau * std::sqrt(std::fma(spread * log2_scale, log2_scale, 1e-6f));
+                int count = 0;
+                float maximum = -std::numeric_limits<float>::max();
+                for (int key_block = 0; key_block < blocks; key_block++) {
+                    scores[key_block] = oracle_vsa_score(
+                        centroid,
+                        mean_key.data() + (static_cast<size_t>(head) * blocks + key_block) * 128,
+                        log2_scale);
+                    routed[key_block] = scores[key_block] > threshold ||
+                                        std::abs(query_block - key_block) <= 1 ||
+                                        (key_block >= sinks[0] && key_block < sinks[1]) ||
+                                        (query_block >= sinks[2] && query_block < sinks[3]);
+                    if (routed[key_block]) {
+                        if (routes != nullptr) {
+                            routes[row * blocks + count] = static_cast<uint16_t>(key_block);
+                        }
+                        count++;
+                    } else {
+                        maximum = std::max(maximum, scores[key_block]);
+                    }
+                }
+                if (route_counts != nullptr) {
+                    route_counts[row] = count;
+                }
+                float total = 0.0f;
+                float weighted[128] = {};
+                for (int key_block = 0; key_block < blocks; key_block++) {
+                    if (routed[key_block]) {
+                        continue;
+                    }
+                    const float weight = std::exp2(scores[key_block] - maximum);
+                    total = std::fma(weight, static_cast<float>(lengths[key_block]), total);
+                    const float *block_sums =
+                        sums.data() + (static_cast<size_t>(head) * blocks + key_block) * 128;
+                    for (int index = 0; index < 128; index++) {
+                        weighted[index] = std::fma(weight, block_sums[index], weighted[index]);
+                    }
+                }
+                if (tail_max != nullptr) {
+                    tail_max[row] = maximum;
+                }
+                if (tail_sum != nullptr) {
+                    tail_sum[row] = total;
+                }
+                if (tail_values != nullptr) {
+                    std::memcpy(tail_values + row * 128, weighted, sizeof(weighted));
+                }
+            }
+        }
+    }
+    if (row_offsets != nullptr) {
+#pragma omp parallel for collapse(2)
+        for (int head = 0; head < heads; head++) {
+            for (int token = 0; token < tokens; token++) {
+                const uint16_t *row = query + static_cast<int64_t>(token) * token_stride[0] +
+                                      static_cast<int64_t>(head) * head_stride[0];
+                float lanes[32];
+                for (int lane = 0; lane < 32; lane++) {
+                    float partial = 0.0f;
+                    for (int part = 0; part < 4; part++) {
+                        partial = std::fma(bf16_to_f32(row[lane + part * 32]),
+                                           means[head * 128 + lane + part * 32], partial);
+                    }
+                    lanes[lane] = partial;
+                }
+                for (int offset = 16; offset > 0; offset /= 2) {
+                    float next[32];
+                    for (int lane = 0; lane < 32; lane++) {
+                        next[lane] = lanes[lane] + lanes[lane ^ offset];
+                    }
+                    std::memcpy(lanes, next, sizeof(next));
+                }
+                row_offsets[static_cast<size_t>(head) * tokens + token] = lanes[0] * log2_scale;
+            }
+        }
+    }
+    auto copy = [](float *destination, const std::vector<float> &source) {
+        if (destination != nullptr) {
+            std::memcpy(destination, source.data(), source.size() * sizeof(float));
+        }
+    };
+    copy(centroids, mean_query);
+    copy(block_keys, mean_key);
+    copy(value_sums, sums);
+    copy(key_mean, means);
+    copy(key_variance, variances);
+}
+
+// Sol-Attn over [tokens, heads, dim] f32 query, key and value, computed densely in f64
+// (reference(), sparse.rs:103-234): block means of the queries and keys and block sums of the
+// values; the block keys centred by their mean, whose variance sets each query block's threshold;
+// a key block is exact when its pooled score clears the threshold, neighbours the query block, or
+// by the sinks; a row's softmax runs over the tokens of the exact blocks (keys centred by the same
+// mean) and one term per other block (pooled score, weight = block length, value = block sum).
+// Returns the fraction of (head, query block, key block) triples routed exactly.
+double oracle_sol_reference(const float *query, const float *key, const float *value, int tokens,
+                            int heads, int dim, float tau, float scale, const int32_t *sinks,
+                            float *output) {
+    const int blocks = (tokens + 63) / 64;
+    auto length = [&](int block) { return std::min(64, tokens - block * 64); };
+    auto at = [&](const float *tensor, int64_t token, int head, int index) {
+        return static_cast<double>(tensor[(token * heads + head) * dim + index]);
+    };
+    const double log2_scale = static_cast<double>(scale) * 1.4426950408889634074;
+    int64_t routed_total = 0;
+#pragma omp parallel for reduction(+ : routed_total)
+    for (int head = 0; head < heads; head++) {
+        auto pool = [&](const float *tensor, bool mean) {
+            std::vector<std::vector<double>> pooled(blocks, std::vector<double>(dim));
+            for (int block = 0; block < blocks; block++) {
+                for (int index = 0; index < dim; index++) {
+                    double sum = 0.0;
+                    for (int row = 0; row < length(block); row++) {
+                        sum += at(tensor, static_cast<int64_t>(block) * 64 + row, head, index);
+                    }
+                    pooled[block][index] = mean ? sum / length(block) : sum;
+                }
+            }
+            return pooled;
+        };
+        const auto centroids = pool(query, true);
+        auto block_keys = pool(key, true);
+        const auto value_sums = pool(value, false);
+        std::vector<double> key_mean(dim), key_variance(dim);
+        for (int index = 0; index < dim; index++) {
+            double sum = 0.0;
+            for (int block = 0; block < blocks; block++) {
+                sum += block_keys[block][index];
+            }
+            key_mean[index] = sum / blocks;
+        }
+        for (int index = 0; index < dim; index++) {
+            double squares = 0.0;
+            for (int block = 0; block < blocks; block++) {
+                block_keys[block][index] -= key_mean[index];
+                squares += block_keys[block][index] * block_keys[block][index];
+            }
+            key_variance[index] = squares / blocks;
+        }
+        std::vector<double> pooled(blocks), scores, weights;
+        std::vector<uint8_t> exact(blocks);
+        std::vector<const double *> rows;
+        std::vector<double> centred;
+        for (int query_block = 0; query_block < blocks; query_block++) {
+            const auto &centroid = centroids[query_block];
+            double spread = 0.0;
+            for (int index = 0; index < dim; index++) {
+                spread += centroid[index] * centroid[index] * key_variance[index];
+            }
+            const double threshold =
+                static_cast<double>(tau) * std::sqrt(spread * log2_scale * log2_scale + 1e-6);
+            for (int key_block = 0; key_block < blocks; key_block++) {
+                double dot = 0.0;
+                for (int index = 0; index < dim; index++) {
+                    dot += centroid[index] * block_keys[key_block][index];
+                }
+                pooled[key_block] = dot * log2_scale;
+                exact[key_block] = pooled[key_block] > threshold ||
+                                   std::abs(query_block - key_block) <= 1 ||
+                                   (key_block >= sinks[0] && key_block < sinks[1]) ||
+                                   (query_block >= sinks[2] && query_block < sinks[3]);
+                routed_total += exact[key_block];
+            }
+            for (int row = 0; row < length(query_block); row++) {
+                const int64_t token = static_cast<int64_t>(query_block) * 64 + row;
+                // One term per key token of an exact block, one per other block.
+                scores.clear();
+                weights.clear();
+                std::vector<std::pair<int, int64_t>> sources; // (1, token) or (0, block)
+                for (int key_block = 0; key_block < blocks; key_block++) {
+                    if (exact[key_block]) {
+                        for (int other = 0; other < length(key_block); other++) {
+                            const int64_t key_token = static_cast<int64_t>(key_block) * 64 + other;
+                            double dot = 0.0;
+                            for (int index = 0; index < dim; index++) {
+                                dot += at(query, token, head, index) *
+                                       (at(key, key_token, head, index) - key_mean[index]);
+                            }
+                            scores.push_back(dot * log2_scale);
+                            weights.push_back(1.0);
+                            sources.emplace_back(1, key_token);
+                        }
+                    } else {
+                        scores.push_back(pooled[key_block]);
+                        weights.push_back(length(key_block));
+                        sources.emplace_back(0, key_block);
+                    }
+                }
+                double maximum = std::numeric_limits<double>::lowest();
+                for (double score : scores) {
+                    maximum = std::max(maximum, score);
+                }
+                std::vector<double> numerator(dim, 0.0);
+                double denominator = 0.0;
+                for (size_t term = 0; term < scores.size(); term++) {
+                    const double probability = std::exp2(scores[term] - maximum);
+                    denominator += probability * weights[term];
+                    for (int index = 0; index < dim; index++) {
+                        const double term_value =
+                            sources[term].first ? at(value, sources[term].second, head, index)
+                                                : value_sums[sources[term].second][index];
+                        numerator[index] += probability * term_value;
+                    }
+                }
+                for (int index = 0; index < dim; index++) {
+                    output[(token * heads + head) * dim + index] =
+                        static_cast<float>(numerator[index] / denominator);
+                }
+            }
+        }
+    }
+    return static_cast<double>(routed_total) /
+           (static_cast<double>(heads) * blocks * static_cast<double>(blocks));
+}
+
+// ---------------------------------------------------------------------------------------------
 // Ulysses partitioning (crates/mmh3-core/src/shard.rs:168-188): contiguous cuts of `count` items
 // (tokens, in units of `alignment`, or heads) over `ranks`, the remainder going to the last rank.
 // Writes ranks + 1 boundaries.

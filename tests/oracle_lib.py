@@ -84,6 +84,12 @@ def load() -> ctypes.CDLL:
     library.oracle_vsa_reference.restype = None
     library.oracle_shard_even.argtypes = [c_int64, c_int, c_int64, c_void_p]
     library.oracle_shard_even.restype = None
+    library.oracle_sol_route.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                         c_int, c_float, c_float, c_void_p] + [c_void_p] * 11
+    library.oracle_sol_route.restype = None
+    library.oracle_sol_reference.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                             c_float, c_float, c_void_p, c_void_p]
+    library.oracle_sol_reference.restype = c_double
     return library
 
 
@@ -95,7 +101,7 @@ def load_reference():
 
     library = ctypes.CDLL(str(REFERENCE))
     for name, arguments in _lib.SIGNATURES.items():
-        if name.startswith("mmh3_b200_") or name == "mmh3_sparse_attention":
+        if name.startswith("mmh3_b200_"):
             continue
         function = getattr(library, name)
         function.argtypes = arguments
@@ -134,3 +140,49 @@ def attention_bf16(library, qkv_bits: np.ndarray, tokens: int, heads: int, scale
         tokens, ptr(token_stride), ptr(head_stride), 1, scale, query_begin, query_end, head_begin,
         head_end, threads)
     return output
+
+
+def sol_route(library, qkv_bits: np.ndarray, tokens: int, heads: int, tau: float, scale: float,
+              sinks=(0, 0, 0, 0)) -> dict:
+    """Sol-Attn's routing workspace in FP32 kernel order from BF16 qkv [tokens, 3, heads, 128]
+    (bit patterns): a dict of the workspace's arrays, shaped."""
+    inner = heads * 128
+    blocks = -(-tokens // 64)
+    flat = np.ascontiguousarray(qkv_bits.reshape(-1))
+    token_stride = np.array([3 * inner] * 3, dtype=np.int64)
+    head_stride = np.array([128] * 3, dtype=np.int64)
+    sink_array = np.array(sinks, dtype=np.int32)
+    result = {
+        "centroids": np.empty((heads, blocks, 128), dtype=np.float32),
+        "block_keys": np.empty((heads, blocks, 128), dtype=np.float32),
+        "value_sums": np.empty((heads, blocks, 128), dtype=np.float32),
+        "key_mean": np.empty((heads, 128), dtype=np.float32),
+        "key_variance": np.empty((heads, 128), dtype=np.float32),
+        "row_offsets": np.empty((heads, tokens), dtype=np.float32),
+        "routes": np.zeros((heads, blocks, blocks), dtype=np.uint16),
+        "route_counts": np.empty((heads, blocks), dtype=np.int32),
+        "tail_max": np.empty((heads, blocks), dtype=np.float32),
+        "tail_sum": np.empty((heads, blocks), dtype=np.float32),
+        "tail_values": np.empty((heads, blocks, 128), dtype=np.float32),
+    }
+    base = flat.ctypes.data
+    library.oracle_sol_route(
+        c_void_p(base), c_void_p(base + 2 * inner), c_void_p(base + 4 * inner),
+        ptr(token_stride), ptr(head_stride), tokens, heads, tau, scale, ptr(sink_array),
+        *(ptr(result[name]) for name in (
+            "centroids", "block_keys", "value_sums", "key_mean", "key_variance", "row_offsets",
+            "routes", "route_counts", "tail_max", "tail_sum", "tail_values")))
+    return result
+
+
+def sol_reference(library, query: np.ndarray, key: np.ndarray, value: np.ndarray, tau: float,
+                  scale: float, sinks=(0, 0, 0, 0)):
+    """f64 Sol-Attn on f32 [tokens, heads, dim] operands: (output f32, routed fraction)."""
+    tokens, heads, dim = query.shape
+    output = np.empty((tokens, heads, dim), dtype=np.float32)
+    sink_array = np.array(sinks, dtype=np.int32)
+    operands = [np.ascontiguousarray(operand, dtype=np.float32) for operand in (query, key, value)]
+    fraction = library.oracle_sol_reference(
+        ptr(operands[0]), ptr(operands[1]), ptr(operands[2]), tokens, heads, dim, tau, scale,
+        ptr(sink_array), ptr(output))
+    return output, fraction

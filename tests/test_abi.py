@@ -83,9 +83,13 @@ def test_bad_arguments_are_rejected_before_any_launch():
     assert library.mmh3_attention_inputs(None, None, None, None, 0, 8, 1, 1e-6, None, None, None,
                                          None, 0, None, None) == invalid
     assert library.mmh3_dit_shard_pack(None, None, 8, 3, 4, 100, 0, 2, None) == invalid
+    # no workspace, no tokens
     assert library.mmh3_sparse_attention(None, None, None, None, 8, 1, ctypes.byref(layout), 0.1,
-                                         0.5, 0, 0, 0, 0, None, None, 0,
-                                         None) == _lib.CUDA_ERROR_NOT_SUPPORTED
+                                         0.5, 0, 0, 0, 0, None, None, 0, None) == invalid
+    sol = _lib.SparseWorkspace()
+    assert library.mmh3_sparse_attention(None, None, None, None, 0, 1, ctypes.byref(layout), 0.1,
+                                         0.5, 0, 0, 0, 0, ctypes.byref(sol), None, 0,
+                                         None) == invalid
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

@@ -1,0 +1,188 @@
+"""Parity of Sol-Attn on a B200, through the C ABI.
+
+Mirrors crates/mmh3-cuda/tests/sparse_attention.rs (per-block random directions so that routing is
+selective, tau 0.5 with sinks and tau 1.3, routed fraction within 0.01 of the f64 reference and
+between 0.1 and 0.9, relative L2 < 0.01 and max error < 0.05) and adds what the drop-in must hold
+bit for bit: the block statistics, the centred keys, their mean and variance, the routes and the
+route counts, against both the CPU oracle and the reference's own kernels.
+"""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib
+from mmh3_b200 import attention, synthetic
+from mmh3_b200.attention import SparseSinks
+
+pytestmark = pytest.mark.gpu
+
+SCALE = synthetic.softmax_scale()
+
+
+def make_case(oracle, tokens, heads):
+    """Every block of keys and queries shares a random direction (sparse_attention.rs:26-43)."""
+    inner = heads * 128
+    blocks = -(-tokens // 64)
+    directions, state = oracle_lib.lcg(oracle, tokens, blocks * 3 * inner, -1.0, 1.0)
+    noise, state = oracle_lib.lcg(oracle, state, tokens * 3 * inner, -1.0, 1.0)
+    block_of = np.arange(tokens) // 64
+    qkv = directions.reshape(blocks, 3 * inner)[block_of] + noise.reshape(tokens, 3 * inner)
+    return synthetic.to_bf16_bits(qkv.reshape(-1)).reshape(tokens, 3, heads, 128)
+
+
+def flat_sinks(sinks):
+    return (*sinks.key_blocks, *sinks.query_blocks)
+
+
+def assert_routes_equal(routes_a, counts_a, routes_b, counts_b):
+    assert np.array_equal(counts_a, counts_b)
+    heads, blocks = counts_a.shape
+    for head in range(heads):
+        for block in range(blocks):
+            count = counts_a[head, block]
+            assert np.array_equal(routes_a[head, block, :count], routes_b[head, block, :count]), (
+                head, block)
+
+
+def bits_equal(tensor, array):
+    return np.array_equal(tensor.cpu().numpy().view(np.uint32),
+                          np.ascontiguousarray(array).reshape(-1).view(np.uint32))
+
+
+CASES = [
+    (1000, 2, 0.5, SparseSinks((0, 2), (1, 2))),
+    (777, 3, 1.3, SparseSinks((0, 1), (0, 0))),
+]
+
+
+@pytest.mark.parametrize("tokens,heads,tau,sinks", CASES)
+def test_matches_the_reference(oracle, reference_kernels, tokens, heads, tau, sinks):
+    bits = make_case(oracle, tokens, heads)
+    inner = heads * 128
+    qkv = synthetic.bf16_tensor(bits, "cuda")
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    workspace = attention.SparseWorkspace(tokens, heads)
+    layout = attention.qkv_layout(heads)
+    attention.sparse(qkv, output, layout, SCALE, tau, sinks, workspace)
+    assert attention.take_status() == 0
+
+    # Routing against the CPU restatement of the kernels' FP32 order: bit for bit where a route
+    # depends on it, close where only the output does.
+    work = oracle_lib.sol_route(oracle, bits, tokens, heads, tau, SCALE, flat_sinks(sinks))
+    for name in ("centroids", "block_keys", "value_sums", "key_mean", "key_variance"):
+        assert bits_equal(getattr(workspace, name), work[name]), name
+    routes, counts = workspace.routes_host()
+    assert_routes_equal(routes, counts, work["routes"], work["route_counts"])
+    assert bits_equal(workspace.tail_max, work["tail_max"])
+    for name in ("tail_sum", "tail_values", "row_offsets"):
+        ours = getattr(workspace, name).cpu().numpy().reshape(work[name].shape)
+        assert np.allclose(ours, work[name], rtol=1e-4, atol=1e-5), name
+
+    # The reference's kernels on the same device buffers.
+    theirs = attention.SparseWorkspace(tokens, heads)
+    reference_output = torch.zeros_like(output)
+    raw = theirs.raw()
+    base = qkv.data_ptr()
+    assert reference_kernels.mmh3_sparse_attention(
+        base, base + 2 * inner, base + 4 * inner, reference_output.data_ptr(), tokens, heads,
+        ctypes.byref(layout), SCALE, tau, *flat_sinks(sinks), ctypes.byref(raw), None, 0,
+        None) == 0
+    torch.cuda.synchronize()
+    assert_routes_equal(routes, counts, *theirs.routes_host())
+    for name in ("centroids", "block_keys", "value_sums", "key_mean", "key_variance", "tail_max"):
+        assert torch.equal(getattr(workspace, name), getattr(theirs, name)), name
+    assert torch.allclose(workspace.tail_sum, theirs.tail_sum, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(workspace.tail_values, theirs.tail_values, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(workspace.row_offsets, theirs.row_offsets, rtol=1e-5, atol=1e-6)
+
+    # Outputs: the f64 reference with the reference test's bounds, then the reference's kernel.
+    values = synthetic.bf16_bits_to_f32(bits)
+    expected, expected_fraction = oracle_lib.sol_reference(
+        oracle, values[:, 0], values[:, 1], values[:, 2], tau, SCALE, flat_sinks(sinks))
+    fraction = workspace.routed_fraction()
+    assert abs(fraction - expected_fraction) < 0.01
+    assert 0.1 < fraction < 0.9
+    actual = output.float().cpu().numpy()
+    difference = np.linalg.norm((actual - expected).astype(np.float64))
+    norm = np.linalg.norm(expected.astype(np.float64))
+    assert difference / norm < 0.01
+    assert np.max(np.abs(actual - expected)) < 0.05
+    other = reference_output.float().cpu().numpy()
+    assert np.max(np.abs(actual - other)) < 2e-2
+    cosine = np.sum(actual.astype(np.float64) * other) / (
+        np.linalg.norm(actual.astype(np.float64)) * np.linalg.norm(other.astype(np.float64)))
+    assert cosine >= 0.9995
+
+
+def test_routing_everything_is_dense_attention():
+    """With a threshold no score fails, every block is exact, the tails are empty, and the result
+    is the dense kernel's (sparse.rs:240-277 on the GPU)."""
+    tokens, heads = 64 * 5 + 17, 2
+    qkv = synthetic.dense_qkv(tokens, heads, seed=5).cuda()
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    dense = torch.zeros_like(output)
+    workspace = attention.SparseWorkspace(tokens, heads)
+    attention.sparse(qkv, output, attention.qkv_layout(heads), SCALE, -1e30, SparseSinks(),
+                     workspace)
+    attention.dense_bf16(qkv, dense, tokens, heads, SCALE)
+    assert attention.take_status() == 0
+    assert workspace.routed_fraction() == 1.0
+    assert (workspace.tail_sum == 0).all()
+    assert torch.max(torch.abs(output.float() - dense.float())).item() < 2e-2
+
+
+def test_block_statistics_from_the_input_pass(oracle):
+    """attention_inputs.rs:126-222: the fused input pass fills the block statistics, and Sol-Attn
+    over prepared inputs routes exactly as it does from the normalized rows themselves."""
+    from test_inputs_gpu import make_inputs, norm_for
+
+    tokens, heads, tau = 600, 2, 0.5
+    sinks = SparseSinks((0, 1), (0, 0))
+    bits, query_weight, key_weight, angles = make_inputs(oracle, tokens, heads)
+    norm = norm_for(query_weight, key_weight, angles)
+    layout = attention.qkv_layout(heads)
+
+    prepared_qkv = synthetic.bf16_tensor(bits, "cuda")
+    prepared = attention.SparseWorkspace(tokens, heads)
+    prepared_output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    attention.prepare_inputs(prepared_qkv, norm, tokens, heads, sol=prepared)
+    attention.sparse(prepared_qkv, prepared_output, layout, SCALE, tau, sinks, prepared,
+                     attention.AttentionInputs.PREPARED)
+
+    raw_qkv = synthetic.bf16_tensor(bits, "cuda")
+    attention.qk_norm_rope(raw_qkv, norm, tokens, heads)
+    raw = attention.SparseWorkspace(tokens, heads)
+    raw_output = torch.zeros_like(prepared_output)
+    attention.sparse(raw_qkv, raw_output, layout, SCALE, tau, sinks, raw)
+    assert attention.take_status() == 0
+
+    assert torch.equal(prepared_qkv, raw_qkv)
+    assert_routes_equal(*prepared.routes_host(), *raw.routes_host())
+    assert torch.equal(prepared_output, raw_output)
+
+
+def test_rejects_what_it_does_not_compute():
+    tokens, heads = 128, 1
+    qkv = synthetic.dense_qkv(tokens, heads, seed=1).cuda()
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    workspace = attention.SparseWorkspace(tokens, heads)
+    layout = attention.qkv_layout(heads)
+    with pytest.raises(attention.CudaError) as raised:
+        attention.sparse(qkv, output, layout, -1.0, 0.5, SparseSinks(), workspace)
+    assert raised.value.code == 1  # cudaErrorInvalidValue
+    from mmh3_b200 import _lib
+
+    raw = workspace.raw()
+    quantized = attention.QuantizedWorkspace(tokens, heads).raw()
+    base = qkv.data_ptr()
+    code = _lib.library().mmh3_sparse_attention(
+        base, base + 256, base + 512, output.data_ptr(), tokens, heads, ctypes.byref(layout),
+        SCALE, 0.5, 0, 0, 0, 0, ctypes.byref(raw), ctypes.byref(quantized), 0, None)
+    assert code == 801  # the INT8/FP8 token attention over Sol-Attn's routes is not built
+    code = _lib.library().mmh3_sparse_attention(
+        base, base + 256, base + 512, output.data_ptr(), 0, heads, ctypes.byref(layout), SCALE,
+        0.5, 0, 0, 0, 0, ctypes.byref(raw), None, 0, None)
+    assert code == 1
