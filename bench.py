@@ -389,7 +389,45 @@ def run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, a
                                     args.vsa_frames)
         except attention.CudaError as error:
             extras["vsa_error"] = str(error)
+    if not args.skip_sol:
+        try:
+            extras["sol"] = run_sol(torch, attention, qkv, output, tokens, heads, scale, steps)
+        except attention.CudaError as error:
+            extras["sol_error"] = str(error)
     return extras
+
+
+def run_sol(torch, attention, qkv, output, tokens, heads, scale, steps) -> dict:
+    """Sol-Attn on the dense workload's q, k, v at the reference's default threshold (tau = 1.3),
+    with the first 512 tokens (8 blocks) as the always-exact conditioning prefix."""
+    workspace = attention.SparseWorkspace(tokens, heads)
+    layout = attention.qkv_layout(heads)
+    sinks = attention.SparseSinks((0, 8), (0, 0))
+
+    def whole():
+        attention.sparse(qkv, output, layout, scale, 1.3, sinks, workspace)
+
+    whole()
+    ms = time_region(torch, whole, steps)
+    blocks = workspace.blocks
+    lengths = torch.full((blocks,), 64.0, dtype=torch.float64, device="cuda")
+    lengths[-1] = tokens - (blocks - 1) * 64
+    counts = workspace.route_counts.view(heads, blocks).to(torch.int64)
+    routes = workspace.routes.view(heads, blocks, blocks)
+    routed_keys = torch.zeros((heads, blocks), dtype=torch.float64, device="cuda")
+    for head in range(heads):
+        mask = torch.arange(blocks, device="cuda")[None, :] < counts[head][:, None]
+        entries = ((routes[head].to(torch.int64) & 0xFFFF) * mask).clamp_(0, blocks - 1)
+        routed_keys[head] = (lengths[entries] * mask).sum(dim=1)
+    sparse_flops = float((routed_keys * lengths[None, :]).sum().item()) * 4.0 * HEAD_DIM
+    return {
+        "workload": f"Sol-Attn L={tokens}, H={heads}, tau 1.3, 8 prefix blocks exact",
+        "ms": ms, "sparse_flops": sparse_flops, "sparse_tflops": sparse_flops / ms / 1e9,
+        "dense_equivalent_tflops": attention_flops(tokens, heads) / ms / 1e9,
+        "kernel_ms": kernel_times(torch, whole),
+        "routed_fraction": workspace.routed_fraction(),
+        "kernel_status": attention.take_status(),
+    }
 
 
 def kernel_times(torch, fn) -> dict:
@@ -559,6 +597,7 @@ def main() -> None:
                         help="a reduced sequence length for profiler captures (N = 1 only)")
     parser.add_argument("--heads", type=int, default=0,
                         help="a reduced head count for profiler captures (N = 1 only)")
+    parser.add_argument("--skip-sol", action="store_true", help="leave Sol-Attn out")
     parser.add_argument("--skip-quantized", action="store_true",
                         help="leave the fused quantize pass and the INT8/FP8 kernel out")
     parser.add_argument("--skip-vsa", action="store_true",
