@@ -120,7 +120,8 @@ int mmh3_attention_inputs(void *qkv, const void *query_weight, const void *key_w
 
 /* INT8 QK^T and FP8 PV attention with FP32 softmax and BF16 output. inputs_ready: 0 computes the
  * workspace from BF16 q, k, v; 1 finds INT8 q, k, their scales and the |v| block maxima there;
- * 2 also the FP8 V and its scales. A non-null `sparse` (Sol-Attn) returns cudaErrorNotSupported.
+ * 2 also the FP8 V and its scales. With a non-null `sparse` the attention runs over the routes and
+ * pooled tails a call of mmh3_sparse_attention left there (Sol-Attn).
  * Replaces crates/mmh3-cuda/kernels/quantized_attention.cu:575-611. */
 int mmh3_attention_quantized(const void *query, const void *key, const void *value, void *output,
                              int tokens, int heads, const Mmh3AttentionLayout *layout, float scale,
@@ -154,7 +155,8 @@ int mmh3_vsa_attention_quantized(const void *value, const void *gate, int64_t ga
  * [sink_key_start, sink_key_end), every block for the query sinks) token by token and the rest
  * through one pooled term each. inputs_ready != 0: the workspace already holds the block statistics
  * (mmh3_attention_inputs). The routes are bit-identical to the reference's. A non-null `quantized`
- * (INT8/FP8 token attention over the routes) returns cudaErrorNotSupported.
+ * runs the token attention over the routes in INT8/FP8, with inputs_ready as for
+ * mmh3_attention_quantized.
  * Replaces crates/mmh3-cuda/kernels/sparse_attention.cu:546-586. */
 int mmh3_sparse_attention(const void *query, const void *key, const void *value, void *output,
                           int tokens, int heads, const Mmh3AttentionLayout *layout, float scale,

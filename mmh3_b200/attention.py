@@ -296,6 +296,8 @@ def prepare_inputs(qkv: torch.Tensor, norm: HeadNorm, tokens: int, heads: int,
     norm.check(qkv, tokens, heads)
     if vsa is not None and vsa.quantized is not None:
         quantized = vsa.quantized
+    if sol is not None and sol.quantized is not None:
+        quantized = sol.quantized
     sparse = vsa.sparse_raw() if vsa is not None else (sol.raw() if sol is not None else None)
     raw = quantized.raw() if quantized is not None else None
     check(
@@ -348,8 +350,6 @@ def vsa(qkv: torch.Tensor, gate: torch.Tensor | None, output: torch.Tensor,
 # -------------------------------------------------------------------------------------------------
 # Sol-Attn
 
-SPARSE_BLOCK = 64
-
 
 class SparseSinks:
     """Block ranges [start, end) that are always exact (mmh3-core/src/dit/sparse.rs:79-101):
@@ -376,13 +376,15 @@ class SparseSinks:
 
 class SparseWorkspace:
     """Scratch buffers of Sol-Attn for one sequence length and head count (attention.rs:818-908).
-    Only BF16 token attention is built: there is no quantized variant of this workspace."""
+    Routing and the pooled tail are BF16/FP32 either way; `quantized` adds the INT8/FP8 workspace
+    of the routed products (`SparseWorkspace::with_precision`)."""
 
-    def __init__(self, tokens: int, heads: int, device="cuda"):
+    def __init__(self, tokens: int, heads: int, quantized: bool = False, device="cuda"):
         blocks = -(-tokens // SPARSE_BLOCK)
         if not 0 < blocks <= 65535:
             raise ValueError(f"invalid block count {blocks}")
         self.tokens, self.heads, self.blocks = tokens, heads, blocks
+        self.quantized = QuantizedWorkspace(tokens, heads, device=device) if quantized else None
         per_block = heads * blocks * HEAD_DIM
         real = dict(dtype=torch.float32, device=device)
         self.centroids = torch.empty(per_block, **real)
@@ -433,12 +435,14 @@ def sparse(qkv: torch.Tensor, output: torch.Tensor, layout: _lib.AttentionLayout
         if last > buffer.numel():
             raise ValueError(f"operand {operand} reaches past its buffer")
     raw = workspace.raw()
+    quantized = workspace.quantized.raw() if workspace.quantized is not None else None
     check(
         _lib.library().mmh3_sparse_attention(
             _pointer(qkv, offsets[0]), _pointer(qkv, offsets[1]), _pointer(qkv, offsets[2]),
             _pointer(output, offsets[3]), tokens, heads, ctypes.byref(layout), scale, tau,
             sinks.key_blocks[0], sinks.key_blocks[1], sinks.query_blocks[0],
-            sinks.query_blocks[1], ctypes.byref(raw), None, int(inputs), _stream()),
+            sinks.query_blocks[1], ctypes.byref(raw),
+            ctypes.byref(quantized) if quantized is not None else None, int(inputs), _stream()),
         "mmh3_sparse_attention",
     )
 

@@ -93,13 +93,15 @@ extern "C" int mmh3_attention_quantized(const void *query, const void *key, cons
         inputs_ready > 2) {
         return INVALID_VALUE;
     }
-    if (sparse != nullptr) {
-        return NOT_SUPPORTED;
-    }
     const int prepared = launch_quantize(query, key, value, tokens, heads, *layout, *workspace,
                                          nullptr, nullptr, 0, inputs_ready, as_stream(stream));
     if (prepared != 0) {
         return prepared;
+    }
+    if (sparse != nullptr) {
+        // Sol-Attn: over the routes and tails a call of mmh3_sparse_attention left in `sparse`.
+        return launch_sol_token_attention_quantized(*workspace, output, tokens, heads, *layout,
+                                                    scale, *sparse, as_stream(stream));
     }
     return launch_quantized_attention(*workspace, output, tokens, heads, *layout, scale, nullptr,
                                       0, nullptr, 0, as_stream(stream));
@@ -177,13 +179,13 @@ extern "C" int mmh3_sparse_attention(const void *query, const void *key, const v
         value == nullptr || output == nullptr) {
         return INVALID_VALUE;
     }
-    if (quantized != nullptr) {
-        // The INT8/FP8 token attention over Sol-Attn's routes is not built.
-        return NOT_SUPPORTED;
+    if (quantized != nullptr && (layout->causal != 0 || layout->heads_per_key_value > 1 ||
+                                 inputs_ready < 0 || inputs_ready > 2)) {
+        return INVALID_VALUE;
     }
     return launch_sparse_attention(query, key, value, output, tokens, heads, *layout, scale, tau,
                                    sink_key_start, sink_key_end, sink_query_start, sink_query_end,
-                                   *workspace, inputs_ready, as_stream(stream));
+                                   *workspace, quantized, inputs_ready, as_stream(stream));
 }
 
 extern "C" int mmh3_dit_shard_pack(const void *source, void *packed, int tokens, int tensors,

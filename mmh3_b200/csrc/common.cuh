@@ -101,12 +101,15 @@ int launch_block_statistics(const void *query, const void *key, const void *valu
                             const Mmh3SparseWorkspace &workspace, cudaStream_t stream);
 
 // sol_attention.cu: Sol-Attn over BF16 q, k, v (block statistics unless inputs_ready, centring,
-// routing, row offsets, token attention merged with the pooled tails).
+// routing, row offsets, token attention merged with the pooled tails). With `quantized`, the token
+// attention runs in INT8/FP8 over that workspace, which inputs_ready = 0 fills, 1 completes with
+// the FP8 V, and 2 finds complete.
 int launch_sparse_attention(const void *query, const void *key, const void *value, void *output,
                             int tokens, int heads, const Mmh3AttentionLayout &layout, float scale,
                             float tau, int sink_key_start, int sink_key_end, int sink_query_start,
                             int sink_query_end, const Mmh3SparseWorkspace &workspace,
-                            int inputs_ready, cudaStream_t stream);
+                            const Mmh3QuantizedWorkspace *quantized, int inputs_ready,
+                            cudaStream_t stream);
 
 // vsa_select.cu
 int launch_select(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int prefix_tiles,
@@ -134,7 +137,14 @@ int launch_sol_token_attention(const void *query, const void *key, const void *v
 int launch_vsa_attention_quantized(const Mmh3QuantizedWorkspace &workspace, void *output,
                                    int tokens, int heads, const Mmh3AttentionLayout &layout,
                                    float scale, const Mmh3VsaWorkspace &vsa, int tiles,
-                                   const void *gate, int64_t gate_stride, cudaStream_t stream);
+                                   const void *gate, int64_t gate_stride, cudaStream_t stream,
+                                   const Mmh3SparseWorkspace *tails = nullptr);
+
+// The INT8/FP8 token attention over Sol-Attn's routes, merged with its pooled tails.
+int launch_sol_token_attention_quantized(const Mmh3QuantizedWorkspace &workspace, void *output,
+                                         int tokens, int heads, const Mmh3AttentionLayout &layout,
+                                         float scale, const Mmh3SparseWorkspace &sparse,
+                                         cudaStream_t stream);
 
 // shard.cu
 int launch_shard_pack(const void *source, void *packed, int tokens, int tensors, int heads, int dim,

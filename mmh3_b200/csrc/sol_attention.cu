@@ -13,7 +13,8 @@
 //    of the rest as an online-softmax state (maximum, weighted sum, weighted values);
 // 4. row_offsets: per token and head q . key mean, which moves a row's token-level scores into the
 //    centred units of the pooled ones;
-// 5. the token attention over the routes (vsa_attention.cu, tcgen05), merged with the tail.
+// 5. the token attention over the routes (vsa_attention.cu, tcgen05; BF16, or INT8/FP8 over a
+//    quantized workspace), merged with the tail.
 //
 // The routes are bit-identical to the reference's. That fixes the FP32 order of everything a route
 // depends on: the block sums run down the rows, the key mean and variance down the blocks, the
@@ -343,7 +344,8 @@ int launch_sparse_attention(const void *query, const void *key, const void *valu
                             int tokens, int heads, const Mmh3AttentionLayout &layout, float scale,
                             float tau, int sink_key_start, int sink_key_end, int sink_query_start,
                             int sink_query_end, const Mmh3SparseWorkspace &workspace,
-                            int inputs_ready, cudaStream_t stream) {
+                            const Mmh3QuantizedWorkspace *quantized, int inputs_ready,
+                            cudaStream_t stream) {
     if (!(scale > 0.0f) || !std::isfinite(scale)) {
         return INVALID_VALUE;
     }
@@ -373,6 +375,17 @@ int launch_sparse_attention(const void *query, const void *key, const void *valu
     const cudaError_t launched = cudaGetLastError();
     if (launched != cudaSuccess) {
         return static_cast<int>(launched);
+    }
+    if (quantized != nullptr) {
+        // As the reference does (sparse_attention.cu:577-580): the quantizer's passes that
+        // inputs_ready leaves to do, then the INT8/FP8 token attention.
+        const int prepared = launch_quantize(query, key, value, tokens, heads, layout, *quantized,
+                                             nullptr, nullptr, 0, inputs_ready, stream);
+        if (prepared != 0) {
+            return prepared;
+        }
+        return launch_sol_token_attention_quantized(*quantized, output, tokens, heads, layout,
+                                                    scale, workspace, stream);
     }
     return launch_sol_token_attention(query, key, value, output, tokens, heads, layout, scale,
                                       workspace, stream);

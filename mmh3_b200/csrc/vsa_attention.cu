@@ -493,10 +493,11 @@ __global__ void __launch_bounds__(THREADS, 2)
                 exists[half] && tile_row < tile_length(query_tiles[half]) && count > 0;
             const int64_t token = stored ? tile_start(query_tiles[half]) + tile_row : 0;
             const float sum = (sums[0].x + sums[0].y) + (sums[1].x + sums[1].y);
-            float inverse = 1.0f / sum;
+            float value_scale = 1.0f;
             if constexpr (QUANTIZED) {
-                inverse *= p.value_scales[head];
+                value_scale = p.value_scales[head];
             }
+            float inverse = value_scale / sum;
             // Sol-Attn: every key block the list leaves out contributes one pooled term; their
             // sum arrives as a softmax state (maximum, sum of weights, weighted values) in the
             // units of the centred scores, which this row's scores reach by its offset.
@@ -508,10 +509,13 @@ __global__ void __launch_bounds__(THREADS, 2)
                 const float tail_maximum = p.tail_max[route_rows[half]];
                 const float merged = fmaxf(centred, tail_maximum);
                 const float routed_weight = exp2f(centred - merged);
-                tail_weight = exp2f(tail_maximum - merged);
-                inverse = 1.0f / (sum * routed_weight + p.tail_sum[route_rows[half]] * tail_weight);
-                tail_weight *= inverse;
-                inverse *= routed_weight;
+                // E4M3 probabilities, and with them the sum and O, carry a factor of 224.
+                constexpr float CARRIED = QUANTIZED ? 224.0f : 1.0f;
+                tail_weight = CARRIED * exp2f(tail_maximum - merged);
+                const float total =
+                    1.0f / (sum * routed_weight + p.tail_sum[route_rows[half]] * tail_weight);
+                tail_weight *= total;
+                inverse = value_scale * routed_weight * total;
             }
             __nv_bfloat16 *output_row = p.output + token * p.output_token_stride +
                                         static_cast<int64_t>(head) * p.output_head_stride;
@@ -689,16 +693,36 @@ int launch_sol_token_attention(const void *query, const void *key, const void *v
     return launch<false>(maps, params, heads, stream);
 }
 
+int launch_sol_token_attention_quantized(const Mmh3QuantizedWorkspace &quantized, void *output,
+                                         int tokens, int heads, const Mmh3AttentionLayout &layout,
+                                         float scale, const Mmh3SparseWorkspace &sparse,
+                                         cudaStream_t stream) {
+    // Blocks of 64 tokens for tiles: the dense quantizer's blocks, scales and FP8 V layout.
+    Mmh3VsaWorkspace workspace = {};
+    workspace.routes = sparse.routes;
+    workspace.route_counts = sparse.route_counts;
+    return launch_vsa_attention_quantized(quantized, output, tokens, heads, layout, scale,
+                                          workspace, (tokens + TILE - 1) / TILE, nullptr, 0, stream,
+                                          &sparse);
+}
+
 int launch_vsa_attention_quantized(const Mmh3QuantizedWorkspace &quantized, void *output,
                                    int tokens, int heads, const Mmh3AttentionLayout &layout,
                                    float scale, const Mmh3VsaWorkspace &workspace, int tiles,
-                                   const void *gate, int64_t gate_stride, cudaStream_t stream) {
+                                   const void *gate, int64_t gate_stride, cudaStream_t stream,
+                                   const Mmh3SparseWorkspace *tails) {
     if (!(scale > 0.0f) || !std::isfinite(scale)) {
         return INVALID_VALUE;
     }
     VsaParams params = {};
     if (!fill_params(params, output, tokens, layout, scale, workspace, tiles, gate, gate_stride)) {
         return static_cast<int>(cudaErrorInvalidDevice);
+    }
+    if (tails != nullptr) {
+        params.tail_max = tails->tail_max;
+        params.tail_sum = tails->tail_sum;
+        params.tail_values = tails->tail_values;
+        params.row_offsets = tails->row_offsets;
     }
     params.query_scales = quantized.query_scales;
     params.key_scales = quantized.key_scales;

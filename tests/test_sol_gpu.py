@@ -58,13 +58,15 @@ CASES = [
 ]
 
 
+@pytest.mark.parametrize("quantized", [False, True])
 @pytest.mark.parametrize("tokens,heads,tau,sinks", CASES)
-def test_matches_the_reference(oracle, reference_kernels, tokens, heads, tau, sinks):
+def test_matches_the_reference(oracle, reference_kernels, tokens, heads, tau, sinks, quantized):
+    """sparse_attention.rs:170-215: both precisions against the same f64 reference and bounds."""
     bits = make_case(oracle, tokens, heads)
     inner = heads * 128
     qkv = synthetic.bf16_tensor(bits, "cuda")
     output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
-    workspace = attention.SparseWorkspace(tokens, heads)
+    workspace = attention.SparseWorkspace(tokens, heads, quantized=quantized)
     layout = attention.qkv_layout(heads)
     attention.sparse(qkv, output, layout, SCALE, tau, sinks, workspace)
     assert attention.take_status() == 0
@@ -82,14 +84,15 @@ def test_matches_the_reference(oracle, reference_kernels, tokens, heads, tau, si
         assert np.allclose(ours, work[name], rtol=1e-4, atol=1e-5), name
 
     # The reference's kernels on the same device buffers.
-    theirs = attention.SparseWorkspace(tokens, heads)
+    theirs = attention.SparseWorkspace(tokens, heads, quantized=quantized)
     reference_output = torch.zeros_like(output)
     raw = theirs.raw()
+    their_quantized = theirs.quantized.raw() if quantized else None
     base = qkv.data_ptr()
     assert reference_kernels.mmh3_sparse_attention(
         base, base + 2 * inner, base + 4 * inner, reference_output.data_ptr(), tokens, heads,
-        ctypes.byref(layout), SCALE, tau, *flat_sinks(sinks), ctypes.byref(raw), None, 0,
-        None) == 0
+        ctypes.byref(layout), SCALE, tau, *flat_sinks(sinks), ctypes.byref(raw),
+        ctypes.byref(their_quantized) if quantized else None, 0, None) == 0
     torch.cuda.synchronize()
     assert_routes_equal(routes, counts, *theirs.routes_host())
     for name in ("centroids", "block_keys", "value_sums", "key_mean", "key_variance", "tail_max"):
@@ -97,6 +100,11 @@ def test_matches_the_reference(oracle, reference_kernels, tokens, heads, tau, si
     assert torch.allclose(workspace.tail_sum, theirs.tail_sum, rtol=1e-4, atol=1e-5)
     assert torch.allclose(workspace.tail_values, theirs.tail_values, rtol=1e-4, atol=1e-4)
     assert torch.allclose(workspace.row_offsets, theirs.row_offsets, rtol=1e-5, atol=1e-6)
+    if quantized:
+        # The quantizer's outputs are the dense path's: INT8 q, k, FP8 V and scales bit for bit.
+        for name in ("query", "key", "value", "query_scales", "key_scales", "value_scales"):
+            assert torch.equal(getattr(workspace.quantized, name),
+                               getattr(theirs.quantized, name)), name
 
     # Outputs: the f64 reference with the reference test's bounds, then the reference's kernel.
     values = synthetic.bf16_bits_to_f32(bits)
@@ -176,12 +184,7 @@ def test_rejects_what_it_does_not_compute():
     from mmh3_b200 import _lib
 
     raw = workspace.raw()
-    quantized = attention.QuantizedWorkspace(tokens, heads).raw()
     base = qkv.data_ptr()
-    code = _lib.library().mmh3_sparse_attention(
-        base, base + 256, base + 512, output.data_ptr(), tokens, heads, ctypes.byref(layout),
-        SCALE, 0.5, 0, 0, 0, 0, ctypes.byref(raw), ctypes.byref(quantized), 0, None)
-    assert code == 801  # the INT8/FP8 token attention over Sol-Attn's routes is not built
     code = _lib.library().mmh3_sparse_attention(
         base, base + 256, base + 512, output.data_ptr(), 0, heads, ctypes.byref(layout), SCALE,
         0.5, 0, 0, 0, 0, ctypes.byref(raw), None, 0, None)
