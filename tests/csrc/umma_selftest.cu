@@ -203,3 +203,46 @@ extern "C" int mmh3_b200_umma_selftest(int mode, const void *a, const void *b, c
     };
     return mode == 0 ? run(selftest_kernel<0>) : run(selftest_kernel<1>);
 }
+
+namespace {
+
+// Every thread waits for a phase of a barrier that nothing completes: the bounded wait gives up
+// after about a second, records `code` in the status word, raises the CTA's abort flag, and the
+// kernel returns; the context stays usable.
+__global__ void expired_wait_kernel(unsigned int *status, unsigned int code, int *gave_up) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        sm100::mbar_init(sm100::smem_u32(&bar), 1);
+        abort_flag = 0;
+        sm100::fence_barrier_init();
+    }
+    __syncthreads();
+    const sm100::Watchdog watchdog = {&abort_flag, status};
+    const bool completed = sm100::mbar_wait(sm100::smem_u32(&bar), 0, watchdog, code);
+    if (!completed) {
+        atomicAdd(gave_up, 1);
+    }
+}
+
+} // namespace
+
+// Launches the kernel above with 64 threads and returns how many of them gave up their wait (after
+// synchronizing), or a negative cudaError_t. The status word afterwards holds `code`.
+extern "C" int mmh3_b200_expired_wait_selftest(unsigned int code) {
+    unsigned int *status = mmh3::status_pointer();
+    if (status == nullptr) {
+        return -static_cast<int>(cudaErrorInvalidDevice);
+    }
+    int *gave_up = nullptr;
+    cudaError_t error = cudaMalloc(&gave_up, sizeof(int));
+    if (error != cudaSuccess) {
+        return -static_cast<int>(error);
+    }
+    cudaMemset(gave_up, 0, sizeof(int));
+    expired_wait_kernel<<<1, 64>>>(status, code, gave_up);
+    int count = 0;
+    error = cudaMemcpy(&count, gave_up, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaFree(gave_up);
+    return error == cudaSuccess ? count : -static_cast<int>(error);
+}

@@ -44,6 +44,26 @@ def load_selftest():
     return library
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_context_survives():
+    """Failure detection without a fault: every wait in the kernels is bounded; one that runs out
+    (here: on a barrier nothing completes) leaves its code in the status word, the kernel returns,
+    take_status reads and clears the word, and the next launch on the same context works."""
+    library = load_selftest()
+    library.mmh3_b200_expired_wait_selftest.argtypes = [ctypes.c_uint]
+    library.mmh3_b200_expired_wait_selftest.restype = ctypes.c_int
+    library.mmh3_b200_take_status.restype = ctypes.c_int
+    code = 0x00770001
+    assert library.mmh3_b200_take_status() == 0
+    assert library.mmh3_b200_expired_wait_selftest(code) == 64  # every thread gave up
+    assert library.mmh3_b200_take_status() == code
+    assert library.mmh3_b200_take_status() == 0
+    test_umma_bf16_building_blocks()
+    tokens, heads = 300, 2
+    bits = synthetic.dense_qkv(tokens, heads, seed=3).view(torch.int16).numpy().view(np.uint16)
+    run_dense(bits, tokens, heads)
+    assert attention.take_status() == 0
+
+
 def test_umma_bf16_building_blocks():
     """scores = A.B^T from shared memory and output = P.V with P in tensor memory, BF16."""
     library = load_selftest()
