@@ -78,8 +78,9 @@ typedef struct Mmh3VsaWorkspace {
 } Mmh3VsaWorkspace;
 
 /* Dense softmax(Q K^T * scale) V. element_type 0 is BF16 and 1 is FP16; head_dim 64 or 128.
- * Implemented here: BF16, head_dim 128, not causal; grouped key/value heads and batches are.
- * Everything else returns cudaErrorNotSupported. `scale` must be positive.
+ * Implemented here: head_dim 128 in BF16 and FP16, causal or not, with grouped key/value heads and
+ * batches (the DiT's and the text encoder's uses). head_dim 64 returns cudaErrorNotSupported.
+ * `scale` must be positive.
  * Replaces crates/mmh3-cuda/kernels/attention.cu:531-536. */
 int mmh3_attention(int element_type, int head_dim, const void *query, const void *key,
                    const void *value, void *output, int tokens, int heads, int batch,

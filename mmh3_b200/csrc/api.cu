@@ -20,11 +20,12 @@ extern "C" int mmh3_attention_roped(int element_type, int head_dim, const void *
     if ((element_type != 0 && element_type != 1) || (head_dim != 64 && head_dim != 128)) {
         return INVALID_VALUE;
     }
-    if (element_type != 0 || head_dim != 128 || layout->causal != 0 || angles != nullptr) {
+    // Heads of 64 and the query's fused RMS norm and RoPE (the VAE decoder's use) are not built.
+    if (head_dim != 128 || angles != nullptr) {
         return NOT_SUPPORTED;
     }
     return launch_dense_bf16(query, key, value, output, tokens, heads, batch, *layout, scale,
-                             as_stream(stream));
+                             as_stream(stream), element_type == 1);
 }
 
 extern "C" int mmh3_attention(int element_type, int head_dim, const void *query, const void *key,

@@ -71,9 +71,10 @@ struct SharedMemoryOptIn {
 };
 
 // Launchers of the kernels, one per .cu file.
+// dense_bf16.cu: heads of 128, BF16 or FP16 (`half`), causal or not, grouped key/value heads.
 int launch_dense_bf16(const void *query, const void *key, const void *value, void *output,
                       int tokens, int heads, int batch, const Mmh3AttentionLayout &layout,
-                      float scale, cudaStream_t stream);
+                      float scale, cudaStream_t stream, bool half = false);
 
 
 // inputs.cu

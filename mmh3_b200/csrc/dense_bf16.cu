@@ -71,10 +71,24 @@ constexpr uint32_t TMEM_COLUMNS = 512;
 constexpr uint32_t TMEM_SCORES = 0;    // + tile * 128
 constexpr uint32_t TMEM_OUTPUT = 256;  // + tile * 128
 
-constexpr uint32_t SCORE_MMA = instruction_descriptor(ACCUMULATE_F32, FORMAT_BF16, FORMAT_BF16, 0,
-                                                      0, TILE_M, TILE_N);
-constexpr uint32_t OUTPUT_MMA = instruction_descriptor(ACCUMULATE_F32, FORMAT_BF16, FORMAT_BF16, 0,
-                                                       1, TILE_M, HEAD_DIM);
+// The 16-bit element of q, k, v, P and the output: BF16, or FP16 (`HALF`).
+template <bool HALF> struct Element {
+    static constexpr uint32_t FORMAT = HALF ? FORMAT_F16 : FORMAT_BF16;
+    static constexpr uint32_t SCORE_MMA =
+        instruction_descriptor(ACCUMULATE_F32, FORMAT, FORMAT, 0, 0, TILE_M, TILE_N);
+    static constexpr uint32_t OUTPUT_MMA =
+        instruction_descriptor(ACCUMULATE_F32, FORMAT, FORMAT, 0, 1, TILE_M, HEAD_DIM);
+    // Two FP32 values rounded to nearest even and packed, the first in the low half.
+    static __device__ __forceinline__ uint32_t pack(float low, float high) {
+        if constexpr (HALF) {
+            uint32_t packed;
+            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(high), "f"(low));
+            return packed;
+        } else {
+            return pack_bf16(low, high);
+        }
+    }
+};
 
 // The maximum may lag the true row maximum by this much (in log2 units) before O is rescaled.
 constexpr float RESCALE_THRESHOLD = 8.0f;
@@ -101,11 +115,14 @@ __device__ __forceinline__ uint64_t value_operand(uint32_t tile) {
 }
 __host__ __device__ constexpr uint32_t value_step(int step) { return step * 16 * 128; }
 
+template <bool HALF, bool CAUSAL>
 __global__ void __launch_bounds__(THREADS, 1)
-    dense_bf16_kernel(const __grid_constant__ DenseMaps maps, __nv_bfloat16 *__restrict__ output,
+    dense_bf16_kernel(const __grid_constant__ DenseMaps maps, uint16_t *__restrict__ output,
                       int tokens, int heads_per_key_value, int64_t output_token_stride,
                       int64_t output_head_stride, int vector_stores, float scale_log2,
                       unsigned int *status) {
+    constexpr uint32_t SCORE_MMA = Element<HALF>::SCORE_MMA;
+    constexpr uint32_t OUTPUT_MMA = Element<HALF>::OUTPUT_MMA;
     extern __shared__ uint8_t shared_memory[];
     const uint32_t base = (smem_u32(shared_memory) + 1023u) & ~1023u;
     uint8_t *aligned = shared_memory + (base - smem_u32(shared_memory));
@@ -124,7 +141,11 @@ __global__ void __launch_bounds__(THREADS, 1)
     const int lane = threadIdx.x % 32;
     const int head = blockIdx.y;
     const int first_query = blockIdx.x * (QUERY_TILES * TILE_M);
-    const int blocks = (tokens + TILE_N - 1) / TILE_N;
+    // A causal row sees the keys up to its own token: the CTA's two query tiles need the key
+    // blocks up to the second tile's diagonal one (the first tile finds its last block all masked).
+    const int blocks = CAUSAL ? min((tokens + TILE_N - 1) / TILE_N,
+                                    first_query / TILE_N + QUERY_TILES)
+                              : (tokens + TILE_N - 1) / TILE_N;
 
     if (threadIdx.x == 0) {
         mbar_init(barrier(QUERY_FULL), 1);
@@ -289,9 +310,13 @@ __global__ void __launch_bounds__(THREADS, 1)
             for (int index = 0; index < TILE_N; index++) {
                 s[index] = __uint_as_float(raw[index / 32][index % 32]);
             }
-            const int valid = tokens - block * TILE_N;
+            // Keys past the last token arrive as zeroes and are masked, and so are, for a causal
+            // row, the keys after its own token: `valid` keys of this block count for this row.
+            int valid = tokens - block * TILE_N;
+            if constexpr (CAUSAL) {
+                valid = min(valid, first_query + tile * TILE_M + row - block * TILE_N + 1);
+            }
             if (valid < TILE_N) {
-                // Keys past the last token arrive as zeroes and are masked.
                 #pragma unroll
                 for (int index = 0; index < TILE_N; index++) {
                     if (index >= valid) {
@@ -354,7 +379,7 @@ __global__ void __launch_bounds__(THREADS, 1)
                         probability = make_float2(exp2_approx(x.x), exp2_approx(x.y));
                     }
                     sums[pair % 2] = __fadd2_rn(sums[pair % 2], probability);
-                    packed[pair] = pack_bf16(probability.x, probability.y);
+                    packed[pair] = Element<HALF>::pack(probability.x, probability.y);
                 }
                 tmem_store_32(scores + chunk * 32, packed);
             }
@@ -370,9 +395,8 @@ __global__ void __launch_bounds__(THREADS, 1)
             tcgen05_fence_after();
             const float inverse = 1.0f / ((sums[0].x + sums[0].y) + (sums[1].x + sums[1].y));
             const int token = first_query + tile * TILE_M + row;
-            __nv_bfloat16 *output_row =
-                output + static_cast<int64_t>(token) * output_token_stride +
-                static_cast<int64_t>(head) * output_head_stride;
+            uint16_t *output_row = output + static_cast<int64_t>(token) * output_token_stride +
+                                   static_cast<int64_t>(head) * output_head_stride;
             #pragma unroll
             for (int chunk = 0; chunk < 4; chunk++) {
                 uint32_t values[32];
@@ -382,8 +406,9 @@ __global__ void __launch_bounds__(THREADS, 1)
                     uint32_t packed[16];
                     #pragma unroll
                     for (int pair = 0; pair < 16; pair++) {
-                        packed[pair] = pack_bf16(__uint_as_float(values[pair * 2]) * inverse,
-                                                 __uint_as_float(values[pair * 2 + 1]) * inverse);
+                        packed[pair] =
+                            Element<HALF>::pack(__uint_as_float(values[pair * 2]) * inverse,
+                                                __uint_as_float(values[pair * 2 + 1]) * inverse);
                     }
                     if (vector_stores) {
                         uint4 *destination = reinterpret_cast<uint4 *>(output_row + chunk * 32);
@@ -421,8 +446,8 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
 }
 
-bool encode_operand(CUtensorMap *map, const void *base, int tokens, int heads, int64_t token_stride,
-                    int64_t head_stride) {
+bool encode_operand(CUtensorMap *map, bool half, const void *base, int tokens, int heads,
+                    int64_t token_stride, int64_t head_stride) {
     const uint64_t dimensions[3] = {static_cast<uint64_t>(HEAD_DIM), static_cast<uint64_t>(tokens),
                                     static_cast<uint64_t>(heads)};
     uint64_t strides[2] = {static_cast<uint64_t>(token_stride) * 2,
@@ -432,15 +457,16 @@ bool encode_operand(CUtensorMap *map, const void *base, int tokens, int heads, i
         strides[1] = strides[0] * static_cast<uint64_t>(tokens);
     }
     const uint32_t box[3] = {64, TILE_M, 1};
-    return encode_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dimensions, strides,
-                             box);
+    return encode_tensor_map(
+        map, half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base,
+        dimensions, strides, box);
 }
 
 } // namespace
 
 int launch_dense_bf16(const void *query, const void *key, const void *value, void *output,
                       int tokens, int heads, int batch, const Mmh3AttentionLayout &layout,
-                      float scale, cudaStream_t stream) {
+                      float scale, cudaStream_t stream, bool half) {
     const int group = layout.heads_per_key_value > 0 ? layout.heads_per_key_value : 1;
     if (!(scale > 0.0f) || !std::isfinite(scale)) {
         return INVALID_VALUE;
@@ -454,26 +480,31 @@ int launch_dense_bf16(const void *query, const void *key, const void *value, voi
     if (status == nullptr) {
         return static_cast<int>(cudaErrorInvalidDevice);
     }
-    static SharedMemoryOptIn shared_memory;
-    const cudaError_t configured = shared_memory.ensure(dense_bf16_kernel, SMEM_BYTES);
+    const bool causal = layout.causal != 0;
+    auto *kernel = half ? (causal ? dense_bf16_kernel<true, true> : dense_bf16_kernel<true, false>)
+                        : (causal ? dense_bf16_kernel<false, true> : dense_bf16_kernel<false, false>);
+    static SharedMemoryOptIn shared_memory[4];
+    const cudaError_t configured =
+        shared_memory[(half ? 2 : 0) + (causal ? 1 : 0)].ensure(kernel, SMEM_BYTES);
     if (configured != cudaSuccess) {
         return static_cast<int>(configured);
     }
-    const auto *q = static_cast<const __nv_bfloat16 *>(query);
-    const auto *k = static_cast<const __nv_bfloat16 *>(key);
-    const auto *v = static_cast<const __nv_bfloat16 *>(value);
-    auto *out = static_cast<__nv_bfloat16 *>(output);
+    // Both element types are 16 bits wide: the strides are in elements either way.
+    const auto *q = static_cast<const uint16_t *>(query);
+    const auto *k = static_cast<const uint16_t *>(key);
+    const auto *v = static_cast<const uint16_t *>(value);
+    auto *out = static_cast<uint16_t *>(output);
     for (int item = 0; item < batch; item++) {
-        const __nv_bfloat16 *batch_query = q + item * layout.batch_stride[QUERY];
-        const __nv_bfloat16 *batch_key = k + item * layout.batch_stride[KEY];
-        const __nv_bfloat16 *batch_value = v + item * layout.batch_stride[VALUE];
-        __nv_bfloat16 *batch_output = out + item * layout.batch_stride[OUTPUT];
+        const uint16_t *batch_query = q + item * layout.batch_stride[QUERY];
+        const uint16_t *batch_key = k + item * layout.batch_stride[KEY];
+        const uint16_t *batch_value = v + item * layout.batch_stride[VALUE];
+        uint16_t *batch_output = out + item * layout.batch_stride[OUTPUT];
         DenseMaps maps;
-        if (!encode_operand(&maps.query, batch_query, tokens, heads, layout.token_stride[QUERY],
-                            layout.head_stride[QUERY]) ||
-            !encode_operand(&maps.key, batch_key, tokens, heads / group, layout.token_stride[KEY],
-                            layout.head_stride[KEY]) ||
-            !encode_operand(&maps.value, batch_value, tokens, heads / group,
+        if (!encode_operand(&maps.query, half, batch_query, tokens, heads,
+                            layout.token_stride[QUERY], layout.head_stride[QUERY]) ||
+            !encode_operand(&maps.key, half, batch_key, tokens, heads / group,
+                            layout.token_stride[KEY], layout.head_stride[KEY]) ||
+            !encode_operand(&maps.value, half, batch_value, tokens, heads / group,
                             layout.token_stride[VALUE], layout.head_stride[VALUE])) {
             // TMA wants 16-byte aligned bases and strides.
             return NOT_SUPPORTED;
@@ -482,7 +513,7 @@ int launch_dense_bf16(const void *query, const void *key, const void *value, voi
                                   layout.token_stride[OUTPUT] % 8 == 0 &&
                                   layout.head_stride[OUTPUT] % 8 == 0;
         const dim3 grid((tokens + QUERY_TILES * TILE_M - 1) / (QUERY_TILES * TILE_M), heads);
-        dense_bf16_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(
+        kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(
             maps, batch_output, tokens, group, layout.token_stride[OUTPUT],
             layout.head_stride[OUTPUT], vector_stores, scale * LOG2_E, status);
         const cudaError_t launched = cudaGetLastError();

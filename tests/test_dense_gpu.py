@@ -186,6 +186,53 @@ def test_grouped_heads_and_batches(oracle):
     assert torch.max(torch.abs(output.cpu().double() - expected)) <= 2e-2
 
 
+def reference_attention(q, k, v, group, causal):
+    """softmax(q k^T * scale) v in float64 with torch, [batch, tokens, heads, 128] operands."""
+    keys = k.double().repeat_interleave(group, dim=2)
+    values = v.double().repeat_interleave(group, dim=2)
+    scores = torch.einsum("bqhd,bkhd->bhqk", q.double(), keys) * SCALE
+    if causal:
+        tokens = q.shape[1]
+        future = torch.triu(torch.ones((tokens, tokens), dtype=torch.bool), diagonal=1)
+        scores = scores.masked_fill(future, float("-inf"))
+    return torch.einsum("bhqk,bkhd->bqhd", scores.softmax(-1), values)
+
+
+@pytest.mark.parametrize("element_type", [0, 1])
+@pytest.mark.parametrize("tokens,causal", [(77, 1), (256, 1), (700, 1), (1000, 0), (513, 1)])
+def test_causal_and_fp16_variants(reference_kernels, element_type, tokens, causal):
+    """The other users of mmh3_attention at heads of 128 (crates/mmh3-cuda/kernels/attention.cu:
+    502-536): the text encoder's causal attention with grouped key/value heads
+    (src/text_encoder.rs:653-666), in BF16 and in FP16, against float64 and against the reference's
+    kernel on the same buffers."""
+    heads, group, batch = 4, 2, 2
+    dtype = torch.float16 if element_type == 1 else torch.bfloat16
+    generator = torch.Generator().manual_seed(tokens + element_type)
+    q = torch.randn((batch, tokens, heads, 128), generator=generator).to(dtype)
+    k = torch.randn((batch, tokens, heads // group, 128), generator=generator).to(dtype)
+    v = torch.randn((batch, tokens, heads // group, 128), generator=generator).to(dtype)
+    kv_inner = heads // group * 128
+    layout = attention.make_layout(
+        (heads * 128, kv_inner, kv_inner, heads * 128),
+        batch_stride=(tokens * heads * 128, tokens * kv_inner, tokens * kv_inner,
+                      tokens * heads * 128),
+        heads_per_key_value=group, causal=causal)
+    device = [tensor.cuda() for tensor in (q, k, v)]
+    ours = torch.zeros((batch, tokens, heads, 128), dtype=dtype, device="cuda")
+    theirs = torch.zeros_like(ours)
+    attention.attention(element_type, 128, *device, ours, tokens, heads, batch, layout, SCALE)
+    assert reference_kernels.mmh3_attention(
+        element_type, 128, *(tensor.data_ptr() for tensor in device), theirs.data_ptr(), tokens,
+        heads, batch, ctypes.byref(layout), SCALE, None) == 0
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    expected = reference_attention(q, k, v, group, causal)
+    assert torch.max(torch.abs(ours.cpu().double() - expected)) <= 2e-2
+    a, b = ours.float().cpu().numpy(), theirs.float().cpu().numpy()
+    assert np.max(np.abs(a - b)) <= 2e-2
+    assert cosine(a, b) >= 0.9995
+
+
 def test_unsupported_combinations_report_an_error():
     tokens, heads = 64, 1
     qkv = torch.zeros((tokens, 3, heads, 128), dtype=torch.bfloat16, device="cuda")
@@ -193,9 +240,11 @@ def test_unsupported_combinations_report_an_error():
     layout = attention.qkv_layout(heads)
     library = _lib.library()
     arguments = (qkv.data_ptr(), qkv.data_ptr() + 256, qkv.data_ptr() + 512, output.data_ptr(),
-                 tokens, heads, 1, ctypes.byref(layout), SCALE, None)
-    assert library.mmh3_attention(1, 128, *arguments) == _lib.CUDA_ERROR_NOT_SUPPORTED
-    assert library.mmh3_attention(0, 64, *arguments) == _lib.CUDA_ERROR_NOT_SUPPORTED
-    assert library.mmh3_attention(2, 128, *arguments) == _lib.CUDA_ERROR_INVALID_VALUE
-    layout.causal = 1
-    assert library.mmh3_attention(0, 128, *arguments) == _lib.CUDA_ERROR_NOT_SUPPORTED
+                 tokens, heads, 1, ctypes.byref(layout), SCALE)
+    # heads of 64 and the query's fused norm and RoPE (the VAE decoder's use) are not built
+    assert library.mmh3_attention(0, 64, *arguments, None) == _lib.CUDA_ERROR_NOT_SUPPORTED
+    assert library.mmh3_attention(1, 64, *arguments, None) == _lib.CUDA_ERROR_NOT_SUPPORTED
+    angles = torch.zeros((tokens, 64), dtype=torch.float32, device="cuda")
+    assert library.mmh3_attention_roped(0, 128, *arguments, angles.data_ptr(), 64, 1e-6,
+                                        None) == _lib.CUDA_ERROR_NOT_SUPPORTED
+    assert library.mmh3_attention(2, 128, *arguments, None) == _lib.CUDA_ERROR_INVALID_VALUE
