@@ -7,7 +7,8 @@ its sources by oracle/Makefile) is present:
 
 For small seeded inputs it records what the reference leaves behind: dense BF16 outputs, the INT8 q
 and k with their scales, FP8 V and its scale, the quantized attention's output, and VSA's routes,
-route counts and output. The CPU tests then hold the oracle to these files (bit-exact for INT8 and
+route counts and output, and Sol-Attn's block statistics, centred keys, routes, pooled tails and
+output (in reference_sol.npz). The CPU tests then hold the oracle to these files (bit-exact for INT8 and
 routes, within the kernels' tolerance for outputs), so the oracle is pinned to the reference itself
 even where no GPU is present. Inputs are regenerated from the seeds by the tests.
 """
@@ -32,6 +33,18 @@ SCALE = synthetic.softmax_scale()
 DENSE_CASES = [(1, 1), (64, 2), (200, 3)]
 QUANTIZED_CASES = [(65, 2), (200, 3)]
 VSA_CASE = dict(text=70, frames=9, height=16, width=24, audio=40, heads=2, sparsity=0.7)
+SOL_CASE = dict(tokens=777, heads=2, tau=0.5, sinks=(0, 1, 2, 3))
+
+
+def sol_inputs(oracle, tokens, heads):
+    """Every block of 64 tokens shares a random direction, so routing is selective."""
+    inner = heads * 128
+    blocks = -(-tokens // 64)
+    directions, state = oracle_lib.lcg(oracle, tokens, blocks * 3 * inner, -1.0, 1.0)
+    noise, state = oracle_lib.lcg(oracle, state, tokens * 3 * inner, -1.0, 1.0)
+    qkv = directions.reshape(blocks, 3 * inner)[np.arange(tokens) // 64] + \
+        noise.reshape(tokens, 3 * inner)
+    return synthetic.to_bf16_bits(qkv.reshape(-1)).reshape(tokens, 3, heads, 128)
 
 
 def lcg_qkv(oracle, tokens, heads, seed):
@@ -119,6 +132,33 @@ def main():
     arrays["vsa_output"] = output.view(torch.int16).cpu().numpy().view(np.uint16)
     np.savez_compressed(out / "reference_kernels.npz", **arrays)
     print("wrote", out / "reference_kernels.npz", sum(a.nbytes for a in arrays.values()), "bytes")
+
+    case = SOL_CASE
+    tokens, heads = case["tokens"], case["heads"]
+    inner = heads * 128
+    bits = sol_inputs(oracle, tokens, heads)
+    qkv = synthetic.bf16_tensor(bits, "cuda")
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    workspace = attention.SparseWorkspace(tokens, heads)
+    sol_layout = attention.qkv_layout(heads)
+    raw = workspace.raw()
+    base = qkv.data_ptr()
+    assert reference.mmh3_sparse_attention(
+        base, base + 2 * inner, base + 4 * inner, output.data_ptr(), tokens, heads,
+        ctypes.byref(sol_layout), SCALE, case["tau"], *case["sinks"], ctypes.byref(raw), None, 0,
+        None) == 0
+    torch.cuda.synchronize()
+    routes, counts = workspace.routes_host()
+    sol = {"routes": np.concatenate([routes[head, block, :counts[head, block]]
+                                     for head in range(heads)
+                                     for block in range(workspace.blocks)]),
+           "route_counts": counts,
+           "output": output.view(torch.int16).cpu().numpy().view(np.uint16)}
+    for name in ("centroids", "block_keys", "value_sums", "key_mean", "key_variance", "tail_max",
+                 "tail_sum", "tail_values", "row_offsets"):
+        sol[name] = getattr(workspace, name).cpu().numpy()
+    np.savez_compressed(out / "reference_sol.npz", **sol)
+    print("wrote", out / "reference_sol.npz", sum(a.nbytes for a in sol.values()), "bytes")
 
 
 if __name__ == "__main__":

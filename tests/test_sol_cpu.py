@@ -80,3 +80,42 @@ def test_routes_and_pooled_tails_reproduce_the_reference(oracle):
     merged = merge_routes_and_tails(work, q.astype(np.float64), k.astype(np.float64),
                                     v.astype(np.float64), tokens, heads, scale)
     assert np.abs(merged - reference).max() < 2e-4
+
+
+def test_oracle_matches_the_reference_kernels_fixture(oracle):
+    """tests/golden/reference_sol.npz holds what the reference's own CUDA kernels
+    (sparse_attention.cu, compiled from its sources) left in the workspace for a seeded input
+    (tests/golden/make_golden.py): the routing restatement reproduces the statistics, the centred
+    keys and the routes bit for bit, the tails and offsets closely, and the f64 reference the
+    output within the reference test's bounds."""
+    import pathlib
+    import sys
+
+    golden_directory = pathlib.Path(__file__).resolve().parent / "golden"
+    sys.path.insert(0, str(golden_directory))
+    import make_golden
+
+    golden = np.load(golden_directory / "reference_sol.npz")
+    case = make_golden.SOL_CASE
+    tokens, heads = case["tokens"], case["heads"]
+    scale = synthetic.softmax_scale()
+    bits = make_golden.sol_inputs(oracle, tokens, heads)
+    work = oracle_lib.sol_route(oracle, bits, tokens, heads, case["tau"], scale, case["sinks"])
+    for name in ("centroids", "block_keys", "value_sums", "key_mean", "key_variance", "tail_max"):
+        assert np.array_equal(work[name].reshape(-1).view(np.uint32),
+                              golden[name].reshape(-1).view(np.uint32)), name
+    assert np.array_equal(work["route_counts"], golden["route_counts"])
+    blocks = -(-tokens // 64)
+    packed = np.concatenate([work["routes"][head, block, :work["route_counts"][head, block]]
+                             for head in range(heads) for block in range(blocks)])
+    assert np.array_equal(packed, golden["routes"])
+    for name in ("tail_sum", "tail_values", "row_offsets"):
+        assert np.allclose(work[name].reshape(-1), golden[name].reshape(-1), rtol=1e-4,
+                           atol=1e-4), name
+    values = synthetic.bf16_bits_to_f32(bits)
+    expected, _ = oracle_lib.sol_reference(oracle, values[:, 0], values[:, 1], values[:, 2],
+                                           case["tau"], scale, case["sinks"])
+    actual = synthetic.bf16_bits_to_f32(golden["output"]).reshape(expected.shape)
+    difference = np.linalg.norm((actual - expected).astype(np.float64))
+    assert difference / np.linalg.norm(expected.astype(np.float64)) < 0.01
+    assert np.max(np.abs(actual - expected)) < 0.05
