@@ -78,16 +78,17 @@ typedef struct Mmh3VsaWorkspace {
 } Mmh3VsaWorkspace;
 
 /* Dense softmax(Q K^T * scale) V. element_type 0 is BF16 and 1 is FP16; head_dim 64 or 128.
- * Implemented here: head_dim 128 in BF16 and FP16, causal or not, with grouped key/value heads and
- * batches (the DiT's and the text encoder's uses). head_dim 64 returns cudaErrorNotSupported.
- * `scale` must be positive.
+ * Causal or not, with grouped key/value heads and batches: the DiT's, the text encoder's and the
+ * VAE decoder's uses. `scale` must be positive; layouts TMA cannot describe (bases or strides that
+ * are not multiples of 16 bytes) return cudaErrorNotSupported.
  * Replaces crates/mmh3-cuda/kernels/attention.cu:531-536. */
 int mmh3_attention(int element_type, int head_dim, const void *query, const void *key,
                    const void *value, void *output, int tokens, int heads, int batch,
                    const Mmh3AttentionLayout *layout, float scale, mmh3_stream_t stream);
 
-/* mmh3_attention with a query RMSNorm + RoPE fused in (the video VAE's decoder). Null `angles`
- * is mmh3_attention; non-null returns cudaErrorNotSupported.
+/* mmh3_attention with a query RMSNorm + RoPE fused in (the video VAE's decoder): `angles` is FP32
+ * [tokens, pairs], dimension p of a query row pairs with p + pairs, 2 * pairs <= head_dim. Null
+ * `angles` is mmh3_attention.
  * Replaces crates/mmh3-cuda/kernels/attention.cu:502-529. */
 int mmh3_attention_roped(int element_type, int head_dim, const void *query, const void *key,
                          const void *value, void *output, int tokens, int heads, int batch,

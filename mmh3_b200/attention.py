@@ -106,6 +106,25 @@ def attention(element_type: int, head_dim: int, query: torch.Tensor, key: torch.
     )
 
 
+def attention_roped(element_type: int, head_dim: int, query: torch.Tensor, key: torch.Tensor,
+                    value: torch.Tensor, output: torch.Tensor, tokens: int, heads: int, batch: int,
+                    layout: _lib.AttentionLayout, scale: float, angles: torch.Tensor, pairs: int,
+                    epsilon: float) -> None:
+    """`attention` with the query's RMS norm and RoPE fused in, as the video VAE's decoder calls it
+    (attention.rs:437-500): `angles` is FP32 [tokens, pairs]; dimension p pairs with p + pairs."""
+    if angles.dtype != torch.float32 or angles.numel() < tokens * pairs:
+        raise ValueError("angles must be FP32 [tokens, pairs]")
+    if 2 * pairs > head_dim:
+        raise ValueError("more rotary pairs than half the head dimension")
+    check(
+        _lib.library().mmh3_attention_roped(
+            element_type, head_dim, _pointer(query), _pointer(key), _pointer(value),
+            _pointer(output), tokens, heads, batch, ctypes.byref(layout), scale,
+            _pointer(angles), pairs, epsilon, _stream()),
+        "mmh3_attention_roped",
+    )
+
+
 def dense_bf16(qkv: torch.Tensor, output: torch.Tensor, tokens: int, heads: int,
                scale: float) -> None:
     """Dense bidirectional attention with head dimension 128 (attention.rs:469-493).

@@ -10,8 +10,6 @@ extern "C" int mmh3_attention_roped(int element_type, int head_dim, const void *
                                     int heads, int batch, const Mmh3AttentionLayout *layout,
                                     float scale, const float *angles, int pairs, float epsilon,
                                     mmh3_stream_t stream) {
-    (void)pairs;
-    (void)epsilon;
     // crates/mmh3-cuda/kernels/attention.cu:507-510
     if (layout == nullptr || tokens <= 0 || heads <= 0 || batch <= 0 ||
         (layout->heads_per_key_value > 0 && heads % layout->heads_per_key_value != 0)) {
@@ -20,12 +18,9 @@ extern "C" int mmh3_attention_roped(int element_type, int head_dim, const void *
     if ((element_type != 0 && element_type != 1) || (head_dim != 64 && head_dim != 128)) {
         return INVALID_VALUE;
     }
-    // Heads of 64 and the query's fused RMS norm and RoPE (the VAE decoder's use) are not built.
-    if (head_dim != 128 || angles != nullptr) {
-        return NOT_SUPPORTED;
-    }
     return launch_dense_bf16(query, key, value, output, tokens, heads, batch, *layout, scale,
-                             as_stream(stream), element_type == 1);
+                             as_stream(stream), element_type == 1, head_dim, angles, pairs,
+                             epsilon);
 }
 
 extern "C" int mmh3_attention(int element_type, int head_dim, const void *query, const void *key,

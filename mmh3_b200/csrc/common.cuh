@@ -71,10 +71,12 @@ struct SharedMemoryOptIn {
 };
 
 // Launchers of the kernels, one per .cu file.
-// dense_bf16.cu: heads of 128, BF16 or FP16 (`half`), causal or not, grouped key/value heads.
+// dense_bf16.cu: heads of 64 or 128, BF16 or FP16 (`half`), causal or not, grouped key/value heads;
+// non-null `angles` [tokens, pairs] normalize and rotate the query inside the kernel.
 int launch_dense_bf16(const void *query, const void *key, const void *value, void *output,
                       int tokens, int heads, int batch, const Mmh3AttentionLayout &layout,
-                      float scale, cudaStream_t stream, bool half = false);
+                      float scale, cudaStream_t stream, bool half = false, int head_dim = 128,
+                      const float *angles = nullptr, int pairs = 0, float epsilon = 0.0f);
 
 
 // inputs.cu

@@ -32,8 +32,7 @@ constexpr int TILE_M = 128;                   // query rows per tile, one per TM
 constexpr int QUERY_TILES = 2;                // query tiles per CTA
 constexpr int TILE_N = 128;                   // keys per block
 constexpr int STAGES = 5;                     // ring of K and V tiles
-constexpr int SLAB_BYTES = 128 * 128;         // 128 rows of 64 BF16
-constexpr int TILE_BYTES = 2 * SLAB_BYTES;    // a 128 x 128 BF16 tile as two slabs of 64 columns
+constexpr int SLAB_BYTES = 128 * 128;         // 128 rows of 64 16-bit elements
 constexpr int SOFTMAX_WARPS = 4 * QUERY_TILES;
 constexpr int LOAD_WARP = SOFTMAX_WARPS;
 constexpr int MMA_WARP = SOFTMAX_WARPS + 1;
@@ -50,11 +49,17 @@ static_assert((LAUNCH_REGISTERS - OTHER_REGISTERS) * 128 >=
                   (SOFTMAX_REGISTERS - LAUNCH_REGISTERS) * SOFTMAX_WARPS * 32,
               "the softmax warps ask for more registers than the other warps release");
 
-constexpr int SMEM_QUERY = 0;
-constexpr int SMEM_RING = QUERY_TILES * TILE_BYTES;
-constexpr int SMEM_BARRIERS = SMEM_RING + STAGES * TILE_BYTES;
-// Barriers, then the TMEM base address and the abort flag. The extra 1024 bytes align the tiles.
-constexpr int SMEM_BYTES = SMEM_BARRIERS + 256 + 1024;
+// Shared memory for heads of DIM (64 or 128): a tile of 128 rows is one slab of 64 columns per 64
+// dimensions.
+template <int DIM> struct Shape {
+    static constexpr int SLABS = DIM / 64;
+    static constexpr int TILE_BYTES = SLABS * SLAB_BYTES;
+    static constexpr int SMEM_QUERY = 0;
+    static constexpr int SMEM_RING = QUERY_TILES * TILE_BYTES;
+    static constexpr int SMEM_BARRIERS = SMEM_RING + STAGES * TILE_BYTES;
+    // Barriers, then the TMEM base address and the abort flag. The extra 1024 bytes align the tiles.
+    static constexpr int SMEM_BYTES = SMEM_BARRIERS + 256 + 1024;
+};
 
 enum Barrier {
     QUERY_FULL = 0,
@@ -63,21 +68,36 @@ enum Barrier {
     SCORES_FULL = RING_EMPTY + STAGES,               // one per query tile
     PROBABILITIES_FULL = SCORES_FULL + QUERY_TILES,  // one per query tile
     OUTPUT_FULL = PROBABILITIES_FULL + QUERY_TILES,
-    BARRIERS = OUTPUT_FULL + 1,
+    QUERY_READY = OUTPUT_FULL + 1,                   // the query tiles are normalized and rotated
+    BARRIERS = QUERY_READY + 1,
 };
 static_assert(BARRIERS * 8 + 8 <= 256, "the barriers outgrew their corner of shared memory");
 
 constexpr uint32_t TMEM_COLUMNS = 512;
 constexpr uint32_t TMEM_SCORES = 0;    // + tile * 128
-constexpr uint32_t TMEM_OUTPUT = 256;  // + tile * 128
+constexpr uint32_t TMEM_OUTPUT = 256;  // + tile * head dimension
 
 // The 16-bit element of q, k, v, P and the output: BF16, or FP16 (`HALF`).
-template <bool HALF> struct Element {
+template <bool HALF, int DIM = 128> struct Element {
     static constexpr uint32_t FORMAT = HALF ? FORMAT_F16 : FORMAT_BF16;
     static constexpr uint32_t SCORE_MMA =
         instruction_descriptor(ACCUMULATE_F32, FORMAT, FORMAT, 0, 0, TILE_M, TILE_N);
     static constexpr uint32_t OUTPUT_MMA =
-        instruction_descriptor(ACCUMULATE_F32, FORMAT, FORMAT, 0, 1, TILE_M, HEAD_DIM);
+        instruction_descriptor(ACCUMULATE_F32, FORMAT, FORMAT, 0, 1, TILE_M, DIM);
+    static __device__ __forceinline__ float to_float(uint16_t bits) {
+        if constexpr (HALF) {
+            return __half2float(__ushort_as_half(bits));
+        } else {
+            return __uint_as_float(static_cast<uint32_t>(bits) << 16);
+        }
+    }
+    static __device__ __forceinline__ uint16_t from_float(float value) {
+        if constexpr (HALF) {
+            return __half_as_ushort(__float2half_rn(value));
+        } else {
+            return __bfloat16_as_ushort(__float2bfloat16_rn(value));
+        }
+    }
     // Two FP32 values rounded to nearest even and packed, the first in the low half.
     static __device__ __forceinline__ uint32_t pack(float low, float high) {
         if constexpr (HALF) {
@@ -101,6 +121,15 @@ struct DenseMaps {
     CUtensorMap value;
 };
 
+// The RMS norm and rotary embedding the VAE decoder's query takes inside the attention
+// (crates/mmh3-cuda/kernels/attention.cu:49-111): angles [tokens, pairs], dimension p pairs with
+// p + pairs.
+struct QueryRope {
+    const float *angles;
+    int pairs;
+    float epsilon;
+};
+
 // K-major descriptor of a Q or K tile, and the byte offset of contraction step `step` (16 of the
 // 128 dimensions) in it.
 __device__ __forceinline__ uint64_t row_operand(uint32_t tile) {
@@ -115,14 +144,19 @@ __device__ __forceinline__ uint64_t value_operand(uint32_t tile) {
 }
 __host__ __device__ constexpr uint32_t value_step(int step) { return step * 16 * 128; }
 
-template <bool HALF, bool CAUSAL>
+template <bool HALF, bool CAUSAL, int DIM, bool ROPE>
 __global__ void __launch_bounds__(THREADS, 1)
     dense_bf16_kernel(const __grid_constant__ DenseMaps maps, uint16_t *__restrict__ output,
                       int tokens, int heads_per_key_value, int64_t output_token_stride,
                       int64_t output_head_stride, int vector_stores, float scale_log2,
-                      unsigned int *status) {
-    constexpr uint32_t SCORE_MMA = Element<HALF>::SCORE_MMA;
-    constexpr uint32_t OUTPUT_MMA = Element<HALF>::OUTPUT_MMA;
+                      QueryRope rope, unsigned int *status) {
+    constexpr uint32_t SCORE_MMA = Element<HALF, DIM>::SCORE_MMA;
+    constexpr uint32_t OUTPUT_MMA = Element<HALF, DIM>::OUTPUT_MMA;
+    constexpr int SLABS = Shape<DIM>::SLABS;
+    constexpr int TILE_BYTES = Shape<DIM>::TILE_BYTES;
+    constexpr int SMEM_QUERY = Shape<DIM>::SMEM_QUERY;
+    constexpr int SMEM_RING = Shape<DIM>::SMEM_RING;
+    constexpr int SMEM_BARRIERS = Shape<DIM>::SMEM_BARRIERS;
     extern __shared__ uint8_t shared_memory[];
     const uint32_t base = (smem_u32(shared_memory) + 1023u) & ~1023u;
     uint8_t *aligned = shared_memory + (base - smem_u32(shared_memory));
@@ -158,6 +192,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             mbar_init(barrier(PROBABILITIES_FULL + tile), TILE_M);
         }
         mbar_init(barrier(OUTPUT_FULL), 1);
+        mbar_init(barrier(QUERY_READY), SOFTMAX_WARPS * 32);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
@@ -181,7 +216,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             const int key_value_head = head / heads_per_key_value;
             mbar_expect_tx(barrier(QUERY_FULL), QUERY_TILES * TILE_BYTES);
             for (int tile = 0; tile < QUERY_TILES; tile++) {
-                for (int slab = 0; slab < 2; slab++) {
+                for (int slab = 0; slab < SLABS; slab++) {
                     tma_load_3d(base + SMEM_QUERY + tile * TILE_BYTES + slab * SLAB_BYTES,
                                 &maps.query, barrier(QUERY_FULL), slab * 64,
                                 first_query + tile * TILE_M, head);
@@ -197,7 +232,7 @@ __global__ void __launch_bounds__(THREADS, 1)
                 }
                 mbar_expect_tx(barrier(RING_FULL + stage), TILE_BYTES);
                 const CUtensorMap *map = (item & 1) ? &maps.value : &maps.key;
-                for (int slab = 0; slab < 2; slab++) {
+                for (int slab = 0; slab < SLABS; slab++) {
                     tma_load_3d(base + SMEM_RING + stage * TILE_BYTES + slab * SLAB_BYTES, map,
                                 barrier(RING_FULL + stage), slab * 64, (item / 2) * TILE_N,
                                 key_value_head);
@@ -213,7 +248,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             auto score = [&](int tile, uint32_t key_tile) {
                 const uint64_t key_operand = row_operand(key_tile);
                 #pragma unroll
-                for (int step = 0; step < HEAD_DIM / 16; step++) {
+                for (int step = 0; step < DIM / 16; step++) {
                     mma_f16_ss(tmem + TMEM_SCORES + tile * TILE_N,
                                advance_descriptor(query_operands[tile], row_step(step)),
                                advance_descriptor(key_operand, row_step(step)), SCORE_MMA,
@@ -226,13 +261,14 @@ __global__ void __launch_bounds__(THREADS, 1)
                 #pragma unroll
                 for (int step = 0; step < TILE_N / 16; step++) {
                     // P is BF16, two to a column: 16 keys are 8 columns.
-                    mma_f16_ts(tmem + TMEM_OUTPUT + tile * HEAD_DIM,
+                    mma_f16_ts(tmem + TMEM_OUTPUT + tile * DIM,
                                tmem + TMEM_SCORES + tile * TILE_N + step * 8,
                                advance_descriptor(operand, value_step(step)), OUTPUT_MMA,
                                !first || step > 0);
                 }
             };
-            bool alive = mbar_wait(barrier(QUERY_FULL), 0, watchdog, STATUS_DENSE | 2) &&
+            bool alive = mbar_wait(barrier(ROPE ? QUERY_READY : QUERY_FULL), 0, watchdog,
+                                   STATUS_DENSE | 2) &&
                          mbar_wait(barrier(RING_FULL + 0), 0, watchdog, STATUS_DENSE | 3);
             if (alive) {
                 tcgen05_fence_after();
@@ -287,11 +323,86 @@ __global__ void __launch_bounds__(THREADS, 1)
         const int row = (warp % 4) * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>((warp % 4) * 32) << 16;
         const uint32_t scores = tmem + lane_base + TMEM_SCORES + tile * TILE_N;
-        const uint32_t accumulator = tmem + lane_base + TMEM_OUTPUT + tile * HEAD_DIM;
+        const uint32_t accumulator = tmem + lane_base + TMEM_OUTPUT + tile * DIM;
         float maximum = -INFINITY; // of the raw scores, before the scale
         float2 sums[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
         bool alive = true;
-        for (int block = 0; block < blocks; block++) {
+        if constexpr (ROPE) {
+            // The eight softmax warps normalize and rotate the 256 query rows where TMA left them,
+            // a warp to a row: lane l holds dimensions l, l + 32, ... of the row.
+            alive = mbar_wait(barrier(QUERY_FULL), 0, watchdog, STATUS_DENSE | 10);
+            alive = __all_sync(0xffffffffu, alive);
+            constexpr int SLOTS = DIM / 32;
+            for (int query_row = warp; alive && query_row < QUERY_TILES * TILE_M;
+                 query_row += SOFTMAX_WARPS) {
+                const int token = first_query + query_row;
+                if (token >= tokens) {
+                    continue;
+                }
+                const int tile_row = query_row % TILE_M;
+                uint32_t addresses[SLOTS];
+                float values[SLOTS];
+                float squares = 0.0f;
+                #pragma unroll
+                for (int slot = 0; slot < SLOTS; slot++) {
+                    const int index = slot * 32 + lane;
+                    // 16-byte chunk c of a row sits at chunk c ^ (row % 8) of its 128-byte line.
+                    const int chunk = ((index % 64) / 8) ^ (tile_row % 8);
+                    addresses[slot] = base + SMEM_QUERY + (query_row / TILE_M) * TILE_BYTES +
+                                      (index / 64) * SLAB_BYTES + tile_row * 128 + chunk * 16 +
+                                      (index % 8) * 2;
+                    uint16_t bits;
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(bits) : "r"(addresses[slot]));
+                    values[slot] = Element<HALF, DIM>::to_float(bits);
+                    squares = fmaf(values[slot], values[slot], squares);
+                }
+                #pragma unroll
+                for (int offset = 16; offset > 0; offset /= 2) {
+                    squares += __shfl_xor_sync(0xffffffffu, squares, offset);
+                }
+                const float inverse = rsqrtf(squares / DIM + rope.epsilon);
+                #pragma unroll
+                for (int slot = 0; slot < SLOTS; slot++) {
+                    values[slot] *= inverse;
+                }
+                float rotated[SLOTS];
+                #pragma unroll
+                for (int slot = 0; slot < SLOTS; slot++) {
+                    const int index = slot * 32 + lane;
+                    const bool leads = index < rope.pairs;
+                    const bool follows = !leads && index < 2 * rope.pairs;
+                    const int partner = leads ? index + rope.pairs
+                                              : (follows ? index - rope.pairs : index);
+                    float other = 0.0f;
+                    #pragma unroll
+                    for (int source = 0; source < SLOTS; source++) {
+                        const float fetched =
+                            __shfl_sync(0xffffffffu, values[source], partner % 32);
+                        other = source == partner / 32 ? fetched : other;
+                    }
+                    float result = values[slot];
+                    if (leads || follows) {
+                        float sine, cosine;
+                        sincosf(rope.angles[static_cast<int64_t>(token) * rope.pairs +
+                                            (leads ? index : partner)],
+                                &sine, &cosine);
+                        result = leads ? values[slot] * cosine - other * sine
+                                       : other * sine + values[slot] * cosine;
+                    }
+                    rotated[slot] = result;
+                }
+                #pragma unroll
+                for (int slot = 0; slot < SLOTS; slot++) {
+                    const uint16_t bits = Element<HALF, DIM>::from_float(rotated[slot]);
+                    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addresses[slot]), "h"(bits)
+                                 : "memory");
+                }
+            }
+            // The MMAs read the tiles through the async proxy.
+            fence_proxy_async();
+            mbar_arrive(barrier(QUERY_READY));
+        }
+        for (int block = 0; alive && block < blocks; block++) {
             alive = mbar_wait(barrier(SCORES_FULL + tile), block & 1, watchdog, STATUS_DENSE | 7);
             // The tensor memory accesses below are warp-wide: the warp goes on or leaves as one.
             alive = __all_sync(0xffffffffu, alive);
@@ -345,7 +456,7 @@ __global__ void __launch_bounds__(THREADS, 1)
                     sums[0] = __fmul2_rn(sums[0], correction2);
                     sums[1] = __fmul2_rn(sums[1], correction2);
                     #pragma unroll
-                    for (int chunk = 0; chunk < 4; chunk++) {
+                    for (int chunk = 0; chunk < DIM / 32; chunk++) {
                         uint32_t values[32];
                         tmem_load_32(accumulator + chunk * 32, values);
                         tmem_wait_load();
@@ -379,7 +490,7 @@ __global__ void __launch_bounds__(THREADS, 1)
                         probability = make_float2(exp2_approx(x.x), exp2_approx(x.y));
                     }
                     sums[pair % 2] = __fadd2_rn(sums[pair % 2], probability);
-                    packed[pair] = Element<HALF>::pack(probability.x, probability.y);
+                    packed[pair] = Element<HALF, DIM>::pack(probability.x, probability.y);
                 }
                 tmem_store_32(scores + chunk * 32, packed);
             }
@@ -398,7 +509,7 @@ __global__ void __launch_bounds__(THREADS, 1)
             uint16_t *output_row = output + static_cast<int64_t>(token) * output_token_stride +
                                    static_cast<int64_t>(head) * output_head_stride;
             #pragma unroll
-            for (int chunk = 0; chunk < 4; chunk++) {
+            for (int chunk = 0; chunk < DIM / 32; chunk++) {
                 uint32_t values[32];
                 tmem_load_32(accumulator + chunk * 32, values);
                 tmem_wait_load();
@@ -407,7 +518,7 @@ __global__ void __launch_bounds__(THREADS, 1)
                     #pragma unroll
                     for (int pair = 0; pair < 16; pair++) {
                         packed[pair] =
-                            Element<HALF>::pack(__uint_as_float(values[pair * 2]) * inverse,
+                            Element<HALF, DIM>::pack(__uint_as_float(values[pair * 2]) * inverse,
                                                 __uint_as_float(values[pair * 2 + 1]) * inverse);
                     }
                     if (vector_stores) {
@@ -446,9 +557,9 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
 }
 
-bool encode_operand(CUtensorMap *map, bool half, const void *base, int tokens, int heads,
-                    int64_t token_stride, int64_t head_stride) {
-    const uint64_t dimensions[3] = {static_cast<uint64_t>(HEAD_DIM), static_cast<uint64_t>(tokens),
+bool encode_operand(CUtensorMap *map, bool half, int head_dim, const void *base, int tokens,
+                    int heads, int64_t token_stride, int64_t head_stride) {
+    const uint64_t dimensions[3] = {static_cast<uint64_t>(head_dim), static_cast<uint64_t>(tokens),
                                     static_cast<uint64_t>(heads)};
     uint64_t strides[2] = {static_cast<uint64_t>(token_stride) * 2,
                            static_cast<uint64_t>(head_stride) * 2};
@@ -462,13 +573,36 @@ bool encode_operand(CUtensorMap *map, bool half, const void *base, int tokens, i
         dimensions, strides, box);
 }
 
+// The kernel instance for an element type, mask, head dimension and query transform, and its
+// shared memory.
+struct Instance {
+    void (*kernel)(const DenseMaps, uint16_t *, int, int, int64_t, int64_t, int, float, QueryRope,
+                   unsigned int *);
+    int shared_bytes;
+};
+
+template <bool HALF, bool CAUSAL, int DIM> Instance instance(bool rope) {
+    return {rope ? dense_bf16_kernel<HALF, CAUSAL, DIM, true>
+                 : dense_bf16_kernel<HALF, CAUSAL, DIM, false>,
+            Shape<DIM>::SMEM_BYTES};
+}
+
+template <bool HALF, bool CAUSAL> Instance instance(int head_dim, bool rope) {
+    return head_dim == 64 ? instance<HALF, CAUSAL, 64>(rope) : instance<HALF, CAUSAL, 128>(rope);
+}
+
 } // namespace
 
 int launch_dense_bf16(const void *query, const void *key, const void *value, void *output,
                       int tokens, int heads, int batch, const Mmh3AttentionLayout &layout,
-                      float scale, cudaStream_t stream, bool half) {
+                      float scale, cudaStream_t stream, bool half, int head_dim,
+                      const float *angles, int pairs, float epsilon) {
     const int group = layout.heads_per_key_value > 0 ? layout.heads_per_key_value : 1;
     if (!(scale > 0.0f) || !std::isfinite(scale)) {
+        return INVALID_VALUE;
+    }
+    if ((head_dim != 64 && head_dim != 128) ||
+        (angles != nullptr && (pairs < 0 || 2 * pairs > head_dim))) {
         return INVALID_VALUE;
     }
     for (int operand = 0; operand < 4; operand++) {
@@ -481,14 +615,18 @@ int launch_dense_bf16(const void *query, const void *key, const void *value, voi
         return static_cast<int>(cudaErrorInvalidDevice);
     }
     const bool causal = layout.causal != 0;
-    auto *kernel = half ? (causal ? dense_bf16_kernel<true, true> : dense_bf16_kernel<true, false>)
-                        : (causal ? dense_bf16_kernel<false, true> : dense_bf16_kernel<false, false>);
-    static SharedMemoryOptIn shared_memory[4];
-    const cudaError_t configured =
-        shared_memory[(half ? 2 : 0) + (causal ? 1 : 0)].ensure(kernel, SMEM_BYTES);
+    const bool rope = angles != nullptr;
+    const Instance chosen =
+        half ? (causal ? instance<true, true>(head_dim, rope) : instance<true, false>(head_dim, rope))
+             : (causal ? instance<false, true>(head_dim, rope)
+                       : instance<false, false>(head_dim, rope));
+    static SharedMemoryOptIn shared_memory[16];
+    const int index = (half ? 8 : 0) + (causal ? 4 : 0) + (head_dim == 64 ? 2 : 0) + (rope ? 1 : 0);
+    const cudaError_t configured = shared_memory[index].ensure(chosen.kernel, chosen.shared_bytes);
     if (configured != cudaSuccess) {
         return static_cast<int>(configured);
     }
+    const QueryRope query_rope = {angles, pairs, epsilon};
     // Both element types are 16 bits wide: the strides are in elements either way.
     const auto *q = static_cast<const uint16_t *>(query);
     const auto *k = static_cast<const uint16_t *>(key);
@@ -500,11 +638,11 @@ int launch_dense_bf16(const void *query, const void *key, const void *value, voi
         const uint16_t *batch_value = v + item * layout.batch_stride[VALUE];
         uint16_t *batch_output = out + item * layout.batch_stride[OUTPUT];
         DenseMaps maps;
-        if (!encode_operand(&maps.query, half, batch_query, tokens, heads,
+        if (!encode_operand(&maps.query, half, head_dim, batch_query, tokens, heads,
                             layout.token_stride[QUERY], layout.head_stride[QUERY]) ||
-            !encode_operand(&maps.key, half, batch_key, tokens, heads / group,
+            !encode_operand(&maps.key, half, head_dim, batch_key, tokens, heads / group,
                             layout.token_stride[KEY], layout.head_stride[KEY]) ||
-            !encode_operand(&maps.value, half, batch_value, tokens, heads / group,
+            !encode_operand(&maps.value, half, head_dim, batch_value, tokens, heads / group,
                             layout.token_stride[VALUE], layout.head_stride[VALUE])) {
             // TMA wants 16-byte aligned bases and strides.
             return NOT_SUPPORTED;
@@ -513,9 +651,9 @@ int launch_dense_bf16(const void *query, const void *key, const void *value, voi
                                   layout.token_stride[OUTPUT] % 8 == 0 &&
                                   layout.head_stride[OUTPUT] % 8 == 0;
         const dim3 grid((tokens + QUERY_TILES * TILE_M - 1) / (QUERY_TILES * TILE_M), heads);
-        kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(
+        chosen.kernel<<<grid, THREADS, chosen.shared_bytes, stream>>>(
             maps, batch_output, tokens, group, layout.token_stride[OUTPUT],
-            layout.head_stride[OUTPUT], vector_stores, scale * LOG2_E, status);
+            layout.head_stride[OUTPUT], vector_stores, scale * LOG2_E, query_rope, status);
         const cudaError_t launched = cudaGetLastError();
         if (launched != cudaSuccess) {
             return static_cast<int>(launched);

@@ -63,7 +63,7 @@ def test_bad_arguments_are_rejected_before_any_launch():
     assert library.mmh3_attention(0, 96, None, None, None, None, 8, 4, 1, ctypes.byref(layout),
                                   0.1, None) == invalid
     assert library.mmh3_attention(1, 64, None, None, None, None, 8, 4, 1, ctypes.byref(layout),
-                                  0.1, None) == _lib.CUDA_ERROR_NOT_SUPPORTED
+                                  -0.1, None) == invalid  # the scale must be positive
     workspace = _lib.QuantizedWorkspaceStruct()
     layout.causal = 1
     assert library.mmh3_attention_quantized(None, None, None, None, 8, 1, ctypes.byref(layout),

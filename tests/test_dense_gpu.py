@@ -233,6 +233,69 @@ def test_causal_and_fp16_variants(reference_kernels, element_type, tokens, causa
     assert cosine(a, b) >= 0.9995
 
 
+def normalized_rotated(q, angles, pairs, epsilon, dtype):
+    """The query after the fused RMS norm and RoPE, rounded to the element type as the kernel
+    rounds it (crates/mmh3-cuda/kernels/attention.cu:62-111)."""
+    values = q.double()
+    values = values * torch.rsqrt(values.pow(2).mean(dim=-1, keepdim=True) + epsilon)
+    first, second = values[..., :pairs], values[..., pairs:2 * pairs]
+    cosine = torch.cos(angles.double())[None, :, None, :]
+    sine = torch.sin(angles.double())[None, :, None, :]
+    rotated = values.clone()
+    rotated[..., :pairs] = first * cosine - second * sine
+    rotated[..., pairs:2 * pairs] = first * sine + second * cosine
+    return rotated.to(dtype)
+
+
+@pytest.mark.parametrize("element_type", [0, 1])
+@pytest.mark.parametrize("head_dim,tokens,causal,pairs", [
+    (64, 300, 0, None), (64, 513, 1, None), (64, 700, 0, 32), (64, 129, 0, 20),
+    (128, 300, 0, 64), (128, 257, 1, 40),
+])
+def test_heads_of_64_and_the_fused_query_rope(reference_kernels, element_type, head_dim, tokens,
+                                              causal, pairs):
+    """The VAE decoder's use of mmh3_attention_roped (src/vae.rs:1008): FP16 heads of 64 in a
+    batched layout with the query's RMS norm and RoPE inside the attention; and the same options in
+    every other combination the reference's kernel takes, against float64 and against that kernel
+    on the same buffers."""
+    heads, batch, epsilon = 3, 2, 1e-6
+    scale = 1.0 / head_dim ** 0.5
+    dtype = torch.float16 if element_type == 1 else torch.bfloat16
+    generator = torch.Generator().manual_seed(tokens + head_dim + element_type)
+    q, k, v = (torch.randn((batch, tokens, heads, head_dim), generator=generator).to(dtype)
+               for _ in range(3))
+    inner = heads * head_dim
+    layout = attention.make_layout((inner,) * 4, head_stride=(head_dim,) * 4,
+                                   batch_stride=(tokens * inner,) * 4, causal=causal)
+    device = [tensor.cuda() for tensor in (q, k, v)]
+    ours = torch.zeros((batch, tokens, heads, head_dim), dtype=dtype, device="cuda")
+    theirs = torch.zeros_like(ours)
+    angles = None
+    if pairs is not None:
+        angles = (torch.rand((tokens, pairs), generator=generator) * 6.0 - 3.0).cuda()
+        attention.attention_roped(element_type, head_dim, *device, ours, tokens, heads, batch,
+                                  layout, scale, angles, pairs, epsilon)
+    else:
+        attention.attention(element_type, head_dim, *device, ours, tokens, heads, batch, layout,
+                            scale)
+    assert reference_kernels.mmh3_attention_roped(
+        element_type, head_dim, *(tensor.data_ptr() for tensor in device), theirs.data_ptr(),
+        tokens, heads, batch, ctypes.byref(layout), scale,
+        angles.data_ptr() if angles is not None else None, pairs or 0, epsilon, None) == 0
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    query = normalized_rotated(q, angles.cpu(), pairs, epsilon, dtype) if pairs else q
+    scores = torch.einsum("bqhd,bkhd->bhqk", query.double(), k.double()) * scale
+    if causal:
+        future = torch.triu(torch.ones((tokens, tokens), dtype=torch.bool), diagonal=1)
+        scores = scores.masked_fill(future, float("-inf"))
+    expected = torch.einsum("bhqk,bkhd->bqhd", scores.softmax(-1), v.double())
+    assert torch.max(torch.abs(ours.cpu().double() - expected)) <= 2e-2
+    a, b = ours.float().cpu().numpy(), theirs.float().cpu().numpy()
+    assert np.max(np.abs(a - b)) <= 2e-2
+    assert cosine(a, b) >= 0.9995
+
+
 def test_unsupported_combinations_report_an_error():
     tokens, heads = 64, 1
     qkv = torch.zeros((tokens, 3, heads, 128), dtype=torch.bfloat16, device="cuda")
@@ -241,10 +304,13 @@ def test_unsupported_combinations_report_an_error():
     library = _lib.library()
     arguments = (qkv.data_ptr(), qkv.data_ptr() + 256, qkv.data_ptr() + 512, output.data_ptr(),
                  tokens, heads, 1, ctypes.byref(layout), SCALE)
-    # heads of 64 and the query's fused norm and RoPE (the VAE decoder's use) are not built
-    assert library.mmh3_attention(0, 64, *arguments, None) == _lib.CUDA_ERROR_NOT_SUPPORTED
-    assert library.mmh3_attention(1, 64, *arguments, None) == _lib.CUDA_ERROR_NOT_SUPPORTED
-    angles = torch.zeros((tokens, 64), dtype=torch.float32, device="cuda")
-    assert library.mmh3_attention_roped(0, 128, *arguments, angles.data_ptr(), 64, 1e-6,
-                                        None) == _lib.CUDA_ERROR_NOT_SUPPORTED
     assert library.mmh3_attention(2, 128, *arguments, None) == _lib.CUDA_ERROR_INVALID_VALUE
+    assert library.mmh3_attention(0, 96, *arguments, None) == _lib.CUDA_ERROR_INVALID_VALUE
+    angles = torch.zeros((tokens, 64), dtype=torch.float32, device="cuda")
+    # more rotary pairs than half a head
+    assert library.mmh3_attention_roped(0, 64, *arguments, angles.data_ptr(), 33, 1e-6,
+                                        None) == _lib.CUDA_ERROR_INVALID_VALUE
+    # a layout TMA cannot describe: a token stride that is not a multiple of 16 bytes
+    odd = attention.make_layout((3 * 128 + 1,) * 3 + (128,))
+    arguments = arguments[:7] + (ctypes.byref(odd),) + arguments[8:]
+    assert library.mmh3_attention(0, 128, *arguments, None) == _lib.CUDA_ERROR_NOT_SUPPORTED
