@@ -1,21 +1,26 @@
-// Dense non-causal BF16 attention for heads of 128 on sm_100a: softmax(Q K^T * scale) V with FP32
-// accumulation and softmax and BF16 output. Computes what the reference's attention_kernel
-// (crates/mmh3-cuda/kernels/attention.cu:122-381) computes, with another design:
+// Dense attention on sm_100a: softmax(Q K^T * scale) V with FP32 accumulation and softmax, for heads
+// of 64 or 128 in BF16 or FP16, causal or not, with grouped key/value heads and batches, and
+// optionally the query's RMS norm and RoPE applied inside the kernel. Computes what the reference's
+// attention_kernel (crates/mmh3-cuda/kernels/attention.cu:62-381) computes, with another design. The
+// instance the DiT uses (BF16, heads of 128, no mask, no query transform) is the one the benchmark
+// times; the others are the same template for the text encoder and the VAE decoder.
 //
 // A CTA owns two tiles of 128 query rows of one head and walks the keys in blocks of 128.
 //
 // - Warp 8 (one thread) streams the tiles with TMA into 128-byte-swizzled shared memory: the two
-//   query tiles once, then K0, V0, K1, V1, ... through a ring of five 32 KiB stages.
+//   query tiles once, then K0, V0, K1, V1, ... through a ring of five stages (32 KiB each for heads
+//   of 128).
 // - Warp 9 (one thread) issues the tcgen05 MMAs. S = Q K^T (128 x 128, FP32) of each query tile
 //   lands in tensor memory; O += P V accumulates there too, with P read from tensor memory. The
 //   two query tiles alternate, so the tensor cores work on one while the softmax of the other runs.
 // - Warps 0-3 and 4-7 are the softmax of tile 0 and tile 1, one thread per query row (a row is one
 //   TMEM lane, so no reduction crosses threads). A thread reads its row of S, keeps the running
-//   maximum and sum, writes P as BF16 over the first half of the S columns it has just read, and
-//   rescales its row of O only when the maximum has grown by more than 2^8, which the final
-//   division by the row sum makes exact again.
+//   maximum and sum, writes P in the element type over the first half of the S columns it has just
+//   read, and rescales its row of O only when the maximum has grown by more than 2^8, which the
+//   final division by the row sum makes exact again. With a query transform, the same eight warps
+//   first normalize and rotate the query tiles where TMA left them.
 //
-// Tensor memory: S0 | S1 | O0 | O1, 128 columns each, all 512 columns of the SM.
+// Tensor memory: S0 | S1 | O0 | O1, S 128 columns each and O one column per head dimension.
 #include <cfloat>
 #include <cmath>
 
