@@ -142,34 +142,53 @@ def test_routing_everything_is_dense_attention():
     assert torch.max(torch.abs(output.float() - dense.float())).item() < 2e-2
 
 
-def test_block_statistics_from_the_input_pass(oracle):
-    """attention_inputs.rs:126-222: the fused input pass fills the block statistics, and Sol-Attn
-    over prepared inputs routes exactly as it does from the normalized rows themselves."""
+@pytest.mark.parametrize("quantized", [False, True])
+@pytest.mark.parametrize("tokens", [1, 63, 64, 65, 200, 1000])
+def test_prepared_inputs_match_separate_passes(oracle, tokens, quantized):
+    """attention_inputs.rs:126-256 (sparse_attention_with_prepared_inputs_matches_separate_passes):
+    the fused input pass fills the block statistics (and the INT8/FP8 workspace), and Sol-Attn over
+    prepared inputs gives the output, bit for bit, of qk_norm_rope followed by Sol-Attn over the
+    normalized rows; so does the pass that also takes the head maxima of |v|."""
     from test_inputs_gpu import make_inputs, norm_for
 
-    tokens, heads, tau = 600, 2, 0.5
+    heads, tau = 3, 1.0
+    inner = heads * 128
     sinks = SparseSinks((0, 1), (0, 0))
     bits, query_weight, key_weight, angles = make_inputs(oracle, tokens, heads)
     norm = norm_for(query_weight, key_weight, angles)
     layout = attention.qkv_layout(heads)
 
-    prepared_qkv = synthetic.bf16_tensor(bits, "cuda")
-    prepared = attention.SparseWorkspace(tokens, heads)
-    prepared_output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
-    attention.prepare_inputs(prepared_qkv, norm, tokens, heads, sol=prepared)
-    attention.sparse(prepared_qkv, prepared_output, layout, SCALE, tau, sinks, prepared,
+    separate = synthetic.bf16_tensor(bits, "cuda")
+    separate_workspace = attention.SparseWorkspace(tokens, heads, quantized=quantized)
+    separate_output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    attention.qk_norm_rope(separate, norm, tokens, heads)
+    attention.sparse(separate, separate_output, layout, SCALE, tau, sinks, separate_workspace)
+
+    fused = synthetic.bf16_tensor(bits, "cuda")
+    fused_workspace = attention.SparseWorkspace(tokens, heads, quantized=quantized)
+    fused_output = torch.zeros_like(separate_output)
+    attention.prepare_inputs(fused, norm, tokens, heads, sol=fused_workspace)
+    attention.sparse(fused, fused_output, layout, SCALE, tau, sinks, fused_workspace,
                      attention.AttentionInputs.PREPARED)
 
-    raw_qkv = synthetic.bf16_tensor(bits, "cuda")
-    attention.qk_norm_rope(raw_qkv, norm, tokens, heads)
-    raw = attention.SparseWorkspace(tokens, heads)
-    raw_output = torch.zeros_like(prepared_output)
-    attention.sparse(raw_qkv, raw_output, layout, SCALE, tau, sinks, raw)
+    if quantized:
+        with_values = synthetic.bf16_tensor(bits, "cuda")
+        workspace = attention.SparseWorkspace(tokens, heads, quantized=True)
+        with_values_output = torch.zeros_like(separate_output)
+        maxima = with_values[:, 2].float().abs().amax(dim=(0, 2)).contiguous()
+        attention.prepare_inputs(with_values, norm, tokens, heads, sol=workspace,
+                                 value_head_maxima=maxima)
+        attention.sparse(with_values, with_values_output, layout, SCALE, tau, sinks, workspace,
+                         attention.AttentionInputs.PREPARED_WITH_VALUES)
+        assert torch.equal(separate_output, with_values_output)
     assert attention.take_status() == 0
 
-    assert torch.equal(prepared_qkv, raw_qkv)
-    assert_routes_equal(*prepared.routes_host(), *raw.routes_host())
-    assert torch.equal(prepared_output, raw_output)
+    assert separate_workspace.routed_fraction() == fused_workspace.routed_fraction()
+    assert_routes_equal(*separate_workspace.routes_host(), *fused_workspace.routes_host())
+    assert torch.equal(separate_output, fused_output)
+    # Quantized attention reads only INT8 keys, so the fused pass leaves k as it was.
+    normalized = 1 if quantized else 2
+    assert torch.equal(separate[:, :normalized], fused[:, :normalized])
 
 
 def test_rejects_what_it_does_not_compute():
