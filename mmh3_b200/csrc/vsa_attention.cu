@@ -13,6 +13,11 @@
 // the pair. Half of each MMA is spent on the off-diagonal blocks; in exchange every row and every
 // softmax thread has work, and the tiles keep their own routes.
 //
+// Key tiles that BOTH route lists hold are taken first, one to a step, for both query tiles at
+// once: S is then 128 rows by that tile's 64 keys and nothing of the MMAs is wasted. The CTA finds
+// them with one bit per tile and list in shared memory; every role (loader, MMA issuer, softmax
+// threads) walks the same schedule from the two lists and the two bitmaps.
+//
 // Rows of a box past a tile's length belong to the next tile (or are zero past the sequence):
 // their scores are masked and their probabilities are zero. A list that ends before its
 // partner's loads zero tiles from past the end of the sequence.
@@ -39,6 +44,10 @@ constexpr int SOFTMAX_WARPS = 4;
 constexpr int LOAD_WARP = SOFTMAX_WARPS;
 constexpr int MMA_WARP = SOFTMAX_WARPS + 1;
 constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
+// Up to this many tiles the two route lists of a CTA are compared (one bit per tile each) and the
+// key tiles both lists hold are walked once for both query tiles; longer sequences pair the lists
+// entry by entry only.
+constexpr int MAX_BITMAP_TILES = 16384;
 constexpr uint32_t TMEM_COLUMNS = 256;
 constexpr uint32_t TMEM_SCORES = 0;
 constexpr uint32_t TMEM_OUTPUT = 128;
@@ -57,7 +66,9 @@ template <bool QUANTIZED> struct Shape {
     static constexpr int SMEM_QUERY = 0;
     static constexpr int SMEM_RING = TILE_BYTES;
     static constexpr int SMEM_BARRIERS = SMEM_RING + STAGES * TILE_BYTES;
-    static constexpr int SMEM_BYTES = SMEM_BARRIERS + 256 + 1024;
+    // After the barriers: one bit per tile for each of the CTA's two route lists.
+    static constexpr int SMEM_BITMAPS = SMEM_BARRIERS + 256;
+    static constexpr int SMEM_BYTES = SMEM_BITMAPS + 2 * (MAX_BITMAP_TILES / 8) + 1024;
     static constexpr int QUERY_FULL = 0;
     static constexpr int RING_FULL = 1;
     static constexpr int RING_EMPTY = RING_FULL + STAGES;
@@ -139,7 +150,81 @@ __global__ void __launch_bounds__(THREADS, 2)
                                   static_cast<size_t>(head) * p.tiles + query_tiles[1]};
     const int counts[2] = {p.route_counts[route_rows[0]],
                            exists[1] ? p.route_counts[route_rows[1]] : 0};
+    const uint16_t *lists[2] = {p.routes + route_rows[0] * p.tiles,
+                                p.routes + (exists[1] ? route_rows[1] : route_rows[0]) * p.tiles};
+    // One bit per tile and list, and how many tiles both lists hold.
+    uint32_t *bitmaps = reinterpret_cast<uint32_t *>(aligned + S::SMEM_BITMAPS);
+    constexpr int BITMAP_WORDS = MAX_BITMAP_TILES / 32;
+    __shared__ int common_tiles;
+    const bool compared = exists[1] && p.tiles <= MAX_BITMAP_TILES;
+    if (compared) {
+        const int words = (p.tiles + 31) / 32;
+        for (int word = threadIdx.x; word < words; word += THREADS) {
+            bitmaps[word] = 0;
+            bitmaps[BITMAP_WORDS + word] = 0;
+        }
+        if (threadIdx.x == 0) {
+            common_tiles = 0;
+        }
+        __syncthreads();
+        for (int half = 0; half < 2; half++) {
+            for (int entry = threadIdx.x; entry < counts[half]; entry += THREADS) {
+                const int tile = lists[half][entry];
+                atomicOr(bitmaps + half * BITMAP_WORDS + tile / 32, 1u << (tile % 32));
+            }
+        }
+        __syncthreads();
+        int both = 0;
+        for (int word = threadIdx.x; word < words; word += THREADS) {
+            both += __popc(bitmaps[word] & bitmaps[BITMAP_WORDS + word]);
+        }
+        #pragma unroll
+        for (int offset = 16; offset > 0; offset /= 2) {
+            both += __shfl_xor_sync(0xffffffffu, both, offset);
+        }
+        if (threadIdx.x % 32 == 0 && both > 0) {
+            atomicAdd(&common_tiles, both);
+        }
+        __syncthreads();
+    }
+    const int common = compared ? common_tiles : 0;
     const int steps = max(counts[0], counts[1]);
+    // The schedule every role walks: first the `common` tiles of both lists, one to a step (found
+    // by scanning list 0 for entries list 1 also holds); then the remaining entries of the two
+    // lists, paired in order. `cursors` are positions in the two lists.
+    auto in_list = [&](int half, int tile) {
+        return (bitmaps[half * BITMAP_WORDS + tile / 32] >> (tile % 32)) & 1u;
+    };
+    struct Cursors {
+        int at[2];
+    };
+    // The key tiles of step `step` (-1: none), and whether it is a step both query tiles share.
+    auto next_step = [&](int step, Cursors &cursors, int (&tiles)[2]) {
+        if (step < common) {
+            int entry = cursors.at[0];
+            while (!in_list(1, lists[0][entry])) {
+                entry++;
+            }
+            tiles[0] = tiles[1] = lists[0][entry];
+            cursors.at[0] = entry + 1;
+            return true;
+        }
+        if (step == common) {
+            cursors.at[0] = cursors.at[1] = 0;
+        }
+        #pragma unroll
+        for (int half = 0; half < 2; half++) {
+            int entry = cursors.at[half];
+            if (common > 0) {
+                while (entry < counts[half] && in_list(1 - half, lists[half][entry])) {
+                    entry++;
+                }
+            }
+            tiles[half] = entry < counts[half] ? lists[half][entry] : -1;
+            cursors.at[half] = entry + 1;
+        }
+        return false;
+    };
 
     if (threadIdx.x == 0) {
         mbar_init(barrier(S::QUERY_FULL), 1);
@@ -183,18 +268,12 @@ __global__ void __launch_bounds__(THREADS, 2)
                           barrier(S::QUERY_FULL),
                           exists[half] ? tile_start(query_tiles[half]) : p.tokens);
             }
-            // The tiles of step 0, then one step ahead of the loads.
-            int tiles_now[2], tiles_next[2];
-            for (int half = 0; half < 2; half++) {
-                tiles_now[half] =
-                    counts[half] > 0 ? p.routes[route_rows[half] * p.tiles] : -1;
-            }
+            Cursors cursors = {{0, 0}};
             for (int step = 0; step < steps; step++) {
-                for (int half = 0; half < 2; half++) {
-                    tiles_next[half] = step + 1 < counts[half]
-                                           ? p.routes[route_rows[half] * p.tiles + step + 1]
-                                           : -1;
-                }
+                int tiles_now[2];
+                const bool shared = next_step(step, cursors, tiles_now);
+                // A shared step fills only the first half of the stage: one key tile for both.
+                const int halves = shared ? 1 : 2;
                 int rows[2];
                 for (int half = 0; half < 2; half++) {
                     rows[half] = tiles_now[half] >= 0 ? tile_start(tiles_now[half]) : p.tokens;
@@ -211,8 +290,8 @@ __global__ void __launch_bounds__(THREADS, 2)
                     }
                     const uint32_t bar = barrier(S::RING_FULL + stage);
                     const uint32_t destination = base + S::SMEM_RING + stage * S::TILE_BYTES;
-                    mbar_expect_tx(bar, S::TILE_BYTES);
-                    for (int half = 0; half < 2; half++) {
+                    mbar_expect_tx(bar, S::TILE_BYTES / 2 * halves);
+                    for (int half = 0; half < halves; half++) {
                         if (QUANTIZED && part == 1) {
                             // FP8 V: 64 keys of tile t are columns t * 64 of [128 dims] rows; each
                             // half is its own tile of 64-byte rows.
@@ -229,8 +308,6 @@ __global__ void __launch_bounds__(THREADS, 2)
                 if (!alive) {
                     break;
                 }
-                tiles_now[0] = tiles_next[0];
-                tiles_now[1] = tiles_next[1];
             }
         }
     } else if (warp == MMA_WARP) {
@@ -247,52 +324,65 @@ __global__ void __launch_bounds__(THREADS, 2)
                                                    PAIR, HEAD_DIM)
                           : instruction_descriptor(ACCUMULATE_F32, FORMAT_BF16, FORMAT_BF16, 0, 1,
                                                    PAIR, HEAD_DIM);
+            // A shared step scores all 128 rows against one key tile: 64 columns instead of 128.
+            constexpr uint32_t SHARED_SCORE_MMA =
+                QUANTIZED ? instruction_descriptor(ACCUMULATE_S32, FORMAT_S8, FORMAT_S8, 0, 0,
+                                                   PAIR, TILE)
+                          : instruction_descriptor(ACCUMULATE_F32, FORMAT_BF16, FORMAT_BF16, 0, 0,
+                                                   PAIR, TILE);
             const uint64_t query_operand = smem_descriptor(query_tile, 16, 1024);
-            auto score = [&](uint32_t key_tile) {
+            auto score = [&](uint32_t key_tile, bool shared) {
                 const uint64_t key_operand = smem_descriptor(key_tile, 16, 1024);
+                const uint32_t shape = shared ? SHARED_SCORE_MMA : SCORE_MMA;
                 if constexpr (QUANTIZED) {
                     #pragma unroll
                     for (int step = 0; step < HEAD_DIM / 32; step++) {
                         mma_i8_ss(tmem + TMEM_SCORES, advance_descriptor(query_operand, step * 32),
-                                  advance_descriptor(key_operand, step * 32), SCORE_MMA, step > 0);
+                                  advance_descriptor(key_operand, step * 32), shape, step > 0);
                     }
                 } else {
                     #pragma unroll
                     for (int step = 0; step < HEAD_DIM / 16; step++) {
                         const uint32_t offset = (step / 4) * (PAIR * 128) + (step % 4) * 32;
                         mma_f16_ss(tmem + TMEM_SCORES, advance_descriptor(query_operand, offset),
-                                   advance_descriptor(key_operand, offset), SCORE_MMA, step > 0);
+                                   advance_descriptor(key_operand, offset), shape, step > 0);
                     }
                 }
                 tcgen05_commit(barrier(S::SCORES_FULL));
             };
-            auto accumulate = [&](uint32_t value_tile, bool first) {
+            // `keys` of P and V take part: 128, or the 64 of a shared step.
+            auto accumulate = [&](uint32_t value_tile, bool first, int keys) {
                 if constexpr (QUANTIZED) {
                     // Two tiles of [128 dims][64 keys] in the 64-byte swizzle.
                     const uint64_t operand = smem_descriptor(value_tile, 16, 512, SWIZZLE_64B);
                     #pragma unroll
                     for (int step = 0; step < PAIR / 32; step++) {
-                        mma_f8_ts(tmem + TMEM_OUTPUT, tmem + TMEM_SCORES + step * 8,
-                                  advance_descriptor(operand, (step / 2) * (HEAD_DIM * TILE) +
-                                                                  (step % 2) * 32),
-                                  OUTPUT_MMA, !first || step > 0);
+                        if (step * 32 < keys) {
+                            mma_f8_ts(tmem + TMEM_OUTPUT, tmem + TMEM_SCORES + step * 8,
+                                      advance_descriptor(operand, (step / 2) * (HEAD_DIM * TILE) +
+                                                                      (step % 2) * 32),
+                                      OUTPUT_MMA, !first || step > 0);
+                        }
                     }
                 } else {
                     const uint64_t operand = smem_descriptor(value_tile, PAIR * 128, 1024);
                     #pragma unroll
                     for (int step = 0; step < PAIR / 16; step++) {
-                        mma_f16_ts(tmem + TMEM_OUTPUT, tmem + TMEM_SCORES + step * 8,
-                                   advance_descriptor(operand, step * 16 * 128), OUTPUT_MMA,
-                                   !first || step > 0);
+                        if (step * 16 < keys) {
+                            mma_f16_ts(tmem + TMEM_OUTPUT, tmem + TMEM_SCORES + step * 8,
+                                       advance_descriptor(operand, step * 16 * 128), OUTPUT_MMA,
+                                       !first || step > 0);
+                        }
                     }
                 }
             };
             bool alive = steps == 0 ||
                          (mbar_wait(barrier(S::QUERY_FULL), 0, watchdog, STATUS_VSA | 2) &&
                           mbar_wait(barrier(S::RING_FULL + 0), 0, watchdog, STATUS_VSA | 3));
+            // Step `step` is shared while step < common: the shared ones come first.
             if (alive && steps > 0) {
                 tcgen05_fence_after();
-                score(ring);
+                score(ring, 0 < common);
                 tcgen05_commit(barrier(S::RING_EMPTY + 0));
             }
             int item = 1;
@@ -311,10 +401,11 @@ __global__ void __launch_bounds__(THREADS, 2)
                     break;
                 }
                 tcgen05_fence_after();
-                accumulate(ring + value_stage * S::TILE_BYTES, step == 0);
+                accumulate(ring + value_stage * S::TILE_BYTES, step == 0,
+                           step < common ? TILE : PAIR);
                 tcgen05_commit(barrier(S::RING_EMPTY + value_stage));
                 if (more) {
-                    score(ring + key_stage * S::TILE_BYTES);
+                    score(ring + key_stage * S::TILE_BYTES, step + 1 < common);
                     tcgen05_commit(barrier(S::RING_EMPTY + key_stage));
                 }
             }
@@ -330,12 +421,11 @@ __global__ void __launch_bounds__(THREADS, 2)
         const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
         // The 64 columns of S that hold this tile's keys, and where its P goes: BF16 P packs two
         // keys to a column (own keys in 32 columns), E4M3 P four (16 columns).
-        const uint32_t scores = tmem + lane_base + TMEM_SCORES + half * TILE;
+        // In a shared step both tiles' threads read columns 0-63 and P fills the first columns
+        // alone.
+        const uint32_t score_columns = tmem + lane_base + TMEM_SCORES;
         constexpr int P_COLUMNS = QUANTIZED ? TILE / 4 : TILE / 2;
-        const uint32_t own_p = tmem + lane_base + TMEM_SCORES + half * P_COLUMNS;
-        const uint32_t other_p = tmem + lane_base + TMEM_SCORES + (1 - half) * P_COLUMNS;
         const uint32_t accumulator = tmem + lane_base + TMEM_OUTPUT;
-        const uint16_t *route = p.routes + route_rows[half] * p.tiles;
         float query_factor = p.scale_log2;
         const float *head_key_scales = nullptr;
         if constexpr (QUANTIZED) {
@@ -344,16 +434,21 @@ __global__ void __launch_bounds__(THREADS, 2)
         }
         float maximum = -INFINITY;
         float2 sums[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
-        int key_tile = count > 0 ? route[0] : 0;
         bool alive = true;
+        Cursors cursors = {{0, 0}};
         for (int step = 0; step < steps; step++) {
-            const bool active = step < count;
+            int tiles_now[2];
+            const bool shared = next_step(step, cursors, tiles_now);
+            const int key_tile = tiles_now[half];
+            const bool active = key_tile >= 0;
             const int valid = active ? tile_length(key_tile) : 0;
             float factor = query_factor;
             if constexpr (QUANTIZED) {
                 factor *= active ? __ldg(head_key_scales + key_tile) : 0.0f;
             }
-            key_tile = step + 1 < count ? route[step + 1] : 0;
+            const uint32_t scores = score_columns + (shared ? 0 : half * TILE);
+            const uint32_t own_p = score_columns + (shared ? 0 : half * P_COLUMNS);
+            const uint32_t other_p = score_columns + (1 - half) * P_COLUMNS;
             alive = mbar_wait(barrier(S::SCORES_FULL), step & 1, watchdog, STATUS_VSA | 7);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) {
@@ -467,10 +562,14 @@ __global__ void __launch_bounds__(THREADS, 2)
                 }
                 if constexpr (QUANTIZED) {
                     tmem_store_16(own_p, packed);
-                    tmem_store_16(other_p, zeroes);
+                    if (!shared) {
+                        tmem_store_16(other_p, zeroes);
+                    }
                 } else {
                     tmem_store_32(own_p, packed);
-                    tmem_store_32(other_p, zeroes);
+                    if (!shared) {
+                        tmem_store_32(other_p, zeroes);
+                    }
                 }
             };
             if (valid < TILE) {
