@@ -188,28 +188,45 @@ __global__ void __launch_bounds__(THREADS, 2)
         __syncthreads();
     }
     const int common = compared ? common_tiles : 0;
-    const int steps = max(counts[0], counts[1]);
-    // The schedule every role walks: first the `common` tiles of both lists, one to a step (found
-    // by scanning list 0 for entries list 1 also holds); then the remaining entries of the two
-    // lists, paired in order. `cursors` are positions in the two lists.
+    // The schedule every role walks. First the `common` tiles, two to a step (both query tiles
+    // against both key tiles: a full 128 x 128 block of S), then the odd one left over alone (a
+    // 128 x 64 block), then the remaining entries of the two lists paired in order, each query
+    // tile against its own key tile (the diagonal 64 x 64 blocks of S).
+    const int double_steps = common / 2;
+    const int single_steps = common % 2;
+    const int steps = double_steps + single_steps + max(counts[0], counts[1]) - common;
+    enum StepKind { BOTH_BOTH, BOTH_ONE, OWN };
+    auto step_kind = [&](int step) {
+        return step < double_steps ? BOTH_BOTH
+                                   : (step < double_steps + single_steps ? BOTH_ONE : OWN);
+    };
     auto in_list = [&](int half, int tile) {
         return (bitmaps[half * BITMAP_WORDS + tile / 32] >> (tile % 32)) & 1u;
     };
+    // Positions in the two route lists.
     struct Cursors {
         int at[2];
     };
-    // The key tiles of step `step` (-1: none), and whether it is a step both query tiles share.
+    // The key tiles of step `step` (-1: none). For the kinds that share, both come from list 0
+    // (the next entries that list 1 also holds); BOTH_ONE fills only tiles[0].
     auto next_step = [&](int step, Cursors &cursors, int (&tiles)[2]) {
-        if (step < common) {
+        const StepKind kind = step_kind(step);
+        if (kind != OWN) {
             int entry = cursors.at[0];
-            while (!in_list(1, lists[0][entry])) {
+            for (int slot = 0; slot < (kind == BOTH_BOTH ? 2 : 1); slot++) {
+                while (!in_list(1, lists[0][entry])) {
+                    entry++;
+                }
+                tiles[slot] = lists[0][entry];
                 entry++;
             }
-            tiles[0] = tiles[1] = lists[0][entry];
-            cursors.at[0] = entry + 1;
-            return true;
+            if (kind == BOTH_ONE) {
+                tiles[1] = -1;
+            }
+            cursors.at[0] = entry;
+            return kind;
         }
-        if (step == common) {
+        if (step == double_steps + single_steps) {
             cursors.at[0] = cursors.at[1] = 0;
         }
         #pragma unroll
@@ -223,7 +240,7 @@ __global__ void __launch_bounds__(THREADS, 2)
             tiles[half] = entry < counts[half] ? lists[half][entry] : -1;
             cursors.at[half] = entry + 1;
         }
-        return false;
+        return kind;
     };
 
     if (threadIdx.x == 0) {
@@ -271,9 +288,10 @@ __global__ void __launch_bounds__(THREADS, 2)
             Cursors cursors = {{0, 0}};
             for (int step = 0; step < steps; step++) {
                 int tiles_now[2];
-                const bool shared = next_step(step, cursors, tiles_now);
-                // A shared step fills only the first half of the stage: one key tile for both.
-                const int halves = shared ? 1 : 2;
+                const StepKind kind = next_step(step, cursors, tiles_now);
+                // A step with one key tile for both query tiles fills only the first half of the
+                // stage.
+                const int halves = kind == BOTH_ONE ? 1 : 2;
                 int rows[2];
                 for (int half = 0; half < 2; half++) {
                     rows[half] = tiles_now[half] >= 0 ? tile_start(tiles_now[half]) : p.tokens;
@@ -379,10 +397,9 @@ __global__ void __launch_bounds__(THREADS, 2)
             bool alive = steps == 0 ||
                          (mbar_wait(barrier(S::QUERY_FULL), 0, watchdog, STATUS_VSA | 2) &&
                           mbar_wait(barrier(S::RING_FULL + 0), 0, watchdog, STATUS_VSA | 3));
-            // Step `step` is shared while step < common: the shared ones come first.
             if (alive && steps > 0) {
                 tcgen05_fence_after();
-                score(ring, 0 < common);
+                score(ring, step_kind(0) == BOTH_ONE);
                 tcgen05_commit(barrier(S::RING_EMPTY + 0));
             }
             int item = 1;
@@ -402,10 +419,10 @@ __global__ void __launch_bounds__(THREADS, 2)
                 }
                 tcgen05_fence_after();
                 accumulate(ring + value_stage * S::TILE_BYTES, step == 0,
-                           step < common ? TILE : PAIR);
+                           step_kind(step) == BOTH_ONE ? TILE : PAIR);
                 tcgen05_commit(barrier(S::RING_EMPTY + value_stage));
                 if (more) {
-                    score(ring + key_stage * S::TILE_BYTES, step + 1 < common);
+                    score(ring + key_stage * S::TILE_BYTES, step_kind(step + 1) == BOTH_ONE);
                     tcgen05_commit(barrier(S::RING_EMPTY + key_stage));
                 }
             }
@@ -434,148 +451,185 @@ __global__ void __launch_bounds__(THREADS, 2)
         }
         float maximum = -INFINITY;
         float2 sums[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+        bool first_pass = true;
+        // MASKED below: the key tile is shorter than 64 (or this list has ended), so the columns past
+        // its length take an exponent of minus infinity. Warps 0-1 and 2-3 may serve different key
+        // tiles, but a warp serves one, so the choice is uniform across a warp.
+        //
+        // The running maximum takes 64 scores in, and O and the sums are rescaled if it grew too
+        // far.
+        auto take_maximum = [&](auto masked, const uint32_t (&raw)[2][32], int valid, float factor,
+                                bool active) {
+            constexpr bool MASKED = decltype(masked)::value;
+            // The block maximum in the units of the exponent: scale * log2(e) times the score.
+            float block_maximum;
+            if constexpr (QUANTIZED) {
+                int partial[2] = {INT_MIN, INT_MIN};
+                #pragma unroll
+                for (int index = 0; index + 1 < TILE; index += 2) {
+                    const int first = static_cast<int>(raw[index / 32][index % 32]);
+                    const int second = static_cast<int>(raw[(index + 1) / 32][(index + 1) % 32]);
+                    partial[(index / 2) % 2] = __vimax3_s32(
+                        partial[(index / 2) % 2], MASKED && index >= valid ? INT_MIN : first,
+                        MASKED && index + 1 >= valid ? INT_MIN : second);
+                }
+                const int largest = max(partial[0], partial[1]);
+                block_maximum =
+                    largest == INT_MIN ? -INFINITY : static_cast<float>(largest) * factor;
+            } else {
+                float partial[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                #pragma unroll
+                for (int index = 0; index < TILE; index++) {
+                    const float score = __uint_as_float(raw[index / 32][index % 32]);
+                    partial[index % 4] =
+                        fmaxf(partial[index % 4], MASKED && index >= valid ? -INFINITY : score);
+                }
+                block_maximum =
+                    fmaxf(fmaxf(partial[0], partial[1]), fmaxf(partial[2], partial[3])) * factor;
+            }
+            // The first step of a list always has keys, so the maximum is finite from then on.
+            const bool grown = active && block_maximum - maximum > RESCALE_LAG<QUANTIZED>;
+            if (first_pass) {
+                maximum = active ? block_maximum : 0.0f;
+            } else if (__any_sync(0xffffffffu, grown)) {
+                const float raised = fmaxf(maximum, block_maximum);
+                const float correction = exp2_approx(maximum - raised);
+                maximum = raised;
+                const float2 correction2 = make_float2(correction, correction);
+                sums[0] = __fmul2_rn(sums[0], correction2);
+                sums[1] = __fmul2_rn(sums[1], correction2);
+                #pragma unroll
+                for (int chunk = 0; chunk < 4; chunk++) {
+                    uint32_t values[32];
+                    tmem_load_32(accumulator + chunk * 32, values);
+                    tmem_wait_load();
+                    #pragma unroll
+                    for (int index = 0; index < 32; index++) {
+                        values[index] =
+                            __float_as_uint(__uint_as_float(values[index]) * correction);
+                    }
+                    tmem_store_32(accumulator + chunk * 32, values);
+                }
+            }
+            first_pass = false;
+        };
+        // The probabilities of 64 scores against the running maximum go to `own_p`, and zeroes to
+        // `other_p` when the other query tile has its own key tile in this step.
+        auto write_probabilities = [&](auto masked, const uint32_t (&raw)[2][32], int valid,
+                                       float factor, uint32_t own_p, uint32_t other_p,
+                                       bool shared) {
+            constexpr bool MASKED = decltype(masked)::value;
+            // p = 2^(factor * score - maximum), times 224 for E4M3; pairs of elements, one
+            // pair in four on the polynomial.
+            const float offset = QUANTIZED ? LOG2_224 - maximum : -maximum;
+            const float2 factor2 = make_float2(factor, factor);
+            const float2 offset2 = make_float2(offset, offset);
+            constexpr int WORDS = QUANTIZED ? TILE / 4 : TILE / 2;
+            uint32_t packed[WORDS], zeroes[WORDS];
+            #pragma unroll
+            for (int pair = 0; pair < TILE / 2; pair++) {
+                const uint32_t words[2] = {raw[(pair * 2) / 32][(pair * 2) % 32],
+                                           raw[(pair * 2 + 1) / 32][(pair * 2 + 1) % 32]};
+                const float2 score =
+                    QUANTIZED ? make_float2(static_cast<float>(static_cast<int32_t>(words[0])),
+                                            static_cast<float>(static_cast<int32_t>(words[1])))
+                              : make_float2(__uint_as_float(words[0]),
+                                            __uint_as_float(words[1]));
+                float2 x = __ffma2_rn(score, factor2, offset2);
+                if (MASKED) {
+                    x.x = pair * 2 < valid ? x.x : -INFINITY;
+                    x.y = pair * 2 + 1 < valid ? x.y : -INFINITY;
+                }
+                float2 probability;
+                if (pair % 4 < POLYNOMIAL_PAIRS_OF_4) {
+                    probability = exp2_polynomial(x);
+                } else {
+                    probability = make_float2(exp2_approx(x.x), exp2_approx(x.y));
+                }
+                sums[pair % 2] = __fadd2_rn(sums[pair % 2], probability);
+                if constexpr (QUANTIZED) {
+                    uint16_t two;
+                    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;"
+                        : "=h"(two)
+                        : "f"(probability.y), "f"(probability.x));
+                    if (pair % 2 == 0) {
+                        packed[pair / 2] = two;
+                    } else {
+                        packed[pair / 2] |= static_cast<uint32_t>(two) << 16;
+                    }
+                } else {
+                    packed[pair] = pack_bf16(probability.x, probability.y);
+                }
+            }
+            #pragma unroll
+            for (int word = 0; word < WORDS; word++) {
+                zeroes[word] = 0;
+            }
+            if constexpr (QUANTIZED) {
+                tmem_store_16(own_p, packed);
+                if (!shared) {
+                    tmem_store_16(other_p, zeroes);
+                }
+            } else {
+                tmem_store_32(own_p, packed);
+                if (!shared) {
+                    tmem_store_32(other_p, zeroes);
+                }
+            }
+        };
         bool alive = true;
         Cursors cursors = {{0, 0}};
         for (int step = 0; step < steps; step++) {
             int tiles_now[2];
-            const bool shared = next_step(step, cursors, tiles_now);
-            const int key_tile = tiles_now[half];
-            const bool active = key_tile >= 0;
-            const int valid = active ? tile_length(key_tile) : 0;
-            float factor = query_factor;
-            if constexpr (QUANTIZED) {
-                factor *= active ? __ldg(head_key_scales + key_tile) : 0.0f;
-            }
-            const uint32_t scores = score_columns + (shared ? 0 : half * TILE);
-            const uint32_t own_p = score_columns + (shared ? 0 : half * P_COLUMNS);
-            const uint32_t other_p = score_columns + (1 - half) * P_COLUMNS;
+            const StepKind kind = next_step(step, cursors, tiles_now);
             alive = mbar_wait(barrier(S::SCORES_FULL), step & 1, watchdog, STATUS_VSA | 7);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) {
                 break;
             }
             tcgen05_fence_after();
-            uint32_t raw[2][32];
-            tmem_load_32(scores, raw[0]);
-            tmem_load_32(scores + 32, raw[1]);
-            tmem_wait_load();
-            // MASKED: the key tile is shorter than 64 (or this list has ended), so the columns
-            // past its length take an exponent of minus infinity. Warps 0-1 and 2-3 serve
-            // different tiles, but a warp serves one, so the choice is uniform across a warp.
-            auto softmax_step = [&](auto masked) {
-                constexpr bool MASKED = decltype(masked)::value;
-                // The block maximum in the units of the exponent: scale * log2(e) times the score.
-                float block_maximum;
+            // A thread takes 64 columns of S at a time: its own tile's key tile in a step of kind
+            // OWN (and zeroes go into the other tile's columns of P); the one key tile of a
+            // BOTH_ONE step; and both key tiles, one after the other, in a BOTH_BOTH step.
+            // BOTH_BOTH: passes 0 and 1 take the two key tiles into the maximum, passes 2 and 3 write
+            // their probabilities.
+            const int passes = kind == BOTH_BOTH ? 4 : 1;
+            for (int pass = 0; pass < passes; pass++) {
+                const bool maximum_phase = kind != BOTH_BOTH || pass < 2;
+                const bool probability_phase = kind != BOTH_BOTH || pass >= 2;
+                const int slot = kind == OWN ? half : pass % 2;
+                const bool shared = kind != OWN;
+                const int key_tile = tiles_now[slot];
+                const bool active = key_tile >= 0;
+                const int valid = active ? tile_length(key_tile) : 0;
+                float factor = query_factor;
                 if constexpr (QUANTIZED) {
-                    int partial[2] = {INT_MIN, INT_MIN};
-                    #pragma unroll
-                    for (int index = 0; index + 1 < TILE; index += 2) {
-                        const int first = static_cast<int>(raw[index / 32][index % 32]);
-                        const int second = static_cast<int>(raw[(index + 1) / 32][(index + 1) % 32]);
-                        partial[(index / 2) % 2] = __vimax3_s32(
-                            partial[(index / 2) % 2], MASKED && index >= valid ? INT_MIN : first,
-                            MASKED && index + 1 >= valid ? INT_MIN : second);
-                    }
-                    const int largest = max(partial[0], partial[1]);
-                    block_maximum =
-                        largest == INT_MIN ? -INFINITY : static_cast<float>(largest) * factor;
-                } else {
-                    float partial[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-                    #pragma unroll
-                    for (int index = 0; index < TILE; index++) {
-                        const float score = __uint_as_float(raw[index / 32][index % 32]);
-                        partial[index % 4] =
-                            fmaxf(partial[index % 4], MASKED && index >= valid ? -INFINITY : score);
-                    }
-                    block_maximum =
-                        fmaxf(fmaxf(partial[0], partial[1]), fmaxf(partial[2], partial[3])) * factor;
+                    factor *= active ? __ldg(head_key_scales + key_tile) : 0.0f;
                 }
-                // The first step of a list always has keys, so the maximum is finite from then on.
-                const bool grown = active && block_maximum - maximum > RESCALE_LAG<QUANTIZED>;
-                if (step == 0) {
-                    maximum = active ? block_maximum : 0.0f;
-                } else if (__any_sync(0xffffffffu, grown)) {
-                    const float raised = fmaxf(maximum, block_maximum);
-                    const float correction = exp2_approx(maximum - raised);
-                    maximum = raised;
-                    const float2 correction2 = make_float2(correction, correction);
-                    sums[0] = __fmul2_rn(sums[0], correction2);
-                    sums[1] = __fmul2_rn(sums[1], correction2);
-                    #pragma unroll
-                    for (int chunk = 0; chunk < 4; chunk++) {
-                        uint32_t values[32];
-                        tmem_load_32(accumulator + chunk * 32, values);
-                        tmem_wait_load();
-                        #pragma unroll
-                        for (int index = 0; index < 32; index++) {
-                            values[index] =
-                                __float_as_uint(__uint_as_float(values[index]) * correction);
-                        }
-                        tmem_store_32(accumulator + chunk * 32, values);
+                const uint32_t scores = score_columns + slot * TILE;
+                const uint32_t own_p = score_columns + slot * P_COLUMNS;
+                const uint32_t other_p = score_columns + (1 - half) * P_COLUMNS;
+                uint32_t raw[2][32];
+                tmem_load_32(scores, raw[0]);
+                tmem_load_32(scores + 32, raw[1]);
+                tmem_wait_load();
+                if (valid < TILE) {
+                    if (maximum_phase) {
+                        take_maximum(std::true_type{}, raw, valid, factor, active);
                     }
-                }
-                // p = 2^(factor * score - maximum), times 224 for E4M3; pairs of elements, one
-                // pair in four on the polynomial.
-                const float offset = QUANTIZED ? LOG2_224 - maximum : -maximum;
-                const float2 factor2 = make_float2(factor, factor);
-                const float2 offset2 = make_float2(offset, offset);
-                constexpr int WORDS = QUANTIZED ? TILE / 4 : TILE / 2;
-                uint32_t packed[WORDS], zeroes[WORDS];
-                #pragma unroll
-                for (int pair = 0; pair < TILE / 2; pair++) {
-                    const uint32_t words[2] = {raw[(pair * 2) / 32][(pair * 2) % 32],
-                                               raw[(pair * 2 + 1) / 32][(pair * 2 + 1) % 32]};
-                    const float2 score =
-                        QUANTIZED ? make_float2(static_cast<float>(static_cast<int32_t>(words[0])),
-                                                static_cast<float>(static_cast<int32_t>(words[1])))
-                                  : make_float2(__uint_as_float(words[0]),
-                                                __uint_as_float(words[1]));
-                    float2 x = __ffma2_rn(score, factor2, offset2);
-                    if (MASKED) {
-                        x.x = pair * 2 < valid ? x.x : -INFINITY;
-                        x.y = pair * 2 + 1 < valid ? x.y : -INFINITY;
-                    }
-                    float2 probability;
-                    if (pair % 4 < POLYNOMIAL_PAIRS_OF_4) {
-                        probability = exp2_polynomial(x);
-                    } else {
-                        probability = make_float2(exp2_approx(x.x), exp2_approx(x.y));
-                    }
-                    sums[pair % 2] = __fadd2_rn(sums[pair % 2], probability);
-                    if constexpr (QUANTIZED) {
-                        uint16_t two;
-                        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;"
-                            : "=h"(two)
-                            : "f"(probability.y), "f"(probability.x));
-                        if (pair % 2 == 0) {
-                            packed[pair / 2] = two;
-                        } else {
-                            packed[pair / 2] |= static_cast<uint32_t>(two) << 16;
-                        }
-                    } else {
-                        packed[pair] = pack_bf16(probability.x, probability.y);
-                    }
-                }
-                #pragma unroll
-                for (int word = 0; word < WORDS; word++) {
-                    zeroes[word] = 0;
-                }
-                if constexpr (QUANTIZED) {
-                    tmem_store_16(own_p, packed);
-                    if (!shared) {
-                        tmem_store_16(other_p, zeroes);
+                    if (probability_phase) {
+                        write_probabilities(std::true_type{}, raw, valid, factor, own_p, other_p,
+                                            shared);
                     }
                 } else {
-                    tmem_store_32(own_p, packed);
-                    if (!shared) {
-                        tmem_store_32(other_p, zeroes);
+                    if (maximum_phase) {
+                        take_maximum(std::false_type{}, raw, valid, factor, active);
+                    }
+                    if (probability_phase) {
+                        write_probabilities(std::false_type{}, raw, valid, factor, own_p, other_p,
+                                            shared);
                     }
                 }
-            };
-            if (valid < TILE) {
-                softmax_step(std::true_type{});
-            } else {
-                softmax_step(std::false_type{});
             }
             tmem_wait_store();
             tcgen05_fence_before();

@@ -7,8 +7,9 @@
 // over a balanced tree that pairs chains by bit 4 of l first and by bit 0 last, then one multiply
 // by the scale. Here one thread evaluates that whole tree: it holds one pooled key in registers and
 // scores it against each of its CTA's eight query tiles, whose pooled queries sit in shared memory
-// regrouped by chain; the reference spreads a score over the lanes of a warp. The selection itself is a function of the scores alone, so it is free
-// to differ: here a warp finds the kept-th largest video score with a four-pass radix select over
+// regrouped by chain; the reference spreads a score over the lanes of a warp. The selection itself
+// is a function of the scores alone, so it is free to differ: here a warp finds the kept-th
+// largest video score with a four-pass radix select over
 // order-preserving integer keys (the reference descends one bit at a time), ties go to the lower
 // tile index, and the route is an ascending list of uint16 tile indices.
 #include <cfloat>
