@@ -85,7 +85,8 @@ class VsaWorkspaceStruct(ctypes.Structure):
 
 P = ctypes.POINTER
 
-# name -> argument types, in the order of include/mmh3_attention.h. Every function returns int.
+# name -> argument types, in the order of include/mmh3_attention.h and
+# include/mmh3_int8_gemm.h. Every function returns int.
 SIGNATURES = {
     "mmh3_attention": [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                        P(AttentionLayout), c_float, c_void_p],
@@ -114,6 +115,15 @@ SIGNATURES = {
     "mmh3_dit_shard_pack": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_void_p],
     "mmh3_dit_shard_unpack": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    # include/mmh3_int8_gemm.h
+    "mmh3_int8_gemm_config_count": [],
+    "mmh3_int8_gemm_group_heights": [c_void_p, c_int],
+    "mmh3_int8_gemm_bf16": [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                            c_int, c_int, c_void_p],
+    "mmh3_int8_gemm": [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                       c_float, c_void_p, c_int, c_void_p],
+    "mmh3_interleave_swiglu_rows": [c_void_p, c_void_p, c_int, c_int, c_void_p],
     "mmh3_b200_attention_quantized_static": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                              P(AttentionLayout), c_float, c_void_p],
     "mmh3_b200_take_status": [],

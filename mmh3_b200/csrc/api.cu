@@ -196,3 +196,54 @@ extern "C" int mmh3_dit_shard_unpack(const void *part, void *output, int tokens,
     return launch_shard_unpack(part, output, tokens, heads, dim, first_head, span,
                                as_stream(stream));
 }
+
+// The band heights a caller may name, as crates/mmh3-cuda/kernels/int8_gemm.cu:735.
+static constexpr int GROUP_HEIGHTS[] = {4, 8, 16};
+
+extern "C" int mmh3_int8_gemm_config_count(void) { return 2; }
+
+extern "C" int mmh3_int8_gemm_group_heights(int *heights, int capacity) {
+    constexpr int COUNT = sizeof(GROUP_HEIGHTS) / sizeof(GROUP_HEIGHTS[0]);
+    for (int index = 0; index < COUNT && index < capacity; index++) {
+        heights[index] = GROUP_HEIGHTS[index];
+    }
+    return COUNT;
+}
+
+extern "C" int mmh3_int8_gemm(int config, int group_m, const int8_t *activations,
+                              const int8_t *weights, const float *activation_scales,
+                              const float *weight_scales, const float *bias, void *output,
+                              int output_is_f16, int swiglu, int m, int n, int k,
+                              int output_stride, const void *adapter_down, const void *adapter_up,
+                              int rank, int adapter_down_stride, float adapter_scale,
+                              unsigned *column_maxima, int maxima_first_column,
+                              mmh3_stream_t stream) {
+    (void)adapter_up;
+    (void)rank;
+    (void)adapter_down_stride;
+    (void)adapter_scale;
+    if (activations == nullptr || weights == nullptr || activation_scales == nullptr ||
+        weight_scales == nullptr || output == nullptr) {
+        return INVALID_VALUE;
+    }
+    if (adapter_down != nullptr) {
+        return NOT_SUPPORTED;
+    }
+    return launch_int8_gemm(config, group_m, activations, weights, activation_scales,
+                            weight_scales, bias, output, output_is_f16 != 0, swiglu != 0, m, n, k,
+                            output_stride, column_maxima, maxima_first_column, as_stream(stream));
+}
+
+extern "C" int mmh3_int8_gemm_bf16(int config, int group_m, const int8_t *activations,
+                                   const int8_t *weights, const float *activation_scales,
+                                   const float *weight_scales, void *output, int m, int n, int k,
+                                   mmh3_stream_t stream) {
+    return mmh3_int8_gemm(config, group_m, activations, weights, activation_scales, weight_scales,
+                          nullptr, output, 0, 0, m, n, k, n, nullptr, nullptr, 0, 0, 0.0f, nullptr,
+                          0, stream);
+}
+
+extern "C" int mmh3_interleave_swiglu_rows(const void *source, void *destination, int rows,
+                                           int row_bytes, mmh3_stream_t stream) {
+    return launch_interleave_swiglu_rows(source, destination, rows, row_bytes, as_stream(stream));
+}

@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/mmh3_attention.h"
+#include "../../include/mmh3_int8_gemm.h"
 
 namespace mmh3 {
 
@@ -148,6 +149,15 @@ int launch_sol_token_attention_quantized(const Mmh3QuantizedWorkspace &workspace
                                          int tokens, int heads, const Mmh3AttentionLayout &layout,
                                          float scale, const Mmh3SparseWorkspace &sparse,
                                          cudaStream_t stream);
+
+// int8_gemm.cu: the scaled INT8 product with its optional bias, SwiGLU and column maxima.
+int launch_int8_gemm(int config, int group_m, const int8_t *activations, const int8_t *weights,
+                     const float *activation_scales, const float *weight_scales, const float *bias,
+                     void *output, bool output_is_f16, bool swiglu, int m, int n, int k,
+                     int output_stride, unsigned *column_maxima, int maxima_first_column,
+                     cudaStream_t stream);
+int launch_interleave_swiglu_rows(const void *source, void *destination, int rows, int row_bytes,
+                                  cudaStream_t stream);
 
 // shard.cu
 int launch_shard_pack(const void *source, void *packed, int tokens, int tensors, int heads, int dim,

@@ -1,0 +1,474 @@
+// The scaled INT8 GEMM of the DiT's linear layers, as the step before attention uses it: the fused
+// qkv projection, which also leaves the maximum |v| of each head for the FP8 quantisation of V.
+//
+//   output[r, c] = round((sum_k activations[r, k] * weights[c, k]) * activation_scales[r]
+//                        * weight_scales[c] + bias[c])
+//
+// rounded once to BF16 or FP16, activations [m, k] and weights [n, k] INT8 with K contiguous. It
+// replaces crates/mmh3-cuda/kernels/int8_gemm.cu:321-591 (mma.sync over a two-stage ring) and
+// keeps its arithmetic: the integer sums are exact, and the FP32 operations after them are the
+// same in the same order, so the outputs and the column maxima are the same bits.
+//
+// One persistent CTA per SM walks tiles of 256 rows by 256 columns in bands of rows of tiles, so
+// the CTAs in flight share rows of activations and columns of weights in L2. A tile is two
+// accumulators of 128 rows by 256 columns of INT32 in tensor memory (all 512 columns of the SM).
+// Warp 0 streams stages of 128 bytes of K (32 KB of activations, 32 KB of weights, 128-byte
+// swizzle) through a ring with TMA; one thread of warp 1 issues tcgen05.mma kind::i8 of
+// 128 x 256 x 32 from shared memory; eight warps scale, round and store the accumulators. At this
+// tile shape a stage of 64 KB feeds 1,024 cycles of MMA, 64 bytes a cycle, which is what an SM
+// can take from L2; a tile of 128 x 256 would leave room for a second pair of accumulators and an
+// epilogue hidden behind the next tile's MMAs, but needs 96 bytes a cycle.
+//
+// The second accumulator runs SKEW stages behind the first, so the first is complete, and the
+// epilogue warps are at work on it, while the MMAs of the second still run; at the other end the
+// MMAs of the next tile's first accumulator start while the second is still being stored.
+#include "common.cuh"
+#include "sm100.cuh"
+
+#include <cuda_fp16.h>
+
+namespace mmh3 {
+namespace {
+
+using namespace sm100;
+
+constexpr int TILE_M = 128;     // rows of one accumulator
+constexpr int ROW_TILES = 2;    // accumulators of a tile
+constexpr int TILE_N = 256;
+constexpr int BLOCK_K = 128;    // INT8 elements of one stage along K
+constexpr int STAGES = 3;
+constexpr int SKEW = 1;
+static_assert(SKEW < STAGES, "the ring must hold the stages between the two accumulators");
+constexpr int ROWS_BYTES = ROW_TILES * TILE_M * BLOCK_K;
+constexpr int COLUMNS_BYTES = TILE_N * BLOCK_K;
+constexpr int STAGE_BYTES = ROWS_BYTES + COLUMNS_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+
+constexpr int LOAD_WARP = 0;
+constexpr int MMA_WARP = 1;
+constexpr int FIRST_EPILOGUE_WARP = 2;
+constexpr int EPILOGUE_WARPS = 8;
+constexpr int THREADS = (FIRST_EPILOGUE_WARP + EPILOGUE_WARPS) * 32;
+constexpr int TMEM_COLUMNS = ROW_TILES * TILE_N;
+constexpr int CHUNK = 32; // columns of one tcgen05.ld
+
+constexpr unsigned int STATUS_GEMM = 0x00040000u;
+
+enum Barrier {
+    RING_FULL = 0,
+    RING_EMPTY = RING_FULL + STAGES,
+    ACCUMULATOR_FULL = RING_EMPTY + STAGES,
+    ACCUMULATOR_EMPTY = ACCUMULATOR_FULL + ROW_TILES,
+    BARRIERS = ACCUMULATOR_EMPTY + ROW_TILES,
+};
+
+constexpr uint32_t PRODUCT_MMA =
+    instruction_descriptor(ACCUMULATE_S32, FORMAT_S8, FORMAT_S8, 0, 0, TILE_M, TILE_N);
+
+struct GemmMaps {
+    CUtensorMap activations;
+    CUtensorMap weights;
+};
+
+struct TileWalk {
+    int tiles_m;
+    int tiles_n;
+    int band;
+
+    __device__ int tiles() const { return tiles_m * tiles_n; }
+
+    // Down a band of `band` rows of tiles, then one column of tiles to the right.
+    __device__ void locate(int tile, int &tile_m, int &tile_n) const {
+        const int band_tiles = band * tiles_n;
+        const int band_first = tile / band_tiles * band;
+        const int height = min(band, tiles_m - band_first);
+        const int within = tile - tile / band_tiles * band_tiles;
+        tile_m = band_first + within % height;
+        tile_n = within / height;
+    }
+};
+
+__device__ __forceinline__ uint32_t pack(__nv_bfloat16 *, float2 pair) {
+    return pack_bf16(pair.x, pair.y);
+}
+
+__device__ __forceinline__ uint32_t pack(__half *, float2 pair) {
+    const __half2 value = __floats2half2_rn(pair.x, pair.y);
+    return *reinterpret_cast<const uint32_t *>(&value);
+}
+
+__device__ __forceinline__ float2 unpack(__nv_bfloat16 *, uint32_t word) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&word));
+}
+
+__device__ __forceinline__ float2 unpack(__half *, uint32_t word) {
+    return __half22float2(*reinterpret_cast<const __half2 *>(&word));
+}
+
+// silu(gate) * up of two features from their rounded products, rounded again, as
+// crates/mmh3-cuda/kernels/int8_gemm.cu:297-305 computes it.
+template <typename Output>
+__device__ __forceinline__ uint32_t gated_pair(Output *output, uint32_t gate_word,
+                                               uint32_t up_word) {
+    const float2 gate = unpack(output, gate_word);
+    const float2 up = unpack(output, up_word);
+    return pack(output, make_float2(gate.x / (1.0f + __expf(-gate.x)) * up.x,
+                                    gate.y / (1.0f + __expf(-gate.y)) * up.y));
+}
+
+template <typename Output, bool SWIGLU>
+__global__ void __launch_bounds__(THREADS, 1)
+    int8_gemm_kernel(const __grid_constant__ GemmMaps maps,
+                     const float *__restrict__ activation_scales,
+                     const float *__restrict__ weight_scales, const float *__restrict__ bias,
+                     Output *__restrict__ output, int m, int n, int k_blocks, int output_stride,
+                     TileWalk walk, unsigned *maxima, int maxima_first_column,
+                     unsigned int *status) {
+    extern __shared__ uint8_t shared_raw[];
+    __shared__ __align__(8) uint64_t barriers[BARRIERS];
+    __shared__ uint32_t tmem_slot_storage;
+    __shared__ uint32_t abort_storage;
+    const uint32_t base = (smem_u32(shared_raw) + 1023u) & ~1023u;
+    volatile uint32_t *abort_flag = &abort_storage;
+    volatile uint32_t *tmem_slot = &tmem_slot_storage;
+    const Watchdog watchdog{abort_flag, status};
+    auto barrier = [&](int index) { return smem_u32(&barriers[index]); };
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    const int tiles = walk.tiles();
+
+    if (threadIdx.x == 0) {
+        for (int stage = 0; stage < STAGES; stage++) {
+            mbar_init(barrier(RING_FULL + stage), 1);
+            mbar_init(barrier(RING_EMPTY + stage), 1);
+        }
+        for (int half = 0; half < ROW_TILES; half++) {
+            mbar_init(barrier(ACCUMULATOR_FULL + half), 1);
+            mbar_init(barrier(ACCUMULATOR_EMPTY + half), EPILOGUE_WARPS);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == MMA_WARP) {
+        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), TMEM_COLUMNS);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == LOAD_WARP) {
+        if (lane == 0) {
+            tma_prefetch_descriptor(&maps.activations);
+            tma_prefetch_descriptor(&maps.weights);
+            int item = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; alive && tile < tiles; tile += gridDim.x) {
+                int tile_m, tile_n;
+                walk.locate(tile, tile_m, tile_n);
+                for (int k_block = 0; k_block < k_blocks; k_block++, item++) {
+                    const int stage = item % STAGES;
+                    const int use = item / STAGES;
+                    if (use > 0 && !mbar_wait(barrier(RING_EMPTY + stage), (use - 1) & 1,
+                                              watchdog, STATUS_GEMM | 1)) {
+                        alive = false;
+                        break;
+                    }
+                    const uint32_t destination = base + stage * STAGE_BYTES;
+                    mbar_expect_tx(barrier(RING_FULL + stage), STAGE_BYTES);
+                    tma_load_2d(destination, &maps.activations, barrier(RING_FULL + stage),
+                                k_block * BLOCK_K, tile_m * (ROW_TILES * TILE_M));
+                    tma_load_2d(destination + ROWS_BYTES, &maps.weights,
+                                barrier(RING_FULL + stage), k_block * BLOCK_K, tile_n * TILE_N);
+                }
+            }
+        }
+    } else if (warp == MMA_WARP) {
+        if (lane == 0) {
+            // The MMAs of one accumulator over one stage: four steps of 32 along K.
+            auto multiply = [&](int half, int stage, bool first) {
+                const uint32_t stage_base = base + stage * STAGE_BYTES;
+                const uint64_t rows =
+                    smem_descriptor(stage_base + half * (TILE_M * BLOCK_K), 16, 1024);
+                const uint64_t columns = smem_descriptor(stage_base + ROWS_BYTES, 16, 1024);
+                #pragma unroll
+                for (int step = 0; step < BLOCK_K / 32; step++) {
+                    mma_i8_ss(tmem + half * TILE_N, advance_descriptor(rows, step * 32),
+                              advance_descriptor(columns, step * 32), PRODUCT_MMA,
+                              !first || step > 0);
+                }
+            };
+            int first_item = 0;
+            int round = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; alive && tile < tiles;
+                 tile += gridDim.x, round++, first_item += k_blocks) {
+                for (int step = 0; alive && step < k_blocks + SKEW; step++) {
+                    if (step < k_blocks) {
+                        const int item = first_item + step;
+                        alive = mbar_wait(barrier(RING_FULL + item % STAGES),
+                                          (item / STAGES) & 1, watchdog, STATUS_GEMM | 2) &&
+                                (step > 0 || round == 0 ||
+                                 mbar_wait(barrier(ACCUMULATOR_EMPTY + 0), (round - 1) & 1,
+                                           watchdog, STATUS_GEMM | 3));
+                        if (!alive) {
+                            break;
+                        }
+                        tcgen05_fence_after();
+                        multiply(0, item % STAGES, step == 0);
+                        if (step == k_blocks - 1) {
+                            tcgen05_commit(barrier(ACCUMULATOR_FULL + 0));
+                        }
+                    }
+                    if (step >= SKEW) {
+                        const int k_block = step - SKEW;
+                        const int item = first_item + k_block;
+                        if (k_block == 0 && round > 0) {
+                            alive = mbar_wait(barrier(ACCUMULATOR_EMPTY + 1), (round - 1) & 1,
+                                              watchdog, STATUS_GEMM | 4);
+                            if (!alive) {
+                                break;
+                            }
+                            tcgen05_fence_after();
+                        }
+                        multiply(1, item % STAGES, k_block == 0);
+                        tcgen05_commit(barrier(RING_EMPTY + item % STAGES));
+                        if (k_block == k_blocks - 1) {
+                            tcgen05_commit(barrier(ACCUMULATOR_FULL + 1));
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        const int epilogue_warp = warp - FIRST_EPILOGUE_WARP;
+        // A warp reads the quarter of the lanes of tensor memory its number selects.
+        const int quarter = warp % 4;
+        const int column_half = epilogue_warp / 4;
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        int round = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; alive && tile < tiles; tile += gridDim.x, round++) {
+            int tile_m, tile_n;
+            walk.locate(tile, tile_m, tile_n);
+            // The warp's 128 columns lie in one group of 128.
+            const int first_column = tile_n * TILE_N + column_half * (TILE_N / 2);
+            const bool inside = first_column < n;
+            const bool track =
+                !SWIGLU && maxima != nullptr && inside && first_column >= maxima_first_column;
+            #pragma unroll 1
+            for (int half = 0; half < ROW_TILES; half++) {
+                alive = mbar_wait(barrier(ACCUMULATOR_FULL + half), round & 1, watchdog,
+                                  STATUS_GEMM | 5);
+                alive = __all_sync(0xffffffffu, alive);
+                if (!alive) {
+                    break;
+                }
+                tcgen05_fence_after();
+                const int row = tile_m * (ROW_TILES * TILE_M) + half * TILE_M + quarter * 32 + lane;
+                const bool stored = inside && row < m;
+                const float row_scale = row < m ? __ldg(activation_scales + row) : 0.0f;
+                const float2 row_scales = make_float2(row_scale, row_scale);
+                const uint32_t accumulator =
+                    tmem + lane_base + half * TILE_N + column_half * (TILE_N / 2);
+                Output *output_row = output + static_cast<size_t>(row) * output_stride;
+                uint32_t magnitudes = 0;
+                #pragma unroll 1
+                for (int chunk = 0; chunk < TILE_N / 2 / CHUNK; chunk += 2) {
+                    uint32_t products[2][CHUNK];
+                    tmem_load_32(accumulator + chunk * CHUNK, products[0]);
+                    tmem_load_32(accumulator + (chunk + 1) * CHUNK, products[1]);
+                    tmem_wait_load();
+                    if (!stored) {
+                        continue;
+                    }
+                    #pragma unroll
+                    for (int part = 0; part < 2; part++) {
+                        const int column = first_column + (chunk + part) * CHUNK;
+                        const float2 *column_scales =
+                            reinterpret_cast<const float2 *>(weight_scales + column);
+                        uint32_t words[CHUNK / 2];
+                        #pragma unroll
+                        for (int pair = 0; pair < CHUNK / 2; pair++) {
+                            float2 scaled = make_float2(
+                                static_cast<float>(static_cast<int32_t>(products[part][pair * 2])),
+                                static_cast<float>(
+                                    static_cast<int32_t>(products[part][pair * 2 + 1])));
+                            scaled = __fmul2_rn(__fmul2_rn(scaled, row_scales),
+                                                __ldg(column_scales + pair));
+                            if (bias != nullptr) {
+                                scaled = __fadd2_rn(
+                                    scaled,
+                                    __ldg(reinterpret_cast<const float2 *>(bias + column) + pair));
+                            }
+                            words[pair] = pack(output, scaled);
+                        }
+                        if constexpr (SWIGLU) {
+                            // Eight columns hold the gates of four features, then their up
+                            // projections: four outputs.
+                            uint2 *destination = reinterpret_cast<uint2 *>(output_row + column / 2);
+                            #pragma unroll
+                            for (int group = 0; group < CHUNK / 8; group++) {
+                                destination[group] = make_uint2(
+                                    gated_pair(output, words[group * 4], words[group * 4 + 2]),
+                                    gated_pair(output, words[group * 4 + 1], words[group * 4 + 3]));
+                            }
+                        } else {
+                            uint4 *destination = reinterpret_cast<uint4 *>(output_row + column);
+                            #pragma unroll
+                            for (int group = 0; group < CHUNK / 8; group++) {
+                                destination[group] =
+                                    make_uint4(words[group * 4], words[group * 4 + 1],
+                                               words[group * 4 + 2], words[group * 4 + 3]);
+                            }
+                            if (track) {
+                                // Magnitudes of BF16 values order like unsigned integers.
+                                #pragma unroll
+                                for (int pair = 0; pair < CHUNK / 2; pair++) {
+                                    magnitudes = __vmaxu2(magnitudes, words[pair] & 0x7fff7fffu);
+                                }
+                            }
+                        }
+                    }
+                }
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(barrier(ACCUMULATOR_EMPTY + half));
+                }
+                if (track) {
+                    const unsigned magnitude = __reduce_max_sync(
+                        0xffffffffu, max(magnitudes & 0xffffu, magnitudes >> 16));
+                    if (lane == 0 && magnitude != 0) {
+                        // As the FP32 bits of the BF16 magnitude.
+                        atomicMax(maxima + (first_column - maxima_first_column) / 128,
+                                  magnitude << 16);
+                    }
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        if (*abort_flag != 0) {
+            // A wait gave up: let copies and MMAs in flight land before tensor memory goes back.
+            for (int spin = 0; spin < 64; spin++) {
+                __nanosleep(1000);
+            }
+        }
+        tcgen05_fence_after();
+        tmem_dealloc(tmem, TMEM_COLUMNS);
+    }
+}
+
+template <typename Output, bool SWIGLU>
+int launch_kernel(const GemmMaps &maps, const float *activation_scales, const float *weight_scales,
+                  const float *bias, Output *output, int m, int n, int k, int output_stride,
+                  int band, unsigned *maxima, int maxima_first_column, cudaStream_t stream) {
+    unsigned int *status = status_pointer();
+    const int processors = multiprocessor_count();
+    if (status == nullptr || processors == 0) {
+        return static_cast<int>(cudaErrorInvalidDevice);
+    }
+    static SharedMemoryOptIn shared_memory;
+    const cudaError_t configured =
+        shared_memory.ensure(int8_gemm_kernel<Output, SWIGLU>, SMEM_BYTES);
+    if (configured != cudaSuccess) {
+        return static_cast<int>(configured);
+    }
+    TileWalk walk;
+    walk.tiles_m = (m + ROW_TILES * TILE_M - 1) / (ROW_TILES * TILE_M);
+    walk.tiles_n = (n + TILE_N - 1) / TILE_N;
+    walk.band = band;
+    const int64_t tiles = static_cast<int64_t>(walk.tiles_m) * walk.tiles_n;
+    if (tiles > INT32_MAX) {
+        return INVALID_VALUE;
+    }
+    const int blocks = tiles < processors ? static_cast<int>(tiles) : processors;
+    int8_gemm_kernel<Output, SWIGLU><<<blocks, THREADS, SMEM_BYTES, stream>>>(
+        maps, activation_scales, weight_scales, bias, output, m, n, k / BLOCK_K, output_stride,
+        walk, maxima, maxima_first_column, status);
+    return static_cast<int>(cudaGetLastError());
+}
+
+__global__ void interleave_rows_kernel(const uint32_t *__restrict__ source,
+                                       uint32_t *__restrict__ destination, int rows,
+                                       int row_words) {
+    // Eight rows to a group: the gates of features 4g to 4g + 3, then their up projections,
+    // which the source keeps in its second half.
+    const int row = blockIdx.x;
+    const int feature = row / 8 * 4 + row % 4;
+    const size_t from = static_cast<size_t>(row % 8 < 4 ? feature : rows / 2 + feature) * row_words;
+    const size_t to = static_cast<size_t>(row) * row_words;
+    for (int word = threadIdx.x; word < row_words; word += blockDim.x) {
+        destination[to + word] = source[from + word];
+    }
+}
+
+} // namespace
+
+int launch_int8_gemm(int config, int group_m, const int8_t *activations, const int8_t *weights,
+                     const float *activation_scales, const float *weight_scales, const float *bias,
+                     void *output, bool output_is_f16, bool swiglu, int m, int n, int k,
+                     int output_stride, unsigned *column_maxima, int maxima_first_column,
+                     cudaStream_t stream) {
+    // crates/mmh3-cuda/kernels/int8_gemm.cu:640-645, 700-712, 720-722: config 0 needs N in
+    // multiples of 128 and config 1 of 256; a negative config is the tiling chosen for the shape.
+    // Here every config runs the one tiling, whose results do not depend on it.
+    if (config > 1 || (config >= 0 && group_m <= 0) || m <= 0 || n <= 0 || k <= 0 ||
+        n % (config == 1 ? 256 : 128) != 0 || k % BLOCK_K != 0) {
+        return INVALID_VALUE;
+    }
+    if (column_maxima != nullptr &&
+        (swiglu || output_is_f16 || maxima_first_column < 0 || maxima_first_column % 128 != 0)) {
+        return INVALID_VALUE;
+    }
+    if (output_stride <= 0) {
+        output_stride = swiglu ? n / 2 : n;
+    }
+    // The epilogue stores 16 bytes at a time (8 with SwiGLU) and reads the scales in pairs.
+    if (reinterpret_cast<uintptr_t>(output) % 16 != 0 || output_stride % 8 != 0 ||
+        reinterpret_cast<uintptr_t>(weight_scales) % 8 != 0 ||
+        reinterpret_cast<uintptr_t>(bias) % 8 != 0) {
+        return INVALID_VALUE;
+    }
+    GemmMaps maps;
+    const uint64_t row_dimensions[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
+    const uint64_t column_dimensions[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k)};
+    const uint32_t row_box[2] = {BLOCK_K, ROW_TILES * TILE_M};
+    const uint32_t column_box[2] = {BLOCK_K, TILE_N};
+    if (!encode_tensor_map(&maps.activations, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, activations,
+                           row_dimensions, strides, row_box) ||
+        !encode_tensor_map(&maps.weights, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, weights,
+                           column_dimensions, strides, column_box)) {
+        return INVALID_VALUE;
+    }
+    const int band = config >= 0 ? group_m : 8;
+#define MMH3_GEMM(OUTPUT, SWIGLU)                                                                  \
+    launch_kernel<OUTPUT, SWIGLU>(maps, activation_scales, weight_scales, bias,                    \
+                                  static_cast<OUTPUT *>(output), m, n, k, output_stride, band,     \
+                                  column_maxima, maxima_first_column, stream)
+    if (output_is_f16) {
+        return swiglu ? MMH3_GEMM(__half, true) : MMH3_GEMM(__half, false);
+    }
+    return swiglu ? MMH3_GEMM(__nv_bfloat16, true) : MMH3_GEMM(__nv_bfloat16, false);
+#undef MMH3_GEMM
+}
+
+int launch_interleave_swiglu_rows(const void *source, void *destination, int rows, int row_bytes,
+                                  cudaStream_t stream) {
+    // crates/mmh3-cuda/kernels/int8_gemm.cu:1000-1009
+    if (rows % 8 != 0 || row_bytes % 4 != 0 || rows <= 0) {
+        return INVALID_VALUE;
+    }
+    interleave_rows_kernel<<<rows, 128, 0, stream>>>(static_cast<const uint32_t *>(source),
+                                                     static_cast<uint32_t *>(destination), rows,
+                                                     row_bytes / 4);
+    return static_cast<int>(cudaGetLastError());
+}
+
+} // namespace mmh3

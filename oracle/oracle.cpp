@@ -1000,4 +1000,85 @@ void oracle_shard_even(int64_t count, int ranks, int64_t alignment, int64_t *bou
     boundaries[ranks] = count;
 }
 
+// The scaled INT8 GEMM of the linear layers: the exact integer sums, then the FP32 operations of
+// crates/mmh3-cuda/kernels/int8_gemm.cu in their order: (sum * activation scale) * weight scale
+// (lines 448-457), + bias (489-508), rounded to BF16 or FP16 (521-525). With `swiglu`, columns come
+// in groups of eight, the gates of four features and then their up projections, and the output
+// [m, n / 2] is silu(gate) * up of the rounded products, rounded again (297-305, 545-554); expf
+// stands where the kernel has __expf, so those bits may differ in the last place. `maxima`, unless
+// null, receives the largest |output| of each group of 128 columns from `first_column` on as the
+// FP32 bits of the BF16 magnitude (112-116, 556-587). `output_stride` elements lie between rows.
+void oracle_int8_gemm(const int8_t *activations, const int8_t *weights,
+                      const float *activation_scales, const float *weight_scales,
+                      const float *bias, uint16_t *output, int f16, int swiglu, int m, int n, int k,
+                      int output_stride, uint32_t *maxima, int first_column) {
+    auto round_bits = [f16](float value) -> uint16_t {
+        if (f16) {
+            const _Float16 half = static_cast<_Float16>(value);
+            uint16_t bits;
+            std::memcpy(&bits, &half, 2);
+            return bits;
+        }
+        return f32_to_bf16(value);
+    };
+    auto widen = [f16](uint16_t bits) -> float {
+        if (f16) {
+            _Float16 half;
+            std::memcpy(&half, &bits, 2);
+            return static_cast<float>(half);
+        }
+        return bf16_to_f32(bits);
+    };
+    const int groups = maxima != nullptr && n > first_column ? (n - first_column) / 128 : 0;
+    std::vector<uint32_t> largest(groups, 0);
+    #pragma omp parallel
+    {
+        std::vector<uint16_t> rounded(n);
+        std::vector<uint32_t> local(groups, 0);
+        #pragma omp for schedule(static)
+        for (int row = 0; row < m; row++) {
+            const int8_t *a = activations + static_cast<size_t>(row) * k;
+            for (int column = 0; column < n; column++) {
+                const int8_t *w = weights + static_cast<size_t>(column) * k;
+                int32_t sum = 0;
+                for (int index = 0; index < k; index++) {
+                    sum += static_cast<int32_t>(a[index]) * static_cast<int32_t>(w[index]);
+                }
+                float value = static_cast<float>(sum) * activation_scales[row];
+                value = value * weight_scales[column];
+                if (bias != nullptr) {
+                    value = value + bias[column];
+                }
+                rounded[column] = round_bits(value);
+            }
+            uint16_t *output_row = output + static_cast<size_t>(row) * output_stride;
+            if (swiglu) {
+                for (int column = 0; column < n; column += 8) {
+                    for (int feature = 0; feature < 4; feature++) {
+                        const float gate = widen(rounded[column + feature]);
+                        const float up = widen(rounded[column + 4 + feature]);
+                        output_row[column / 2 + feature] =
+                            round_bits(gate / (1.0f + std::exp(-gate)) * up);
+                    }
+                }
+            } else {
+                for (int column = 0; column < n; column++) {
+                    output_row[column] = rounded[column];
+                    if (column >= first_column && groups > 0) {
+                        uint32_t &slot = local[(column - first_column) / 128];
+                        slot = std::max(slot, static_cast<uint32_t>(rounded[column] & 0x7fffu) << 16);
+                    }
+                }
+            }
+        }
+        #pragma omp critical
+        for (int group = 0; group < groups; group++) {
+            largest[group] = std::max(largest[group], local[group]);
+        }
+    }
+    for (int group = 0; group < groups; group++) {
+        maxima[group] = std::max(maxima[group], largest[group]);
+    }
+}
+
 } // extern "C"

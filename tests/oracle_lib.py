@@ -90,6 +90,10 @@ def load() -> ctypes.CDLL:
     library.oracle_sol_reference.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                              c_float, c_float, c_void_p, c_void_p]
     library.oracle_sol_reference.restype = c_double
+    library.oracle_int8_gemm.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                         c_void_p, c_int]
+    library.oracle_int8_gemm.restype = None
     return library
 
 
@@ -186,3 +190,25 @@ def sol_reference(library, query: np.ndarray, key: np.ndarray, value: np.ndarray
         ptr(operands[0]), ptr(operands[1]), ptr(operands[2]), tokens, heads, dim, tau, scale,
         ptr(sink_array), ptr(output))
     return output, fraction
+
+
+def int8_gemm(library, activations: np.ndarray, weights: np.ndarray, activation_scales: np.ndarray,
+              weight_scales: np.ndarray, bias: np.ndarray | None = None, f16: bool = False,
+              swiglu: bool = False, maxima_first_column: int | None = None):
+    """The scaled INT8 GEMM in the kernels' FP32 order: (output bit patterns [m, n] or [m, n / 2],
+    column maxima as FP32 or None)."""
+    m, k = activations.shape
+    n = weights.shape[0]
+    output = np.zeros((m, n // 2 if swiglu else n), dtype=np.uint16)
+    maxima = None
+    if maxima_first_column is not None:
+        maxima = np.zeros(max((n - maxima_first_column) // 128, 1), dtype=np.uint32)
+    kept = [np.ascontiguousarray(activations, dtype=np.int8),
+            np.ascontiguousarray(weights, dtype=np.int8),
+            np.ascontiguousarray(activation_scales, dtype=np.float32),
+            np.ascontiguousarray(weight_scales, dtype=np.float32),
+            None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)]
+    library.oracle_int8_gemm(ptr(kept[0]), ptr(kept[1]), ptr(kept[2]), ptr(kept[3]), ptr(kept[4]),
+                             ptr(output), int(f16), int(swiglu), m, n, k, output.shape[1],
+                             ptr(maxima), maxima_first_column or 0)
+    return output, None if maxima is None else maxima.view(np.float32)

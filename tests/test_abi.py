@@ -1,4 +1,4 @@
-"""The C-ABI library loads without a GPU, exports every symbol include/mmh3_attention.h declares,
+"""The C-ABI library loads without a GPU, exports every symbol the headers of include/ declare,
 lays its structs out as the reference's #[repr(C)] mirrors do, and rejects bad arguments with the
 reference's error codes before touching a device. No kernel runs here."""
 
@@ -12,22 +12,27 @@ import pytest
 from mmh3_b200 import _lib
 
 REPO = pathlib.Path(__file__).resolve().parent.parent
-HEADER = REPO / "include" / "mmh3_attention.h"
+HEADERS = sorted((REPO / "include").glob("*.h"))
 
 
 def declared_functions():
-    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
-    return sorted(set(re.findall(r"^int\s+(mmh3_\w+)\s*\(", text, flags=re.M)))
+    names = set()
+    for header in HEADERS:
+        text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
+        names.update(re.findall(r"^int\s+(mmh3_\w+)\s*\(", text, flags=re.M))
+    return sorted(names)
 
 
-def test_header_compiles_as_c():
-    subprocess.run(["gcc", "-std=c99", "-fsyntax-only", "-x", "c", str(HEADER)], check=True)
+def test_headers_compile_as_c():
+    assert [header.name for header in HEADERS] == ["mmh3_attention.h", "mmh3_int8_gemm.h"]
+    for header in HEADERS:
+        subprocess.run(["gcc", "-std=c99", "-fsyntax-only", "-x", "c", str(header)], check=True)
 
 
 def test_every_declared_symbol_is_exported():
     library = _lib.library()
     names = declared_functions()
-    assert len(names) == 13
+    assert len(names) == 18
     assert sorted(_lib.SIGNATURES) == names
     for name in names:
         assert getattr(library, name) is not None
@@ -97,3 +102,33 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIBRARY", tmp_path / "absent.so")
     with pytest.raises(RuntimeError, match="no fallback"):
         _lib.library()
+
+
+def test_gemm_arguments_are_rejected_before_any_launch():
+    # crates/mmh3-cuda/kernels/int8_gemm.cu:640-645, 710, 720, 919-921
+    library = _lib.library()
+    invalid = _lib.CUDA_ERROR_INVALID_VALUE
+    assert library.mmh3_int8_gemm_config_count() == 2
+    heights = (ctypes.c_int * 2)()
+    assert library.mmh3_int8_gemm_group_heights(heights, 2) == 3 and list(heights) == [4, 8]
+    operand = ctypes.c_void_p(4096)  # never dereferenced: every call below fails its checks
+
+    def call(config=0, group_m=8, m=64, n=256, k=256, f16=0, swiglu=0, down=None, maxima=None,
+             first_column=0, activations=operand):
+        return library.mmh3_int8_gemm(config, group_m, activations, operand, operand, operand,
+                                      None, operand, f16, swiglu, m, n, k, 0, down, None, 0, 0,
+                                      0.0, maxima, first_column, None)
+
+    assert call(activations=None) == invalid
+    assert call(n=192) == invalid
+    assert call(config=1, n=384) == invalid
+    assert call(k=100) == invalid
+    assert call(m=0) == invalid
+    assert call(group_m=0) == invalid
+    assert call(config=2) == invalid
+    assert call(maxima=operand, f16=1) == invalid
+    assert call(maxima=operand, swiglu=1) == invalid
+    assert call(maxima=operand, first_column=64) == invalid
+    assert call(down=operand) == _lib.CUDA_ERROR_NOT_SUPPORTED
+    assert library.mmh3_interleave_swiglu_rows(operand, operand, 12, 256, None) == invalid
+    assert library.mmh3_interleave_swiglu_rows(operand, operand, 16, 6, None) == invalid

@@ -1,0 +1,224 @@
+"""Parity of the scaled INT8 GEMM on a B200, through the C ABI.
+
+Mirrors crates/mmh3-cuda/tests/int8_gemm.rs without the low-rank adapter (the same shapes, value
+ranges and bounds against the definition in float64, the column maxima equal to those of the
+kernel's own output, every tiling the same bits) and adds what the drop-in must hold: outputs and
+maxima bit-identical to the CPU restatement and to the reference's own kernel, and the per-head
+maxima of |v| feeding the fused attention inputs.
+"""
+
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import gemm_cases
+import oracle_lib
+from mmh3_b200 import _lib, attention, gemm, synthetic
+from mmh3_b200.gemm import ColumnMaxima, Int8Tiling, Output
+
+pytestmark = pytest.mark.gpu
+
+TILINGS = [None, Int8Tiling(0, 4), Int8Tiling(0, 16), Int8Tiling(1, 8)]
+
+
+def upload(array):
+    return None if array is None else torch.from_numpy(np.ascontiguousarray(array)).cuda()
+
+
+def run(case, m, n, k, f16=False, swiglu=False, first_column=None, tiling=None, stride=0):
+    a, w, a_scales, w_scales, bias = (upload(array) for array in case)
+    columns = n // 2 if swiglu else n
+    row = stride if stride else columns
+    # A sentinel shows what the kernel does not write.
+    output = torch.full((m, row), 0x7fc1, dtype=torch.int16, device="cuda")
+    maxima = None
+    if first_column is not None:
+        maxima = ColumnMaxima(torch.zeros(max((n - first_column) // 128, 1), dtype=torch.float32,
+                                          device="cuda"), first_column)
+    gemm.int8(tiling, a, w, a_scales, w_scales,
+              Output(output, f16=f16, bias=bias, swiglu=swiglu, column_maxima=maxima,
+                     stride=stride), m, n, k)
+    assert attention.take_status() == 0
+    bits = output.cpu().numpy().view(np.uint16)
+    return bits, None if maxima is None else maxima.values.cpu().numpy()
+
+
+def run_reference(library, case, m, n, k, f16=False, swiglu=False, first_column=None):
+    a, w, a_scales, w_scales, bias = (upload(array) for array in case)
+    columns = n // 2 if swiglu else n
+    output = torch.zeros((m, columns), dtype=torch.int16, device="cuda")
+    maxima = torch.zeros(max((n - (first_column or 0)) // 128, 1), dtype=torch.float32,
+                         device="cuda")
+    pointer = lambda tensor: ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+    torch.cuda.synchronize()
+    code = library.mmh3_int8_gemm(
+        0, 8, pointer(a), pointer(w), pointer(a_scales), pointer(w_scales), pointer(bias),
+        pointer(output), int(f16), int(swiglu), m, n, k, 0, None, None, 0, 0, 0.0,
+        pointer(maxima if first_column is not None else None), first_column or 0, None)
+    assert code == 0
+    torch.cuda.synchronize()
+    return output.cpu().numpy().view(np.uint16), maxima.cpu().numpy()
+
+
+@pytest.mark.parametrize("m,n,k,f16,seed", [
+    (300, 512, 384, False, 7),      # int8_gemm.rs:231-233
+    (2000, 3072, 384, False, 8),    # 236-240: more tiles than SMs, a ragged last row of tiles
+    (600, 3072, 256, True, 11),     # 256-258: FP16 with a bias
+    (257, 384, 128, False, 3),      # one row into the second tile, a last tile of 128 columns
+])
+def test_matches_the_definition_oracle_and_reference(oracle, reference_kernels, m, n, k, f16, seed):
+    case = gemm_cases.operands(m, n, k, seed, bias=f16)
+    first_column = None if f16 else 128
+    bits, maxima = run(case, m, n, k, f16=f16, first_column=first_column)
+    expected = gemm_cases.definition(*case)
+    actual = gemm_cases.widen(bits, f16)
+    assert np.all(np.abs(actual - expected) <= np.abs(expected) / 256.0 + 1e-4)  # rs:212
+    oracle_bits, oracle_maxima = oracle_lib.int8_gemm(oracle, *case, f16=f16,
+                                                      maxima_first_column=first_column)
+    assert np.array_equal(bits, oracle_bits)
+    reference_bits, reference_maxima = run_reference(reference_kernels, case, m, n, k, f16=f16,
+                                                     first_column=first_column)
+    assert np.array_equal(bits, reference_bits)
+    if not f16:
+        expected_maxima = gemm_cases.column_maxima(bits, first_column)
+        assert np.array_equal(maxima, expected_maxima)  # rs:199-203
+        assert np.array_equal(maxima, oracle_maxima)
+        assert np.array_equal(maxima, reference_maxima)
+    for tiling in TILINGS[1:]:
+        if tiling.config == 1 and n % 256:
+            continue
+        other, other_maxima = run(case, m, n, k, f16=f16, first_column=first_column,
+                                  tiling=tiling)
+        assert np.array_equal(bits, other), tiling  # rs:221-227
+        if not f16:
+            assert np.array_equal(maxima, other_maxima)
+
+
+@pytest.mark.parametrize("f16", [False, True])
+def test_swiglu_of_interleaved_rows(oracle, reference_kernels, f16):
+    # int8_gemm.rs:269-383 without the adapter; the rows interleaved by the library itself.
+    m, features, k = 300, 1024, 256
+    n = 2 * features
+    a, w, a_scales, w_scales, bias = gemm_cases.operands(m, n, k, 12 + f16, bias=True,
+                                                          swiglu=True)
+
+    def interleaved(array, row_bytes):
+        source = upload(array)
+        destination = torch.empty_like(source)
+        gemm.interleave_swiglu_rows(source, destination, n, row_bytes)
+        return destination.cpu().numpy()
+
+    w_mixed = interleaved(w, k)
+    assert np.array_equal(w_mixed, gemm_cases.interleave(w))
+    case = (a, w_mixed, a_scales, interleaved(w_scales, 4), interleaved(bias, 4))
+    bits, _ = run(case, m, n, k, f16=f16, swiglu=True)
+    assert bits.shape == (m, features)
+    products = gemm_cases.definition(a, w, a_scales, w_scales, bias).astype(np.float32)
+    if f16:
+        products = products.astype(np.float16).astype(np.float32)
+    else:
+        products = synthetic.bf16_bits_to_f32(synthetic.to_bf16_bits(products)).reshape(m, n)
+    gate, up = products[:, :features].astype(np.float64), products[:, features:].astype(np.float64)
+    expected = gate / (1.0 + np.exp(-gate)) * up
+    actual = gemm_cases.widen(bits, f16)
+    assert np.all(np.abs(actual - expected) <= np.abs(expected) / 64.0 + 1e-3)  # rs:375
+    reference_bits, _ = run_reference(reference_kernels, case, m, n, k, f16=f16, swiglu=True)
+    assert np.array_equal(bits, reference_bits)
+
+
+def test_writes_rows_at_their_stride():
+    # A shared-out step writes one rank's columns into a row that holds every rank's
+    # (crates/mmh3-cuda/src/gemm.rs:175-177).
+    m, n, k, stride = 130, 256, 128, 640
+    case = gemm_cases.operands(m, n, k, 21)
+    bits, _ = run(case, m, n, k)
+    wide, _ = run(case, m, n, k, stride=stride)
+    assert np.array_equal(wide[:, :n], bits)
+    assert np.all(wide[:, n:] == 0x7fc1)
+
+
+def test_bf16_entry_point(oracle):
+    m, n, k = 100, 256, 256
+    case = gemm_cases.operands(m, n, k, 5)
+    a, w, a_scales, w_scales, _ = (upload(array) for array in case)
+    output = torch.zeros((m, n), dtype=torch.int16, device="cuda")
+    pointer = lambda tensor: ctypes.c_void_p(tensor.data_ptr())
+    code = _lib.library().mmh3_int8_gemm_bf16(1, 4, pointer(a), pointer(w), pointer(a_scales),
+                                              pointer(w_scales), pointer(output), m, n, k, None)
+    assert code == 0 and attention.take_status() == 0
+    expected, _ = oracle_lib.int8_gemm(oracle, *case)
+    assert np.array_equal(output.cpu().numpy().view(np.uint16), expected)
+
+
+def test_rejects_what_the_reference_rejects():
+    m, n, k = 64, 256, 256
+    case = gemm_cases.operands(m, n, k, 1)
+    a, w, a_scales, w_scales, _ = (upload(array) for array in case)
+    output = torch.zeros((m, n), dtype=torch.int16, device="cuda")
+    maxima = torch.zeros(2, dtype=torch.float32, device="cuda")
+    pointer = lambda tensor: ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+
+    def call(config=0, group_m=8, m=m, n=n, k=k, f16=0, swiglu=0, down=None, maxima=None,
+             first_column=0):
+        return _lib.library().mmh3_int8_gemm(
+            config, group_m, pointer(a), pointer(w), pointer(a_scales), pointer(w_scales), None,
+            pointer(output), f16, swiglu, m, n, k, 0, pointer(down), None, 0, 0, 0.0,
+            pointer(maxima), first_column, None)
+
+    invalid = _lib.CUDA_ERROR_INVALID_VALUE
+    assert call() == 0
+    assert call(n=192) == invalid                          # int8_gemm.cu:640
+    assert call(config=1, n=128) == invalid                # the wide tiling needs 256 columns
+    assert call(k=192) == invalid
+    assert call(m=0) == invalid
+    assert call(group_m=0) == invalid
+    assert call(config=2) == invalid                       # int8_gemm.cu:710
+    assert call(config=-1, group_m=0) == 0                 # the chosen tiling names no band
+    assert call(maxima=maxima, f16=1) == invalid           # int8_gemm.cu:919-921
+    assert call(maxima=maxima, swiglu=1) == invalid        # int8_gemm.cu:720
+    assert call(maxima=maxima, first_column=64) == invalid
+    assert call(down=a) == _lib.CUDA_ERROR_NOT_SUPPORTED   # the adapter is not built
+    assert attention.take_status() == 0
+    assert gemm.configs() == 2 and gemm.group_heights() == [4, 8, 16]
+
+
+def test_value_maxima_feed_the_attention_inputs():
+    """crates/mmh3-cuda/src/dit.rs:1873-1877, 1965: the qkv projection leaves the maximum |v| of
+    each head, and the fused input pass quantizes V by them: the same FP8 V and scales as the
+    quantizer finds from the BF16 values itself."""
+    tokens, heads, k = 333, 2, 256
+    inner = heads * 128
+    n = 3 * inner
+    case = gemm_cases.operands(tokens, n, k, 31)
+    a, w, a_scales, w_scales, _ = (upload(array) for array in case)
+    qkv = torch.zeros((tokens, n), dtype=torch.bfloat16, device="cuda")
+    quantized = attention.QuantizedWorkspace(tokens, heads)
+    maxima = torch.zeros(heads, dtype=torch.float32, device="cuda")
+    gemm.int8(None, a, w, a_scales, w_scales,
+              Output(qkv.view(torch.int16), column_maxima=ColumnMaxima(maxima, 2 * inner)),
+              tokens, n, k)
+    values = qkv.view(tokens, 3, heads, 128)[:, 2].float().abs().amax(dim=(0, 2))
+    assert torch.equal(maxima, values)
+
+    weight = torch.ones(128, dtype=torch.bfloat16, device="cuda")
+    norm = attention.HeadNorm(weight, weight, None, 0, 1e-6)
+    prepared = qkv.clone()
+    attention.prepare_inputs(prepared, norm, tokens, heads, quantized, value_head_maxima=maxima)
+    # The separate passes: the norm in place, then the quantizer over the BF16 rows.
+    separate = qkv.clone()
+    attention.qk_norm_rope(separate, norm, tokens, heads)
+    own = attention.QuantizedWorkspace(tokens, heads)
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    attention.dense_quantized(separate, output, synthetic.softmax_scale(), own,
+                              inputs=attention.AttentionInputs.RAW)
+    assert attention.take_status() == 0
+    assert torch.equal(quantized.value, own.value)
+    assert torch.equal(quantized.value_scales, own.value_scales)
+    # And the attention over inputs made complete that way (inputs_ready = 2) is the same.
+    complete = torch.zeros_like(output)
+    attention.dense_quantized(prepared, complete, synthetic.softmax_scale(), quantized,
+                              inputs=attention.AttentionInputs.PREPARED_WITH_VALUES)
+    assert attention.take_status() == 0
+    assert torch.equal(complete, output)
