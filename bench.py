@@ -394,7 +394,50 @@ def run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, a
             extras["sol"] = run_sol(torch, attention, qkv, output, tokens, heads, scale, steps)
         except attention.CudaError as error:
             extras["sol_error"] = str(error)
+    if not args.skip_gemm:
+        try:
+            extras["qkv_gemm"] = run_gemm(torch, attention, qkv, tokens, heads, steps)
+        except attention.CudaError as error:
+            extras["qkv_gemm_error"] = str(error)
     return extras
+
+
+def run_gemm(torch, attention, qkv, tokens, heads, steps) -> dict:
+    """The step before attention: the INT8 qkv projection [tokens, heads * 128] x
+    [3 * heads * 128, heads * 128]^T into the BF16 qkv rows, leaving the per-head maxima of |v|.
+    Uniform INT8 operands; the weights (50 MB at 32 heads) stay in L2, the activations stream."""
+    from mmh3_b200 import gemm
+
+    inner = heads * HEAD_DIM
+    generator = torch.Generator(device="cuda").manual_seed(3)
+    activations = torch.randint(-127, 128, (tokens, inner), dtype=torch.int8, device="cuda",
+                                generator=generator)
+    weights = torch.randint(-127, 128, (3 * inner, inner), dtype=torch.int8, device="cuda",
+                            generator=generator)
+    activation_scales = torch.rand(tokens, device="cuda", generator=generator) + 0.5
+    weight_scales = torch.rand(3 * inner, device="cuda", generator=generator) * 1e-4 + 1e-5
+    maxima = torch.zeros(heads, dtype=torch.float32, device="cuda")
+    target = torch.empty_like(qkv)
+
+    def project():
+        gemm.int8(None, activations, weights, activation_scales, weight_scales,
+                  gemm.Output(target.view(torch.int16),
+                              column_maxima=gemm.ColumnMaxima(maxima, 2 * inner)),
+                  tokens, 3 * inner, inner)
+
+    project()
+    ms = time_region(torch, project, steps)
+    operations = 2.0 * tokens * 3 * inner * inner
+    peaks, source = measured_peaks()
+    return {
+        "workload": f"qkv projection M={tokens}, N={3 * inner}, K={inner}, INT8 -> BF16 + |v| maxima",
+        "ms": ms, "tops": operations / ms / 1e9,
+        # No INT8 peak is measured on this pool: twice the measured BF16 rate stands in for it.
+        "frac_of_twice_bf16_peak": operations / ms / 1e9 / (2.0 * peaks["bf16_tflops"]),
+        "frac_of_twice_bf16_sustained": operations / ms / 1e9 /
+        (2.0 * peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])),
+        "peak_source": source, "kernel_status": attention.take_status(),
+    }
 
 
 def run_sol(torch, attention, qkv, output, tokens, heads, scale, steps) -> dict:
@@ -598,6 +641,8 @@ def main() -> None:
     parser.add_argument("--heads", type=int, default=0,
                         help="a reduced head count for profiler captures (N = 1 only)")
     parser.add_argument("--skip-sol", action="store_true", help="leave Sol-Attn out")
+    parser.add_argument("--skip-gemm", action="store_true",
+                        help="leave the INT8 qkv projection out")
     parser.add_argument("--skip-quantized", action="store_true",
                         help="leave the fused quantize pass and the INT8/FP8 kernel out")
     parser.add_argument("--skip-vsa", action="store_true",

@@ -13,15 +13,12 @@
 // the CTAs in flight share rows of activations and columns of weights in L2. A tile is two
 // accumulators of 128 rows by 256 columns of INT32 in tensor memory (all 512 columns of the SM).
 // Warp 0 streams stages of 128 bytes of K (32 KB of activations, 32 KB of weights, 128-byte
-// swizzle) through a ring with TMA; one thread of warp 1 issues tcgen05.mma kind::i8 of
-// 128 x 256 x 32 from shared memory; eight warps scale, round and store the accumulators. At this
-// tile shape a stage of 64 KB feeds 1,024 cycles of MMA, 64 bytes a cycle, which is what an SM
-// can take from L2; a tile of 128 x 256 would leave room for a second pair of accumulators and an
-// epilogue hidden behind the next tile's MMAs, but needs 96 bytes a cycle.
-//
-// The second accumulator runs SKEW stages behind the first, so the first is complete, and the
-// epilogue warps are at work on it, while the MMAs of the second still run; at the other end the
-// MMAs of the next tile's first accumulator start while the second is still being stored.
+// swizzle) through a ring of three with TMA; one thread of warp 1 issues tcgen05.mma kind::i8 of
+// 128 x 256 x 32 from shared memory; eight warps scale, round and store the accumulators while the
+// ring fills for the next tile. At this tile shape a stage of 64 KB feeds 1,024 cycles of MMA,
+// 64 bytes a cycle, which is what an SM can take from L2; a tile of 128 x 256 would leave room for
+// a second pair of accumulators and an epilogue hidden behind the next tile's MMAs, but needs
+// 96 bytes a cycle.
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -37,8 +34,6 @@ constexpr int ROW_TILES = 2;    // accumulators of a tile
 constexpr int TILE_N = 256;
 constexpr int BLOCK_K = 128;    // INT8 elements of one stage along K
 constexpr int STAGES = 3;
-constexpr int SKEW = 1;
-static_assert(SKEW < STAGES, "the ring must hold the stages between the two accumulators");
 constexpr int ROWS_BYTES = ROW_TILES * TILE_M * BLOCK_K;
 constexpr int COLUMNS_BYTES = TILE_N * BLOCK_K;
 constexpr int STAGE_BYTES = ROWS_BYTES + COLUMNS_BYTES;
@@ -58,8 +53,8 @@ enum Barrier {
     RING_FULL = 0,
     RING_EMPTY = RING_FULL + STAGES,
     ACCUMULATOR_FULL = RING_EMPTY + STAGES,
-    ACCUMULATOR_EMPTY = ACCUMULATOR_FULL + ROW_TILES,
-    BARRIERS = ACCUMULATOR_EMPTY + ROW_TILES,
+    ACCUMULATOR_EMPTY,
+    BARRIERS,
 };
 
 constexpr uint32_t PRODUCT_MMA =
@@ -142,10 +137,8 @@ __global__ void __launch_bounds__(THREADS, 1)
             mbar_init(barrier(RING_FULL + stage), 1);
             mbar_init(barrier(RING_EMPTY + stage), 1);
         }
-        for (int half = 0; half < ROW_TILES; half++) {
-            mbar_init(barrier(ACCUMULATOR_FULL + half), 1);
-            mbar_init(barrier(ACCUMULATOR_EMPTY + half), EPILOGUE_WARPS);
-        }
+        mbar_init(barrier(ACCUMULATOR_FULL), 1);
+        mbar_init(barrier(ACCUMULATOR_EMPTY), EPILOGUE_WARPS);
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
@@ -199,45 +192,29 @@ __global__ void __launch_bounds__(THREADS, 1)
                               !first || step > 0);
                 }
             };
-            int first_item = 0;
+            int item = 0;
             int round = 0;
             bool alive = true;
-            for (int tile = blockIdx.x; alive && tile < tiles;
-                 tile += gridDim.x, round++, first_item += k_blocks) {
-                for (int step = 0; alive && step < k_blocks + SKEW; step++) {
-                    if (step < k_blocks) {
-                        const int item = first_item + step;
-                        alive = mbar_wait(barrier(RING_FULL + item % STAGES),
-                                          (item / STAGES) & 1, watchdog, STATUS_GEMM | 2) &&
-                                (step > 0 || round == 0 ||
-                                 mbar_wait(barrier(ACCUMULATOR_EMPTY + 0), (round - 1) & 1,
-                                           watchdog, STATUS_GEMM | 3));
-                        if (!alive) {
-                            break;
-                        }
-                        tcgen05_fence_after();
-                        multiply(0, item % STAGES, step == 0);
-                        if (step == k_blocks - 1) {
-                            tcgen05_commit(barrier(ACCUMULATOR_FULL + 0));
-                        }
+            for (int tile = blockIdx.x; alive && tile < tiles; tile += gridDim.x, round++) {
+                for (int k_block = 0; k_block < k_blocks; k_block++, item++) {
+                    const int stage = item % STAGES;
+                    alive = mbar_wait(barrier(RING_FULL + stage), (item / STAGES) & 1, watchdog,
+                                      STATUS_GEMM | 2);
+                    if (alive && k_block == 0 && round > 0) {
+                        // The epilogue warps have read the last tile out of both accumulators.
+                        alive = mbar_wait(barrier(ACCUMULATOR_EMPTY), (round - 1) & 1, watchdog,
+                                          STATUS_GEMM | 3);
                     }
-                    if (step >= SKEW) {
-                        const int k_block = step - SKEW;
-                        const int item = first_item + k_block;
-                        if (k_block == 0 && round > 0) {
-                            alive = mbar_wait(barrier(ACCUMULATOR_EMPTY + 1), (round - 1) & 1,
-                                              watchdog, STATUS_GEMM | 4);
-                            if (!alive) {
-                                break;
-                            }
-                            tcgen05_fence_after();
-                        }
-                        multiply(1, item % STAGES, k_block == 0);
-                        tcgen05_commit(barrier(RING_EMPTY + item % STAGES));
-                        if (k_block == k_blocks - 1) {
-                            tcgen05_commit(barrier(ACCUMULATOR_FULL + 1));
-                        }
+                    if (!alive) {
+                        break;
                     }
+                    tcgen05_fence_after();
+                    multiply(0, stage, k_block == 0);
+                    multiply(1, stage, k_block == 0);
+                    tcgen05_commit(barrier(RING_EMPTY + stage));
+                }
+                if (alive) {
+                    tcgen05_commit(barrier(ACCUMULATOR_FULL));
                 }
             }
         }
@@ -257,15 +234,14 @@ __global__ void __launch_bounds__(THREADS, 1)
             const bool inside = first_column < n;
             const bool track =
                 !SWIGLU && maxima != nullptr && inside && first_column >= maxima_first_column;
+            alive = mbar_wait(barrier(ACCUMULATOR_FULL), round & 1, watchdog, STATUS_GEMM | 4);
+            alive = __all_sync(0xffffffffu, alive);
+            if (!alive) {
+                break;
+            }
+            tcgen05_fence_after();
             #pragma unroll 1
             for (int half = 0; half < ROW_TILES; half++) {
-                alive = mbar_wait(barrier(ACCUMULATOR_FULL + half), round & 1, watchdog,
-                                  STATUS_GEMM | 5);
-                alive = __all_sync(0xffffffffu, alive);
-                if (!alive) {
-                    break;
-                }
-                tcgen05_fence_after();
                 const int row = tile_m * (ROW_TILES * TILE_M) + half * TILE_M + quarter * 32 + lane;
                 const bool stored = inside && row < m;
                 const float row_scale = row < m ? __ldg(activation_scales + row) : 0.0f;
@@ -332,10 +308,12 @@ __global__ void __launch_bounds__(THREADS, 1)
                         }
                     }
                 }
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(barrier(ACCUMULATOR_EMPTY + half));
+                if (half == ROW_TILES - 1) {
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(barrier(ACCUMULATOR_EMPTY));
+                    }
                 }
                 if (track) {
                     const unsigned magnitude = __reduce_max_sync(
