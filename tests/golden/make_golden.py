@@ -8,7 +8,8 @@ its sources by oracle/Makefile) is present:
 For small seeded inputs it records what the reference leaves behind: dense BF16 outputs, the INT8 q
 and k with their scales, FP8 V and its scale, the quantized attention's output, and VSA's routes,
 route counts and output, and Sol-Attn's block statistics, centred keys, routes, pooled tails and
-output (in reference_sol.npz). The CPU tests then hold the oracle to these files (bit-exact for INT8 and
+output (in reference_sol.npz), and the scaled INT8 GEMM's outputs and column maxima (in
+reference_int8_gemm.npz). The CPU tests then hold the oracle to these files (bit-exact for INT8 and
 routes, within the kernels' tolerance for outputs), so the oracle is pinned to the reference itself
 even where no GPU is present. Inputs are regenerated from the seeds by the tests.
 """
@@ -24,6 +25,7 @@ REPO = pathlib.Path(__file__).resolve().parent.parent.parent
 sys.path.insert(0, str(REPO))
 sys.path.insert(0, str(REPO / "tests"))
 
+import gemm_cases  # noqa: E402
 import oracle_lib  # noqa: E402
 from mmh3_b200 import attention, synthetic  # noqa: E402
 from mmh3_b200.vsa import PackedLayout, VsaPlan  # noqa: E402
@@ -34,6 +36,19 @@ DENSE_CASES = [(1, 1), (64, 2), (200, 3)]
 QUANTIZED_CASES = [(65, 2), (200, 3)]
 VSA_CASE = dict(text=70, frames=9, height=16, width=24, audio=40, heads=2, sparsity=0.7)
 SOL_CASE = dict(tokens=777, heads=2, tau=0.5, sinks=(0, 1, 2, 3))
+# name -> (m, n, k, seed, FP16 output with a bias, SwiGLU)
+GEMM_CASES = {"bf16": (130, 384, 256, 41, False, False), "f16_bias": (70, 256, 128, 42, True, False),
+              "swiglu": (40, 512, 128, 43, False, True)}
+
+
+def gemm_operands(name):
+    """The operands of a GEMM case as the kernel takes them (SwiGLU rows interleaved)."""
+    m, n, k, seed, f16, swiglu = GEMM_CASES[name]
+    a, w, a_scales, w_scales, bias = gemm_cases.operands(m, n, k, seed, bias=f16 or swiglu,
+                                                          swiglu=swiglu)
+    if swiglu:
+        w, w_scales, bias = (gemm_cases.interleave(rows) for rows in (w, w_scales, bias))
+    return a, w, a_scales, w_scales, bias
 
 
 def sol_inputs(oracle, tokens, heads):
@@ -159,6 +174,27 @@ def main():
         sol[name] = getattr(workspace, name).cpu().numpy()
     np.savez_compressed(out / "reference_sol.npz", **sol)
     print("wrote", out / "reference_sol.npz", sum(a.nbytes for a in sol.values()), "bytes")
+
+    gemm = {}
+    for name, (m, n, k, _, f16, swiglu) in GEMM_CASES.items():
+        operands = [None if array is None else torch.from_numpy(np.ascontiguousarray(array)).cuda()
+                    for array in gemm_operands(name)]
+        pointers = [ctypes.c_void_p(0 if tensor is None else tensor.data_ptr())
+                    for tensor in operands]
+        result = torch.zeros((m, n // 2 if swiglu else n), dtype=torch.int16, device="cuda")
+        tracked = not f16 and not swiglu
+        maxima = torch.zeros(max((n - 128) // 128, 1), dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        assert reference.mmh3_int8_gemm(
+            0, 8, *pointers, ctypes.c_void_p(result.data_ptr()), int(f16), int(swiglu), m, n, k, 0,
+            None, None, 0, 0, 0.0, ctypes.c_void_p(maxima.data_ptr() if tracked else 0), 128,
+            None) == 0
+        torch.cuda.synchronize()
+        gemm[f"{name}_output"] = result.cpu().numpy().view(np.uint16)
+        if tracked:
+            gemm[f"{name}_maxima"] = maxima.cpu().numpy()
+    np.savez_compressed(out / "reference_int8_gemm.npz", **gemm)
+    print("wrote", out / "reference_int8_gemm.npz", sum(a.nbytes for a in gemm.values()), "bytes")
 
 
 if __name__ == "__main__":

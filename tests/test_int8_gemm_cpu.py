@@ -63,3 +63,32 @@ def test_swiglu_of_interleaved_rows(oracle, f16):
     # int8_gemm.rs:375
     assert np.all(np.abs(actual - expected) <= np.abs(expected) / 64.0 + 1e-3)
 
+
+
+def test_oracle_matches_the_reference_kernel_fixture(oracle):
+    """tests/golden/reference_int8_gemm.npz holds what the reference's own kernel (int8_gemm.cu,
+    compiled from its sources) wrote for seeded operands (tests/golden/make_golden.py): the
+    restatement reproduces the outputs and the column maxima bit for bit, and the SwiGLU outputs
+    to the last place of the rounded result (expf stands where the kernel has __expf)."""
+    import pathlib
+    import sys
+
+    golden = pathlib.Path(__file__).resolve().parent / "golden"
+    sys.path.insert(0, str(golden))
+    import make_golden
+
+    fixture = np.load(golden / "reference_int8_gemm.npz")
+    for name, (m, n, k, _, f16, swiglu) in make_golden.GEMM_CASES.items():
+        tracked = not f16 and not swiglu
+        bits, maxima = oracle_lib.int8_gemm(oracle, *make_golden.gemm_operands(name), f16=f16,
+                                            swiglu=swiglu,
+                                            maxima_first_column=128 if tracked else None)
+        expected = fixture[f"{name}_output"]
+        if swiglu:
+            # BF16 bit patterns of one sign are ordered: at most one step apart.
+            assert np.all(np.abs(bits.astype(np.int32) - expected.astype(np.int32)) <= 1)
+            assert np.mean(bits != expected) < 0.01
+        else:
+            assert np.array_equal(bits, expected), name
+        if tracked:
+            assert np.array_equal(maxima, fixture[f"{name}_maxima"])
