@@ -590,6 +590,8 @@ def run_sharded(args) -> None:
     for _ in range(max(1, args.warmup // 2)):
         end_to_end()
     e2e_ms = time_region(torch, end_to_end, args.steps, barrier=dist.barrier)
+    wires = None if args.skip_gemm else sharded_block(torch, dist, attention, args, shard, layer,
+                                                      dense, qkv, output, tokens, heads)
     status = attention.take_status()
     times = torch.tensor([ms, e2e_ms, float(status)], dtype=torch.float64, device="cuda")
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -622,9 +624,68 @@ def run_sharded(args) -> None:
             "cpu_baseline": None,
             "clocks": sampler.summary(),
         }
+        if wires is not None:
+            line["extra"] = {"projection_and_attention": wires}
         print(json.dumps(line))
     dist.barrier()
     dist.destroy_process_group()
+
+
+def sharded_block(torch, dist, attention, args, shard, layer, dense, qkv, output, tokens,
+                  heads) -> dict:
+    """The INT8 qkv projection and the attention of one sharded block, with either wire format:
+    q, k and v exchanged after projecting this rank's tokens onto every head (two all-to-alls), or
+    the INT8 block input gathered and every token projected onto this rank's heads (an all-gather
+    and one all-to-all). Both do the same arithmetic per rank and must give the same bits."""
+    from mmh3_b200 import gemm
+    from mmh3_b200.shard import ProjectedUlyssesAttention, own_projection_rows
+
+    inner = heads * HEAD_DIM
+    own = shard.own_tokens
+    generator = torch.Generator(device="cuda").manual_seed(5)
+    weights = torch.randint(-127, 128, (3 * inner, inner), dtype=torch.int8, device="cuda",
+                            generator=generator)
+    weight_scales = torch.rand(3 * inner, device="cuda", generator=generator) * 2e-4 + 1e-4
+    generator.manual_seed(7 + own.start)
+    rows = torch.randint(-127, 128, (len(own), inner), dtype=torch.int8, device="cuda",
+                         generator=generator)
+    row_scales = torch.rand(len(own), device="cuda", generator=generator) * 0.02 + 0.01
+    selected = own_projection_rows(heads, shard.own_heads).cuda()
+    own_weights = weights[selected].contiguous()
+    own_weight_scales = weight_scales[selected].contiguous()
+
+    def project_own_heads(part_rows, part_scales, target):
+        gemm.int8(None, part_rows, own_weights, part_scales, own_weight_scales,
+                  gemm.Output(target.view(torch.int16)), part_rows.shape[0],
+                  own_weights.shape[0], inner)
+
+    projected = ProjectedUlyssesAttention(shard, tokens, heads, inner, project_own_heads, dense,
+                                          "cuda", torch.bfloat16, unpack=attention.shard_unpack)
+
+    def wire_qkv():
+        gemm.int8(None, rows, weights, row_scales, weight_scales,
+                  gemm.Output(qkv.view(torch.int16)), len(own), 3 * inner, inner)
+        layer.run(qkv, output)
+
+    def wire_rows():
+        projected.run(rows, row_scales, output)
+
+    steps = max(2, args.steps // 2)
+    wire_qkv()
+    first = output.clone()
+    qkv_ms = time_region(torch, wire_qkv, steps, barrier=dist.barrier)
+    wire_rows()
+    agree = float(torch.equal(first, output))
+    rows_ms = time_region(torch, wire_rows, steps, barrier=dist.barrier)
+    times = torch.tensor([qkv_ms, rows_ms, -agree], dtype=torch.float64, device="cuda")
+    dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    qkv_ms, rows_ms, disagree = times.tolist()
+    return {
+        "workload": f"INT8 qkv projection (K = {inner}) + dense attention, L={tokens}, H={heads}",
+        "qkv_wire_ms": qkv_ms, "qkv_wire_bytes_per_rank": layer.exchange_bytes(),
+        "int8_wire_ms": rows_ms, "int8_wire_bytes_per_rank": projected.exchange_bytes(),
+        "outputs_identical": disagree == -1.0,
+    }
 
 
 def main() -> None:

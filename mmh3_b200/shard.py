@@ -7,6 +7,11 @@ The reference moves the data with its own socket/RDMA/peer-copy exchange; here t
 NCCL all-to-alls over NVLink through `torch.distributed`, one process per GPU. On CPU ranks (gloo)
 the same code runs with the attention itself supplied by the caller, which is how the partitioning
 and the exchange are tested without a GPU.
+
+`UlyssesAttention` exchanges the projected q, k and v. `ProjectedUlyssesAttention` is the
+reference's own wire format (crates/mmh3-cuda/src/dit.rs:1609-1711): the ranks exchange the
+quantized block input, INT8 rows with one scale each, and every rank projects the whole sequence
+onto its own heads.
 """
 
 from __future__ import annotations
@@ -86,7 +91,7 @@ class UlyssesAttention:
 
     def __init__(self, shard: Shard, total_tokens: int, heads: int, attention: AttentionFn,
                  device, dtype=torch.bfloat16, pack: PackFn | None = None,
-                 unpack: PackFn | None = None, group=None):
+                 unpack: PackFn | None = None, group=None, exchanges_qkv: bool = True):
         self.shard, self.tokens, self.heads = shard, total_tokens, heads
         self.attention = attention
         self.group = group
@@ -97,7 +102,8 @@ class UlyssesAttention:
         make = dict(dtype=dtype, device=device)
         # Sent: for each peer, its heads of my tokens. Received: my heads of every rank's tokens,
         # which is already [all tokens, 3, own heads, 128] because tokens are outermost.
-        self.send_inputs = torch.empty(own_tokens * 3 * heads * HEAD_DIM, **make)
+        self.send_inputs = torch.empty(own_tokens * 3 * heads * HEAD_DIM if exchanges_qkv else 0,
+                                       **make)
         self.inputs = torch.empty(total_tokens * 3 * own_heads * HEAD_DIM, **make)
         self.attended = torch.empty(total_tokens * own_heads * HEAD_DIM, **make)
         self.received = torch.empty(own_tokens * heads * HEAD_DIM, **make)
@@ -127,11 +133,102 @@ class UlyssesAttention:
         dist.all_to_all_single(self.inputs, self.send_inputs, self.input_recv_splits,
                                self.input_send_splits, group=self.group)
         self.attention(self.inputs, self.attended, self.tokens, self.own_heads)
+        self.exchange_outputs(output_own)
+
+    def exchange_outputs(self, output_own: torch.Tensor) -> None:
+        """Turns "every token, my heads" in `attended` back into "my tokens, every head"
+        (dit.rs:1713-1800)."""
         dist.all_to_all_single(self.received, self.attended, self.output_recv_splits,
                                self.output_send_splits, group=self.group)
         offset = 0
-        for peer, heads in enumerate(shard.heads):
+        for peer, heads in enumerate(self.shard.heads):
             count = self.output_recv_splits[peer]
             self.unpack(self.received[offset:offset + count], output_own, self.own_tokens,
                         self.heads, heads.start, len(heads))
             offset += count
+
+
+# project(rows INT8 [count, hidden], scales FP32 [count], qkv [count, 3, own heads, 128]): the
+# rank's own columns of the fused qkv projection over `count` rows of the block input.
+ProjectFn = Callable[[torch.Tensor, torch.Tensor, torch.Tensor], None]
+
+
+def own_projection_rows(heads: int, own: range) -> torch.Tensor:
+    """Rows of the fused qkv weight [3 * heads * 128, hidden] that produce q, k and v of the heads
+    in `own`, in the order [3, own heads, 128]."""
+    inner = heads * HEAD_DIM
+    one = torch.arange(own.start * HEAD_DIM, own.stop * HEAD_DIM)
+    return torch.cat([one, inner + one, 2 * inner + one])
+
+
+class ProjectedUlyssesAttention(UlyssesAttention):
+    """One attention layer over a sequence-sharded, quantized block input.
+
+    `run(rows_own, scales_own, output_own)` takes this rank's rows of the block input as the INT8
+    GEMM reads them, [own tokens, hidden] with one FP32 scale a row, gathers every rank's
+    (dit.rs:1609-1711: publish, send, fetch), projects the whole sequence onto this rank's heads
+    with `project`, attends, and fills this rank's rows of the output like `UlyssesAttention`.
+    The rank's own rows are projected while the others' are on the wire.
+    """
+
+    def __init__(self, shard: Shard, total_tokens: int, heads: int, hidden: int,
+                 project: ProjectFn, attention: AttentionFn, device, dtype=torch.bfloat16,
+                 unpack: PackFn | None = None, group=None):
+        super().__init__(shard, total_tokens, heads, attention, device, dtype, None, unpack,
+                         group, exchanges_qkv=False)
+        self.hidden, self.project = hidden, project
+        self.rows = torch.empty((total_tokens, hidden), dtype=torch.int8, device=device)
+        self.scales = torch.empty(total_tokens, dtype=torch.float32, device=device)
+        shares = {len(cut) for cut in shard.tokens}
+        self.even = len(shares) == 1
+
+    def exchange_bytes(self) -> int:
+        """Bytes this rank sends to other ranks per layer."""
+        rank = self.shard.rank
+        peers = self.shard.ranks - 1
+        gathered = peers * self.own_tokens * (self.hidden + 4)
+        outputs = sum(self.output_send_splits) - self.output_send_splits[rank]
+        return gathered + outputs * self.attended.element_size()
+
+    def gather_inputs(self, rows_own: torch.Tensor, scales_own: torch.Tensor):
+        """Starts the exchange of the block input and returns what to wait on."""
+        shard = self.shard
+        if self.even:
+            return [dist.all_gather_into_tensor(self.rows, rows_own, group=self.group,
+                                                async_op=True),
+                    dist.all_gather_into_tensor(self.scales, scales_own, group=self.group,
+                                                async_op=True)]
+        # Uneven cuts: every rank's rows go out as one broadcast into their place.
+        own = shard.own_tokens
+        self.rows[own.start:own.stop].copy_(rows_own)
+        self.scales[own.start:own.stop].copy_(scales_own)
+        pending = []
+        for peer, cut in enumerate(shard.tokens):
+            source = peer if self.group is None else dist.get_global_rank(self.group, peer)
+            pending.append(dist.broadcast(self.rows[cut.start:cut.stop], source,
+                                          group=self.group, async_op=True))
+            pending.append(dist.broadcast(self.scales[cut.start:cut.stop], source,
+                                          group=self.group, async_op=True))
+        return pending
+
+    def run(self, rows_own: torch.Tensor, scales_own: torch.Tensor,  # type: ignore[override]
+            output_own: torch.Tensor) -> None:
+        shard = self.shard
+        width = 3 * self.own_heads * HEAD_DIM
+        inputs = self.inputs.view(self.tokens, width)
+        if shard.is_whole:
+            self.project(rows_own, scales_own, inputs)
+            self.attention(self.inputs, output_own, self.tokens, self.heads)
+            return
+        pending = self.gather_inputs(rows_own, scales_own)
+        own = shard.own_tokens
+        self.project(rows_own, scales_own, inputs[own.start:own.stop])
+        for work in pending:
+            work.wait()
+        # The rows before and after this rank's own.
+        for cut in (range(0, own.start), range(own.stop, self.tokens)):
+            if len(cut) > 0:
+                self.project(self.rows[cut.start:cut.stop], self.scales[cut.start:cut.stop],
+                             inputs[cut.start:cut.stop])
+        self.attention(self.inputs, self.attended, self.tokens, self.own_heads)
+        self.exchange_outputs(output_own)

@@ -210,3 +210,52 @@ def test_video_sparse_attention_at_the_benchmark_size(reference_kernels):
     report("VSA, L=125,504, H=32, 252 of 2,016 video tiles kept",
            milliseconds(lambda: attention.vsa(qkv, None, ours, vsa_layout, SCALE, kept, workspace)),
            milliseconds(reference_call))
+
+
+def test_qkv_projection_at_the_benchmark_size(reference_kernels):
+    """The INT8 qkv projection of the same layer (M = 66,048, N = 12,288, K = 4,096): outputs and
+    per-head |v| maxima bit-identical to the reference's kernel, whole tensors; and a property that
+    needs no reference: doubling every activation scale doubles every output exactly."""
+    from mmh3_b200 import gemm
+
+    generator = torch.Generator(device="cuda").manual_seed(4)
+    activations = torch.randint(-127, 128, (TOKENS, INNER), dtype=torch.int8, device="cuda",
+                                generator=generator)
+    weights = torch.randint(-127, 128, (3 * INNER, INNER), dtype=torch.int8, device="cuda",
+                            generator=generator)
+    activation_scales = torch.rand(TOKENS, device="cuda", generator=generator) + 0.5
+    weight_scales = torch.rand(3 * INNER, device="cuda", generator=generator) * 1e-4 + 1e-5
+    ours = torch.zeros((TOKENS, 3 * INNER), dtype=torch.int16, device="cuda")
+    theirs = torch.zeros_like(ours)
+    maxima = torch.zeros(HEADS, dtype=torch.float32, device="cuda")
+    their_maxima = torch.zeros_like(maxima)
+
+    def call(scales=activation_scales, output=ours, tracked=maxima):
+        gemm.int8(None, activations, weights, scales, weight_scales,
+                  gemm.Output(output, column_maxima=gemm.ColumnMaxima(tracked, 2 * INNER)),
+                  TOKENS, 3 * INNER, INNER)
+
+    def reference_call():
+        assert reference_kernels.mmh3_int8_gemm(
+            -1, 0, activations.data_ptr(), weights.data_ptr(), activation_scales.data_ptr(),
+            weight_scales.data_ptr(), None, theirs.data_ptr(), 0, 0, TOKENS, 3 * INNER, INNER, 0,
+            None, None, 0, 0, 0.0, their_maxima.data_ptr(), 2 * INNER, None) == 0
+
+    call()
+    torch.cuda.synchronize()
+    reference_call()
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    assert torch.equal(ours, theirs)
+    assert torch.equal(maxima, their_maxima)
+    values = ours.view(torch.bfloat16).view(TOKENS, 3, HEADS, 128)[:, 2]
+    assert torch.equal(maxima, values.float().abs().amax(dim=(0, 2)))
+
+    doubled = torch.zeros_like(ours)
+    call(scales=activation_scales * 2.0, output=doubled, tracked=torch.zeros_like(maxima))
+    assert torch.equal(doubled.view(torch.bfloat16).float(), ours.view(torch.bfloat16).float() * 2.0)
+    del doubled
+
+    # The reference times its tilings on the first call of a shape; it has, above.
+    report("INT8 qkv projection, M=66,048, N=12,288, K=4,096", milliseconds(call),
+           milliseconds(reference_call))

@@ -14,7 +14,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from mmh3_b200.shard import Shard, UlyssesAttention
+from mmh3_b200.shard import (ProjectedUlyssesAttention, Shard, UlyssesAttention,
+                              own_projection_rows)
 
 HEAD_DIM = 128
 
@@ -59,6 +60,72 @@ def test_split_run_equals_whole_run(ranks, tokens, heads):
     mp.spawn(worker, args=(ranks, port, tokens, heads, results), nprocs=ranks, join=True)
     assert len(results) == ranks
     assert all(error < 1e-5 for error in results.values()), dict(results)
+
+
+def projected_worker(rank, ranks, port, tokens, heads, hidden, results):
+    """The INT8 wire format: every rank gathers the quantized block input and projects the whole
+    sequence onto its own heads. The projection here is the GEMM's definition in float64."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=ranks)
+    try:
+        generator = torch.Generator().manual_seed(11)
+        rows = torch.randint(-127, 128, (tokens, hidden), generator=generator, dtype=torch.int8)
+        scales = torch.rand(tokens, generator=generator) * 0.01 + 0.005
+        weights = torch.randint(-127, 128, (3 * heads * HEAD_DIM, hidden), generator=generator,
+                                dtype=torch.int8)
+        weight_scales = torch.rand(3 * heads * HEAD_DIM, generator=generator) * 0.01 + 0.005
+
+        def projection(selected):
+            def project(part_rows, part_scales, qkv):
+                sums = part_rows.double() @ weights[selected].double().T
+                qkv.copy_((sums * part_scales.double()[:, None] *
+                           weight_scales[selected].double()[None, :]).float())
+            return project
+
+        shard = Shard.even(rank, ranks, tokens, heads, 1)
+        own = shard.own_tokens
+        layer = ProjectedUlyssesAttention(
+            shard, tokens, heads, hidden, projection(own_projection_rows(heads, shard.own_heads)),
+            torch_attention, "cpu", torch.float32)
+        output = torch.zeros((len(own), heads, HEAD_DIM))
+        layer.run(rows[own.start:own.stop].contiguous(), scales[own.start:own.stop].contiguous(),
+                  output)
+        whole_shard = Shard.even(0, 1, tokens, heads, 1)
+        whole_layer = ProjectedUlyssesAttention(
+            whole_shard, tokens, heads, hidden,
+            projection(own_projection_rows(heads, range(heads))), torch_attention, "cpu",
+            torch.float32)
+        whole = torch.zeros((tokens, heads, HEAD_DIM))
+        whole_layer.run(rows, scales, whole)
+        results[rank] = (float((output - whole[own.start:own.stop]).abs().max()),
+                         layer.exchange_bytes())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("ranks,tokens,heads", [(2, 96, 4), (3, 100, 7)])
+def test_projected_split_run_equals_whole_run(ranks, tokens, heads):
+    hidden = 64
+    port = free_port()
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(projected_worker, args=(ranks, port, tokens, heads, hidden, results), nprocs=ranks,
+             join=True)
+    assert len(results) == ranks
+    assert all(error < 1e-4 for error, _ in results.values()), dict(results)
+    # What a rank sends: its rows and scales to every peer, and its heads of the others' tokens.
+    shard = Shard.even(0, ranks, tokens, heads, 1)
+    own_tokens, own_heads = len(shard.own_tokens), len(shard.own_heads)
+    expected = (ranks - 1) * own_tokens * (hidden + 4) + \
+        (tokens - own_tokens) * own_heads * HEAD_DIM * 4
+    assert results[0][1] == expected
+
+
+def test_own_projection_rows():
+    rows = own_projection_rows(4, range(1, 3))
+    assert rows.tolist()[:2] == [128, 129] and len(rows) == 3 * 2 * 128
+    assert rows[256].item() == 4 * 128 + 128 and rows[512].item() == 8 * 128 + 128
 
 
 def test_even_cuts():
