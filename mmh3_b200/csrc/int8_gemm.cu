@@ -37,13 +37,17 @@ constexpr int STAGES = 3;
 constexpr int ROWS_BYTES = ROW_TILES * TILE_M * BLOCK_K;
 constexpr int COLUMNS_BYTES = TILE_N * BLOCK_K;
 constexpr int STAGE_BYTES = ROWS_BYTES + COLUMNS_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+// Where an epilogue warp turns its 32 rows of 64 columns around for the stores.
+constexpr int STAGING_ROW = 128;
+constexpr int STAGING_BYTES = 32 * STAGING_ROW;
 
 constexpr int LOAD_WARP = 0;
 constexpr int MMA_WARP = 1;
 constexpr int FIRST_EPILOGUE_WARP = 2;
 constexpr int EPILOGUE_WARPS = 8;
 constexpr int THREADS = (FIRST_EPILOGUE_WARP + EPILOGUE_WARPS) * 32;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPILOGUE_WARPS * STAGING_BYTES + 1024;
+static_assert(SMEM_BYTES + 256 <= 227 * 1024, "ring, staging and barriers exceed an SM");
 constexpr int TMEM_COLUMNS = ROW_TILES * TILE_N;
 constexpr int CHUNK = 32; // columns of one tcgen05.ld
 
@@ -224,6 +228,8 @@ __global__ void __launch_bounds__(THREADS, 1)
         const int quarter = warp % 4;
         const int column_half = epilogue_warp / 4;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        uint8_t *staging = shared_raw + (base - smem_u32(shared_raw)) + STAGES * STAGE_BYTES +
+                           epilogue_warp * STAGING_BYTES;
         int round = 0;
         bool alive = true;
         for (int tile = blockIdx.x; alive && tile < tiles; tile += gridDim.x, round++) {
@@ -242,13 +248,13 @@ __global__ void __launch_bounds__(THREADS, 1)
             tcgen05_fence_after();
             #pragma unroll 1
             for (int half = 0; half < ROW_TILES; half++) {
-                const int row = tile_m * (ROW_TILES * TILE_M) + half * TILE_M + quarter * 32 + lane;
-                const bool stored = inside && row < m;
+                const int first_row =
+                    tile_m * (ROW_TILES * TILE_M) + half * TILE_M + quarter * 32;
+                const int row = first_row + lane;
                 const float row_scale = row < m ? __ldg(activation_scales + row) : 0.0f;
                 const float2 row_scales = make_float2(row_scale, row_scale);
                 const uint32_t accumulator =
                     tmem + lane_base + half * TILE_N + column_half * (TILE_N / 2);
-                Output *output_row = output + static_cast<size_t>(row) * output_stride;
                 uint32_t magnitudes = 0;
                 #pragma unroll 1
                 for (int chunk = 0; chunk < TILE_N / 2 / CHUNK; chunk += 2) {
@@ -256,14 +262,16 @@ __global__ void __launch_bounds__(THREADS, 1)
                     tmem_load_32(accumulator + chunk * CHUNK, products[0]);
                     tmem_load_32(accumulator + (chunk + 1) * CHUNK, products[1]);
                     tmem_wait_load();
-                    if (!stored) {
-                        continue;
+                    if (!inside || first_row >= m) {
+                        continue; // the whole warp: nothing of these rows and columns exists
                     }
+                    const int column = first_column + chunk * CHUNK;
                     #pragma unroll
                     for (int part = 0; part < 2; part++) {
-                        const int column = first_column + (chunk + part) * CHUNK;
                         const float2 *column_scales =
-                            reinterpret_cast<const float2 *>(weight_scales + column);
+                            reinterpret_cast<const float2 *>(weight_scales + column + part * CHUNK);
+                        const float2 *column_bias =
+                            reinterpret_cast<const float2 *>(bias + column + part * CHUNK);
                         uint32_t words[CHUNK / 2];
                         #pragma unroll
                         for (int pair = 0; pair < CHUNK / 2; pair++) {
@@ -274,39 +282,68 @@ __global__ void __launch_bounds__(THREADS, 1)
                             scaled = __fmul2_rn(__fmul2_rn(scaled, row_scales),
                                                 __ldg(column_scales + pair));
                             if (bias != nullptr) {
-                                scaled = __fadd2_rn(
-                                    scaled,
-                                    __ldg(reinterpret_cast<const float2 *>(bias + column) + pair));
+                                scaled = __fadd2_rn(scaled, __ldg(column_bias + pair));
                             }
                             words[pair] = pack(output, scaled);
                         }
+                        if (track && row < m) {
+                            // Magnitudes of BF16 values order like unsigned integers.
+                            #pragma unroll
+                            for (int pair = 0; pair < CHUNK / 2; pair++) {
+                                magnitudes = __vmaxu2(magnitudes, words[pair] & 0x7fff7fffu);
+                            }
+                        }
+                        // The lane's row goes to the warp's staging tile, 16 bytes at a time, at
+                        // positions swizzled by the row so that neither these stores nor the
+                        // loads below meet in a bank.
                         if constexpr (SWIGLU) {
                             // Eight columns hold the gates of four features, then their up
-                            // projections: four outputs.
-                            uint2 *destination = reinterpret_cast<uint2 *>(output_row + column / 2);
+                            // projections: four outputs, 8 bytes.
                             #pragma unroll
-                            for (int group = 0; group < CHUNK / 8; group++) {
-                                destination[group] = make_uint2(
-                                    gated_pair(output, words[group * 4], words[group * 4 + 2]),
-                                    gated_pair(output, words[group * 4 + 1], words[group * 4 + 3]));
+                            for (int group = 0; group < CHUNK / 8; group += 2) {
+                                const int slot = part * 2 + group / 2;
+                                *reinterpret_cast<uint4 *>(staging + lane * STAGING_ROW +
+                                                           ((slot ^ (lane & 7)) << 4)) =
+                                    make_uint4(
+                                        gated_pair(output, words[group * 4], words[group * 4 + 2]),
+                                        gated_pair(output, words[group * 4 + 1],
+                                                   words[group * 4 + 3]),
+                                        gated_pair(output, words[group * 4 + 4],
+                                                   words[group * 4 + 6]),
+                                        gated_pair(output, words[group * 4 + 5],
+                                                   words[group * 4 + 7]));
                             }
                         } else {
-                            uint4 *destination = reinterpret_cast<uint4 *>(output_row + column);
                             #pragma unroll
                             for (int group = 0; group < CHUNK / 8; group++) {
-                                destination[group] =
+                                const int slot = part * 4 + group;
+                                *reinterpret_cast<uint4 *>(staging + lane * STAGING_ROW +
+                                                           ((slot ^ (lane & 7)) << 4)) =
                                     make_uint4(words[group * 4], words[group * 4 + 1],
                                                words[group * 4 + 2], words[group * 4 + 3]);
                             }
-                            if (track) {
-                                // Magnitudes of BF16 values order like unsigned integers.
-                                #pragma unroll
-                                for (int pair = 0; pair < CHUNK / 2; pair++) {
-                                    magnitudes = __vmaxu2(magnitudes, words[pair] & 0x7fff7fffu);
-                                }
-                            }
                         }
                     }
+                    __syncwarp();
+                    // Back out by rows: a store instruction covers whole 128-byte runs of four
+                    // rows (64-byte runs of eight with SwiGLU) instead of 16 bytes of 32 rows.
+                    constexpr int SLOTS = SWIGLU ? 4 : 8;       // 16-byte pieces of a staged row
+                    constexpr int ROWS_AT_ONCE = 32 / SLOTS;
+                    const int slot = lane % SLOTS;
+                    #pragma unroll
+                    for (int pass = 0; pass < 32 / ROWS_AT_ONCE; pass++) {
+                        const int staged_row = pass * ROWS_AT_ONCE + lane / SLOTS;
+                        const uint4 piece = *reinterpret_cast<const uint4 *>(
+                            staging + staged_row * STAGING_ROW + ((slot ^ (staged_row & 7)) << 4));
+                        if (first_row + staged_row < m) {
+                            Output *destination =
+                                output +
+                                static_cast<size_t>(first_row + staged_row) * output_stride +
+                                (SWIGLU ? column / 2 : column) + slot * 8;
+                            *reinterpret_cast<uint4 *>(destination) = piece;
+                        }
+                    }
+                    __syncwarp();
                 }
                 if (half == ROW_TILES - 1) {
                     tcgen05_fence_before();
