@@ -14,8 +14,10 @@
 // accumulators of 128 rows by 256 columns of INT32 in tensor memory (all 512 columns of the SM).
 // Warp 0 streams stages of 128 bytes of K (32 KB of activations, 32 KB of weights, 128-byte
 // swizzle) through a ring of three with TMA; one thread of warp 1 issues tcgen05.mma kind::i8 of
-// 128 x 256 x 32 from shared memory; eight warps scale, round and store the accumulators while the
-// ring fills for the next tile. At this tile shape a stage of 64 KB feeds 1,024 cycles of MMA,
+// 128 x 256 x 32 from shared memory; eight warps scale and round the accumulators, turn their rows
+// around in a staging tile of shared memory so that the stores cover whole 128-byte runs, and give
+// tensor memory back as soon as the last columns are in registers, while the ring fills for the
+// next tile. At this tile shape a stage of 64 KB feeds 1,024 cycles of MMA,
 // 64 bytes a cycle, which is what an SM can take from L2; a tile of 128 x 256 would leave room for
 // a second pair of accumulators and an epilogue hidden behind the next tile's MMAs, but needs
 // 96 bytes a cycle.
@@ -240,96 +242,113 @@ __global__ void __launch_bounds__(THREADS, 1)
             const bool inside = first_column < n;
             const bool track =
                 !SWIGLU && maxima != nullptr && inside && first_column >= maxima_first_column;
+            // While the MMAs run: this warp's column scales, bias and row scales into L1.
+            if (inside) {
+                const int line = lane % 4;
+                const void *wanted = nullptr;
+                if (lane < 4) {
+                    wanted = weight_scales + first_column + line * 32;
+                } else if (lane < 8 && bias != nullptr) {
+                    wanted = bias + first_column + line * 32;
+                } else if (lane >= 8 && lane < 8 + ROW_TILES) {
+                    const int rows = tile_m * (ROW_TILES * TILE_M) + (lane - 8) * TILE_M +
+                                     quarter * 32;
+                    wanted = rows < m ? activation_scales + rows : nullptr;
+                }
+                if (wanted != nullptr) {
+                    prefetch_l1(wanted);
+                }
+            }
             alive = mbar_wait(barrier(ACCUMULATOR_FULL), round & 1, watchdog, STATUS_GEMM | 4);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) {
                 break;
             }
             tcgen05_fence_after();
+            auto accumulator = [&](int half, int chunk) {
+                return tmem + lane_base + half * TILE_N + column_half * (TILE_N / 2) +
+                       chunk * CHUNK;
+            };
+            // Two buffers take turns: the load of the next 32 columns is in flight while these
+            // are scaled. tcgen05.wait::ld waits for every load, so the next one is issued right
+            // after it.
+            uint32_t even[CHUNK], odd[CHUNK];
+            tmem_load_32(accumulator(0, 0), even);
             #pragma unroll 1
             for (int half = 0; half < ROW_TILES; half++) {
                 const int first_row =
                     tile_m * (ROW_TILES * TILE_M) + half * TILE_M + quarter * 32;
                 const int row = first_row + lane;
+                // Nothing of these rows and columns exists: the whole warp only drains.
+                const bool idle = !inside || first_row >= m;
                 const float row_scale = row < m ? __ldg(activation_scales + row) : 0.0f;
                 const float2 row_scales = make_float2(row_scale, row_scale);
-                const uint32_t accumulator =
-                    tmem + lane_base + half * TILE_N + column_half * (TILE_N / 2);
                 uint32_t magnitudes = 0;
-                #pragma unroll 1
-                for (int chunk = 0; chunk < TILE_N / 2 / CHUNK; chunk += 2) {
-                    uint32_t products[2][CHUNK];
-                    tmem_load_32(accumulator + chunk * CHUNK, products[0]);
-                    tmem_load_32(accumulator + (chunk + 1) * CHUNK, products[1]);
-                    tmem_wait_load();
-                    if (!inside || first_row >= m) {
-                        continue; // the whole warp: nothing of these rows and columns exists
-                    }
+
+                // Scales, rounds and stages 32 columns of the lane's row.
+                auto scale = [&](const uint32_t (&products)[CHUNK], int chunk) {
                     const int column = first_column + chunk * CHUNK;
+                    const float2 *column_scales =
+                        reinterpret_cast<const float2 *>(weight_scales + column);
+                    const float2 *column_bias = reinterpret_cast<const float2 *>(bias + column);
+                    uint32_t words[CHUNK / 2];
                     #pragma unroll
-                    for (int part = 0; part < 2; part++) {
-                        const float2 *column_scales =
-                            reinterpret_cast<const float2 *>(weight_scales + column + part * CHUNK);
-                        const float2 *column_bias =
-                            reinterpret_cast<const float2 *>(bias + column + part * CHUNK);
-                        uint32_t words[CHUNK / 2];
+                    for (int pair = 0; pair < CHUNK / 2; pair++) {
+                        float2 scaled = make_float2(
+                            static_cast<float>(static_cast<int32_t>(products[pair * 2])),
+                            static_cast<float>(static_cast<int32_t>(products[pair * 2 + 1])));
+                        scaled = __fmul2_rn(__fmul2_rn(scaled, row_scales),
+                                            __ldg(column_scales + pair));
+                        if (bias != nullptr) {
+                            scaled = __fadd2_rn(scaled, __ldg(column_bias + pair));
+                        }
+                        words[pair] = pack(output, scaled);
+                    }
+                    if (track && row < m) {
+                        // Magnitudes of BF16 values order like unsigned integers.
                         #pragma unroll
                         for (int pair = 0; pair < CHUNK / 2; pair++) {
-                            float2 scaled = make_float2(
-                                static_cast<float>(static_cast<int32_t>(products[part][pair * 2])),
-                                static_cast<float>(
-                                    static_cast<int32_t>(products[part][pair * 2 + 1])));
-                            scaled = __fmul2_rn(__fmul2_rn(scaled, row_scales),
-                                                __ldg(column_scales + pair));
-                            if (bias != nullptr) {
-                                scaled = __fadd2_rn(scaled, __ldg(column_bias + pair));
-                            }
-                            words[pair] = pack(output, scaled);
-                        }
-                        if (track && row < m) {
-                            // Magnitudes of BF16 values order like unsigned integers.
-                            #pragma unroll
-                            for (int pair = 0; pair < CHUNK / 2; pair++) {
-                                magnitudes = __vmaxu2(magnitudes, words[pair] & 0x7fff7fffu);
-                            }
-                        }
-                        // The lane's row goes to the warp's staging tile, 16 bytes at a time, at
-                        // positions swizzled by the row so that neither these stores nor the
-                        // loads below meet in a bank.
-                        if constexpr (SWIGLU) {
-                            // Eight columns hold the gates of four features, then their up
-                            // projections: four outputs, 8 bytes.
-                            #pragma unroll
-                            for (int group = 0; group < CHUNK / 8; group += 2) {
-                                const int slot = part * 2 + group / 2;
-                                *reinterpret_cast<uint4 *>(staging + lane * STAGING_ROW +
-                                                           ((slot ^ (lane & 7)) << 4)) =
-                                    make_uint4(
-                                        gated_pair(output, words[group * 4], words[group * 4 + 2]),
-                                        gated_pair(output, words[group * 4 + 1],
-                                                   words[group * 4 + 3]),
-                                        gated_pair(output, words[group * 4 + 4],
-                                                   words[group * 4 + 6]),
-                                        gated_pair(output, words[group * 4 + 5],
-                                                   words[group * 4 + 7]));
-                            }
-                        } else {
-                            #pragma unroll
-                            for (int group = 0; group < CHUNK / 8; group++) {
-                                const int slot = part * 4 + group;
-                                *reinterpret_cast<uint4 *>(staging + lane * STAGING_ROW +
-                                                           ((slot ^ (lane & 7)) << 4)) =
-                                    make_uint4(words[group * 4], words[group * 4 + 1],
-                                               words[group * 4 + 2], words[group * 4 + 3]);
-                            }
+                            magnitudes = __vmaxu2(magnitudes, words[pair] & 0x7fff7fffu);
                         }
                     }
-                    __syncwarp();
-                    // Back out by rows: a store instruction covers whole 128-byte runs of four
-                    // rows (64-byte runs of eight with SwiGLU) instead of 16 bytes of 32 rows.
-                    constexpr int SLOTS = SWIGLU ? 4 : 8;       // 16-byte pieces of a staged row
+                    // The lane's row goes to the warp's staging tile, 16 bytes at a time, at
+                    // positions swizzled by the row so that neither these stores nor the loads
+                    // of `store_rows` meet in a bank.
+                    const int part = chunk % 2;
+                    if constexpr (SWIGLU) {
+                        // Eight columns hold the gates of four features, then their up
+                        // projections: four outputs, 8 bytes.
+                        #pragma unroll
+                        for (int group = 0; group < CHUNK / 8; group += 2) {
+                            const int slot = part * 2 + group / 2;
+                            *reinterpret_cast<uint4 *>(staging + lane * STAGING_ROW +
+                                                       ((slot ^ (lane & 7)) << 4)) =
+                                make_uint4(
+                                    gated_pair(output, words[group * 4], words[group * 4 + 2]),
+                                    gated_pair(output, words[group * 4 + 1], words[group * 4 + 3]),
+                                    gated_pair(output, words[group * 4 + 4], words[group * 4 + 6]),
+                                    gated_pair(output, words[group * 4 + 5], words[group * 4 + 7]));
+                        }
+                    } else {
+                        #pragma unroll
+                        for (int group = 0; group < CHUNK / 8; group++) {
+                            const int slot = part * 4 + group;
+                            *reinterpret_cast<uint4 *>(staging + lane * STAGING_ROW +
+                                                       ((slot ^ (lane & 7)) << 4)) =
+                                make_uint4(words[group * 4], words[group * 4 + 1],
+                                           words[group * 4 + 2], words[group * 4 + 3]);
+                        }
+                    }
+                };
+                // The 64 staged columns back out by rows: a store instruction covers whole
+                // 128-byte runs of four rows (64-byte runs of eight with SwiGLU) instead of 16
+                // bytes of 32 rows.
+                auto store_rows = [&](int chunk) {
+                    constexpr int SLOTS = SWIGLU ? 4 : 8; // 16-byte pieces of a staged row
                     constexpr int ROWS_AT_ONCE = 32 / SLOTS;
+                    const int column = first_column + chunk * CHUNK;
                     const int slot = lane % SLOTS;
+                    __syncwarp();
                     #pragma unroll
                     for (int pass = 0; pass < 32 / ROWS_AT_ONCE; pass++) {
                         const int staged_row = pass * ROWS_AT_ONCE + lane / SLOTS;
@@ -344,13 +363,39 @@ __global__ void __launch_bounds__(THREADS, 1)
                         }
                     }
                     __syncwarp();
+                };
+
+                tmem_wait_load();
+                tmem_load_32(accumulator(half, 1), odd);
+                if (!idle) {
+                    scale(even, 0);
                 }
-                if (half == ROW_TILES - 1) {
+                tmem_wait_load();
+                tmem_load_32(accumulator(half, 2), even);
+                if (!idle) {
+                    scale(odd, 1);
+                    store_rows(0);
+                }
+                tmem_wait_load();
+                tmem_load_32(accumulator(half, 3), odd);
+                if (!idle) {
+                    scale(even, 2);
+                }
+                tmem_wait_load();
+                if (half + 1 < ROW_TILES) {
+                    tmem_load_32(accumulator(half + 1, 0), even);
+                } else {
+                    // Everything is out of tensor memory: the next tile's MMAs may start while
+                    // the last columns are scaled and stored.
                     tcgen05_fence_before();
                     __syncwarp();
                     if (lane == 0) {
                         mbar_arrive(barrier(ACCUMULATOR_EMPTY));
                     }
+                }
+                if (!idle) {
+                    scale(odd, 3);
+                    store_rows(2);
                 }
                 if (track) {
                     const unsigned magnitude = __reduce_max_sync(

@@ -111,6 +111,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t destination, const CUtensor
                  : "memory");
 }
 
+// A hint: the 128-byte line holding `address` into L1.
+__device__ __forceinline__ void prefetch_l1(const void *address) {
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(address));
+}
+
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
