@@ -146,6 +146,82 @@ def dense_bf16(qkv: torch.Tensor, output: torch.Tensor, tokens: int, heads: int,
     )
 
 
+class HostPipeline:
+    """Dense BF16 attention from pinned host buffers to pinned host buffers, for hosts that keep
+    activations off the device between layers.
+
+    Heads are independent, so the sequence of copy in, attention and copy out is run per group of
+    heads on three streams: while one group is attended, the next one's q, k and v cross the bus
+    and the last one's output goes back. Each group's rows are strided in the fused layouts
+    ([tokens, 3, heads, 128] and [tokens, heads, 128]), which a 2D copy describes, and the entry
+    point takes a group as a pointer offset with the same strides. The copies go through
+    cuda-python's runtime binding; torch owns the buffers and the streams.
+    """
+
+    def __init__(self, tokens: int, heads: int, groups: int = 8):
+        from cuda.bindings import runtime
+
+        self.runtime = runtime
+        self.tokens, self.heads = tokens, heads
+        groups = max(1, min(groups, heads))
+        each, extra = divmod(heads, groups)
+        self.groups = []
+        first = 0
+        for group in range(groups):
+            span = each + (1 if group < extra else 0)
+            self.groups.append((first, span))
+            first += span
+        self.copy_in, self.copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+        self.arrived = [torch.cuda.Event() for _ in self.groups]
+        self.attended = [torch.cuda.Event() for _ in self.groups]
+        self.finished = torch.cuda.Event()
+
+    def _copy(self, destination: int, source: int, pitch: int, width: int, rows: int,
+              to_device: bool, stream: torch.cuda.Stream) -> None:
+        kind = (self.runtime.cudaMemcpyKind.cudaMemcpyHostToDevice if to_device
+                else self.runtime.cudaMemcpyKind.cudaMemcpyDeviceToHost)
+        (code,) = self.runtime.cudaMemcpy2DAsync(destination, pitch, source, pitch, width, rows,
+                                                 kind, stream.cuda_stream)
+        check(int(code), "cudaMemcpy2DAsync")
+
+    def run(self, host_qkv: torch.Tensor, qkv: torch.Tensor, output: torch.Tensor,
+            host_output: torch.Tensor, scale: float) -> None:
+        """Enqueues everything and returns; the current stream ends up behind the last copy."""
+        tokens, heads = self.tokens, self.heads
+        inner = heads * HEAD_DIM
+        if min(host_qkv.numel(), qkv.numel()) < tokens * 3 * inner or \
+                min(host_output.numel(), output.numel()) < tokens * inner:
+            raise ValueError("a buffer is smaller than the sequence")
+        if not (host_qkv.is_pinned() and host_output.is_pinned()):
+            raise ValueError("the host buffers must be pinned")
+        current = torch.cuda.current_stream()
+        # What the last call left running on the device buffers comes first.
+        self.copy_in.wait_stream(current)
+        self.copy_out.wait_stream(current)
+        pitch = inner * 2
+        for index, (first, span) in enumerate(self.groups):
+            offset = first * HEAD_DIM * 2
+            self._copy(qkv.data_ptr() + offset, host_qkv.data_ptr() + offset, pitch,
+                       span * HEAD_DIM * 2, tokens * 3, True, self.copy_in)
+            self.arrived[index].record(self.copy_in)
+        for index, (first, span) in enumerate(self.groups):
+            current.wait_event(self.arrived[index])
+            offset = first * HEAD_DIM
+            check(
+                _lib.library().mmh3_attention_bf16(
+                    _pointer(qkv, offset), _pointer(qkv, inner + offset),
+                    _pointer(qkv, 2 * inner + offset), _pointer(output, offset), tokens, span,
+                    3 * inner, 3 * inner, 3 * inner, inner, scale, _stream()),
+                "mmh3_attention_bf16",
+            )
+            self.attended[index].record(current)
+            self.copy_out.wait_event(self.attended[index])
+            self._copy(host_output.data_ptr() + offset * 2, output.data_ptr() + offset * 2, pitch,
+                       span * HEAD_DIM * 2, tokens, False, self.copy_out)
+        self.finished.record(self.copy_out)
+        current.wait_event(self.finished)
+
+
 # -------------------------------------------------------------------------------------------------
 # Quantized
 

@@ -31,7 +31,9 @@ constexpr unsigned int STATUS_DENSE = 0x00010000u;
 constexpr unsigned int STATUS_QUANTIZED = 0x00020000u;
 constexpr unsigned int STATUS_VSA = 0x00030000u;
 
-inline cudaStream_t as_stream(mmh3_stream_t stream) { return reinterpret_cast<cudaStream_t>(stream); }
+inline cudaStream_t as_stream(mmh3_stream_t stream) {
+    return reinterpret_cast<cudaStream_t>(stream);
+}
 
 // The current device, or -1.
 inline int current_device() {
@@ -45,9 +47,9 @@ unsigned int *status_pointer();
 // Multiprocessors of the current device, or 0.
 int multiprocessor_count();
 
-// Encodes a tiled tensor map of up to five dimensions with a swizzle (128 bytes unless told) and zero fill of
-// out-of-range boxes. `strides` are in bytes for dimensions 1 and up. Returns false when the
-// driver refuses, e.g. for a base or a stride that is not a multiple of 16 bytes.
+// Encodes a tiled tensor map of up to five dimensions with a swizzle (128 bytes unless told) and
+// zero fill of out-of-range boxes. `strides` are in bytes for dimensions 1 and up. Returns false
+// when the driver refuses, e.g. for a base or a stride that is not a multiple of 16 bytes.
 bool encode_tensor_map(CUtensorMap *map, CUtensorMapDataType type, int rank, const void *base,
                        const uint64_t *dimensions, const uint64_t *strides, const uint32_t *box,
                        CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B);

@@ -140,7 +140,9 @@ struct QueryRope {
 __device__ __forceinline__ uint64_t row_operand(uint32_t tile) {
     return smem_descriptor(tile, 16, 1024);
 }
-__host__ __device__ constexpr uint32_t row_step(int step) { return (step / 4) * SLAB_BYTES + (step % 4) * 32; }
+__host__ __device__ constexpr uint32_t row_step(int step) {
+    return (step / 4) * SLAB_BYTES + (step % 4) * 32;
+}
 
 // MN-major descriptor of a V tile (N runs along the rows of both slabs), and the byte offset of
 // contraction step `step` (16 of the 128 keys) in it.

@@ -658,7 +658,8 @@ __global__ void __launch_bounds__(THREADS, 2)
             const float *tail_values = tailed ? p.tail_values + route_rows[half] * HEAD_DIM : nullptr;
             float tail_weight = 0.0f;
             if (tailed && stored) {
-                const float centred = maximum - p.row_offsets[static_cast<size_t>(head) * p.tokens + token];
+                const float centred =
+                    maximum - p.row_offsets[static_cast<size_t>(head) * p.tokens + token];
                 const float tail_maximum = p.tail_max[route_rows[half]];
                 const float merged = fmaxf(centred, tail_maximum);
                 const float routed_weight = exp2f(centred - merged);

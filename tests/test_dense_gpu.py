@@ -314,3 +314,24 @@ def test_unsupported_combinations_report_an_error():
     odd = attention.make_layout((3 * 128 + 1,) * 3 + (128,))
     arguments = arguments[:7] + (ctypes.byref(odd),) + arguments[8:]
     assert library.mmh3_attention(0, 128, *arguments, None) == _lib.CUDA_ERROR_NOT_SUPPORTED
+
+
+@pytest.mark.parametrize("groups", [1, 4])
+def test_host_pipeline_equals_one_call(groups):
+    """Pinned host buffers in and out, a group of heads at a time on three streams: the same bits
+    as one call over device buffers, twice in a row over the same buffers."""
+    tokens, heads = 700, 6
+    host_qkv = synthetic.dense_qkv(tokens, heads, seed=21, pinned=True)
+    expected = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    attention.dense_bf16(host_qkv.cuda(), expected, tokens, heads, SCALE)
+    qkv = torch.zeros((tokens, 3, heads, 128), dtype=torch.bfloat16, device="cuda")
+    output = torch.zeros_like(expected)
+    host_output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16).pin_memory()
+    pipeline = attention.HostPipeline(tokens, heads, groups=groups)
+    assert [span for _, span in pipeline.groups] == ([6] if groups == 1 else [2, 2, 1, 1])
+    for _ in range(2):
+        host_output.zero_()
+        pipeline.run(host_qkv, qkv, output, host_output, SCALE)
+        torch.cuda.synchronize()
+        assert attention.take_status() == 0
+        assert torch.equal(host_output, expected.cpu())
