@@ -48,6 +48,26 @@ int mmh3_int8_gemm(int config, int group_m, const int8_t *activations, const int
                    int adapter_down_stride, float adapter_scale, unsigned *column_maxima,
                    int maxima_first_column, mmh3_stream_t stream);
 
+/* The bookkeeping of the reference's tiling search, which times the tilings of a shape on its first
+ * call and lets the host save and restore what it chose (bound in
+ * crates/mmh3-cuda/src/algorithms.rs:42-44). This library runs one tiling for every shape, so
+ * nothing is ever chosen: mmh3_int8_gemm_tilings reports no entries (returns 0 and writes nothing),
+ * mmh3_int8_gemm_adopt ignores what it is given, and mmh3_int8_gemm_tiling_key writes a line naming
+ * the GPU and this library into `key` (`capacity` bytes; cudaErrorInvalidValue if it does not fit),
+ * so that files saved by the reference's search are recognised as foreign.
+ * Replace crates/mmh3-cuda/kernels/int8_gemm.cu:864-871, 940-998. */
+typedef struct Mmh3Int8Tiling {
+    int64_t m;
+    int64_t n;
+    int64_t k;
+    int64_t rank;
+    int64_t config;
+    int64_t group_m;
+} Mmh3Int8Tiling;
+int mmh3_int8_gemm_tilings(Mmh3Int8Tiling *chosen, int capacity);
+void mmh3_int8_gemm_adopt(const Mmh3Int8Tiling *chosen, int count);
+int mmh3_int8_gemm_tiling_key(char *key, int capacity);
+
 /* Reorders the rows of a [rows, row_bytes] matrix whose first half are SwiGLU gates and second half
  * the matching up projections into groups of eight: the gates of four features, then their up
  * projections. Replaces crates/mmh3-cuda/kernels/int8_gemm.cu:1000-1009. */

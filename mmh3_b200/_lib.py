@@ -124,6 +124,8 @@ SIGNATURES = {
                        c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
                        c_float, c_void_p, c_int, c_void_p],
     "mmh3_interleave_swiglu_rows": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "mmh3_int8_gemm_tilings": [c_void_p, c_int],
+    "mmh3_int8_gemm_tiling_key": [ctypes.c_char_p, c_int],
     "mmh3_b200_attention_quantized_static": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                              P(AttentionLayout), c_float, c_void_p],
     "mmh3_b200_take_status": [],

@@ -1,6 +1,8 @@
 // The extern "C" entry points of libmmh3_attn_b200.so: argument checks in the reference's terms,
 // then the launchers. Declarations and the reference function each one replaces are in
 // include/mmh3_attention.h.
+#include <cstdio>
+
 #include "common.cuh"
 
 using namespace mmh3;
@@ -241,6 +243,36 @@ extern "C" int mmh3_int8_gemm_bf16(int config, int group_m, const int8_t *activa
     return mmh3_int8_gemm(config, group_m, activations, weights, activation_scales, weight_scales,
                           nullptr, output, 0, 0, m, n, k, n, nullptr, nullptr, 0, 0, 0.0f, nullptr,
                           0, stream);
+}
+
+extern "C" int mmh3_int8_gemm_tilings(Mmh3Int8Tiling *chosen, int capacity) {
+    (void)chosen;
+    (void)capacity;
+    return 0;
+}
+
+extern "C" void mmh3_int8_gemm_adopt(const Mmh3Int8Tiling *chosen, int count) {
+    (void)chosen;
+    (void)count;
+}
+
+extern "C" int mmh3_int8_gemm_tiling_key(char *key, int capacity) {
+    int device = 0;
+    cudaDeviceProp properties;
+    cudaError_t status = cudaGetDevice(&device);
+    if (status == cudaSuccess) {
+        status = cudaGetDeviceProperties(&properties, device);
+    }
+    if (status != cudaSuccess) {
+        return static_cast<int>(status);
+    }
+    if (key == nullptr || capacity <= 0) {
+        return INVALID_VALUE;
+    }
+    const int written =
+        std::snprintf(key, static_cast<size_t>(capacity), "%s, sm_%d%d, one tcgen05 tiling",
+                      properties.name, properties.major, properties.minor);
+    return written < 0 || written >= capacity ? INVALID_VALUE : 0;
 }
 
 extern "C" int mmh3_interleave_swiglu_rows(const void *source, void *destination, int rows,

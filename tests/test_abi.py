@@ -32,9 +32,9 @@ def test_headers_compile_as_c():
 def test_every_declared_symbol_is_exported():
     library = _lib.library()
     names = declared_functions()
-    assert len(names) == 18
+    assert len(names) == 20
     assert sorted(_lib.SIGNATURES) == names
-    for name in names:
+    for name in names + ["mmh3_int8_gemm_adopt"]:  # the one declared function that returns void
         assert getattr(library, name) is not None
 
 
@@ -130,5 +130,9 @@ def test_gemm_arguments_are_rejected_before_any_launch():
     assert call(maxima=operand, swiglu=1) == invalid
     assert call(maxima=operand, first_column=64) == invalid
     assert call(down=operand) == _lib.CUDA_ERROR_NOT_SUPPORTED
+    # Nothing is ever chosen, and what the reference's search saved is not adopted.
+    assert library.mmh3_int8_gemm_tilings(None, 0) == 0
+    library.mmh3_int8_gemm_adopt.restype = None
+    library.mmh3_int8_gemm_adopt(None, 0)
     assert library.mmh3_interleave_swiglu_rows(operand, operand, 12, 256, None) == invalid
     assert library.mmh3_interleave_swiglu_rows(operand, operand, 16, 6, None) == invalid

@@ -182,6 +182,11 @@ def test_rejects_what_the_reference_rejects():
     assert call(down=a) == _lib.CUDA_ERROR_NOT_SUPPORTED   # the adapter is not built
     assert attention.take_status() == 0
     assert gemm.configs() == 2 and gemm.group_heights() == [4, 8, 16]
+    # The tiling search's bookkeeping: nothing chosen, a key that names this library.
+    key = ctypes.create_string_buffer(128)
+    assert _lib.library().mmh3_int8_gemm_tilings(None, 0) == 0
+    assert _lib.library().mmh3_int8_gemm_tiling_key(key, 128) == 0 and b"tcgen05" in key.value
+    assert _lib.library().mmh3_int8_gemm_tiling_key(key, 4) == invalid
 
 
 def test_value_maxima_feed_the_attention_inputs():
