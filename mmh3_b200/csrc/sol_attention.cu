@@ -109,8 +109,8 @@ __global__ void __launch_bounds__(THREADS)
 }
 
 // One CTA takes QUERIES consecutive query blocks of one head. A thread holds one centred block key
-// in registers and scores it against each of the CTA's centroids, which sit in shared memory
-// regrouped by chain; then the next key block, 128 further on.
+// in registers and scores it against each of the CTA's centroids, which sit in shared memory; then
+// the next key block, 128 further on.
 template <int QUERIES>
 __global__ void __launch_bounds__(THREADS, 3)
     route_kernel(Mmh3SparseWorkspace workspace, int tokens, int blocks, float tau, float log2_scale,
@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(THREADS, 3)
     const float variance = workspace.key_variance[head * HEAD_DIM + threadIdx.x];
     for (int query = 0; query < queries; query++) {
         const float centroid = workspace.centroids[(first_row + query) * HEAD_DIM + threadIdx.x];
-        reinterpret_cast<float *>(&centroids[query][threadIdx.x % 32])[threadIdx.x / 32] = centroid;
+        reinterpret_cast<float *>(&centroids[query][0])[threadIdx.x] = centroid;
         const float spread =
             cta_reduce(__fmul_rn(__fmul_rn(centroid, centroid), variance), scratch, false);
         if (threadIdx.x == 0) {
@@ -146,21 +146,12 @@ __global__ void __launch_bounds__(THREADS, 3)
 
     const float *head_keys = workspace.block_keys + static_cast<size_t>(head) * blocks * HEAD_DIM;
     for (int key_block = threadIdx.x; key_block < blocks; key_block += THREADS) {
-        float key[HEAD_DIM];
-        const float4 *row = reinterpret_cast<const float4 *>(
-            head_keys + static_cast<size_t>(key_block) * HEAD_DIM);
-        #pragma unroll
-        for (int chunk = 0; chunk < HEAD_DIM / 4; chunk++) {
-            const float4 loaded = __ldg(row + chunk);
-            key[chunk * 4] = loaded.x;
-            key[chunk * 4 + 1] = loaded.y;
-            key[chunk * 4 + 2] = loaded.z;
-            key[chunk * 4 + 3] = loaded.w;
-        }
+        float2 key[HEAD_DIM / 2];
+        load_row(head_keys + static_cast<size_t>(key_block) * HEAD_DIM, key);
         #pragma unroll 1
         for (int query = 0; query < queries; query++) {
             const int query_block = first_query + query;
-            const float score = __fmul_rn(score_tree<1, 0>(centroids[query], key), log2_scale);
+            const float score = __fmul_rn(score_tree(centroids[query], key), log2_scale);
             weights[static_cast<size_t>(query) * blocks + key_block] = score;
             routed[static_cast<size_t>(query) * blocks + key_block] =
                 score > thresholds[query] || abs(query_block - key_block) <= 1 ||

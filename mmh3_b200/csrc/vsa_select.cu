@@ -6,8 +6,8 @@
 // score: 32 chains of four fused multiply-adds over dimensions l, l + 32, l + 64, l + 96, summed
 // over a balanced tree that pairs chains by bit 4 of l first and by bit 0 last, then one multiply
 // by the scale. Here one thread evaluates that whole tree: it holds one pooled key in registers and
-// scores it against each of its CTA's eight query tiles, whose pooled queries sit in shared memory
-// regrouped by chain; the reference spreads a score over the lanes of a warp. The selection itself
+// scores it against each of its CTA's eight query tiles, whose pooled queries sit in shared
+// memory, two chains to a packed operation; the reference spreads a score over the lanes of a warp. The selection itself
 // is a function of the scores alone, so it is free to differ: here a warp finds the kept-th
 // largest video score with a four-pass radix select over
 // order-preserving integer keys (the reference descends one bit at a time), ties go to the lower
@@ -51,7 +51,7 @@ __device__ __forceinline__ float block_reduce(float value, float *scratch, bool 
 
 // One CTA takes QUERIES consecutive query tiles of one head. A thread holds one pooled key in
 // registers (read once, straight from L2) and scores it against each of the CTA's queries, which
-// sit in shared memory regrouped by chain; then the next key, 128 tiles further on.
+// sit in shared memory; then the next key, 128 tiles further on.
 template <int QUERIES>
 __global__ void __launch_bounds__(THREADS, 3)
     select_kernel(Mmh3VsaWorkspace workspace, int tiles, int prefix_tiles, int kept, float scale,
@@ -69,34 +69,24 @@ __global__ void __launch_bounds__(THREADS, 3)
     const size_t first_row = static_cast<size_t>(head) * tiles + first_query;
 
     for (int index = threadIdx.x; index < QUERIES * 32; index += THREADS) {
-        const int query = index / 32, chain = index % 32;
-        float4 grouped = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const int query = index / 32, four = index % 32;
+        float4 values = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         if (query < query_count) {
-            const float *pooled = workspace.pooled_query + (first_row + query) * HEAD_DIM;
-            grouped = make_float4(pooled[chain], pooled[chain + 32], pooled[chain + 64],
-                                  pooled[chain + 96]);
+            values = reinterpret_cast<const float4 *>(workspace.pooled_query +
+                                                      (first_row + query) * HEAD_DIM)[four];
         }
-        queries[query][chain] = grouped;
+        queries[query][four] = values;
     }
     __syncthreads();
 
     const float *head_keys = workspace.pooled_key + static_cast<size_t>(head) * tiles * HEAD_DIM;
     for (int tile = threadIdx.x; tile < tiles; tile += THREADS) {
-        float key[HEAD_DIM];
-        const float4 *row = reinterpret_cast<const float4 *>(head_keys +
-                                                             static_cast<size_t>(tile) * HEAD_DIM);
-        #pragma unroll
-        for (int chunk = 0; chunk < HEAD_DIM / 4; chunk++) {
-            const float4 loaded = __ldg(row + chunk);
-            key[chunk * 4] = loaded.x;
-            key[chunk * 4 + 1] = loaded.y;
-            key[chunk * 4 + 2] = loaded.z;
-            key[chunk * 4 + 3] = loaded.w;
-        }
+        float2 key[HEAD_DIM / 2];
+        load_row(head_keys + static_cast<size_t>(tile) * HEAD_DIM, key);
         #pragma unroll 1
         for (int query = 0; query < query_count; query++) {
             scores[static_cast<size_t>(query) * tiles + tile] =
-                __fmul_rn(score_tree<1, 0>(queries[query], key), scale);
+                __fmul_rn(score_tree(queries[query], key), scale);
         }
     }
     __syncthreads();
