@@ -37,9 +37,14 @@ int mmh3_int8_gemm_bf16(int config, int group_m, const int8_t *activations, cons
  *   128 columns from maxima_first_column (a multiple of 128) on, as the FP32 bits of the BF16
  *   magnitude, raised with atomicMax; the caller zeroes it first. For the qkv projection with
  *   maxima_first_column = 2 * heads * 128 these are the per-head maxima of |v|.
- * A negative config runs the tiling chosen for the shape. Outputs and maxima are bit-identical to
- * the reference's for every config. The low-rank adapter (adapter_down non-null) is not built:
- * cudaErrorNotSupported.
+ * - adapter_down, adapter_up (both non-null, adapter_scale != 0): the low-rank adapter
+ *   adapter_scale * adapter_down . adapter_up^T is added in FP32 before the single rounding;
+ *   adapter_down is BF16 [m, rank] with rows adapter_down_stride elements apart (a multiple of 8,
+ *   at least rank), adapter_up BF16 [n, rank], rank a multiple of 64.
+ * A negative config runs the tiling chosen for the shape. Without an adapter, outputs and maxima
+ * are bit-identical to the reference's for every config; with one, the BF16 products are summed
+ * in FP32 by the tensor cores in an order of their own, and the result is within the bounds of
+ * the reference's tests (|error| <= |x| / 256 + 1e-4).
  * Replaces crates/mmh3-cuda/kernels/int8_gemm.cu:905-936. */
 int mmh3_int8_gemm(int config, int group_m, const int8_t *activations, const int8_t *weights,
                    const float *activation_scales, const float *weight_scales, const float *bias,

@@ -220,20 +220,14 @@ extern "C" int mmh3_int8_gemm(int config, int group_m, const int8_t *activations
                               int rank, int adapter_down_stride, float adapter_scale,
                               unsigned *column_maxima, int maxima_first_column,
                               mmh3_stream_t stream) {
-    (void)adapter_up;
-    (void)rank;
-    (void)adapter_down_stride;
-    (void)adapter_scale;
     if (activations == nullptr || weights == nullptr || activation_scales == nullptr ||
         weight_scales == nullptr || output == nullptr) {
         return INVALID_VALUE;
     }
-    if (adapter_down != nullptr) {
-        return NOT_SUPPORTED;
-    }
     return launch_int8_gemm(config, group_m, activations, weights, activation_scales,
                             weight_scales, bias, output, output_is_f16 != 0, swiglu != 0, m, n, k,
-                            output_stride, column_maxima, maxima_first_column, as_stream(stream));
+                            output_stride, adapter_down, adapter_up, rank, adapter_down_stride,
+                            adapter_scale, column_maxima, maxima_first_column, as_stream(stream));
 }
 
 extern "C" int mmh3_int8_gemm_bf16(int config, int group_m, const int8_t *activations,

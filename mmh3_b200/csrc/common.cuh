@@ -152,12 +152,14 @@ int launch_sol_token_attention_quantized(const Mmh3QuantizedWorkspace &workspace
                                          float scale, const Mmh3SparseWorkspace &sparse,
                                          cudaStream_t stream);
 
-// int8_gemm.cu: the scaled INT8 product with its optional bias, SwiGLU and column maxima.
+// int8_gemm.cu: the scaled INT8 product with its optional bias, low-rank adapter, SwiGLU and
+// column maxima.
 int launch_int8_gemm(int config, int group_m, const int8_t *activations, const int8_t *weights,
                      const float *activation_scales, const float *weight_scales, const float *bias,
                      void *output, bool output_is_f16, bool swiglu, int m, int n, int k,
-                     int output_stride, unsigned *column_maxima, int maxima_first_column,
-                     cudaStream_t stream);
+                     int output_stride, const void *adapter_down, const void *adapter_up, int rank,
+                     int adapter_down_stride, float adapter_scale, unsigned *column_maxima,
+                     int maxima_first_column, cudaStream_t stream);
 int launch_interleave_swiglu_rows(const void *source, void *destination, int rows, int row_bytes,
                                   cudaStream_t stream);
 

@@ -2,12 +2,18 @@
 // qkv projection, which also leaves the maximum |v| of each head for the FP8 quantisation of V.
 //
 //   output[r, c] = round((sum_k activations[r, k] * weights[c, k]) * activation_scales[r]
-//                        * weight_scales[c] + bias[c])
+//                        * weight_scales[c]
+//                        + adapter_scale * sum_j adapter_down[r, j] * adapter_up[c, j] + bias[c])
 //
-// rounded once to BF16 or FP16, activations [m, k] and weights [n, k] INT8 with K contiguous. It
+// rounded once to BF16 or FP16, activations [m, k] and weights [n, k] INT8 with K contiguous, the
+// low-rank adapter (BF16) and the bias optional. It
 // replaces crates/mmh3-cuda/kernels/int8_gemm.cu:321-591 (mma.sync over a two-stage ring) and
 // keeps its arithmetic: the integer sums are exact, and the FP32 operations after them are the
-// same in the same order, so the outputs and the column maxima are the same bits.
+// same in the same order, so without an adapter the outputs and the column maxima are the same
+// bits. With an adapter a tile is 128 rows: its INT32 accumulator and an FP32 accumulator for
+// down . up^T sit side by side in tensor memory, and after the K blocks the ring carries blocks of
+// 64 ranks of the two BF16 operands, in the same 128-byte rows, for kind::f16 MMAs. Those sums
+// come in the tensor cores' own order, so that result is held to the reference's bounds instead.
 //
 // One persistent CTA per SM walks tiles of 256 rows by 256 columns in bands of rows of tiles, so
 // the CTAs in flight share rows of activations and columns of weights in L2. A tile is two
@@ -32,33 +38,42 @@ namespace {
 using namespace sm100;
 
 constexpr int TILE_M = 128;     // rows of one accumulator
-constexpr int ROW_TILES = 2;    // accumulators of a tile
 constexpr int TILE_N = 256;
-constexpr int BLOCK_K = 128;    // INT8 elements of one stage along K
-constexpr int STAGES = 3;
-constexpr int ROWS_BYTES = ROW_TILES * TILE_M * BLOCK_K;
+constexpr int BLOCK_K = 128;    // bytes of one stage along K: 128 INT8 values, 64 BF16 ranks
 constexpr int COLUMNS_BYTES = TILE_N * BLOCK_K;
-constexpr int STAGE_BYTES = ROWS_BYTES + COLUMNS_BYTES;
 // Where an epilogue warp turns its 32 rows of 64 columns around for the stores.
 constexpr int STAGING_ROW = 128;
 constexpr int STAGING_BYTES = 32 * STAGING_ROW;
+constexpr int EPILOGUE_WARPS = 8;
+constexpr int MAX_STAGES = 4;
+
+// Without a low-rank adapter a tile is 256 rows: two INT32 accumulators fill tensor memory. With
+// one it is 128 rows: one INT32 accumulator, and one FP32 accumulator for down . up^T beside it.
+template <bool ADAPTED> struct Shape {
+    static constexpr int ROW_TILES = ADAPTED ? 1 : 2;
+    static constexpr int STAGES = ADAPTED ? 4 : 3;
+    static constexpr int ROWS_BYTES = ROW_TILES * TILE_M * BLOCK_K;
+    static constexpr int STAGE_BYTES = ROWS_BYTES + COLUMNS_BYTES;
+    static constexpr int SMEM_BYTES =
+        STAGES * STAGE_BYTES + EPILOGUE_WARPS * STAGING_BYTES + 1024;
+    static_assert(STAGES <= MAX_STAGES, "more stages than barriers");
+    static_assert(SMEM_BYTES + 256 <= 227 * 1024, "ring, staging and barriers exceed an SM");
+};
 
 constexpr int LOAD_WARP = 0;
 constexpr int MMA_WARP = 1;
 constexpr int FIRST_EPILOGUE_WARP = 2;
-constexpr int EPILOGUE_WARPS = 8;
 constexpr int THREADS = (FIRST_EPILOGUE_WARP + EPILOGUE_WARPS) * 32;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPILOGUE_WARPS * STAGING_BYTES + 1024;
-static_assert(SMEM_BYTES + 256 <= 227 * 1024, "ring, staging and barriers exceed an SM");
-constexpr int TMEM_COLUMNS = ROW_TILES * TILE_N;
+constexpr int TMEM_COLUMNS = 2 * TILE_N;
+constexpr uint32_t TMEM_ADAPTER = TILE_N; // the adapter's accumulator, beside the INT32 one
 constexpr int CHUNK = 32; // columns of one tcgen05.ld
 
 constexpr unsigned int STATUS_GEMM = 0x00040000u;
 
 enum Barrier {
     RING_FULL = 0,
-    RING_EMPTY = RING_FULL + STAGES,
-    ACCUMULATOR_FULL = RING_EMPTY + STAGES,
+    RING_EMPTY = RING_FULL + MAX_STAGES,
+    ACCUMULATOR_FULL = RING_EMPTY + MAX_STAGES,
     ACCUMULATOR_EMPTY,
     BARRIERS,
 };
@@ -66,9 +81,14 @@ enum Barrier {
 constexpr uint32_t PRODUCT_MMA =
     instruction_descriptor(ACCUMULATE_S32, FORMAT_S8, FORMAT_S8, 0, 0, TILE_M, TILE_N);
 
+constexpr uint32_t ADAPTER_MMA =
+    instruction_descriptor(ACCUMULATE_F32, FORMAT_BF16, FORMAT_BF16, 0, 0, TILE_M, TILE_N);
+
 struct GemmMaps {
-    CUtensorMap activations;
-    CUtensorMap weights;
+    CUtensorMap activations;  // [m, k] INT8
+    CUtensorMap weights;      // [n, k] INT8
+    CUtensorMap adapter_down; // [m, rank] BF16, rows down_stride apart
+    CUtensorMap adapter_up;   // [n, rank] BF16
 };
 
 struct TileWalk {
@@ -117,14 +137,18 @@ __device__ __forceinline__ uint32_t gated_pair(Output *output, uint32_t gate_wor
                                     gate.y / (1.0f + __expf(-gate.y)) * up.y));
 }
 
-template <typename Output, bool SWIGLU>
+template <typename Output, bool SWIGLU, bool ADAPTED>
 __global__ void __launch_bounds__(THREADS, 1)
     int8_gemm_kernel(const __grid_constant__ GemmMaps maps,
                      const float *__restrict__ activation_scales,
                      const float *__restrict__ weight_scales, const float *__restrict__ bias,
                      Output *__restrict__ output, int m, int n, int k_blocks, int output_stride,
                      TileWalk walk, unsigned *maxima, int maxima_first_column,
-                     unsigned int *status) {
+                     int adapter_blocks, float adapter_scale, unsigned int *status) {
+    constexpr int ROW_TILES = Shape<ADAPTED>::ROW_TILES;
+    constexpr int STAGES = Shape<ADAPTED>::STAGES;
+    constexpr int ROWS_BYTES = Shape<ADAPTED>::ROWS_BYTES;
+    constexpr int STAGE_BYTES = Shape<ADAPTED>::STAGE_BYTES;
     extern __shared__ uint8_t shared_raw[];
     __shared__ __align__(8) uint64_t barriers[BARRIERS];
     __shared__ uint32_t tmem_slot_storage;
@@ -161,12 +185,18 @@ __global__ void __launch_bounds__(THREADS, 1)
         if (lane == 0) {
             tma_prefetch_descriptor(&maps.activations);
             tma_prefetch_descriptor(&maps.weights);
+            if constexpr (ADAPTED) {
+                tma_prefetch_descriptor(&maps.adapter_down);
+                tma_prefetch_descriptor(&maps.adapter_up);
+            }
             int item = 0;
             bool alive = true;
             for (int tile = blockIdx.x; alive && tile < tiles; tile += gridDim.x) {
                 int tile_m, tile_n;
                 walk.locate(tile, tile_m, tile_n);
-                for (int k_block = 0; k_block < k_blocks; k_block++, item++) {
+                // The K blocks of the INT8 operands, then the adapter's blocks of 64 ranks: the
+                // same 128-byte rows in the same places.
+                for (int block = 0; block < k_blocks + adapter_blocks; block++, item++) {
                     const int stage = item % STAGES;
                     const int use = item / STAGES;
                     if (use > 0 && !mbar_wait(barrier(RING_EMPTY + stage), (use - 1) & 1,
@@ -175,11 +205,15 @@ __global__ void __launch_bounds__(THREADS, 1)
                         break;
                     }
                     const uint32_t destination = base + stage * STAGE_BYTES;
+                    const bool adapter = block >= k_blocks;
+                    // Coordinates are in elements: bytes for INT8, BF16 values for the adapter.
+                    const int along = adapter ? (block - k_blocks) * (BLOCK_K / 2) : block * BLOCK_K;
                     mbar_expect_tx(barrier(RING_FULL + stage), STAGE_BYTES);
-                    tma_load_2d(destination, &maps.activations, barrier(RING_FULL + stage),
-                                k_block * BLOCK_K, tile_m * (ROW_TILES * TILE_M));
-                    tma_load_2d(destination + ROWS_BYTES, &maps.weights,
-                                barrier(RING_FULL + stage), k_block * BLOCK_K, tile_n * TILE_N);
+                    tma_load_2d(destination, adapter ? &maps.adapter_down : &maps.activations,
+                                barrier(RING_FULL + stage), along, tile_m * (ROW_TILES * TILE_M));
+                    tma_load_2d(destination + ROWS_BYTES,
+                                adapter ? &maps.adapter_up : &maps.weights,
+                                barrier(RING_FULL + stage), along, tile_n * TILE_N);
                 }
             }
         }
@@ -198,15 +232,27 @@ __global__ void __launch_bounds__(THREADS, 1)
                               !first || step > 0);
                 }
             };
+            // down . up^T over one stage of 64 ranks: four steps of 16 BF16 values along K.
+            auto adapt = [&](int stage, bool first) {
+                const uint32_t stage_base = base + stage * STAGE_BYTES;
+                const uint64_t rows = smem_descriptor(stage_base, 16, 1024);
+                const uint64_t columns = smem_descriptor(stage_base + ROWS_BYTES, 16, 1024);
+                #pragma unroll
+                for (int step = 0; step < BLOCK_K / 32; step++) {
+                    mma_f16_ss(tmem + TMEM_ADAPTER, advance_descriptor(rows, step * 32),
+                               advance_descriptor(columns, step * 32), ADAPTER_MMA,
+                               !first || step > 0);
+                }
+            };
             int item = 0;
             int round = 0;
             bool alive = true;
             for (int tile = blockIdx.x; alive && tile < tiles; tile += gridDim.x, round++) {
-                for (int k_block = 0; k_block < k_blocks; k_block++, item++) {
+                for (int block = 0; block < k_blocks + adapter_blocks; block++, item++) {
                     const int stage = item % STAGES;
                     alive = mbar_wait(barrier(RING_FULL + stage), (item / STAGES) & 1, watchdog,
                                       STATUS_GEMM | 2);
-                    if (alive && k_block == 0 && round > 0) {
+                    if (alive && block == 0 && round > 0) {
                         // The epilogue warps have read the last tile out of both accumulators.
                         alive = mbar_wait(barrier(ACCUMULATOR_EMPTY), (round - 1) & 1, watchdog,
                                           STATUS_GEMM | 3);
@@ -215,8 +261,14 @@ __global__ void __launch_bounds__(THREADS, 1)
                         break;
                     }
                     tcgen05_fence_after();
-                    multiply(0, stage, k_block == 0);
-                    multiply(1, stage, k_block == 0);
+                    if (ADAPTED && block >= k_blocks) {
+                        adapt(stage, block == k_blocks);
+                    } else {
+                        #pragma unroll
+                        for (int half = 0; half < ROW_TILES; half++) {
+                            multiply(half, stage, block == 0);
+                        }
+                    }
                     tcgen05_commit(barrier(RING_EMPTY + stage));
                 }
                 if (alive) {
@@ -273,7 +325,16 @@ __global__ void __launch_bounds__(THREADS, 1)
             // are scaled. tcgen05.wait::ld waits for every load, so the next one is issued right
             // after it.
             uint32_t even[CHUNK], odd[CHUNK];
-            tmem_load_32(accumulator(0, 0), even);
+            if constexpr (!ADAPTED) {
+                tmem_load_32(accumulator(0, 0), even);
+            }
+            // adapter_scale * (down . up^T) joins the scaled product as the reference adds it:
+            // (product / adapter_scale + down . up^T) * adapter_scale
+            // (crates/mmh3-cuda/kernels/int8_gemm.cu:461-487).
+            const float inverse_adapter_scale = ADAPTED ? 1.0f / adapter_scale : 0.0f;
+            const float2 inverse_adapter_scales =
+                make_float2(inverse_adapter_scale, inverse_adapter_scale);
+            const float2 adapter_scales = make_float2(adapter_scale, adapter_scale);
             #pragma unroll 1
             for (int half = 0; half < ROW_TILES; half++) {
                 const int first_row =
@@ -286,7 +347,8 @@ __global__ void __launch_bounds__(THREADS, 1)
                 uint32_t magnitudes = 0;
 
                 // Scales, rounds and stages 32 columns of the lane's row.
-                auto scale = [&](const uint32_t (&products)[CHUNK], int chunk) {
+                auto scale = [&](const uint32_t (&products)[CHUNK],
+                                 const uint32_t (&low_rank)[CHUNK], int chunk) {
                     const int column = first_column + chunk * CHUNK;
                     const float2 *column_scales =
                         reinterpret_cast<const float2 *>(weight_scales + column);
@@ -299,6 +361,13 @@ __global__ void __launch_bounds__(THREADS, 1)
                             static_cast<float>(static_cast<int32_t>(products[pair * 2 + 1])));
                         scaled = __fmul2_rn(__fmul2_rn(scaled, row_scales),
                                             __ldg(column_scales + pair));
+                        if constexpr (ADAPTED) {
+                            const float2 added = make_float2(__uint_as_float(low_rank[pair * 2]),
+                                                             __uint_as_float(low_rank[pair * 2 + 1]));
+                            scaled = __fmul2_rn(
+                                __fadd2_rn(__fmul2_rn(scaled, inverse_adapter_scales), added),
+                                adapter_scales);
+                        }
                         if (bias != nullptr) {
                             scaled = __fadd2_rn(scaled, __ldg(column_bias + pair));
                         }
@@ -365,37 +434,60 @@ __global__ void __launch_bounds__(THREADS, 1)
                     __syncwarp();
                 };
 
-                tmem_wait_load();
-                tmem_load_32(accumulator(half, 1), odd);
-                if (!idle) {
-                    scale(even, 0);
-                }
-                tmem_wait_load();
-                tmem_load_32(accumulator(half, 2), even);
-                if (!idle) {
-                    scale(odd, 1);
-                    store_rows(0);
-                }
-                tmem_wait_load();
-                tmem_load_32(accumulator(half, 3), odd);
-                if (!idle) {
-                    scale(even, 2);
-                }
-                tmem_wait_load();
-                if (half + 1 < ROW_TILES) {
-                    tmem_load_32(accumulator(half + 1, 0), even);
-                } else {
-                    // Everything is out of tensor memory: the next tile's MMAs may start while
-                    // the last columns are scaled and stored.
-                    tcgen05_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(barrier(ACCUMULATOR_EMPTY));
+                if constexpr (ADAPTED) {
+                    // The product and the adapter's sum of the same 32 columns, side by side.
+                    #pragma unroll
+                    for (int chunk = 0; chunk < TILE_N / 2 / CHUNK; chunk++) {
+                        tmem_load_32(accumulator(0, chunk), even);
+                        tmem_load_32(accumulator(0, chunk) + TMEM_ADAPTER, odd);
+                        tmem_wait_load();
+                        if (chunk == TILE_N / 2 / CHUNK - 1) {
+                            tcgen05_fence_before();
+                            __syncwarp();
+                            if (lane == 0) {
+                                mbar_arrive(barrier(ACCUMULATOR_EMPTY));
+                            }
+                        }
+                        if (!idle) {
+                            scale(even, odd, chunk);
+                            if (chunk % 2 == 1) {
+                                store_rows(chunk - 1);
+                            }
+                        }
                     }
-                }
-                if (!idle) {
-                    scale(odd, 3);
-                    store_rows(2);
+                } else {
+                    tmem_wait_load();
+                    tmem_load_32(accumulator(half, 1), odd);
+                    if (!idle) {
+                        scale(even, even, 0);
+                    }
+                    tmem_wait_load();
+                    tmem_load_32(accumulator(half, 2), even);
+                    if (!idle) {
+                        scale(odd, odd, 1);
+                        store_rows(0);
+                    }
+                    tmem_wait_load();
+                    tmem_load_32(accumulator(half, 3), odd);
+                    if (!idle) {
+                        scale(even, even, 2);
+                    }
+                    tmem_wait_load();
+                    if (half + 1 < ROW_TILES) {
+                        tmem_load_32(accumulator(half + 1, 0), even);
+                    } else {
+                        // Everything is out of tensor memory: the next tile's MMAs may start while
+                        // the last columns are scaled and stored.
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            mbar_arrive(barrier(ACCUMULATOR_EMPTY));
+                        }
+                    }
+                    if (!idle) {
+                        scale(odd, odd, 3);
+                        store_rows(2);
+                    }
                 }
                 if (track) {
                     const unsigned magnitude = __reduce_max_sync(
@@ -424,23 +516,26 @@ __global__ void __launch_bounds__(THREADS, 1)
     }
 }
 
-template <typename Output, bool SWIGLU>
+template <typename Output, bool SWIGLU, bool ADAPTED>
 int launch_kernel(const GemmMaps &maps, const float *activation_scales, const float *weight_scales,
                   const float *bias, Output *output, int m, int n, int k, int output_stride,
-                  int band, unsigned *maxima, int maxima_first_column, cudaStream_t stream) {
+                  int band, unsigned *maxima, int maxima_first_column, int rank,
+                  float adapter_scale, cudaStream_t stream) {
     unsigned int *status = status_pointer();
     const int processors = multiprocessor_count();
     if (status == nullptr || processors == 0) {
         return static_cast<int>(cudaErrorInvalidDevice);
     }
+    constexpr int SMEM_BYTES = Shape<ADAPTED>::SMEM_BYTES;
     static SharedMemoryOptIn shared_memory;
     const cudaError_t configured =
-        shared_memory.ensure(int8_gemm_kernel<Output, SWIGLU>, SMEM_BYTES);
+        shared_memory.ensure(int8_gemm_kernel<Output, SWIGLU, ADAPTED>, SMEM_BYTES);
     if (configured != cudaSuccess) {
         return static_cast<int>(configured);
     }
+    constexpr int TILE_ROWS = Shape<ADAPTED>::ROW_TILES * TILE_M;
     TileWalk walk;
-    walk.tiles_m = (m + ROW_TILES * TILE_M - 1) / (ROW_TILES * TILE_M);
+    walk.tiles_m = (m + TILE_ROWS - 1) / TILE_ROWS;
     walk.tiles_n = (n + TILE_N - 1) / TILE_N;
     walk.band = band;
     const int64_t tiles = static_cast<int64_t>(walk.tiles_m) * walk.tiles_n;
@@ -448,9 +543,10 @@ int launch_kernel(const GemmMaps &maps, const float *activation_scales, const fl
         return INVALID_VALUE;
     }
     const int blocks = tiles < processors ? static_cast<int>(tiles) : processors;
-    int8_gemm_kernel<Output, SWIGLU><<<blocks, THREADS, SMEM_BYTES, stream>>>(
+    int8_gemm_kernel<Output, SWIGLU, ADAPTED><<<blocks, THREADS, SMEM_BYTES, stream>>>(
         maps, activation_scales, weight_scales, bias, output, m, n, k / BLOCK_K, output_stride,
-        walk, maxima, maxima_first_column, status);
+        walk, maxima, maxima_first_column, ADAPTED ? rank * 2 / BLOCK_K : 0, adapter_scale,
+        status);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -473,13 +569,22 @@ __global__ void interleave_rows_kernel(const uint32_t *__restrict__ source,
 int launch_int8_gemm(int config, int group_m, const int8_t *activations, const int8_t *weights,
                      const float *activation_scales, const float *weight_scales, const float *bias,
                      void *output, bool output_is_f16, bool swiglu, int m, int n, int k,
-                     int output_stride, unsigned *column_maxima, int maxima_first_column,
-                     cudaStream_t stream) {
+                     int output_stride, const void *adapter_down, const void *adapter_up, int rank,
+                     int adapter_down_stride, float adapter_scale, unsigned *column_maxima,
+                     int maxima_first_column, cudaStream_t stream) {
     // crates/mmh3-cuda/kernels/int8_gemm.cu:640-645, 700-712, 720-722: config 0 needs N in
     // multiples of 128 and config 1 of 256; a negative config is the tiling chosen for the shape.
     // Here every config runs the one tiling, whose results do not depend on it.
+    // int8_gemm.cu:622-624
+    const bool adapted = adapter_down != nullptr && adapter_up != nullptr && adapter_scale != 0.0f;
     if (config > 1 || (config >= 0 && group_m <= 0) || m <= 0 || n <= 0 || k <= 0 ||
         n % (config == 1 ? 256 : 128) != 0 || k % BLOCK_K != 0) {
+        return INVALID_VALUE;
+    }
+    // The adapter comes in blocks of 64 ranks, its down rows at a stride that keeps them 16-byte
+    // aligned (int8_gemm.cu:642-644).
+    if (adapted && (rank <= 0 || rank * 2 % BLOCK_K != 0 || adapter_down_stride < rank ||
+                    adapter_down_stride % 8 != 0)) {
         return INVALID_VALUE;
     }
     if (column_maxima != nullptr &&
@@ -499,7 +604,7 @@ int launch_int8_gemm(int config, int group_m, const int8_t *activations, const i
     const uint64_t row_dimensions[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(m)};
     const uint64_t column_dimensions[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n)};
     const uint64_t strides[1] = {static_cast<uint64_t>(k)};
-    const uint32_t row_box[2] = {BLOCK_K, ROW_TILES * TILE_M};
+    const uint32_t row_box[2] = {BLOCK_K, static_cast<uint32_t>((adapted ? 1 : 2) * TILE_M)};
     const uint32_t column_box[2] = {BLOCK_K, TILE_N};
     if (!encode_tensor_map(&maps.activations, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, activations,
                            row_dimensions, strides, row_box) ||
@@ -507,15 +612,32 @@ int launch_int8_gemm(int config, int group_m, const int8_t *activations, const i
                            column_dimensions, strides, column_box)) {
         return INVALID_VALUE;
     }
-    const int band = config >= 0 ? group_m : 8;
-#define MMH3_GEMM(OUTPUT, SWIGLU)                                                                  \
-    launch_kernel<OUTPUT, SWIGLU>(maps, activation_scales, weight_scales, bias,                    \
-                                  static_cast<OUTPUT *>(output), m, n, k, output_stride, band,     \
-                                  column_maxima, maxima_first_column, stream)
-    if (output_is_f16) {
-        return swiglu ? MMH3_GEMM(__half, true) : MMH3_GEMM(__half, false);
+    maps.adapter_down = maps.activations;
+    maps.adapter_up = maps.weights;
+    if (adapted) {
+        const uint64_t down_dimensions[2] = {static_cast<uint64_t>(rank), static_cast<uint64_t>(m)};
+        const uint64_t up_dimensions[2] = {static_cast<uint64_t>(rank), static_cast<uint64_t>(n)};
+        const uint64_t down_strides[1] = {static_cast<uint64_t>(adapter_down_stride) * 2};
+        const uint64_t up_strides[1] = {static_cast<uint64_t>(rank) * 2};
+        const uint32_t down_box[2] = {BLOCK_K / 2, TILE_M};
+        const uint32_t up_box[2] = {BLOCK_K / 2, TILE_N};
+        if (!encode_tensor_map(&maps.adapter_down, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                               adapter_down, down_dimensions, down_strides, down_box) ||
+            !encode_tensor_map(&maps.adapter_up, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, adapter_up,
+                               up_dimensions, up_strides, up_box)) {
+            return INVALID_VALUE;
+        }
     }
-    return swiglu ? MMH3_GEMM(__nv_bfloat16, true) : MMH3_GEMM(__nv_bfloat16, false);
+    const int band = config >= 0 ? group_m : 8;
+#define MMH3_GEMM(OUTPUT, SWIGLU, ADAPTED)                                                         \
+    launch_kernel<OUTPUT, SWIGLU, ADAPTED>(                                                        \
+        maps, activation_scales, weight_scales, bias, static_cast<OUTPUT *>(output), m, n, k,      \
+        output_stride, band, column_maxima, maxima_first_column, rank, adapter_scale, stream)
+#define MMH3_GEMM_OUTPUT(OUTPUT)                                                                   \
+    (swiglu ? (adapted ? MMH3_GEMM(OUTPUT, true, true) : MMH3_GEMM(OUTPUT, true, false))           \
+            : (adapted ? MMH3_GEMM(OUTPUT, false, true) : MMH3_GEMM(OUTPUT, false, false)))
+    return output_is_f16 ? MMH3_GEMM_OUTPUT(__half) : MMH3_GEMM_OUTPUT(__nv_bfloat16);
+#undef MMH3_GEMM_OUTPUT
 #undef MMH3_GEMM
 }
 

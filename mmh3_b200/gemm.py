@@ -2,7 +2,7 @@
 
 Mirrors the safe wrapper of niw/mmh3's CUDA crate (crates/mmh3-cuda/src/gemm.rs:345-462): the same
 names, argument meaning and bounds checks, with `torch` tensors standing where the crate has
-`DeviceBuffer`s. The low-rank adapter is not built; passing one raises `CudaError` 801.
+`DeviceBuffer`s.
 """
 
 from __future__ import annotations
@@ -23,6 +23,18 @@ class Int8Tiling:
 
     config: int
     group_m: int
+
+
+@dataclasses.dataclass
+class Adapter:
+    """A low-rank adapter scale * down . up^T (gemm.rs:140-156): `down` BF16 [m, rank] with rows
+    `down_stride` elements apart, `up` BF16 [n, rank]; the rank a multiple of 64."""
+
+    down: torch.Tensor
+    up: torch.Tensor
+    rank: int
+    down_stride: int
+    scale: float
 
 
 @dataclasses.dataclass
@@ -59,9 +71,10 @@ def group_heights() -> list[int]:
 
 def int8(tiling: Int8Tiling | None, activations: torch.Tensor, weights: torch.Tensor,
          activation_scales: torch.Tensor, weight_scales: torch.Tensor, output: Output, m: int,
-         n: int, k: int, adapter=None) -> None:
+         n: int, k: int, adapter: Adapter | None = None) -> None:
     """output[m, n] = round(sum_k activations[m, k] * weights[n, k] * activation_scales[m] *
-    weight_scales[n] + the bias). K must be a multiple of 128 and N of the tile width."""
+    weight_scales[n] + the adapter + the bias). K must be a multiple of 128 and N of the tile
+    width."""
     assert activations.numel() * activations.element_size() >= m * k, \
         "activations are smaller than m x k"
     assert weights.numel() * weights.element_size() >= n * k, "weights are smaller than n x k"
@@ -77,7 +90,15 @@ def int8(tiling: Int8Tiling | None, activations: torch.Tensor, weights: torch.Te
         assert maxima.first_column <= n and \
             maxima.values.numel() >= (n - maxima.first_column) // 128, \
             "column maxima are smaller than the groups of 128 columns from first_column"
-    down, up, rank, down_stride, scale = adapter if adapter is not None else (None, None, 0, 0, 0.0)
+    if adapter is not None:
+        assert adapter.down_stride >= adapter.rank and \
+            adapter.down.numel() >= m * adapter.down_stride, \
+            "adapter down activations are smaller than m x down_stride"
+        assert adapter.up.numel() >= n * adapter.rank, "adapter up weights are smaller than n x rank"
+        down, up, rank, down_stride, scale = (adapter.down, adapter.up, adapter.rank,
+                                              adapter.down_stride, adapter.scale)
+    else:
+        down, up, rank, down_stride, scale = None, None, 0, 0, 0.0
     check(_lib.library().mmh3_int8_gemm(
         -1 if tiling is None else tiling.config, 0 if tiling is None else tiling.group_m,
         _pointer(activations), _pointer(weights), _pointer(activation_scales),

@@ -20,15 +20,36 @@ def operands(m: int, n: int, k: int, seed: int, bias: bool = False, swiglu: bool
     return activations, weights, activation_scales, weight_scales, bias_values
 
 
-def definition(activations, weights, activation_scales, weight_scales, bias=None) -> np.ndarray:
-    """sum_k a[m, k] w[n, k] * scale[m] * scale[n] + bias[n] in float64, [m, n]."""
+def definition(activations, weights, activation_scales, weight_scales, bias=None,
+               adapter=None) -> np.ndarray:
+    """sum_k a[m, k] w[n, k] * scale[m] * scale[n] + adapter_scale * down . up^T + bias[n] in
+    float64, [m, n]. `adapter` is (down BF16 bits [m, stride], up BF16 bits [n, rank], rank,
+    scale)."""
     # float64 holds these integer sums exactly.
     sums = activations.astype(np.float64) @ weights.astype(np.float64).T
     result = sums * activation_scales.astype(np.float64)[:, None] * \
         weight_scales.astype(np.float64)[None, :]
+    if adapter is not None:
+        down, up, rank, scale = adapter
+        result = result + scale * (widen(down[:, :rank], False) @ widen(up, False).T)
     if bias is not None:
         result = result + bias.astype(np.float64)[None, :]
     return result
+
+
+def adapter_operands(m: int, n: int, rank: int, stride: int, seed: int, span: float = 2.0):
+    """BF16 down [m, stride] (columns past the rank hold 1000, which must not be read) and up
+    [n, rank], as crates/mmh3-cuda/tests/int8_gemm.rs:93-103 draws them."""
+    random = np.random.RandomState(seed)
+
+    def bf16(values):
+        bits = np.ascontiguousarray(values, dtype=np.float32).view(np.uint32).astype(np.uint64)
+        return (((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) & 0xFFFF).astype(np.uint16)
+
+    down = random.uniform(-span, span, size=(m, stride)).astype(np.float32)
+    down[:, rank:] = 1000.0
+    up = random.uniform(-span, span, size=(n, rank)).astype(np.float32)
+    return bf16(down), bf16(up)
 
 
 def interleave(rows: np.ndarray) -> np.ndarray:

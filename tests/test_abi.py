@@ -129,7 +129,6 @@ def test_gemm_arguments_are_rejected_before_any_launch():
     assert call(maxima=operand, f16=1) == invalid
     assert call(maxima=operand, swiglu=1) == invalid
     assert call(maxima=operand, first_column=64) == invalid
-    assert call(down=operand) == _lib.CUDA_ERROR_NOT_SUPPORTED
     # Nothing is ever chosen, and what the reference's search saved is not adopted.
     assert library.mmh3_int8_gemm_tilings(None, 0) == 0
     library.mmh3_int8_gemm_adopt.restype = None
