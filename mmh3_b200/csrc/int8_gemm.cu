@@ -6,9 +6,9 @@
 //                        + adapter_scale * sum_j adapter_down[r, j] * adapter_up[c, j] + bias[c])
 //
 // rounded once to BF16 or FP16, activations [m, k] and weights [n, k] INT8 with K contiguous, the
-// low-rank adapter (BF16) and the bias optional. It
-// replaces crates/mmh3-cuda/kernels/int8_gemm.cu:321-591 (mma.sync over a two-stage ring) and
-// keeps its arithmetic: the integer sums are exact, and the FP32 operations after them are the
+// low-rank adapter (BF16) and the bias optional. It replaces
+// crates/mmh3-cuda/kernels/int8_gemm.cu:321-591 (mma.sync over a two-stage ring) and keeps its
+// arithmetic: the integer sums are exact, and the FP32 operations after them are the
 // same in the same order, so without an adapter the outputs and the column maxima are the same
 // bits. With an adapter a tile is 128 rows: its INT32 accumulator and an FP32 accumulator for
 // down . up^T sit side by side in tensor memory, and after the K blocks the ring carries blocks of
@@ -23,10 +23,9 @@
 // 128 x 256 x 32 from shared memory; eight warps scale and round the accumulators, turn their rows
 // around in a staging tile of shared memory so that the stores cover whole 128-byte runs, and give
 // tensor memory back as soon as the last columns are in registers, while the ring fills for the
-// next tile. At this tile shape a stage of 64 KB feeds 1,024 cycles of MMA,
-// 64 bytes a cycle, which is what an SM can take from L2; a tile of 128 x 256 would leave room for
-// a second pair of accumulators and an epilogue hidden behind the next tile's MMAs, but needs
-// 96 bytes a cycle.
+// next tile. At this tile shape a stage of 64 KB feeds 1,024 cycles of MMA, 64 bytes a cycle,
+// which is what an SM can take from L2; a tile of 128 x 256 would leave room for a second pair of
+// accumulators and an epilogue hidden behind the next tile's MMAs, but needs 96 bytes a cycle.
 #include "common.cuh"
 #include "sm100.cuh"
 
