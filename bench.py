@@ -555,7 +555,7 @@ def run_sharded(args) -> None:
     import torch.distributed as dist
 
     from mmh3_b200 import attention, synthetic
-    from mmh3_b200.shard import Shard, UlyssesAttention
+    from mmh3_b200.shard import HostUlyssesPipeline, Shard, UlyssesAttention
 
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
@@ -581,10 +581,14 @@ def run_sharded(args) -> None:
     def step():
         layer.run(qkv, output)
 
+    # End to end the layer goes through a group of heads at a time (two heads of every rank at
+    # least), so that the copies of one group hide behind the exchange and attention of another.
+    groups = max(1, min(4, len(shard.own_heads) // 2))
+    pipeline = HostUlyssesPipeline(shard, tokens, heads, dense, groups,
+                                   pack=attention.shard_pack, unpack=attention.shard_unpack)
+
     def end_to_end():
-        qkv.copy_(generator_rows, non_blocking=True)
-        layer.run(qkv, output)
-        host_output.copy_(output, non_blocking=True)
+        pipeline.run(generator_rows, qkv, output, host_output)
 
     with ClockSampler(local) as sampler:
         for _ in range(args.warmup):
@@ -594,12 +598,19 @@ def run_sharded(args) -> None:
     for _ in range(max(1, args.warmup // 2)):
         end_to_end()
     e2e_ms = time_region(torch, end_to_end, args.steps, barrier=dist.barrier)
+    # The pipelined layer must leave what the layer over resident inputs leaves.
+    step()
+    resident = output.clone()
+    end_to_end()
+    torch.cuda.synchronize()
+    agrees = float(torch.equal(host_output.cuda(), resident))
     wires = None if args.skip_gemm else sharded_block(torch, dist, attention, args, shard, layer,
                                                       dense, qkv, output, tokens, heads)
     status = attention.take_status()
-    times = torch.tensor([ms, e2e_ms, float(status)], dtype=torch.float64, device="cuda")
+    times = torch.tensor([ms, e2e_ms, float(status), -agrees], dtype=torch.float64,
+                         device="cuda")
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, status = times.tolist()
+    ms, e2e_ms, status, disagrees = times.tolist()
     if rank == 0:
         flops = attention_flops(tokens, heads)
         peaks, source = measured_peaks()
@@ -616,7 +627,9 @@ def run_sharded(args) -> None:
                        "l2": "inputs exceed L2 (126 MB)"},
             "e2e": {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": generator_rows.numel() * 2 * world,
-                    "d2h_bytes_per_step": host_output.numel() * 2 * world},
+                    "d2h_bytes_per_step": host_output.numel() * 2 * world,
+                    "head_groups": len(pipeline.cuts),
+                    "equals_resident_run": disagrees == -1.0},
             # per rank and step: N packs, the attention kernel, N unpacks (NCCL's kernels aside)
             "gpu_launches": args.steps * (2 * world + 1),
             "roofline": {"bound": "tensor", "achieved": value, "peak": peaks["bf16_tflops"] * world,

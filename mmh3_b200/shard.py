@@ -102,11 +102,12 @@ class UlyssesAttention:
         make = dict(dtype=dtype, device=device)
         # Sent: for each peer, its heads of my tokens. Received: my heads of every rank's tokens,
         # which is already [all tokens, 3, own heads, 128] because tokens are outermost.
-        self.send_inputs = torch.empty(own_tokens * 3 * heads * HEAD_DIM if exchanges_qkv else 0,
-                                       **make)
+        exchanged = sum(len(peer) for peer in shard.heads)  # all heads, or a group of them
+        self.send_inputs = torch.empty(own_tokens * 3 * exchanged * HEAD_DIM if exchanges_qkv
+                                       else 0, **make)
         self.inputs = torch.empty(total_tokens * 3 * own_heads * HEAD_DIM, **make)
         self.attended = torch.empty(total_tokens * own_heads * HEAD_DIM, **make)
-        self.received = torch.empty(own_tokens * heads * HEAD_DIM, **make)
+        self.received = torch.empty(own_tokens * exchanged * HEAD_DIM, **make)
         self.input_send_splits = [own_tokens * 3 * len(peer) * HEAD_DIM for peer in shard.heads]
         self.input_recv_splits = [len(peer) * 3 * own_heads * HEAD_DIM for peer in shard.tokens]
         self.output_send_splits = [len(peer) * own_heads * HEAD_DIM for peer in shard.tokens]
@@ -127,12 +128,14 @@ class UlyssesAttention:
         offset = 0
         for peer, heads in enumerate(shard.heads):
             count = self.input_send_splits[peer]
-            self.pack(qkv_own, self.send_inputs[offset:offset + count], self.own_tokens, 3,
-                      self.heads, heads.start, len(heads))
+            if count:
+                self.pack(qkv_own, self.send_inputs[offset:offset + count], self.own_tokens, 3,
+                          self.heads, heads.start, len(heads))
             offset += count
         dist.all_to_all_single(self.inputs, self.send_inputs, self.input_recv_splits,
                                self.input_send_splits, group=self.group)
-        self.attention(self.inputs, self.attended, self.tokens, self.own_heads)
+        if self.own_heads:
+            self.attention(self.inputs, self.attended, self.tokens, self.own_heads)
         self.exchange_outputs(output_own)
 
     def exchange_outputs(self, output_own: torch.Tensor) -> None:
@@ -143,9 +146,79 @@ class UlyssesAttention:
         offset = 0
         for peer, heads in enumerate(self.shard.heads):
             count = self.output_recv_splits[peer]
-            self.unpack(self.received[offset:offset + count], output_own, self.own_tokens,
-                        self.heads, heads.start, len(heads))
+            if count:
+                self.unpack(self.received[offset:offset + count], output_own, self.own_tokens,
+                            self.heads, heads.start, len(heads))
             offset += count
+
+
+def head_groups(shard: Shard, groups: int) -> list[Shard]:
+    """Cuts every rank's heads into `groups` runs: shard g holds the g-th run of each rank. The
+    layer can then go through a group at a time, every rank busy in every group."""
+    cuts = []
+    for group in range(groups):
+        heads = tuple(range(owned.start + len(owned) * group // groups,
+                            owned.start + len(owned) * (group + 1) // groups)
+                      for owned in shard.heads)
+        if any(len(run) for run in heads):
+            cuts.append(Shard(shard.rank, shard.tokens, heads))
+    return cuts
+
+
+class HostUlyssesPipeline:
+    """`UlyssesAttention` from this rank's rows in pinned host memory to its rows of the output in
+    pinned host memory, a group of heads at a time (`head_groups`): while one group is exchanged
+    and attended, the rows of the next cross the bus and the output of the last goes back, on three
+    streams, as `attention.HostPipeline` does on one GPU. A group's heads are one run per rank, so
+    its rows are that many strided 2D copies each way."""
+
+    def __init__(self, shard: Shard, total_tokens: int, heads: int, attention: AttentionFn,
+                 groups: int, pack: PackFn | None = None, unpack: PackFn | None = None,
+                 group=None):
+        from .attention import HostPipeline
+
+        self.shard, self.heads = shard, heads
+        self.own_tokens = len(shard.own_tokens)
+        self.cuts = [shard] if shard.is_whole else head_groups(shard, groups)
+        self.layers = [UlyssesAttention(cut, total_tokens, heads, attention, "cuda",
+                                        torch.bfloat16, pack, unpack, group)
+                       for cut in self.cuts]
+        # Only its streams and its 2D copy are used.
+        self.copies = HostPipeline(total_tokens, heads, groups=1)
+        self.arrived = [torch.cuda.Event() for _ in self.cuts]
+        self.attended = [torch.cuda.Event() for _ in self.cuts]
+        self.finished = torch.cuda.Event()
+
+    def _rows(self, device: torch.Tensor, host: torch.Tensor, cut: Shard, tensors: int,
+              to_device: bool, stream) -> None:
+        pitch = self.heads * HEAD_DIM * 2
+        for run in (cut.heads if not cut.is_whole else (range(self.heads),)):
+            if len(run) == 0:
+                continue
+            offset = run.start * HEAD_DIM * 2
+            source, destination = (host, device) if to_device else (device, host)
+            self.copies._copy(destination.data_ptr() + offset, source.data_ptr() + offset, pitch,
+                              len(run) * HEAD_DIM * 2, self.own_tokens * tensors, to_device,
+                              stream)
+
+    def run(self, host_qkv: torch.Tensor, qkv: torch.Tensor, output: torch.Tensor,
+            host_output: torch.Tensor) -> None:
+        """Enqueues everything and returns; the current stream ends up behind the last copy."""
+        copy_in, copy_out = self.copies.copy_in, self.copies.copy_out
+        current = torch.cuda.current_stream()
+        copy_in.wait_stream(current)
+        copy_out.wait_stream(current)
+        for index, cut in enumerate(self.cuts):
+            self._rows(qkv, host_qkv, cut, 3, True, copy_in)
+            self.arrived[index].record(copy_in)
+        for index, (cut, layer) in enumerate(zip(self.cuts, self.layers)):
+            current.wait_event(self.arrived[index])
+            layer.run(qkv, output)
+            self.attended[index].record(current)
+            copy_out.wait_event(self.attended[index])
+            self._rows(output, host_output, cut, 1, False, copy_out)
+        self.finished.record(copy_out)
+        current.wait_event(self.finished)
 
 
 # project(rows INT8 [count, hidden], scales FP32 [count], qkv [count, 3, own heads, 128]): the

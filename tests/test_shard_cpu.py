@@ -14,7 +14,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from mmh3_b200.shard import (ProjectedUlyssesAttention, Shard, UlyssesAttention,
+from mmh3_b200.shard import (ProjectedUlyssesAttention, Shard, UlyssesAttention, head_groups,
                               own_projection_rows)
 
 HEAD_DIM = 128
@@ -47,7 +47,14 @@ def worker(rank, ranks, port, tokens, heads, results):
         layer.run(qkv[own.start:own.stop].contiguous(), output)
         whole = torch.zeros((tokens, heads, HEAD_DIM))
         torch_attention(qkv.contiguous(), whole, tokens, heads)
-        results[rank] = float((output - whole[own.start:own.stop]).abs().max())
+        error = float((output - whole[own.start:own.stop]).abs().max())
+        # The same layer a group of heads at a time: every rank's heads cut in two runs (one of
+        # them may be empty when a rank owns a single head).
+        grouped = torch.zeros_like(output)
+        for cut in head_groups(shard, 2):
+            UlyssesAttention(cut, tokens, heads, torch_attention, "cpu", torch.float32).run(
+                qkv[own.start:own.stop].contiguous(), grouped)
+        results[rank] = max(error, float((grouped - whole[own.start:own.stop]).abs().max()))
     finally:
         dist.destroy_process_group()
 
@@ -126,6 +133,15 @@ def test_own_projection_rows():
     rows = own_projection_rows(4, range(1, 3))
     assert rows.tolist()[:2] == [128, 129] and len(rows) == 3 * 2 * 128
     assert rows[256].item() == 4 * 128 + 128 and rows[512].item() == 8 * 128 + 128
+
+
+def test_head_groups():
+    shard = Shard.even(1, 2, 10, 7, 1)  # heads 0-2 and 3-6
+    cuts = head_groups(shard, 2)
+    assert [cut.heads for cut in cuts] == [(range(0, 1), range(3, 5)), (range(1, 3), range(5, 7))]
+    assert all(cut.tokens == shard.tokens and cut.rank == 1 for cut in cuts)
+    # More groups than a rank has heads: its empty runs stay, wholly empty groups go.
+    assert len(head_groups(Shard.even(0, 2, 10, 2, 1), 4)) == 1
 
 
 def test_even_cuts():
