@@ -335,3 +335,26 @@ def test_host_pipeline_equals_one_call(groups):
         torch.cuda.synchronize()
         assert attention.take_status() == 0
         assert torch.equal(host_output, expected.cpu())
+
+
+def test_sharded_host_pipeline_on_one_rank():
+    """World size 1: the sharded pipeline is one copy in, the dense layer, one copy out. (With
+    more ranks `bench.py --gpus N` compares it with the resident run on every rank.)"""
+    from mmh3_b200.shard import HostUlyssesPipeline, Shard
+
+    tokens, heads = 500, 3
+    host_qkv = synthetic.dense_qkv(tokens, heads, seed=22, pinned=True)
+    expected = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    attention.dense_bf16(host_qkv.cuda(), expected, tokens, heads, SCALE)
+
+    def dense(qkv, output, count, span):
+        attention.dense_bf16(qkv, output, count, span, SCALE)
+
+    pipeline = HostUlyssesPipeline(Shard.even(0, 1, tokens, heads), tokens, heads, dense, 2)
+    qkv = torch.zeros((tokens, 3, heads, 128), dtype=torch.bfloat16, device="cuda")
+    output = torch.zeros_like(expected)
+    host_output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16).pin_memory()
+    pipeline.run(host_qkv, qkv, output, host_output)
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    assert torch.equal(host_output, expected.cpu())
