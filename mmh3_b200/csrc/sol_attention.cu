@@ -115,7 +115,7 @@ template <int QUERIES>
 __global__ void __launch_bounds__(THREADS, 3)
     route_kernel(Mmh3SparseWorkspace workspace, int tokens, int blocks, float tau, float log2_scale,
                  int sink_key_start, int sink_key_end, int sink_query_start, int sink_query_end) {
-    extern __shared__ __align__(16) float weights[]; // [QUERIES][blocks], scores at first
+    extern __shared__ __align__(16) float weights[]; // [blocks][QUERIES], scores at first
     uint8_t *routed = reinterpret_cast<uint8_t *>(weights + static_cast<size_t>(QUERIES) * blocks);
     __shared__ float4 centroids[QUERIES][32];
     __shared__ float thresholds[QUERIES];
@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(THREADS, 3)
         for (int query = 0; query < queries; query++) {
             const int query_block = first_query + query;
             const float score = __fmul_rn(score_tree(centroids[query], key), log2_scale);
-            weights[static_cast<size_t>(query) * blocks + key_block] = score;
+            weights[static_cast<size_t>(key_block) * QUERIES + query] = score;
             routed[static_cast<size_t>(query) * blocks + key_block] =
                 score > thresholds[query] || abs(query_block - key_block) <= 1 ||
                 (key_block >= sink_key_start && key_block < sink_key_end) ||
@@ -164,20 +164,22 @@ __global__ void __launch_bounds__(THREADS, 3)
     // The tail of each query block: the key blocks it does not route, as softmax weights against
     // their maximum, each counted once per token it stands for.
     for (int query = 0; query < queries; query++) {
-        float *query_weights = weights + static_cast<size_t>(query) * blocks;
+        float *query_weights = weights + query; // QUERIES apart
         const uint8_t *query_routed = routed + static_cast<size_t>(query) * blocks;
         float maximum = -FLT_MAX;
         for (int key_block = threadIdx.x; key_block < blocks; key_block += THREADS) {
             if (!query_routed[key_block]) {
-                maximum = fmaxf(maximum, query_weights[key_block]);
+                maximum = fmaxf(maximum, query_weights[static_cast<size_t>(key_block) * QUERIES]);
             }
         }
         maximum = cta_reduce(maximum, scratch, true);
         float sum = 0.0f;
         for (int key_block = threadIdx.x; key_block < blocks; key_block += THREADS) {
             const float weight =
-                query_routed[key_block] ? 0.0f : exp2f(query_weights[key_block] - maximum);
-            query_weights[key_block] = weight;
+                query_routed[key_block]
+                    ? 0.0f
+                    : exp2f(query_weights[static_cast<size_t>(key_block) * QUERIES] - maximum);
+            query_weights[static_cast<size_t>(key_block) * QUERIES] = weight;
             sum = fmaf(weight, static_cast<float>(block_rows(key_block, tokens)), sum);
         }
         sum = cta_reduce(sum, scratch, false);
@@ -192,6 +194,9 @@ __global__ void __launch_bounds__(THREADS, 3)
     // blocks, which every query block of the CTA weighs its own way.
     const float *values =
         workspace.value_sums + static_cast<size_t>(head) * blocks * HEAD_DIM + threadIdx.x;
+    // A key block's weights for the CTA's query blocks lie side by side, so one or two 16-byte
+    // loads bring all of them, and two query blocks share a packed multiply-add. Each sum still
+    // runs over the key blocks in order.
     float tails[QUERIES] = {};
     constexpr int BATCH = 16;
     for (int first = 0; first < blocks; first += BATCH) {
@@ -204,13 +209,29 @@ __global__ void __launch_bounds__(THREADS, 3)
         #pragma unroll
         for (int index = 0; index < BATCH; index++) {
             if (first + index < blocks) {
-                #pragma unroll
-                for (int query = 0; query < QUERIES; query++) {
-                    // Routed blocks and query blocks past the last one have weight zero.
-                    const float weight =
-                        query < queries ? weights[static_cast<size_t>(query) * blocks + first + index]
-                                        : 0.0f;
-                    tails[query] = fmaf(weight, loaded[index], tails[query]);
+                // Routed blocks have weight zero; query blocks past the last one are not stored.
+                const float *block_weights = weights + static_cast<size_t>(first + index) * QUERIES;
+                if constexpr (QUERIES % 4 == 0) {
+                    const float2 value = make_float2(loaded[index], loaded[index]);
+                    #pragma unroll
+                    for (int four = 0; four < QUERIES / 4; four++) {
+                        const float4 weight = reinterpret_cast<const float4 *>(block_weights)[four];
+                        const float2 low = __ffma2_rn(make_float2(weight.x, weight.y), value,
+                                                      make_float2(tails[four * 4],
+                                                                  tails[four * 4 + 1]));
+                        const float2 high = __ffma2_rn(make_float2(weight.z, weight.w), value,
+                                                       make_float2(tails[four * 4 + 2],
+                                                                   tails[four * 4 + 3]));
+                        tails[four * 4] = low.x;
+                        tails[four * 4 + 1] = low.y;
+                        tails[four * 4 + 2] = high.x;
+                        tails[four * 4 + 3] = high.y;
+                    }
+                } else {
+                    #pragma unroll
+                    for (int query = 0; query < QUERIES; query++) {
+                        tails[query] = fmaf(block_weights[query], loaded[index], tails[query]);
+                    }
                 }
             }
         }
