@@ -526,6 +526,8 @@ def run_vsa(torch, attention, synthetic, heads, scale, steps, frames=31) -> dict
 
     whole()
     ms = time_region(torch, whole, steps)
+    kernels = kernel_times(torch, whole)
+    selected = workspace.selected_fraction()
     lengths = torch.tensor(plan.tile_lengths, dtype=torch.float64, device="cuda")
     counts = workspace.route_counts.view(heads, plan.tiles).to(torch.int64)
     # Keys each query tile attends: the sum of the lengths of its routed tiles.
@@ -538,13 +540,29 @@ def run_vsa(torch, attention, synthetic, heads, scale, steps, frames=31) -> dict
         table = lengths[entries]
         routed_keys[head] = (table * mask).sum(dim=1)
     sparse_flops = float((routed_keys * lengths[None, :]).sum().item()) * 4.0 * HEAD_DIM
+    # The same layer in INT8/FP8 over inputs the fused pass prepared (identity norm, no rotation):
+    # selection and token attention, as the DiT calls it with inputs_ready = 2.
+    del workspace
+    quantized = attention.VsaWorkspace(plan, tokens, heads, quantized=True)
+    ones = torch.ones(HEAD_DIM, dtype=torch.bfloat16, device="cuda")
+    maxima = qkv[:, 2].float().abs().amax(dim=(0, 2)).contiguous()
+    attention.prepare_inputs(qkv, attention.HeadNorm(ones, ones, None, 0, 1e-6), tokens, heads,
+                             vsa=quantized, value_head_maxima=maxima)
+
+    def whole_quantized():
+        attention.vsa(qkv, None, output, vsa_layout, scale, kept, quantized,
+                      attention.AttentionInputs.PREPARED_WITH_VALUES)
+
+    whole_quantized()
+    quantized_ms = time_region(torch, whole_quantized, steps)
     return {
         "workload": (f"VSA L={tokens} ({plan.prefix_tiles} prefix + {plan.video_tiles} video "
                      f"tiles), H={heads}, kept {kept}"),
         "ms": ms, "sparse_flops": sparse_flops, "sparse_tflops": sparse_flops / ms / 1e9,
+        "int8_fp8_ms": quantized_ms,
         "dense_equivalent_tflops": attention_flops(tokens, heads) / ms / 1e9,
-        "kernel_ms": kernel_times(torch, whole),
-        "selected_fraction": workspace.selected_fraction(),
+        "kernel_ms": kernels,
+        "selected_fraction": selected,
         "expected_selected_fraction": plan.expected_selected_fraction(kept),
         "kernel_status": attention.take_status(),
     }
