@@ -58,6 +58,10 @@ template <bool QUANTIZED> constexpr float RESCALE_LAG = QUANTIZED ? 1.0f : 8.0f;
 constexpr float LOG2_224 = 7.807354922057604f;
 // Of every four pairs of probabilities, how many take the polynomial exp2 instead of the MUFU.
 constexpr int POLYNOMIAL_PAIRS_OF_4 = 1;
+// In the INT8/FP8 form every exponential takes the MUFU, and an integer score s, |s| < 2^22,
+// becomes the float 1.5 * 2^23 + s by adding these bits to it, as in quantized_attention.cu.
+constexpr int32_t MAGIC_BITS = 0x4B400000;
+constexpr float MAGIC_VALUE = 12582912.0f;
 
 template <bool QUANTIZED> struct Shape {
     // Bytes of a 128-row operand tile and of the half of it one VSA tile fills.
@@ -519,9 +523,12 @@ __global__ void __launch_bounds__(THREADS, 2)
                                        float factor, uint32_t own_p, uint32_t other_p,
                                        bool shared) {
             constexpr bool MASKED = decltype(masked)::value;
-            // p = 2^(factor * score - maximum), times 224 for E4M3; pairs of elements, one
-            // pair in four on the polynomial.
-            const float offset = QUANTIZED ? LOG2_224 - maximum : -maximum;
+            // p = 2^(factor * score - maximum), times 224 for E4M3; pairs of elements, in BF16
+            // one pair in four on the polynomial.
+            // (MAGIC + s) * factor + (offset - MAGIC * factor) = s * factor + offset, the product
+            // exact inside the FMA.
+            const float offset =
+                QUANTIZED ? fmaf(-MAGIC_VALUE, factor, LOG2_224 - maximum) : -maximum;
             const float2 factor2 = make_float2(factor, factor);
             const float2 offset2 = make_float2(offset, offset);
             constexpr int WORDS = QUANTIZED ? TILE / 4 : TILE / 2;
@@ -531,8 +538,8 @@ __global__ void __launch_bounds__(THREADS, 2)
                 const uint32_t words[2] = {raw[(pair * 2) / 32][(pair * 2) % 32],
                                            raw[(pair * 2 + 1) / 32][(pair * 2 + 1) % 32]};
                 const float2 score =
-                    QUANTIZED ? make_float2(static_cast<float>(static_cast<int32_t>(words[0])),
-                                            static_cast<float>(static_cast<int32_t>(words[1])))
+                    QUANTIZED ? make_float2(__int_as_float(static_cast<int32_t>(words[0]) + MAGIC_BITS),
+                                            __int_as_float(static_cast<int32_t>(words[1]) + MAGIC_BITS))
                               : make_float2(__uint_as_float(words[0]),
                                             __uint_as_float(words[1]));
                 float2 x = __ffma2_rn(score, factor2, offset2);
@@ -541,7 +548,7 @@ __global__ void __launch_bounds__(THREADS, 2)
                     x.y = pair * 2 + 1 < valid ? x.y : -INFINITY;
                 }
                 float2 probability;
-                if (pair % 4 < POLYNOMIAL_PAIRS_OF_4) {
+                if (!QUANTIZED && pair % 4 < POLYNOMIAL_PAIRS_OF_4) {
                     probability = exp2_polynomial(x);
                 } else {
                     probability = make_float2(exp2_approx(x.x), exp2_approx(x.y));
