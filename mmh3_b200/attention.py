@@ -176,8 +176,9 @@ class HostPipeline:
         self.attended = [torch.cuda.Event() for _ in self.groups]
         self.finished = torch.cuda.Event()
 
-    def _copy(self, destination: int, source: int, pitch: int, width: int, rows: int,
-              to_device: bool, stream: torch.cuda.Stream) -> None:
+    def copy_rows(self, destination: int, source: int, pitch: int, width: int, rows: int,
+                  to_device: bool, stream: torch.cuda.Stream) -> None:
+        """`rows` runs of `width` bytes, `pitch` bytes apart on both sides, on `stream`."""
         kind = (self.runtime.cudaMemcpyKind.cudaMemcpyHostToDevice if to_device
                 else self.runtime.cudaMemcpyKind.cudaMemcpyDeviceToHost)
         (code,) = self.runtime.cudaMemcpy2DAsync(destination, pitch, source, pitch, width, rows,
@@ -201,8 +202,8 @@ class HostPipeline:
         pitch = inner * 2
         for index, (first, span) in enumerate(self.groups):
             offset = first * HEAD_DIM * 2
-            self._copy(qkv.data_ptr() + offset, host_qkv.data_ptr() + offset, pitch,
-                       span * HEAD_DIM * 2, tokens * 3, True, self.copy_in)
+            self.copy_rows(qkv.data_ptr() + offset, host_qkv.data_ptr() + offset, pitch,
+                           span * HEAD_DIM * 2, tokens * 3, True, self.copy_in)
             self.arrived[index].record(self.copy_in)
         for index, (first, span) in enumerate(self.groups):
             current.wait_event(self.arrived[index])
@@ -216,8 +217,8 @@ class HostPipeline:
             )
             self.attended[index].record(current)
             self.copy_out.wait_event(self.attended[index])
-            self._copy(host_output.data_ptr() + offset * 2, output.data_ptr() + offset * 2, pitch,
-                       span * HEAD_DIM * 2, tokens, False, self.copy_out)
+            self.copy_rows(host_output.data_ptr() + offset * 2, output.data_ptr() + offset * 2,
+                           pitch, span * HEAD_DIM * 2, tokens, False, self.copy_out)
         self.finished.record(self.copy_out)
         current.wait_event(self.finished)
 

@@ -197,9 +197,9 @@ class HostUlyssesPipeline:
                 continue
             offset = run.start * HEAD_DIM * 2
             source, destination = (host, device) if to_device else (device, host)
-            self.copies._copy(destination.data_ptr() + offset, source.data_ptr() + offset, pitch,
-                              len(run) * HEAD_DIM * 2, self.own_tokens * tensors, to_device,
-                              stream)
+            self.copies.copy_rows(destination.data_ptr() + offset, source.data_ptr() + offset,
+                                  pitch, len(run) * HEAD_DIM * 2, self.own_tokens * tensors,
+                                  to_device, stream)
 
     def run(self, host_qkv: torch.Tensor, qkv: torch.Tensor, output: torch.Tensor,
             host_output: torch.Tensor) -> None:
