@@ -11,8 +11,11 @@ batch of seeded synthetic activations.
   attention layer, L = 124,992 + 512, H = 32, sequence-sharded inputs, NCCL all-to-all both ways,
   dense attention on 32 / N heads per rank. The total work is fixed, so scaling is strong.
 - `--impl reference`: the reference's CPU attention path (the f64 oracle restating
-  crates/mmh3-cpu/src/dit.rs:79-118; Rust is not installed here) on all host threads, each step a
-  bounded sample of query rows of the same workload.
+  crates/mmh3-cpu/src/dit.rs:79-118; Rust is not installed here) on every host core this process
+  may run on, each step a sample of query rows of the same workload sized by time so that the
+  whole run ends within a minute or two. Its `ms_per_step` is the time of one sample; the layer
+  time extrapolated from it is in `cpu_baseline`. At N = 1 the line's `extra` also carries the
+  reference's own CUDA kernels (compiled for sm_100a, oracle/_ref) timed on the same inputs.
 
 Rank 0 prints one JSON line.
 """
@@ -165,10 +168,18 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(inside), "source": self.source}
 
 
-def cpu_attention_sampler(tokens: int, heads: int, seed: int, rows: int, qkv=None,
-                          threads: int = 0):
-    """A function that times the CPU oracle on `rows` query rows of every head against all keys of
-    the workload and returns (seconds, flops, threads used)."""
+def host_cores() -> int:
+    """The cores this process may run on. torch.distributed.run exports OMP_NUM_THREADS=1 to its
+    ranks, so OpenMP's own default is not the core count there; the affinity mask is."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_attention_sampler(tokens: int, heads: int, seed: int, qkv=None, threads: int = 0):
+    """A function sample(rows, threads=None) that times the CPU oracle on `rows` query rows of
+    every head against all keys of the workload and returns (seconds, flops, threads used)."""
     import numpy as np
     import torch
 
@@ -176,13 +187,14 @@ def cpu_attention_sampler(tokens: int, heads: int, seed: int, rows: int, qkv=Non
     from mmh3_b200 import synthetic
 
     oracle = oracle_lib.load()
-    used = threads or oracle.oracle_max_threads()
+    cores = threads or host_cores()
     if qkv is None:
         qkv = synthetic.dense_qkv(tokens, heads, seed)
     bits = qkv.view(torch.int16).numpy().view(np.uint16)
     first = (tokens // 2 // 64) * 64
 
-    def sample():
+    def sample(rows: int, threads: int | None = None):
+        used = threads or cores
         start = time.perf_counter()
         oracle_lib.attention_bf16(oracle, bits, tokens, heads, synthetic.softmax_scale(), first,
                                   first + rows, 0, heads, used)
@@ -192,42 +204,167 @@ def cpu_attention_sampler(tokens: int, heads: int, seed: int, rows: int, qkv=Non
     return sample
 
 
+def workload_config(gpus: int, tokens: int, heads: int) -> dict:
+    """What both arms say about the workload, key for key."""
+    config = {"workload": workload_name(gpus), "tokens": tokens, "heads": heads,
+              "head_dim": HEAD_DIM, "flops_per_step": attention_flops(tokens, heads),
+              "l2": f"inputs ({tokens * 3 * heads * HEAD_DIM * 2 / 1e9:.2f} GB) exceed L2 (126 MB)"}
+    if gpus > 1:
+        config["parallelism"] = f"ulysses{gpus}"
+    return config
+
+
 def run_reference(args) -> None:
-    """The reference arm: the CPU path on the box's host cores, rank 0 only."""
+    """The reference arm: the CPU path on the box's host cores, rank 0 only. A step is a sample of
+    query rows; the row count is chosen once, from a short calibration, so that warm-up and steps
+    together take about a minute whatever the core count."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     tokens = DENSE_TOKENS if args.gpus == 1 else VIDEO_TOKENS
-    rows = args.cpu_rows
+    sample = cpu_attention_sampler(tokens, HEADS, 1)
+    seconds, flops, used = sample(2)
+    per_row = seconds / 2
+    budget = min(2.5, args.reference_seconds / max(1, args.warmup + args.steps))
+    rows = max(1, min(args.cpu_rows, int(budget / per_row)))
     times = []
-    flops = used = 0
-    sample = cpu_attention_sampler(tokens, HEADS, 1, rows)
     for step in range(args.warmup + args.steps):
-        seconds, flops, used = sample()
+        seconds, flops, used = sample(rows)
         if step >= args.warmup:
             times.append(seconds)
     mean = sum(times) / len(times)
     value = flops / mean / 1e12
+    layer_flops = attention_flops(tokens, HEADS)
     described = (f"{rows} query rows x {HEADS} heads against all {tokens} keys per step "
-                 f"({flops / 1e9:.1f} GFLOP of the layer's "
-                 f"{attention_flops(tokens, HEADS) / 1e12:.1f} TFLOP)")
+                 f"({flops / 1e9:.1f} GFLOP of the layer's {layer_flops / 1e12:.1f} TFLOP, "
+                 f"{mean:.2f} s; a whole layer at this rate would take "
+                 f"{mean * layer_flops / flops:.0f} s)")
     line = {
         "impl": "reference", "metric": "attention_tflops", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": mean * 1e3 * attention_flops(tokens, HEADS) / flops,
+        "ms_per_step": mean * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64",
         "data": "synthetic",
-        "config": {"workload": workload_name(args.gpus), "tokens": tokens, "heads": HEADS,
-                   "head_dim": HEAD_DIM, "ms_per_step": "extrapolated from the sample to a layer"},
+        "config": workload_config(args.gpus, tokens, HEADS),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": used, "kind": "port",
                          "sample": described},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "step_is": "a sample of query rows of the layer, not a whole layer",
     }
+    if args.gpus == 1 and not args.no_reference_kernels:
+        line["extra"] = {"reference_cuda_kernels": reference_kernel_times(tokens, HEADS)}
     print(json.dumps(line))
 
 
-def workload_name(gpus: int) -> str:
+def reference_kernel_times(tokens: int, heads: int, qkv=None, output=None) -> dict:
+    """The reference's own CUDA kernels for the path (its mma.sync / cp.async code compiled
+    unchanged for sm_100a into oracle/_ref) on the benchmark's inputs on this GPU: dense BF16, and
+    INT8/FP8 over a workspace it prepared itself. They run on the legacy default stream, outside
+    every timed region of this library's kernels; none of this library's kernels run here."""
+    try:
+        import torch
+
+        import oracle_lib
+        from mmh3_b200 import _lib, synthetic
+
+        reference = oracle_lib.load_reference()
+        if reference is None or not torch.cuda.is_available():
+            return {"unavailable": "oracle/_ref/libmmh3_ref.so is not built or no GPU is visible"}
+        torch.cuda.set_device(0)
+        inner = heads * HEAD_DIM
+        scale = synthetic.softmax_scale()
+        if qkv is None:
+            qkv = synthetic.dense_qkv(tokens, heads, seed=1).cuda()
+        if output is None:
+            output = torch.zeros((tokens, heads, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
+        base = qkv.data_ptr()
+        flops = attention_flops(tokens, heads)
+
+        def dense():
+            code = reference.mmh3_attention_bf16(base, base + 2 * inner, base + 4 * inner,
+                                                 output.data_ptr(), tokens, heads, 3 * inner,
+                                                 3 * inner, 3 * inner, inner, scale, None)
+            if code != 0:
+                raise RuntimeError(f"the reference's mmh3_attention_bf16 returned {code}")
+
+        torch.cuda.synchronize()
+        dense()
+        ms = time_region(torch, dense, 2)
+        result = {"dense_bf16": {"ms": ms, "tflops": flops / ms / 1e9},
+                  "library": "oracle/_ref/libmmh3_ref.so (the reference's kernels, sm_100a)",
+                  "stream": "legacy default"}
+        blocks = -(-tokens // 64)
+        byte = dict(dtype=torch.uint8, device="cuda")
+        real = dict(dtype=torch.float32, device="cuda")
+        buffers = [torch.empty(tokens * inner, **byte), torch.empty(tokens * inner, **byte),
+                   torch.empty(blocks * 64 * inner, **byte), torch.empty(heads * blocks, **real),
+                   torch.empty(heads * blocks, **real), torch.empty(heads, **real),
+                   torch.empty(heads * blocks, **real)]
+        workspace = _lib.QuantizedWorkspaceStruct(*(buffer.data_ptr() for buffer in buffers))
+        layout = _lib.AttentionLayout()
+        for index in range(4):
+            layout.token_stride[index] = inner if index == 3 else 3 * inner
+            layout.head_stride[index] = HEAD_DIM
+
+        def quantized(ready):
+            code = reference.mmh3_attention_quantized(
+                base, base + 2 * inner, base + 4 * inner, output.data_ptr(), tokens, heads,
+                ctypes.byref(layout), scale, None, ctypes.byref(workspace), ready, None)
+            if code != 0:
+                raise RuntimeError(f"the reference's mmh3_attention_quantized returned {code}")
+
+        quantized(0)
+        ms = time_region(torch, lambda: quantized(2), 2)
+        result["int8_fp8_prepared"] = {"ms": ms, "tflops": flops / ms / 1e9}
+        return result
+    except Exception as error:  # context only: never a reason to lose the line
+        return {"unavailable": str(error)[:160]}
+
+
+def eight_bit_peaks(torch) -> dict:
+    """INT8 and FP8 GEMM rates of this GPU from the vendor library, measured the way the BF16 peak
+    in MEASURED_PEAKS.json is: 8192^3, best of 10 after a warm-up, CUDA events. They anchor the
+    roofline fractions of the INT8/FP8 attention and of the INT8 projection."""
+    size = 8192
+    operations = 2.0 * size ** 3
+    result = {"how": f"{size}^3, best of 10, CUDA events; torch._int_mm and torch._scaled_mm"}
+
+    def best(call):
+        call()
+        torch.cuda.synchronize()
+        fastest = float("inf")
+        for _ in range(10):
+            start = torch.cuda.Event(enable_timing=True)
+            end = torch.cuda.Event(enable_timing=True)
+            start.record()
+            call()
+            end.record()
+            torch.cuda.synchronize()
+            fastest = min(fastest, start.elapsed_time(end))
+        return operations / fastest / 1e9
+
+    try:
+        a = torch.randint(-127, 128, (size, size), dtype=torch.int8, device="cuda")
+        b = torch.randint(-127, 128, (size, size), dtype=torch.int8, device="cuda").t()
+        result["int8_tops"] = best(lambda: torch._int_mm(a, b))
+    except Exception as error:
+        result["int8_error"] = str(error)[:120]
+    try:
+        a = torch.randn((size, size), device="cuda").to(torch.float8_e4m3fn)
+        b = torch.randn((size, size), device="cuda").to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device="cuda")
+        result["fp8_tflops"] = best(lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one,
+                                                             out_dtype=torch.bfloat16))
+    except Exception as error:
+        result["fp8_error"] = str(error)[:120]
+    return result
+
+
+def workload_name(gpus: int, video: bool = False) -> str:
+    if gpus == 1 and video:
+        return ("dense BF16 video attention layer, L=124992+512, H=32, D=128, one GPU (the "
+                "sharded workload unsharded)")
     if gpus == 1:
         return "dense BF16 attention, L=65536+512, H=32, D=128 (BASELINE configs[1])"
     return (f"Ulysses head-sharded dense BF16 video attention layer, L=124992+512, H=32, D=128, "
@@ -302,26 +439,35 @@ def run_single(args) -> None:
     peaks, source = measured_peaks()
     achieved = flops / dense_ms / 1e9
     peak = peaks["bf16_tflops"]
+    config = workload_config(1, tokens, heads)
+    if (tokens, heads) != (DENSE_TOKENS, HEADS):
+        config["workload"] = (f"dense BF16 attention, reduced case L={tokens}, H={heads} (not the "
+                              "benchmark configuration)")
     cpu = None
     if not args.no_cpu:
-        seconds, sample_flops, used = cpu_attention_sampler(tokens, heads, 1, args.cpu_rows,
-                                                            qkv=host_qkv)()
+        sample = cpu_attention_sampler(tokens, heads, 1, qkv=host_qkv)
+        seconds, sample_flops, used = sample(args.cpu_rows)
+        # The reference's attention() is single-threaded: the same loop on one core, on a sample
+        # a sixteenth the size.
+        single_rows = max(1, args.cpu_rows // 16)
+        single_seconds, single_flops, _ = sample(single_rows, threads=1)
         cpu = {"value": sample_flops / seconds / 1e12, "unit": "TFLOP/s", "cores": used,
                "kind": "port",
                "sample": (f"{args.cpu_rows} query rows x {heads} heads against all {tokens} keys "
-                          f"({sample_flops / 1e9:.1f} GFLOP, {seconds:.1f} s)")}
+                          f"({sample_flops / 1e9:.1f} GFLOP, {seconds:.1f} s)"),
+               "one_core": {"value": single_flops / single_seconds / 1e12, "unit": "TFLOP/s",
+                            "cores": 1,
+                            "sample": (f"{single_rows} query rows x {heads} heads against all "
+                                       f"{tokens} keys ({single_flops / 1e9:.1f} GFLOP, "
+                                       f"{single_seconds:.1f} s): the reference's loop as it "
+                                       "runs it, on one thread")}}
     line = {
         "metric": "attention_tflops", "value": achieved, "unit": "TFLOP/s", "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dense_ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": workload_name(1) if (tokens, heads) == (DENSE_TOKENS, HEADS)
-                   else f"dense BF16 attention, reduced case L={tokens}, H={heads} (not the "
-                        "benchmark configuration)",
-                   "tokens": tokens, "heads": heads, "head_dim": HEAD_DIM,
-                   "flops_per_step": flops,
-                   "l2": f"inputs ({host_qkv.numel() * 2 / 1e9:.2f} GB) exceed L2 (126 MB)",
-                   "kernel_status": status},
+        "config": config,
+        "kernel_status": status,
         "e2e": {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": host_qkv.numel() * 2,
                 "d2h_bytes_per_step": host_output.numel() * 2,
@@ -348,6 +494,8 @@ def run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, a
     peaks, source = measured_peaks()
     flops = attention_flops(tokens, heads)
     steps = max(2, args.steps // 2)
+    eight_bit = eight_bit_peaks(torch)
+    extras["peaks"] = eight_bit
     if args.skip_quantized:
         workspace = prepared = None
     try:
@@ -380,6 +528,10 @@ def run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, a
         quantized()
         ms = time_region(torch, quantized, steps)
         extras["int8_fp8_attention"] = {"ms": ms, "tflops": flops / ms / 1e9}
+        # Half the work is INT8, half FP8: the time either peak alone would allow, added up.
+        if "int8_tops" in eight_bit and "fp8_tflops" in eight_bit:
+            floor_ms = (flops / 2 / eight_bit["int8_tops"] + flops / 2 / eight_bit["fp8_tflops"]) / 1e9
+            extras["int8_fp8_attention"]["frac_of_measured_8bit_peaks"] = floor_ms / ms
         extras["kernel_status"] = attention.take_status()
     except StopIteration:
         pass
@@ -390,7 +542,7 @@ def run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, a
     if not args.skip_vsa:
         try:
             extras["vsa"] = run_vsa(torch, attention, synthetic, heads, scale, steps,
-                                    args.vsa_frames)
+                                    args.vsa_frames, args.no_reference_kernels)
         except attention.CudaError as error:
             extras["vsa_error"] = str(error)
     if not args.skip_sol:
@@ -401,9 +553,39 @@ def run_extras(torch, attention, synthetic, qkv, output, tokens, heads, scale, a
     if not args.skip_gemm:
         try:
             extras["qkv_gemm"] = run_gemm(torch, attention, qkv, tokens, heads, steps)
+            if "int8_tops" in eight_bit:
+                extras["qkv_gemm"]["frac_of_measured_int8_peak"] = (
+                    extras["qkv_gemm"]["tops"] / eight_bit["int8_tops"])
         except attention.CudaError as error:
             extras["qkv_gemm_error"] = str(error)
+    if not args.no_reference_kernels:
+        extras["reference_kernels"] = reference_kernel_times(tokens, heads, qkv, output)
+    if not args.skip_video_layer:
+        try:
+            extras["video_layer_one_gpu"] = run_video_layer(torch, attention, synthetic, heads,
+                                                            scale, steps)
+        except attention.CudaError as error:
+            extras["video_layer_error"] = str(error)
     return extras
+
+
+def run_video_layer(torch, attention, synthetic, heads, scale, steps) -> dict:
+    """The 125,504-token video layer of the sharded benchmark on this one GPU (the dense kernel
+    over all heads, which is what one rank of one runs): the 1-GPU end of the scaling curve,
+    measured by the same program that measures the N-GPU end."""
+    layout, plan = synthetic.video_plan()
+    tokens = len(layout)
+    qkv = synthetic.video_qkv_device(layout, plan, heads, seed=3)
+    output = torch.zeros((tokens, heads, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
+
+    def layer():
+        attention.dense_bf16(qkv, output, tokens, heads, scale)
+
+    layer()
+    ms = time_region(torch, layer, steps)
+    flops = attention_flops(tokens, heads)
+    return {"workload": workload_name(1, video=True), "tokens": tokens, "heads": heads, "ms": ms,
+            "tflops": flops / ms / 1e9, "kernel_status": attention.take_status()}
 
 
 def run_gemm(torch, attention, qkv, tokens, heads, steps) -> dict:
@@ -498,25 +680,45 @@ def kernel_times(torch, fn) -> dict:
         return {"unavailable": str(error)[:80]}
 
 
-def run_vsa(torch, attention, synthetic, heads, scale, steps, frames=31) -> dict:
+def reference_vsa_ms(torch, plan, qkv, output, tokens, heads, scale, kept, vsa_layout):
+    """The reference's own mmh3_vsa_attention (oracle/_ref, sm_100a) on the same rows, with a
+    workspace of its own: milliseconds per layer, or None when that library is not built."""
+    try:
+        import oracle_lib
+        from mmh3_b200 import attention
+
+        reference = oracle_lib.load_reference()
+        if reference is None:
+            return None
+        workspace = attention.VsaWorkspace(plan, tokens, heads)
+        raw = workspace.raw()
+        inner = heads * HEAD_DIM
+        base = qkv.data_ptr()
+
+        def call():
+            code = reference.mmh3_vsa_attention(
+                base, base + 2 * inner, base + 4 * inner, None, inner, output.data_ptr(), tokens,
+                heads, ctypes.byref(vsa_layout), scale, plan.tiles, plan.prefix_tiles, kept,
+                ctypes.byref(raw), None, 0, None)
+            if code != 0:
+                raise RuntimeError(f"the reference's mmh3_vsa_attention returned {code}")
+
+        torch.cuda.synchronize()
+        call()
+        return time_region(torch, call, 2)
+    except Exception:
+        return None
+
+
+def run_vsa(torch, attention, synthetic, heads, scale, steps, frames=31,
+            no_reference_kernels=False) -> dict:
     """Video sparse attention on the 31 x 48 x 84 grid + 512 text tokens (BASELINE configs[3]):
     pool, select and token attention timed apart. Inputs are drawn on the device: N(0, 1) plus 0.5 x
     a trilinearly upsampled low-resolution field per head and channel, in the plan's cube order."""
     layout, plan = synthetic.video_plan(frames=frames)
     tokens = len(layout)
     kept = plan.kept_video_tiles(0.875)
-    generator = torch.Generator(device="cuda").manual_seed(3)
-    qkv = torch.randn((tokens, 3, heads, HEAD_DIM), generator=generator, device="cuda",
-                      dtype=torch.float32).bfloat16()
-    grid = (layout.latent_frames, layout.latent_height // 2, layout.latent_width // 2)
-    order = torch.tensor(plan.video_order, dtype=torch.int64, device="cuda")
-    video = slice(plan.video_start, plan.video_start + len(plan.video_order))
-    for head in range(heads):
-        low = torch.randn((1, 3 * HEAD_DIM, 4, 6, 11), generator=generator, device="cuda")
-        smooth = torch.nn.functional.interpolate(low, size=grid, mode="trilinear",
-                                                 align_corners=True)
-        smooth = smooth.reshape(3 * HEAD_DIM, -1).t().reshape(-1, 3, HEAD_DIM)[order]
-        qkv[video, :, head, :] = (qkv[video, :, head, :].float() + 0.5 * smooth).bfloat16()
+    qkv = synthetic.video_qkv_device(layout, plan, heads, seed=3)
     output = torch.zeros((tokens, heads, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
     workspace = attention.VsaWorkspace(plan, tokens, heads)
     vsa_layout = attention.qkv_layout(heads)
@@ -555,11 +757,18 @@ def run_vsa(torch, attention, synthetic, heads, scale, steps, frames=31) -> dict
 
     whole_quantized()
     quantized_ms = time_region(torch, whole_quantized, steps)
+    quantized_kernels = kernel_times(torch, whole_quantized)
+    reference_ms = None
+    if not no_reference_kernels:
+        reference_ms = reference_vsa_ms(torch, plan, qkv, output, tokens, heads, scale, kept,
+                                        vsa_layout)
     return {
         "workload": (f"VSA L={tokens} ({plan.prefix_tiles} prefix + {plan.video_tiles} video "
                      f"tiles), H={heads}, kept {kept}"),
         "ms": ms, "sparse_flops": sparse_flops, "sparse_tflops": sparse_flops / ms / 1e9,
         "int8_fp8_ms": quantized_ms,
+        "int8_fp8_kernel_ms": quantized_kernels,
+        "reference_kernels_ms": reference_ms,
         "dense_equivalent_tflops": attention_flops(tokens, heads) / ms / 1e9,
         "kernel_ms": kernels,
         "selected_fraction": selected,
@@ -590,8 +799,20 @@ def run_sharded(args) -> None:
 
     layer = UlyssesAttention(shard, tokens, heads, dense, "cuda", torch.bfloat16,
                              pack=attention.shard_pack, unpack=attention.shard_unpack)
-    # Every rank draws the same stream and keeps its own rows, so the data does not depend on N.
-    generator_rows = synthetic.dense_qkv(len(own), heads, seed=3 + own.start, pinned=True)
+    # Every rank draws the whole layer from the same seed (the video configuration's
+    # distribution) and keeps its own rows, so the data does not depend on the rank count. Two
+    # heads of every token stay on the host for the check against the CPU oracle below.
+    video_layout, plan = synthetic.video_plan()
+    assert len(video_layout) == tokens
+    everything = synthetic.video_qkv_device(video_layout, plan, heads, seed=3)
+    checked_heads = sorted({(5 * rank) % heads, heads - 1 - rank % heads})
+    checked_qkv = {head: everything[:, :, head:head + 1, :].contiguous().cpu()
+                   for head in checked_heads}
+    generator_rows = torch.empty((len(own), 3, heads, HEAD_DIM), dtype=torch.bfloat16,
+                                 pin_memory=True)
+    generator_rows.copy_(everything[own.start:own.stop])
+    del everything
+    torch.cuda.empty_cache()
     qkv = generator_rows.cuda()
     output = torch.zeros((len(own), heads, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
     host_output = torch.empty((len(own), heads, HEAD_DIM), dtype=torch.bfloat16, pin_memory=True)
@@ -619,16 +840,18 @@ def run_sharded(args) -> None:
     # The pipelined layer must leave what the layer over resident inputs leaves.
     step()
     resident = output.clone()
+    oracle_error, oracle_rows = sharded_oracle_error(torch, resident, checked_qkv, own, tokens,
+                                                     scale)
     end_to_end()
     torch.cuda.synchronize()
     agrees = float(torch.equal(host_output.cuda(), resident))
     wires = None if args.skip_gemm else sharded_block(torch, dist, attention, args, shard, layer,
                                                       dense, qkv, output, tokens, heads)
     status = attention.take_status()
-    times = torch.tensor([ms, e2e_ms, float(status), -agrees], dtype=torch.float64,
+    times = torch.tensor([ms, e2e_ms, float(status), -agrees, oracle_error], dtype=torch.float64,
                          device="cuda")
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, status, disagrees = times.tolist()
+    ms, e2e_ms, status, disagrees, oracle_error = times.tolist()
     if rank == 0:
         flops = attention_flops(tokens, heads)
         peaks, source = measured_peaks()
@@ -638,11 +861,14 @@ def run_sharded(args) -> None:
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": {"workload": workload_name(world), "tokens": tokens, "heads": heads,
-                       "head_dim": HEAD_DIM, "flops_per_step": flops,
-                       "parallelism": f"ulysses{world}", "kernel_status": int(status),
-                       "exchange_bytes_per_rank": layer.exchange_bytes(),
-                       "l2": "inputs exceed L2 (126 MB)"},
+            "config": workload_config(world, tokens, heads),
+            "kernel_status": int(status),
+            "exchange_bytes_per_rank": layer.exchange_bytes(),
+            # Rows of every rank's share of the sharded layer's output against the f64 CPU oracle
+            # over all keys of the layer: the largest error over all ranks, and the bound.
+            "oracle_check": {"max_abs_error": oracle_error, "bound": 2e-2,
+                             "rows_per_rank": oracle_rows, "ranks": world,
+                             "passed": oracle_error <= 2e-2},
             "e2e": {"value": flops / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": generator_rows.numel() * 2 * world,
                     "d2h_bytes_per_step": host_output.numel() * 2 * world,
@@ -664,6 +890,29 @@ def run_sharded(args) -> None:
         print(json.dumps(line))
     dist.barrier()
     dist.destroy_process_group()
+
+
+def sharded_oracle_error(torch, output, checked_qkv, own, tokens, scale):
+    """The largest difference between rows of this rank's output [own tokens, heads, 128] and the
+    f64 CPU oracle over all `tokens` keys, for the first, middle and last of the rank's tokens
+    and the heads of `checked_qkv` (head -> BF16 [tokens, 3, 1, 128] on the host). Returns
+    (error, rows checked)."""
+    import numpy as np
+
+    import oracle_lib
+
+    oracle = oracle_lib.load()
+    worst, count = 0.0, 0
+    rows = sorted({own.start, own.start + len(own) // 2, own.stop - 1})
+    for head, host in checked_qkv.items():
+        bits = host.view(torch.int16).numpy().view(np.uint16)
+        for row in rows:
+            expected = oracle_lib.attention_bf16(oracle, bits, tokens, 1, scale, row, row + 1,
+                                                 0, 1, host_cores())
+            actual = output[row - own.start, head].float().cpu().numpy()
+            worst = max(worst, float(np.max(np.abs(actual - expected[0, 0]))))
+            count += 1
+    return worst, count
 
 
 def sharded_block(torch, dist, attention, args, shard, layer, dense, qkv, output, tokens,
@@ -749,6 +998,12 @@ def main() -> None:
     parser.add_argument("--vsa-frames", type=int, default=31,
                         help="latent frames of the video sparse attention case (31 is the "
                              "benchmark configuration; fewer for profiler captures)")
+    parser.add_argument("--skip-video-layer", action="store_true",
+                        help="leave the 125,504-token dense layer on one GPU out")
+    parser.add_argument("--no-reference-kernels", action="store_true",
+                        help="do not time the reference's own CUDA kernels (oracle/_ref)")
+    parser.add_argument("--reference-seconds", type=float, default=60.0,
+                        help="about how long the reference arm's warm-up and steps take together")
     parser.add_argument("--dense-only", action="store_true",
                         help="time only the dense BF16 kernel (for profiler captures)")
     args = parser.parse_args()

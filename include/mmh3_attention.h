@@ -170,6 +170,8 @@ int mmh3_sparse_attention(const void *query, const void *key, const void *value,
 /* Ulysses layout changes: gather heads [first_head, first_head + span) of
  * [tokens][tensors][heads][dim] into [tokens][tensors][span][dim], and scatter
  * [tokens][span][dim] back into [tokens][heads][dim]. Elements are 16 bits; dim is a multiple of 8.
+ * Both buffers are moved in 16-byte groups: a pointer off a 16-byte boundary returns
+ * cudaErrorInvalidValue (the reference would fault on the device).
  * Replace crates/mmh3-cuda/kernels/dit.cu:998-1023. */
 int mmh3_dit_shard_pack(const void *source, void *packed, int tokens, int tensors, int heads,
                         int dim, int first_head, int span, mmh3_stream_t stream);
@@ -188,7 +190,10 @@ int mmh3_dit_shard_unpack(const void *part, void *output, int tokens, int heads,
  * The layout must not be causal nor share key/value heads, as for mmh3_attention_quantized.
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress); make
- * that first call outside any stream capture. All calls on a device share the one array, which
+ * that first call outside any stream capture. With the CUDA runtime's default lazy module loading
+ * that first call is also when the driver loads this part of the library and backs the 12 MiB on
+ * that device, not the dlopen: a host that budgets every byte should make one small warm-up call
+ * per device before it measures what is left. Calls after the first take no device memory. All calls on a device share the one array, which
  * keeps what the last call left in it; every byte a call reads it has written first, so results do
  * not depend on earlier calls, but two calls whose kernels overlap on the GPU (different streams)
  * race and must be ordered by the caller. */

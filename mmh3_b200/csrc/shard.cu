@@ -39,6 +39,12 @@ __global__ void __launch_bounds__(THREADS)
     }
 }
 
+// The kernels move 16-byte groups: a pointer off that boundary would fault on the device, so it is
+// refused on the host instead.
+bool aligned(const void *first, const void *second) {
+    return (reinterpret_cast<uintptr_t>(first) | reinterpret_cast<uintptr_t>(second)) % 16 == 0;
+}
+
 // Enough CTAs to fill the device several times over, walked with a grid stride.
 unsigned grid_for(int64_t groups) {
     const int64_t wanted = (groups + THREADS - 1) / THREADS;
@@ -59,6 +65,9 @@ int launch_shard_pack(const void *source, void *packed, int tokens, int tensors,
     if (groups == 0) {
         return 0;
     }
+    if (source == nullptr || packed == nullptr || !aligned(source, packed)) {
+        return INVALID_VALUE;
+    }
     shard_pack_kernel<<<grid_for(groups), THREADS, 0, stream>>>(
         static_cast<const uint4 *>(source), static_cast<uint4 *>(packed), groups, heads,
         dim_groups, first_head, span);
@@ -74,6 +83,9 @@ int launch_shard_unpack(const void *part, void *output, int tokens, int heads, i
     const int64_t groups = static_cast<int64_t>(tokens) * span * dim_groups;
     if (groups == 0) {
         return 0;
+    }
+    if (part == nullptr || output == nullptr || !aligned(part, output)) {
+        return INVALID_VALUE;
     }
     shard_unpack_kernel<<<grid_for(groups), THREADS, 0, stream>>>(
         static_cast<const uint4 *>(part), static_cast<uint4 *>(output), groups, heads, dim_groups,

@@ -10,7 +10,9 @@
 // allocated or freed here, by the CUDA runtime or by anything else.
 //
 // The price: the array has a fixed, modest size, every GPU that loads the library carries it until
-// the process exits, and all calls share it.
+// the process exits, and all calls share it. With lazy module loading (the runtime's default) the
+// driver backs the array on a device when the first call there looks up its address, not when the
+// library is opened; calls after that take no device memory at all.
 #include <atomic>
 #include <cstdio>
 

@@ -97,3 +97,25 @@ def video_qkv(layout: PackedLayout, plan: VsaPlan, heads: int, seed: int,
         noise[video] += weight * smooth[order]
         qkv[:, :, head, :] = noise.to(torch.bfloat16)
     return qkv
+
+
+def video_qkv_device(layout: PackedLayout, plan: VsaPlan, heads: int, seed: int,
+                     coarse_grid=(4, 6, 11), weight: float = 0.5, device="cuda") -> torch.Tensor:
+    """`video_qkv` drawn on the device's own generator: the same distribution, and the same values
+    on every GPU of one kind for one seed, without the minute the CPU generator takes at 125,504
+    tokens x 32 heads. Every rank of a sharded run draws the whole tensor and keeps its rows, so
+    the data does not depend on the rank count."""
+    generator = torch.Generator(device=device).manual_seed(seed)
+    tokens = len(layout)
+    grid = (layout.latent_frames, layout.latent_height // 2, layout.latent_width // 2)
+    order = torch.tensor(plan.video_order, dtype=torch.int64, device=device)
+    qkv = torch.randn((tokens, 3, heads, HEAD_DIM), generator=generator, device=device,
+                      dtype=torch.float32).bfloat16()
+    video = slice(plan.video_start, plan.video_start + len(plan.video_order))
+    for head in range(heads):
+        low = torch.randn((1, 3 * HEAD_DIM, *coarse_grid), generator=generator, device=device)
+        smooth = torch.nn.functional.interpolate(low, size=grid, mode="trilinear",
+                                                 align_corners=True)
+        smooth = smooth.reshape(3 * HEAD_DIM, -1).t().reshape(-1, 3, HEAD_DIM)[order]
+        qkv[video, :, head, :] = (qkv[video, :, head, :].float() + weight * smooth).bfloat16()
+    return qkv

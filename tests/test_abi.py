@@ -88,6 +88,13 @@ def test_bad_arguments_are_rejected_before_any_launch():
     assert library.mmh3_attention_inputs(None, None, None, None, 0, 8, 1, 1e-6, None, None, None,
                                          None, 0, None, None) == invalid
     assert library.mmh3_dit_shard_pack(None, None, 8, 3, 4, 100, 0, 2, None) == invalid
+    # The gathers move 16-byte groups: a pointer off that boundary is refused on the host.
+    even, odd = ctypes.c_void_p(4096), ctypes.c_void_p(4096 + 8)
+    assert library.mmh3_dit_shard_pack(odd, even, 8, 3, 4, 128, 0, 2, None) == invalid
+    assert library.mmh3_dit_shard_pack(even, odd, 8, 3, 4, 128, 0, 2, None) == invalid
+    assert library.mmh3_dit_shard_unpack(odd, even, 8, 4, 128, 0, 2, None) == invalid
+    assert library.mmh3_dit_shard_unpack(even, odd, 8, 4, 128, 0, 2, None) == invalid
+    assert library.mmh3_dit_shard_unpack(even, even, 8, 4, 128, 3, 2, None) == invalid
     # no workspace, no tokens
     assert library.mmh3_sparse_attention(None, None, None, None, 8, 1, ctypes.byref(layout), 0.1,
                                          0.5, 0, 0, 0, 0, None, None, 0, None) == invalid

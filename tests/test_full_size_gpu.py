@@ -169,10 +169,10 @@ def test_sol_attention_at_the_benchmark_size(reference_kernels, dense_case):
            milliseconds(reference_call))
 
 
-def test_video_sparse_attention_at_the_benchmark_size(reference_kernels):
+@pytest.fixture(scope="module")
+def video_case():
     layout, plan = synthetic.video_plan()
     tokens = len(layout)
-    kept = plan.kept_video_tiles(0.875)
     generator = torch.Generator(device="cuda").manual_seed(3)
     qkv = torch.randn((tokens, 3, HEADS, 128), generator=generator, device="cuda").bfloat16()
     # A smooth component per head and channel so that the pooled scores are not uniform.
@@ -181,6 +181,11 @@ def test_video_sparse_attention_at_the_benchmark_size(reference_kernels):
         phase = torch.rand((3, 128), generator=generator, device="cuda") * 6.283
         qkv[:, :, head, :] = (qkv[:, :, head, :].float() +
                               0.5 * torch.sin(positions[:, None, None] + phase)).bfloat16()
+    return plan, tokens, plan.kept_video_tiles(0.875), qkv
+
+
+def test_video_sparse_attention_at_the_benchmark_size(reference_kernels, video_case):
+    plan, tokens, kept, qkv = video_case
     ours = torch.zeros((tokens, HEADS, 128), dtype=torch.bfloat16, device="cuda")
     theirs = torch.zeros_like(ours)
     workspace = attention.VsaWorkspace(plan, tokens, HEADS)
@@ -209,6 +214,102 @@ def test_video_sparse_attention_at_the_benchmark_size(reference_kernels):
     assert torch.max(torch.abs(ours.float() - theirs.float())).item() <= 2e-2
     report("VSA, L=125,504, H=32, 252 of 2,016 video tiles kept",
            milliseconds(lambda: attention.vsa(qkv, None, ours, vsa_layout, SCALE, kept, workspace)),
+           milliseconds(reference_call))
+
+
+def test_quantized_video_sparse_attention_at_the_benchmark_size(reference_kernels, video_case):
+    """The INT8/FP8 form of the same layer, as the DiT calls it with inputs_ready = 2: both
+    libraries prepare their own copy of the rows (norm, INT8 q/k, FP8 V, pooled tiles), select and
+    attend. Everything the fused pass and the selection leave is held to the reference's bits,
+    whole tensors; the output to its cosine."""
+    plan, tokens, kept, source = video_case
+    ones = torch.ones(128, dtype=torch.bfloat16, device="cuda")
+    norm = attention.HeadNorm(ones, ones, None, 0, 1e-6)
+    maxima = source[:, 2].float().abs().amax(dim=(0, 2)).contiguous()
+    vsa_layout = attention.qkv_layout(HEADS)
+    prepared = attention.AttentionInputs.PREPARED_WITH_VALUES
+
+    qkv = source.clone()
+    ours = torch.zeros((tokens, HEADS, 128), dtype=torch.bfloat16, device="cuda")
+    workspace = attention.VsaWorkspace(plan, tokens, HEADS, quantized=True)
+    attention.prepare_inputs(qkv, norm, tokens, HEADS, vsa=workspace, value_head_maxima=maxima)
+    attention.vsa(qkv, None, ours, vsa_layout, SCALE, kept, workspace, prepared)
+
+    their_qkv = source.clone()
+    theirs = torch.zeros_like(ours)
+    other = attention.VsaWorkspace(plan, tokens, HEADS, quantized=True)
+    sparse, quantized, raw = other.sparse_raw(), other.quantized.raw(), other.raw()
+    assert reference_kernels.mmh3_attention_inputs(
+        their_qkv.data_ptr(), ones.data_ptr(), ones.data_ptr(), None, 0, tokens, HEADS, 1e-6,
+        ctypes.byref(sparse), ctypes.byref(quantized), other.tile_starts.data_ptr(),
+        other.tile_lengths.data_ptr(), other.tiles, maxima.data_ptr(), None) == 0
+    base = their_qkv.data_ptr()
+
+    def reference_call():
+        assert reference_kernels.mmh3_vsa_attention(
+            base, base + 2 * INNER, base + 4 * INNER, None, INNER, theirs.data_ptr(), tokens,
+            HEADS, ctypes.byref(vsa_layout), SCALE, plan.tiles, plan.prefix_tiles, kept,
+            ctypes.byref(raw), ctypes.byref(quantized), int(prepared), None) == 0
+
+    reference_call()
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    assert torch.equal(qkv, their_qkv)  # the normalized rows both left in place
+    for name in ("query", "key", "value", "query_scales", "key_scales", "value_scales"):
+        assert torch.equal(getattr(workspace.quantized, name), getattr(other.quantized, name)), name
+    for name in ("pooled_query", "pooled_key", "pooled_value", "route_counts"):
+        assert torch.equal(getattr(workspace, name), getattr(other, name)), name
+    assert abs(workspace.selected_fraction() - plan.expected_selected_fraction(kept)) < 1e-9
+    valid = (torch.arange(plan.tiles, device="cuda")[None, :] <
+             workspace.route_counts.view(-1, 1))
+    assert torch.equal(workspace.routes.view(-1, plan.tiles)[valid],
+                       other.routes.view(-1, plan.tiles)[valid])
+    assert cosine(ours, theirs) >= 0.9995
+    assert torch.max(torch.abs(ours.float() - theirs.float())).item() <= 0.1
+    report("INT8/FP8 VSA over prepared inputs, L=125,504, H=32",
+           milliseconds(lambda: attention.vsa(qkv, None, ours, vsa_layout, SCALE, kept, workspace,
+                                              prepared)),
+           milliseconds(reference_call))
+
+
+def test_quantized_sol_attention_at_the_benchmark_size(reference_kernels, dense_case):
+    """Sol-Attn with INT8 QK / FP8 PV routed products at L = 66,048: routes, block statistics and
+    the quantizer's outputs bit for bit against the reference's kernels, the output to its
+    cosine."""
+    _, qkv = dense_case
+    tau, sinks = 1.3, SparseSinks((0, 8), (0, 0))
+    ours = torch.zeros((TOKENS, HEADS, 128), dtype=torch.bfloat16, device="cuda")
+    theirs = torch.zeros_like(ours)
+    workspace = attention.SparseWorkspace(TOKENS, HEADS, quantized=True)
+    other = attention.SparseWorkspace(TOKENS, HEADS, quantized=True)
+    layout = attention.qkv_layout(HEADS)
+    attention.sparse(qkv, ours, layout, SCALE, tau, sinks, workspace)
+    raw, their_quantized = other.raw(), other.quantized.raw()
+    base = qkv.data_ptr()
+
+    def reference_call():
+        assert reference_kernels.mmh3_sparse_attention(
+            base, base + 2 * INNER, base + 4 * INNER, theirs.data_ptr(), TOKENS, HEADS,
+            ctypes.byref(layout), SCALE, tau, *sinks.key_blocks, *sinks.query_blocks,
+            ctypes.byref(raw), ctypes.byref(their_quantized), 0, None) == 0
+
+    reference_call()
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    assert torch.equal(workspace.route_counts, other.route_counts)
+    blocks = workspace.blocks
+    valid = (torch.arange(blocks, device="cuda")[None, :] <
+             workspace.route_counts.view(-1, 1))
+    assert torch.equal(workspace.routes.view(-1, blocks)[valid],
+                       other.routes.view(-1, blocks)[valid])
+    for name in ("centroids", "block_keys", "value_sums", "key_mean", "key_variance", "tail_max"):
+        assert torch.equal(getattr(workspace, name), getattr(other, name)), name
+    for name in ("query", "key", "value", "query_scales", "key_scales", "value_scales"):
+        assert torch.equal(getattr(workspace.quantized, name), getattr(other.quantized, name)), name
+    assert cosine(ours, theirs) >= 0.9995
+    assert torch.max(torch.abs(ours.float() - theirs.float())).item() <= 0.1
+    report("Sol-Attn with INT8/FP8 routed products, L=66,048, H=32, tau 1.3",
+           milliseconds(lambda: attention.sparse(qkv, ours, layout, SCALE, tau, sinks, workspace)),
            milliseconds(reference_call))
 
 

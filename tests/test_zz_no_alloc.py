@@ -23,7 +23,9 @@ SCALE = synthetic.softmax_scale()
 
 
 def test_static_scratch_matches_a_caller_owned_workspace_twice_in_a_row():
-    for tokens, heads, seed in [(1000, 3, 21), (321, 2, 22)]:
+    # The second shape fills the array to its last byte (4,096 tokens of 8 heads is the limit);
+    # the third is smaller, so the array still holds the bytes of the one before.
+    for tokens, heads, seed in [(1000, 3, 21), (4096, 8, 23), (321, 2, 22)]:
         qkv = synthetic.dense_qkv(tokens, heads, seed=seed).cuda()
         expected = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
         actual = torch.zeros_like(expected)
@@ -33,6 +35,25 @@ def test_static_scratch_matches_a_caller_owned_workspace_twice_in_a_row():
         assert attention.take_status() == 0
         assert float(expected.float().abs().max()) > 0.0
         assert torch.equal(actual.view(torch.int16), expected.view(torch.int16)), (tokens, heads)
+
+
+def test_a_repeated_call_takes_no_device_memory():
+    """Once the first call on the device has run (it is where the driver backs the array and loads
+    the kernels), a further call leaves the device's free memory where it was: nothing is
+    allocated, by the CUDA runtime or by torch's allocator."""
+    tokens, heads = 640, 4
+    qkv = synthetic.dense_qkv(tokens, heads, seed=24).cuda()
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    attention.dense_quantized_static(qkv, output, tokens, heads, SCALE)
+    torch.cuda.synchronize()
+    reserved = torch.cuda.memory_reserved()
+    free_before, _ = torch.cuda.mem_get_info()
+    attention.dense_quantized_static(qkv, output, tokens, heads, SCALE)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert attention.take_status() == 0
+    assert torch.cuda.memory_reserved() == reserved
+    assert free_after == free_before
 
 
 def test_shapes_past_the_scratch_are_refused():
