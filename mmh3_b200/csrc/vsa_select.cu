@@ -1,259 +1,739 @@
-// VSA's tile selection: per head and query tile, the pooled scores against every tile, the exact
-// set of tiles it attends token by token, and the coarse output softmax(scores) . mean values.
+// VSA's tile selection: for every head and query tile the exact set of tiles it attends token by
+// token, and, when the layer is gated, the coarse output softmax(scores) . mean values.
 //
-// The routes are bit-identical to the reference's select_kernel
-// (crates/mmh3-cuda/kernels/vsa_attention.cu:96-273). That fixes the FP32 evaluation order of a
-// score: 32 chains of four fused multiply-adds over dimensions l, l + 32, l + 64, l + 96, summed
-// over a balanced tree that pairs chains by bit 4 of l first and by bit 0 last, then one multiply
-// by the scale. Here one thread evaluates that whole tree: it holds one pooled key in registers and
-// scores it against each of its CTA's eight query tiles, whose pooled queries sit in shared
-// memory, two chains to a packed operation; the reference spreads a score over the lanes of a warp. The selection itself
-// is a function of the scores alone, so it is free to differ: here a warp finds the kept-th
-// largest video score with a four-pass radix select over
-// order-preserving integer keys (the reference descends one bit at a time), ties go to the lower
-// tile index, and the route is an ascending list of uint16 tile indices.
+// What has to come out is what the reference's select_kernel leaves
+// (crates/mmh3-cuda/kernels/vsa_attention.cu:96-273): every prefix tile, then the `kept` video
+// tiles with the largest pooled scores, ties to the lower tile index, as an ascending list of
+// uint16 tile indices, bit for bit. A pooled score there is one particular FP32 evaluation of
+// (mean q) . (mean k) * scale: 32 chains of four fused multiply-adds over dimensions l, l + 32,
+// l + 64, l + 96, summed over a butterfly that pairs the chains by bit 4 of l first and bit 0 last.
+// Scoring every pair of tiles that way is 128 FMAs a pair on the CUDA cores, and almost all of it
+// decides nothing: a route only depends on the scores close to its own threshold.
+//
+// So the work is split by what it needs:
+//
+// 1. `cosine_kernel`: all pairs on the tensor cores. tcgen05.mma kind::tf32 over the FP32 tile
+//    means (TMA into swizzled shared memory, accumulators in tensor memory) gives every score to
+//    about 2^-9 of |q| |k|. The epilogue divides by the two norms and stores the cosine as a
+//    signed 16-bit fraction in the very slot of the route table the pair owns (the table is
+//    [heads][tiles][tiles] uint16, one slot a pair), so no other scratch is needed.
+// 2. `route_kernel`: a warp per query tile. It rebuilds the approximate scores from its row of
+//    cosines, finds the bin of a 512-bin histogram that holds the kept-th largest, and from the
+//    proven bound B >= |approximate - exact| sorts the tiles into "certainly kept" (more than 2 B
+//    above that bin), "certainly dropped" (more than 2 B below) and the few in between. Only those
+//    are scored again, exactly, in the reference's FP32 order, a lane to a chain; a radix select
+//    over their order-preserving bit patterns finds the threshold among them and how many ties at
+//    it are kept; and one ballot pass over the row emits the ascending list. If the counts ever
+//    fail to add up (they cannot while the bound holds), the row is redone with every tile scored
+//    exactly.
+// 3. `coarse_kernel`, only for gated layers: a warp per query tile walks the tiles 32 at a time
+//    with an online softmax in FP32 (this output is held to a tolerance, not to bits).
+#include <algorithm>
 #include <cfloat>
 
 #include "common.cuh"
-#include "pooled_score.cuh"
+#include "sm100.cuh"
 
 namespace mmh3 {
 
 namespace {
 
-constexpr int THREADS = 128;
-constexpr int WARPS = THREADS / 32;
-constexpr int MAX_QUERIES = 8;
+using namespace sm100;
 
-// Maps a float to an unsigned integer with the same order.
-__device__ __forceinline__ uint32_t ordered_bits(float value) {
-    const uint32_t bits = __float_as_uint(value);
-    return (bits & 0x80000000u) ? ~bits : bits | 0x80000000u;
+// ---------------------------------------------------------------------------------------------
+// 1. Cosines of all pairs of tile means, on the tensor cores.
+
+constexpr int PANEL = 128;                     // query tiles and key tiles to a CTA
+constexpr int PANEL_SLAB = PANEL * 128;        // 128 rows of 32 floats
+constexpr int PANEL_SLABS = HEAD_DIM / 32;
+constexpr int PANEL_BYTES = PANEL_SLABS * PANEL_SLAB;
+constexpr int COSINE_THREADS = 160;            // four warps own the TMEM lanes, the fifth loads and issues
+constexpr int COSINE_SMEM_NORMS = 2 * PANEL_BYTES;
+constexpr int COSINE_SMEM_BARRIERS = COSINE_SMEM_NORMS + PANEL * 4;
+constexpr int COSINE_SMEM_BYTES = COSINE_SMEM_BARRIERS + 64 + 1024;
+constexpr float COSINE_ONE = 32767.0f;
+constexpr uint32_t FORMAT_TF32 = 2;            // kind::tf32
+constexpr uint32_t COSINE_MMA =
+    instruction_descriptor(ACCUMULATE_F32, FORMAT_TF32, FORMAT_TF32, 0, 0, PANEL, PANEL);
+constexpr unsigned int STATUS_SELECT = 0x00040000u;
+
+struct CosineMaps {
+    CUtensorMap query; // [128, tiles, heads] FP32
+    CUtensorMap key;
+};
+
+__device__ __forceinline__ void mma_tf32(uint32_t d, uint64_t a, uint64_t b, uint32_t accumulate) {
+    asm volatile("{\n"
+                 ".reg .pred p;\n"
+                 "setp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+                 "}" ::"r"(d),
+                 "l"(a), "l"(b), "r"(COSINE_MMA), "r"(accumulate)
+                 : "memory");
 }
 
-__device__ __forceinline__ float block_reduce(float value, float *scratch, bool maximum) {
+// The sum of the squares of row `row` of a panel as TMA left it: 32 floats to a 128-byte line,
+// 16-byte chunk c of a line at c ^ (row % 8).
+__device__ __forceinline__ float panel_row_square(const uint8_t *panel, int row) {
+    float sum = 0.0f;
     #pragma unroll
-    for (int offset = 16; offset > 0; offset /= 2) {
-        const float other = __shfl_xor_sync(0xffffffffu, value, offset);
-        value = maximum ? fmaxf(value, other) : value + other;
+    for (int slab = 0; slab < PANEL_SLABS; slab++) {
+        const uint8_t *line = panel + slab * PANEL_SLAB + row * 128;
+        #pragma unroll
+        for (int chunk = 0; chunk < 8; chunk++) {
+            const float4 four = *reinterpret_cast<const float4 *>(line + ((chunk ^ (row & 7)) * 16));
+            sum = fmaf(four.x, four.x, sum);
+            sum = fmaf(four.y, four.y, sum);
+            sum = fmaf(four.z, four.z, sum);
+            sum = fmaf(four.w, four.w, sum);
+        }
     }
-    if (threadIdx.x % 32 == 0) {
-        scratch[threadIdx.x / 32] = value;
-    }
-    __syncthreads();
-    float result = scratch[0];
-    for (int warp = 1; warp < WARPS; warp++) {
-        result = maximum ? fmaxf(result, scratch[warp]) : result + scratch[warp];
-    }
-    __syncthreads();
-    return result;
+    return sum;
 }
 
-// One CTA takes QUERIES consecutive query tiles of one head. A thread holds one pooled key in
-// registers (read once, straight from L2) and scores it against each of the CTA's queries, which
-// sit in shared memory; then the next key, 128 tiles further on.
-template <int QUERIES>
-__global__ void __launch_bounds__(THREADS, 3)
-    select_kernel(Mmh3VsaWorkspace workspace, int tiles, int prefix_tiles, int kept, float scale,
-                  int coarse) {
-    extern __shared__ __align__(16) float scores[]; // [QUERIES][tiles]
-    __shared__ float4 queries[QUERIES][32];
-    __shared__ float sums[QUERIES];
-    __shared__ float scratch[WARPS];
-    __shared__ int histogram[WARPS][256];
-    const int first_query = blockIdx.x * QUERIES;
-    const int query_count = min(QUERIES, tiles - first_query);
-    const int head = blockIdx.y;
-    const int lane = threadIdx.x % 32;
-    const int warp = threadIdx.x / 32;
-    const size_t first_row = static_cast<size_t>(head) * tiles + first_query;
-
-    for (int index = threadIdx.x; index < QUERIES * 32; index += THREADS) {
-        const int query = index / 32, four = index % 32;
-        float4 values = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (query < query_count) {
-            values = reinterpret_cast<const float4 *>(workspace.pooled_query +
-                                                      (first_row + query) * HEAD_DIM)[four];
-        }
-        queries[query][four] = values;
-    }
-    __syncthreads();
-
-    const float *head_keys = workspace.pooled_key + static_cast<size_t>(head) * tiles * HEAD_DIM;
-    for (int tile = threadIdx.x; tile < tiles; tile += THREADS) {
-        float2 key[HEAD_DIM / 2];
-        load_row(head_keys + static_cast<size_t>(tile) * HEAD_DIM, key);
-        #pragma unroll 1
-        for (int query = 0; query < query_count; query++) {
-            scores[static_cast<size_t>(query) * tiles + tile] =
-                __fmul_rn(score_tree(queries[query], key), scale);
-        }
-    }
-    __syncthreads();
-
-    // Each warp selects the tiles of one query tile: a radix select, one byte of the ordered keys
-    // at a time from the top, finds the kept-th largest video score; then one pass emits the
-    // prefix tiles, the video tiles above it and the first of those equal to it.
-    const int video_tiles = tiles - prefix_tiles;
-    for (int query = warp; query < query_count; query += WARPS) {
-        const int query_tile = first_query + query;
-        const float *query_scores = scores + static_cast<size_t>(query) * tiles;
-        const bool everything = query_tile < prefix_tiles || kept >= video_tiles;
-        uint32_t threshold = 0;  // ordered key of the kept-th largest video score
-        int remaining = kept;    // how many scores equal to the threshold are kept
-        if (!everything) {
-            int *bins = histogram[warp];
-            uint32_t settled = 0; // mask of the key bits `threshold` already holds
-            for (int shift = 24; shift >= 0; shift -= 8) {
-                for (int bin = lane; bin < 256; bin += 32) {
-                    bins[bin] = 0;
-                }
-                __syncwarp();
-                for (int first = prefix_tiles; first < tiles; first += 32) {
-                    const int tile = first + lane;
-                    const uint32_t bits = tile < tiles ? ordered_bits(query_scores[tile]) : 0;
-                    const bool counted = tile < tiles && (bits & settled) == threshold;
-                    // Scores crowd into a few bins, so the lanes of a bin add their count once.
-                    const uint32_t bin = counted ? (bits >> shift) & 255u : 256u;
-                    const unsigned same = __match_any_sync(0xffffffffu, bin);
-                    if (counted && lane == __ffs(same) - 1) {
-                        bins[bin] += __popc(same);
-                    }
-                    __syncwarp();
-                }
-                __syncwarp();
-                // Lane l owns bins 8 l .. 8 l + 7. `above` counts the candidates in higher bins.
-                int owned[8];
-                int total = 0;
-                #pragma unroll
-                for (int bin = 0; bin < 8; bin++) {
-                    owned[bin] = bins[lane * 8 + bin];
-                    total += owned[bin];
-                }
-                int above = total;
-                #pragma unroll
-                for (int offset = 1; offset < 32; offset *= 2) {
-                    const int other = __shfl_down_sync(0xffffffffu, above, offset);
-                    if (lane + offset < 32) {
-                        above += other;
-                    }
-                }
-                above -= total;
-                const bool holds = above < remaining && remaining <= above + total;
-                int digit = 0, passed = 0;
-                if (holds) {
-                    int seen = above;
-                    #pragma unroll
-                    for (int bin = 7; bin >= 0; bin--) {
-                        if (seen < remaining && remaining <= seen + owned[bin]) {
-                            digit = lane * 8 + bin;
-                            passed = seen;
-                        }
-                        seen += owned[bin];
-                    }
-                }
-                const int holder = __ffs(__ballot_sync(0xffffffffu, holds)) - 1;
-                digit = __shfl_sync(0xffffffffu, digit, holder);
-                passed = __shfl_sync(0xffffffffu, passed, holder);
-                remaining -= passed;
-                threshold |= static_cast<uint32_t>(digit) << shift;
-                settled |= 255u << shift;
-                __syncwarp();
-            }
-        }
-        uint16_t *route = workspace.routes + (first_row + query) * tiles;
-        int count = 0;
-        int equal_before = 0;
-        for (int start = 0; start < tiles; start += 32) {
-            const int tile = start + lane;
-            bool keep = tile < tiles;
-            bool equal = false;
-            if (keep && !everything && tile >= prefix_tiles) {
-                const uint32_t bits = ordered_bits(query_scores[tile]);
-                equal = bits == threshold;
-                keep = bits > threshold;
-            }
-            const unsigned equal_mask = __ballot_sync(0xffffffffu, equal);
-            // Ties go to the lower tile index.
-            if (equal && equal_before + __popc(equal_mask & ((1u << lane) - 1)) < remaining) {
-                keep = true;
-            }
-            equal_before += __popc(equal_mask);
-            const unsigned kept_mask = __ballot_sync(0xffffffffu, keep);
-            if (keep) {
-                route[count + __popc(kept_mask & ((1u << lane) - 1))] =
-                    static_cast<uint16_t>(tile);
-            }
-            count += __popc(kept_mask);
-        }
-        if (lane == 0) {
-            workspace.route_counts[first_row + query] = count;
-        }
-    }
-    __syncthreads();
-
-    if (!coarse) {
+__global__ void __launch_bounds__(COSINE_THREADS, 1)
+    cosine_kernel(const __grid_constant__ CosineMaps maps, uint16_t *__restrict__ table, int tiles,
+                  unsigned int *status) {
+    extern __shared__ uint8_t shared_memory[];
+    const uint32_t base = (smem_u32(shared_memory) + 1023u) & ~1023u;
+    uint8_t *aligned = shared_memory + (base - smem_u32(shared_memory));
+    const uint32_t loaded = base + COSINE_SMEM_BARRIERS, multiplied = loaded + 8;
+    float *inverse_key_norms = reinterpret_cast<float *>(aligned + COSINE_SMEM_NORMS);
+    volatile uint32_t *tmem_slot =
+        reinterpret_cast<volatile uint32_t *>(aligned + COSINE_SMEM_BARRIERS + 16);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+    const Watchdog watchdog = {abort_flag, status};
+    if (*reinterpret_cast<volatile unsigned int *>(status) != 0) {
         return;
     }
-    // softmax(scores) . (summed values / tile length), one thread per dimension.
-    for (int query = 0; query < query_count; query++) {
-        float *query_scores = scores + static_cast<size_t>(query) * tiles;
-        float maximum = -FLT_MAX;
-        for (int tile = threadIdx.x; tile < tiles; tile += THREADS) {
-            maximum = fmaxf(maximum, query_scores[tile]);
-        }
-        maximum = block_reduce(maximum, scratch, true);
-        float sum = 0.0f;
-        for (int tile = threadIdx.x; tile < tiles; tile += THREADS) {
-            const float weight = expf(query_scores[tile] - maximum);
-            query_scores[tile] = weight / static_cast<float>(workspace.tile_lengths[tile]);
-            sum += weight;
-        }
-        sum = block_reduce(sum, scratch, false);
-        if (threadIdx.x == 0) {
-            sums[query] = sum;
-        }
+    const int warp = threadIdx.x / 32;
+    const int lane = threadIdx.x % 32;
+    const int first_key = blockIdx.x * PANEL;
+    const int first_query = blockIdx.y * PANEL;
+    const int head = blockIdx.z;
+
+    if (threadIdx.x == 0) {
+        mbar_init(loaded, 1);
+        mbar_init(multiplied, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
     }
+    if (warp == 4) {
+        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), PANEL);
+    }
+    tcgen05_fence_before();
     __syncthreads();
-    const float *values =
-        workspace.pooled_value + static_cast<size_t>(head) * tiles * HEAD_DIM + threadIdx.x;
-    float outputs[QUERIES] = {};
-    constexpr int VALUE_BATCH = 8;
-    for (int first = 0; first < tiles; first += VALUE_BATCH) {
-        float loaded[VALUE_BATCH];
-        #pragma unroll
-        for (int batch = 0; batch < VALUE_BATCH; batch++) {
-            loaded[batch] = first + batch < tiles
-                                ? __ldg(values + static_cast<size_t>(first + batch) * HEAD_DIM)
-                                : 0.0f;
-        }
-        #pragma unroll
-        for (int batch = 0; batch < VALUE_BATCH; batch++) {
-            if (first + batch < tiles) {
+    tcgen05_fence_after();
+    const uint32_t tmem = *tmem_slot;
+
+    if (warp == 4) {
+        if (lane == 0) {
+            mbar_expect_tx(loaded, 2 * PANEL_BYTES);
+            for (int slab = 0; slab < PANEL_SLABS; slab++) {
+                tma_load_3d(base + slab * PANEL_SLAB, &maps.query, loaded, slab * 32, first_query,
+                            head);
+                tma_load_3d(base + PANEL_BYTES + slab * PANEL_SLAB, &maps.key, loaded, slab * 32,
+                            first_key, head);
+            }
+            if (mbar_wait(loaded, 0, watchdog, STATUS_SELECT | 1)) {
+                tcgen05_fence_after();
+                // Eight floats, 32 bytes, to an MMA: four steps to a slab of 32 dimensions.
                 #pragma unroll
-                for (int query = 0; query < QUERIES; query++) {
-                    if (query < query_count) {
-                        outputs[query] =
-                            fmaf(scores[static_cast<size_t>(query) * tiles + first + batch],
-                                 loaded[batch], outputs[query]);
+                for (int step = 0; step < HEAD_DIM / 8; step++) {
+                    const uint32_t offset = (step / 4) * PANEL_SLAB + (step % 4) * 32;
+                    mma_tf32(tmem, smem_descriptor(base + offset, 16, 1024),
+                             smem_descriptor(base + PANEL_BYTES + offset, 16, 1024), step > 0);
+                }
+                tcgen05_commit(multiplied);
+            }
+        }
+    } else {
+        // Thread r: the norm of query row r and of key row r while the MMAs run, then row r of the
+        // products.
+        const int row = warp * 32 + lane;
+        bool alive = __all_sync(0xffffffffu, mbar_wait(loaded, 0, watchdog, STATUS_SELECT | 2));
+        float inverse_query_norm = 0.0f;
+        if (alive) {
+            const float query_square = panel_row_square(aligned, row);
+            const float key_square = panel_row_square(aligned + PANEL_BYTES, row);
+            inverse_query_norm = query_square > 0.0f ? rsqrtf(query_square) : 0.0f;
+            inverse_key_norms[row] = key_square > 0.0f ? rsqrtf(key_square) : 0.0f;
+        }
+        // The four warps that own the rows, not the one that loads.
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        alive = alive &&
+                __all_sync(0xffffffffu, mbar_wait(multiplied, 0, watchdog, STATUS_SELECT | 3));
+        if (alive) {
+            tcgen05_fence_after();
+            const int query_tile = first_query + row;
+            const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+            uint16_t *slots = table + (static_cast<size_t>(head) * tiles + query_tile) * tiles +
+                              first_key;
+            // Whole 16-byte groups of a row can be stored as such when every row starts on one.
+            const bool vector_stores = tiles % 8 == 0 && reinterpret_cast<uintptr_t>(table) % 16 == 0;
+            #pragma unroll
+            for (int chunk = 0; chunk < PANEL / 32; chunk++) {
+                uint32_t values[32];
+                tmem_load_32(tmem + lane_base + chunk * 32, values);
+                tmem_wait_load();
+                uint32_t packed[16];
+                #pragma unroll
+                for (int pair = 0; pair < 16; pair++) {
+                    int fractions[2];
+                    #pragma unroll
+                    for (int side = 0; side < 2; side++) {
+                        const int column = chunk * 32 + pair * 2 + side;
+                        const float cosine = __uint_as_float(values[pair * 2 + side]) *
+                                             inverse_query_norm * inverse_key_norms[column];
+                        fractions[side] =
+                            __float2int_rn(fminf(fmaxf(cosine, -1.0f), 1.0f) * COSINE_ONE);
+                    }
+                    packed[pair] = (static_cast<uint32_t>(fractions[0]) & 0xffffu) |
+                                   (static_cast<uint32_t>(fractions[1]) << 16);
+                }
+                if (query_tile < tiles) {
+                    const int column = first_key + chunk * 32;
+                    if (vector_stores && column + 32 <= tiles) {
+                        uint4 *destination = reinterpret_cast<uint4 *>(slots + chunk * 32);
+                        #pragma unroll
+                        for (int part = 0; part < 4; part++) {
+                            destination[part] = make_uint4(packed[part * 4], packed[part * 4 + 1],
+                                                           packed[part * 4 + 2],
+                                                           packed[part * 4 + 3]);
+                        }
+                    } else {
+                        #pragma unroll
+                        for (int index = 0; index < 32; index++) {
+                            if (column + index < tiles) {
+                                slots[chunk * 32 + index] = static_cast<uint16_t>(
+                                    packed[index / 2] >> (16 * (index % 2)));
+                            }
+                        }
                     }
                 }
             }
         }
     }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        if (*abort_flag != 0) {
+            for (int spin = 0; spin < 64; spin++) {
+                __nanosleep(1000);
+            }
+        }
+        tcgen05_fence_after();
+        tmem_dealloc(tmem, PANEL);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 2. Routes from the cosines.
+
+constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_THREADS = ROUTE_WARPS * 32;
+constexpr int BINS = 512;
+// |approximate - exact| <= BOUND * |q| |k| * scale. Operands cut to TF32 are each off by less
+// than 2^-10 of themselves, so a product by less than 2^-8.99 of its size, and the sum of the 128
+// sizes is at most |q| |k|; the FP32 accumulation, the 16-bit cosine (2^-16) and the rounding of
+// the exact evaluation itself add less than 2^-13 together. 2^-8 leaves a factor of 1.8.
+constexpr float BOUND = 0.00390625f;
+enum Fate : uint8_t { DROPPED = 0, KEPT = 1, OPEN = 2 };
+
+__device__ __forceinline__ uint32_t order_preserving(float value) {
+    const uint32_t bits = __float_as_uint(value);
+    return bits ^ ((bits >> 31) ? 0xffffffffu : 0x80000000u);
+}
+
+__device__ __forceinline__ float warp_sum(float value) {
     #pragma unroll
-    for (int query = 0; query < QUERIES; query++) {
-        if (query < query_count) {
-            workspace.coarse[(first_row + query) * HEAD_DIM + threadIdx.x] =
-                outputs[query] / sums[query];
+    for (int offset = 16; offset > 0; offset /= 2) {
+        value += __shfl_xor_sync(0xffffffffu, value, offset);
+    }
+    return value;
+}
+
+// The pooled scores of BATCH tiles in the reference's FP32 order, by a whole warp: lane l holds
+// dimensions l, l + 32, l + 64, l + 96 of the query and reads the same of each key (coalesced
+// loads, all BATCH tiles' in flight together: a route's open tiles are scattered over a head's
+// megabyte of means, and one tile at a time would wait for L2 a hundred times a row), chains four
+// fused multiply-adds from zero, and the xor butterfly from bit 4 down to bit 0 adds the 32 chains
+// in the reference's tree (an addition commutes, so every lane ends with the same bits).
+template <int BATCH>
+__device__ __forceinline__ void exact_scores(const float (&query)[4],
+                                             const float *__restrict__ head_keys,
+                                             const uint16_t *tiles, int count, int lane,
+                                             float scale, float (&scores)[BATCH]) {
+    float loaded[BATCH][4];
+    #pragma unroll
+    for (int index = 0; index < BATCH; index++) {
+        const float *key =
+            head_keys + static_cast<size_t>(tiles[index < count ? index : 0]) * HEAD_DIM + lane;
+        #pragma unroll
+        for (int part = 0; part < 4; part++) {
+            loaded[index][part] = __ldg(key + part * 32);
+        }
+    }
+    #pragma unroll
+    for (int index = 0; index < BATCH; index++) {
+        float chain = 0.0f;
+        #pragma unroll
+        for (int part = 0; part < 4; part++) {
+            chain = __fmaf_rn(query[part], loaded[index][part], chain);
+        }
+        scores[index] = chain;
+    }
+    #pragma unroll
+    for (int offset = 16; offset > 0; offset /= 2) {
+        #pragma unroll
+        for (int index = 0; index < BATCH; index++) {
+            scores[index] =
+                __fadd_rn(scores[index], __shfl_xor_sync(0xffffffffu, scores[index], offset));
+        }
+    }
+    #pragma unroll
+    for (int index = 0; index < BATCH; index++) {
+        scores[index] = __fmul_rn(scores[index], scale);
+    }
+}
+
+// Among the `count` tiles listed in `list`, whose exact scores are in `values`: the order-preserving
+// bits of the `wanted`-th largest score, and how many of the tiles equal to it belong to the
+// `wanted` largest. One byte of the bits at a time from the top; `bins` is 256 counters.
+__device__ __forceinline__ void select_among(const uint16_t *list, int count, const float *values,
+                                             int wanted, int *bins, int lane, uint32_t &threshold,
+                                             int &ties) {
+    uint32_t settled = 0;
+    threshold = 0;
+    ties = wanted;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int bin = lane; bin < 256; bin += 32) {
+            bins[bin] = 0;
+        }
+        __syncwarp();
+        for (int first = 0; first < count; first += 32) {
+            const int index = first + lane;
+            const uint32_t bits = index < count ? order_preserving(values[list[index]]) : 0;
+            const bool counted = index < count && (bits & settled) == threshold;
+            // Equal scores crowd into one counter: the lanes that share one add their number once.
+            const uint32_t digit = counted ? (bits >> shift) & 255u : 256u;
+            const unsigned same = __match_any_sync(0xffffffffu, digit);
+            if (counted && lane == __ffs(same) - 1) {
+                bins[digit] += __popc(same);
+            }
+            __syncwarp();
+        }
+        // Lane l looks after counters 255 - 8 l down to 248 - 8 l, so that lane order is score
+        // order; `before` is how many candidates sit in counters above this lane's.
+        int own[8];
+        int total = 0;
+        #pragma unroll
+        for (int index = 0; index < 8; index++) {
+            own[index] = bins[255 - (lane * 8 + index)];
+            total += own[index];
+        }
+        int before = total;
+        #pragma unroll
+        for (int offset = 1; offset < 32; offset *= 2) {
+            const int other = __shfl_up_sync(0xffffffffu, before, offset);
+            if (lane >= offset) {
+                before += other;
+            }
+        }
+        before -= total;
+        int digit = -1, passed = 0;
+        #pragma unroll
+        for (int index = 0; index < 8; index++) {
+            if (digit < 0 && before + own[index] >= ties) {
+                digit = 255 - (lane * 8 + index);
+                passed = before;
+            }
+            before += own[index];
+        }
+        const int holder = __ffs(__ballot_sync(0xffffffffu, digit >= 0)) - 1;
+        digit = __shfl_sync(0xffffffffu, digit, max(holder, 0));
+        passed = __shfl_sync(0xffffffffu, passed, max(holder, 0));
+        ties -= passed;
+        threshold |= static_cast<uint32_t>(digit & 255) << shift;
+        settled |= 255u << shift;
+        __syncwarp();
+    }
+}
+
+__global__ void __launch_bounds__(ROUTE_THREADS, 3)
+    route_kernel(Mmh3VsaWorkspace workspace, int tiles, int prefix_tiles, int kept, float scale) {
+    // [tiles] key norms, then per warp: [tiles] scores, [BINS] counters, [tiles] tile numbers,
+    // [tiles] fates.
+    extern __shared__ __align__(16) uint8_t route_memory[];
+    const int lane = threadIdx.x % 32;
+    const int warp = threadIdx.x / 32;
+    const int head = blockIdx.y;
+    const int padded = (tiles + 3) & ~3;
+    float *key_norms = reinterpret_cast<float *>(route_memory);
+    uint8_t *mine = route_memory + padded * 4 + static_cast<size_t>(warp) * (padded * 7 + BINS * 4);
+    float *values = reinterpret_cast<float *>(mine);
+    int *bins = reinterpret_cast<int *>(mine + padded * 4);
+    uint16_t *list = reinterpret_cast<uint16_t *>(mine + padded * 4 + BINS * 4);
+    uint8_t *fates = mine + padded * 6 + BINS * 4;
+    __shared__ float warp_maxima[ROUTE_WARPS];
+
+    const float *head_keys = workspace.pooled_key + static_cast<size_t>(head) * tiles * HEAD_DIM;
+    const int video_tiles = tiles - prefix_tiles;
+
+    // The norms of this head's key means, a warp to a tile and eight tiles' loads in flight,
+    // and the largest of them.
+    float largest = 0.0f;
+    for (int first = warp * 8; first < tiles; first += ROUTE_WARPS * 8) {
+        float4 loaded[8];
+        #pragma unroll
+        for (int index = 0; index < 8; index++) {
+            const int tile = min(first + index, tiles - 1);
+            loaded[index] = __ldg(
+                reinterpret_cast<const float4 *>(head_keys + static_cast<size_t>(tile) * HEAD_DIM) +
+                lane);
+        }
+        float squares[8];
+        #pragma unroll
+        for (int index = 0; index < 8; index++) {
+            const float4 four = loaded[index];
+            squares[index] =
+                fmaf(four.x, four.x, fmaf(four.y, four.y, fmaf(four.z, four.z, four.w * four.w)));
+        }
+        #pragma unroll
+        for (int offset = 16; offset > 0; offset /= 2) {
+            #pragma unroll
+            for (int index = 0; index < 8; index++) {
+                squares[index] += __shfl_xor_sync(0xffffffffu, squares[index], offset);
+            }
+        }
+        #pragma unroll
+        for (int index = 0; index < 8; index++) {
+            const float norm = sqrtf(squares[index]);
+            if (lane == index && first + index < tiles) {
+                key_norms[first + index] = norm;
+            }
+            largest = fmaxf(largest, norm);
+        }
+    }
+    if (lane == 0) {
+        warp_maxima[warp] = largest;
+    }
+    __syncthreads();
+    largest = fmaxf(fmaxf(warp_maxima[0], warp_maxima[1]), fmaxf(warp_maxima[2], warp_maxima[3]));
+
+    // The CTAs of a head share its query tiles round robin, a warp to a tile.
+    for (int query_tile = blockIdx.x * ROUTE_WARPS + warp; query_tile < tiles;
+         query_tile += gridDim.x * ROUTE_WARPS) {
+        const size_t row = static_cast<size_t>(head) * tiles + query_tile;
+        uint16_t *route = workspace.routes + row * tiles;
+        if (query_tile < prefix_tiles || kept >= video_tiles) {
+            // Every tile, in order.
+            for (int tile = lane; tile < tiles; tile += 32) {
+                route[tile] = static_cast<uint16_t>(tile);
+            }
+            if (lane == 0) {
+                workspace.route_counts[row] = tiles;
+            }
+            continue;
+        }
+        float query[4];
+        float square = 0.0f;
+        #pragma unroll
+        for (int part = 0; part < 4; part++) {
+            query[part] = __ldg(workspace.pooled_query + row * HEAD_DIM + lane + part * 32);
+            square = fmaf(query[part], query[part], square);
+        }
+        const float query_norm = sqrtf(warp_sum(square));
+        const float unit = query_norm * scale / COSINE_ONE;
+        const float bound = BOUND * query_norm * largest * scale;
+
+        // The approximate scores of the video tiles, counted into BINS equal steps down from the
+        // largest value a score of this row can have.
+        const float reach = query_norm * largest * scale;
+        const float step = 2.0f * reach / BINS;
+        float keep_above = FLT_MAX, drop_below = -FLT_MAX;
+        const bool binned = step > 0.0f && step < FLT_MAX;
+        if (binned) {
+            const float steps_per_unit = 1.0f / step;
+            for (int bin = lane; bin < BINS; bin += 32) {
+                bins[bin] = 0;
+            }
+            __syncwarp();
+            // Eight of a lane's cosines are read before any is used: the row comes from L2.
+            for (int first = prefix_tiles + lane; first < tiles; first += 8 * 32) {
+                uint16_t cosines[8];
+                #pragma unroll
+                for (int index = 0; index < 8; index++) {
+                    const int tile = first + index * 32;
+                    cosines[index] = tile < tiles ? route[tile] : 0;
+                }
+                #pragma unroll
+                for (int index = 0; index < 8; index++) {
+                    const int tile = first + index * 32;
+                    if (tile < tiles) {
+                        const float value = static_cast<float>(static_cast<int16_t>(cosines[index])) *
+                                            (unit * key_norms[tile]);
+                        values[tile] = value;
+                        const int bin = static_cast<int>((reach - value) * steps_per_unit);
+                        atomicAdd(&bins[min(max(bin, 0), BINS - 1)], 1);
+                    }
+                }
+            }
+            __syncwarp();
+            // Which bin holds the kept-th largest: lane l owns bins 16 l .. 16 l + 15, and
+            // `before` counts the scores in the bins above its own.
+            int total = 0;
+            for (int index = 0; index < BINS / 32; index++) {
+                total += bins[lane * (BINS / 32) + index];
+            }
+            int before = total;
+            #pragma unroll
+            for (int offset = 1; offset < 32; offset *= 2) {
+                const int other = __shfl_up_sync(0xffffffffu, before, offset);
+                if (lane >= offset) {
+                    before += other;
+                }
+            }
+            before -= total;
+            int found = -1;
+            for (int index = 0; index < BINS / 32; index++) {
+                const int held = bins[lane * (BINS / 32) + index];
+                if (found < 0 && before + held >= kept) {
+                    found = lane * (BINS / 32) + index;
+                }
+                before += held;
+            }
+            const int holder = __ffs(__ballot_sync(0xffffffffu, found >= 0)) - 1;
+            found = __shfl_sync(0xffffffffu, found, max(holder, 0));
+            if (holder >= 0) {
+                // A bin to either side allows for the rounding of the binning itself.
+                keep_above = reach - static_cast<float>(found - 1) * step + 2.0f * bound;
+                drop_below = reach - static_cast<float>(found + 2) * step - 2.0f * bound;
+            }
+            __syncwarp();
+        }
+
+        // Every tile's fate, and the open ones listed in ascending order. Everything is open when
+        // the scores could not be binned or the counts do not add up.
+        int certain = 0, listed = 0;
+        for (int first = prefix_tiles; first < tiles; first += 32) {
+            const int tile = first + lane;
+            uint8_t fate = DROPPED;
+            if (tile < tiles) {
+                const float value = binned ? values[tile] : 0.0f;
+                fate = value > keep_above ? KEPT : (value < drop_below ? DROPPED : OPEN);
+                fates[tile] = fate;
+            }
+            certain += __popc(__ballot_sync(0xffffffffu, fate == KEPT));
+            const unsigned open_mask = __ballot_sync(0xffffffffu, tile < tiles && fate == OPEN);
+            if (tile < tiles && fate == OPEN) {
+                list[listed + __popc(open_mask & ((1u << lane) - 1))] = static_cast<uint16_t>(tile);
+            }
+            listed += __popc(open_mask);
+        }
+        if (kept - certain < 1 || kept - certain > listed) {
+            for (int tile = prefix_tiles + lane; tile < tiles; tile += 32) {
+                fates[tile] = OPEN;
+                list[tile - prefix_tiles] = static_cast<uint16_t>(tile);
+            }
+            certain = 0;
+            listed = video_tiles;
+        }
+        __syncwarp();
+
+        // The open tiles scored exactly, eight at a time.
+        constexpr int BATCH = 8;
+        for (int first = 0; first < listed; first += BATCH) {
+            float scores[BATCH];
+            exact_scores<BATCH>(query, head_keys, list + first, listed - first, lane, scale, scores);
+            #pragma unroll
+            for (int index = 0; index < BATCH; index++) {
+                if (lane == index && first + index < listed) {
+                    values[list[first + index]] = scores[index];
+                }
+            }
+        }
+        __syncwarp();
+        uint32_t threshold;
+        int ties;
+        select_among(list, listed, values, kept - certain, bins, lane, threshold, ties);
+
+        // The prefix tiles, the certain ones, and of the open ones those above the threshold and
+        // the first `ties` at it. The list lands on the cosines it was computed from, which are
+        // all read by now.
+        int count = 0, ties_seen = 0;
+        for (int first = 0; first < tiles; first += 32) {
+            const int tile = first + lane;
+            bool keep = tile < tiles && tile < prefix_tiles;
+            bool tie = false;
+            if (tile < tiles && tile >= prefix_tiles) {
+                const uint8_t fate = fates[tile];
+                if (fate == OPEN) {
+                    const uint32_t bits = order_preserving(values[tile]);
+                    keep = bits > threshold;
+                    tie = bits == threshold;
+                } else {
+                    keep = fate == KEPT;
+                }
+            }
+            const unsigned tie_mask = __ballot_sync(0xffffffffu, tie);
+            if (tie && ties_seen + __popc(tie_mask & ((1u << lane) - 1)) < ties) {
+                keep = true;
+            }
+            ties_seen += __popc(tie_mask);
+            const unsigned keep_mask = __ballot_sync(0xffffffffu, keep);
+            if (keep) {
+                route[count + __popc(keep_mask & ((1u << lane) - 1))] = static_cast<uint16_t>(tile);
+            }
+            count += __popc(keep_mask);
+        }
+        if (lane == 0) {
+            workspace.route_counts[row] = count;
+        }
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 3. The coarse output of a gated layer: softmax over all tiles of the pooled scores, times the
+// tiles' mean values (the workspace holds their sums).
+
+constexpr int COARSE_WARPS = 4;
+constexpr int COARSE_CHUNK = 32;   // tiles staged at a time
+constexpr int COARSE_PITCH = HEAD_DIM + 4;
+
+__global__ void __launch_bounds__(COARSE_WARPS * 32)
+    coarse_kernel(Mmh3VsaWorkspace workspace, int tiles, float scale) {
+    __shared__ __align__(16) float keys[COARSE_CHUNK][COARSE_PITCH];
+    __shared__ __align__(16) float means[COARSE_CHUNK][COARSE_PITCH];
+    __shared__ __align__(16) float queries[COARSE_WARPS][HEAD_DIM];
+    const int lane = threadIdx.x % 32;
+    const int warp = threadIdx.x / 32;
+    const int head = blockIdx.y;
+    const int query_tile = blockIdx.x * COARSE_WARPS + warp;
+    const bool active = query_tile < tiles;
+    const size_t head_rows = static_cast<size_t>(head) * tiles;
+    if (active) {
+        for (int part = 0; part < 4; part++) {
+            queries[warp][lane + part * 32] =
+                workspace.pooled_query[(head_rows + query_tile) * HEAD_DIM + lane + part * 32];
+        }
+    }
+    float maximum = -FLT_MAX, sum = 0.0f;
+    float outputs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int first = 0; first < tiles; first += COARSE_CHUNK) {
+        __syncthreads();
+        // The chunk's key means, and its value sums divided by the tile lengths.
+        for (int index = threadIdx.x; index < COARSE_CHUNK * (HEAD_DIM / 4); index += COARSE_WARPS * 32) {
+            const int tile = first + index / (HEAD_DIM / 4), four = index % (HEAD_DIM / 4);
+            float4 key = make_float4(0.0f, 0.0f, 0.0f, 0.0f), mean = key;
+            if (tile < tiles) {
+                key = __ldg(reinterpret_cast<const float4 *>(workspace.pooled_key +
+                                                             (head_rows + tile) * HEAD_DIM) + four);
+                mean = __ldg(reinterpret_cast<const float4 *>(workspace.pooled_value +
+                                                              (head_rows + tile) * HEAD_DIM) + four);
+                const float inverse = 1.0f / static_cast<float>(workspace.tile_lengths[tile]);
+                mean = make_float4(mean.x * inverse, mean.y * inverse, mean.z * inverse,
+                                   mean.w * inverse);
+            }
+            *reinterpret_cast<float4 *>(&keys[index / (HEAD_DIM / 4)][four * 4]) = key;
+            *reinterpret_cast<float4 *>(&means[index / (HEAD_DIM / 4)][four * 4]) = mean;
+        }
+        __syncthreads();
+        if (!active) {
+            continue;
+        }
+        // Lane l scores tile first + l.
+        float score = 0.0f;
+        #pragma unroll 8
+        for (int four = 0; four < HEAD_DIM / 4; four++) {
+            const float4 key = *reinterpret_cast<const float4 *>(&keys[lane][four * 4]);
+            const float4 query = *reinterpret_cast<const float4 *>(&queries[warp][four * 4]);
+            score = fmaf(key.x, query.x, score);
+            score = fmaf(key.y, query.y, score);
+            score = fmaf(key.z, query.z, score);
+            score = fmaf(key.w, query.w, score);
+        }
+        score = first + lane < tiles ? score * scale : -FLT_MAX;
+        float chunk_maximum = score;
+        #pragma unroll
+        for (int offset = 16; offset > 0; offset /= 2) {
+            chunk_maximum = fmaxf(chunk_maximum, __shfl_xor_sync(0xffffffffu, chunk_maximum, offset));
+        }
+        const float raised = fmaxf(maximum, chunk_maximum);
+        const float correction = expf(maximum - raised);
+        maximum = raised;
+        const float weight = first + lane < tiles ? expf(score - maximum) : 0.0f;
+        sum = sum * correction + warp_sum(weight);
+        #pragma unroll
+        for (int part = 0; part < 4; part++) {
+            outputs[part] *= correction;
+        }
+        // Lane l accumulates dimensions l, l + 32, l + 64, l + 96.
+        #pragma unroll 8
+        for (int tile = 0; tile < COARSE_CHUNK; tile++) {
+            const float shared_weight = __shfl_sync(0xffffffffu, weight, tile);
+            #pragma unroll
+            for (int part = 0; part < 4; part++) {
+                outputs[part] = fmaf(shared_weight, means[tile][lane + part * 32], outputs[part]);
+            }
+        }
+    }
+    if (active) {
+        const float inverse = 1.0f / sum;
+        for (int part = 0; part < 4; part++) {
+            workspace.coarse[(head_rows + query_tile) * HEAD_DIM + lane + part * 32] =
+                outputs[part] * inverse;
         }
     }
 }
 
-template <int QUERIES>
-int launch_queries(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int prefix_tiles,
-                   int kept, float scale, int coarse, cudaStream_t stream) {
-    const size_t shared = static_cast<size_t>(QUERIES) * tiles * sizeof(float);
+size_t route_shared_bytes(int tiles) {
+    const size_t padded = (static_cast<size_t>(tiles) + 3) & ~static_cast<size_t>(3);
+    return padded * 4 + ROUTE_WARPS * (padded * 7 + BINS * 4);
+}
+
+} // namespace
+
+int launch_select(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int prefix_tiles,
+                  int kept, float scale, int coarse, cudaStream_t stream) {
+    // The route kernel keeps a row of scores per warp in shared memory.
+    const size_t shared = route_shared_bytes(tiles);
+    if (shared > 200 * 1024) {
+        return INVALID_VALUE;
+    }
+    unsigned int *status = status_pointer();
+    if (status == nullptr) {
+        return static_cast<int>(cudaErrorInvalidDevice);
+    }
+    const int video_tiles = tiles - prefix_tiles;
+    if (kept < video_tiles) {
+        static SharedMemoryOptIn cosine_memory;
+        const cudaError_t configured = cosine_memory.ensure(cosine_kernel, COSINE_SMEM_BYTES);
+        if (configured != cudaSuccess) {
+            return static_cast<int>(configured);
+        }
+        CosineMaps maps;
+        const uint64_t dimensions[3] = {HEAD_DIM, static_cast<uint64_t>(tiles),
+                                        static_cast<uint64_t>(heads)};
+        const uint64_t strides[2] = {HEAD_DIM * sizeof(float),
+                                     static_cast<uint64_t>(tiles) * HEAD_DIM * sizeof(float)};
+        const uint32_t box[3] = {32, PANEL, 1};
+        if (!encode_tensor_map(&maps.query, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                               workspace.pooled_query, dimensions, strides, box) ||
+            !encode_tensor_map(&maps.key, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, workspace.pooled_key,
+                               dimensions, strides, box)) {
+            return NOT_SUPPORTED;
+        }
+        const int panels = (tiles + PANEL - 1) / PANEL;
+        cosine_kernel<<<dim3(panels, panels, heads), COSINE_THREADS, COSINE_SMEM_BYTES, stream>>>(
+            maps, workspace.routes, tiles, status);
+        const cudaError_t launched = cudaGetLastError();
+        if (launched != cudaSuccess) {
+            return static_cast<int>(launched);
+        }
+    }
     // The opt-in limit only ever grows, and is per device.
     static std::atomic<size_t> configured[MAX_DEVICES];
     const int device = current_device();
@@ -261,41 +741,26 @@ int launch_queries(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int 
         return static_cast<int>(cudaErrorInvalidDevice);
     }
     if (shared > configured[device].load(std::memory_order_relaxed)) {
-        const cudaError_t status =
-            cudaFuncSetAttribute(select_kernel<QUERIES>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(shared));
-        if (status != cudaSuccess) {
-            return static_cast<int>(status);
+        const cudaError_t raised = cudaFuncSetAttribute(
+            route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+        if (raised != cudaSuccess) {
+            return static_cast<int>(raised);
         }
         configured[device].store(shared, std::memory_order_relaxed);
     }
-    select_kernel<QUERIES><<<dim3((tiles + QUERIES - 1) / QUERIES, heads), THREADS, shared,
-                             stream>>>(workspace, tiles, prefix_tiles, kept, scale, coarse);
+    // Every CTA computes its head's key norms once, so there are only as many CTAs as the device
+    // holds at a time (three to an SM), shared out evenly over the heads.
+    const int resident = 3 * multiprocessor_count();
+    const int per_head = std::max(1, std::min((tiles + ROUTE_WARPS - 1) / ROUTE_WARPS, resident / heads));
+    route_kernel<<<dim3(per_head, heads), ROUTE_THREADS, shared, stream>>>(
+        workspace, tiles, prefix_tiles, kept, scale);
+    cudaError_t launched = cudaGetLastError();
+    if (launched != cudaSuccess || !coarse) {
+        return static_cast<int>(launched);
+    }
+    coarse_kernel<<<dim3((tiles + COARSE_WARPS - 1) / COARSE_WARPS, heads), COARSE_WARPS * 32, 0,
+                    stream>>>(workspace, tiles, scale);
     return static_cast<int>(cudaGetLastError());
-}
-
-} // namespace
-
-int launch_select(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int prefix_tiles,
-                  int kept, float scale, int coarse, cudaStream_t stream) {
-    // As many query tiles per CTA as keep its scores within a third of an SM's shared memory
-    // (three CTAs per SM), fewer for very long sequences, down to one.
-    const size_t row = static_cast<size_t>(tiles) * sizeof(float);
-    constexpr size_t SHARE = 66 * 1024, LIMIT = 200 * 1024;
-    if (MAX_QUERIES * row <= SHARE) {
-        return launch_queries<8>(workspace, tiles, heads, prefix_tiles, kept, scale, coarse, stream);
-    }
-    if (4 * row <= SHARE) {
-        return launch_queries<4>(workspace, tiles, heads, prefix_tiles, kept, scale, coarse, stream);
-    }
-    if (2 * row <= SHARE) {
-        return launch_queries<2>(workspace, tiles, heads, prefix_tiles, kept, scale, coarse, stream);
-    }
-    if (row <= LIMIT) {
-        return launch_queries<1>(workspace, tiles, heads, prefix_tiles, kept, scale, coarse, stream);
-    }
-    return INVALID_VALUE;
 }
 
 } // namespace mmh3
