@@ -18,8 +18,17 @@
 //
 // The routes are bit-identical to the reference's. That fixes the FP32 order of everything a route
 // depends on: the block sums run down the rows, the key mean and variance down the blocks, the
-// spread of a query block over a xor butterfly and then over the four warps, and a pooled score
-// over the tree of pooled_score.cuh. The tail sums are free to differ in order and do.
+// spread of a query block over four butterflies of 32 dimensions each that are then added in
+// order, and a pooled score over the tree of pooled_score.cuh. The tail sums are free to differ in
+// order and do.
+//
+// How the routing kernel is cut: a CTA of four warps takes eight query blocks of a head. A warp
+// owns two query blocks' thresholds, route lists and tail statistics; a thread owns a key block while
+// the scores are taken (the key's mean in its registers, against the eight query means in shared
+// memory), and in that same pass decides the block's fate for all eight queries, keeps the eight
+// running maxima of what is not routed, and casts its vote into the bit mask of routed blocks
+// (a ballot is 32 key blocks of one query: one word of the mask). The route lists are expanded
+// from those words, a lane to a word.
 #include <atomic>
 #include <cfloat>
 #include <cmath>
@@ -32,246 +41,307 @@ namespace mmh3 {
 namespace {
 
 constexpr int BLOCK = 64;
-constexpr int THREADS = 128;
-constexpr int WARPS = THREADS / 32;
-constexpr int MAX_QUERIES = 8;
-static_assert(THREADS == HEAD_DIM, "the routing kernels give each thread one dimension");
+constexpr int GROUP = 8;                 // query blocks to a CTA
+constexpr int ROUTE_WARPS = 4;           // each looks after two of them
+constexpr int ROUTE_THREADS = ROUTE_WARPS * 32;
+static_assert(ROUTE_THREADS == HEAD_DIM, "the tail values give each thread one dimension");
 
-__device__ __forceinline__ int block_rows(int block, int tokens) {
+// Tokens in block `block` of a sequence of `tokens`.
+__device__ __forceinline__ int tokens_in(int block, int tokens) {
     return min(BLOCK, tokens - block * BLOCK);
 }
 
-// Sum or maximum over the CTA: a xor butterfly in each warp, then the warps in order.
-__device__ __forceinline__ float cta_reduce(float value, float *scratch, bool maximum) {
-    #pragma unroll
-    for (int offset = 16; offset > 0; offset /= 2) {
-        const float other = __shfl_xor_sync(0xffffffffu, value, offset);
-        value = maximum ? fmaxf(value, other) : __fadd_rn(value, other);
-    }
-    if (threadIdx.x % 32 == 0) {
-        scratch[threadIdx.x / 32] = value;
-    }
-    __syncthreads();
-    float result = scratch[0];
-    for (int warp = 1; warp < WARPS; warp++) {
-        result = maximum ? fmaxf(result, scratch[warp]) : __fadd_rn(result, scratch[warp]);
-    }
-    __syncthreads();
-    return result;
-}
-
-// One CTA per head, one thread per dimension: the mean of the block keys, the centred block keys in
-// place, and their variance. The blocks are walked in order (the sums are order-dependent), eight
-// loads in flight at a time.
-__global__ void __launch_bounds__(THREADS)
+// One warp per 32 dimensions of a head: lane l walks the block keys of dimension d = 32 w + l down
+// the blocks, in order (the sums depend on it), eight rows in flight: their mean, then the keys
+// centred in place and their variance.
+__global__ void __launch_bounds__(32)
     centre_keys_kernel(float *__restrict__ block_keys, int blocks, float *__restrict__ key_mean,
                        float *__restrict__ key_variance) {
-    const int head = blockIdx.x;
-    const int dimension = threadIdx.x;
+    const int head = blockIdx.y;
+    const int dimension = blockIdx.x * 32 + threadIdx.x;
     float *column = block_keys + static_cast<size_t>(head) * blocks * HEAD_DIM + dimension;
-    constexpr int BATCH = 8;
+    constexpr int ROWS = 8;
     float total = 0.0f;
-    for (int first = 0; first < blocks; first += BATCH) {
-        float loaded[BATCH];
+    for (int first = 0; first < blocks; first += ROWS) {
+        float rows[ROWS];
         #pragma unroll
-        for (int index = 0; index < BATCH; index++) {
-            loaded[index] =
-                first + index < blocks ? column[static_cast<size_t>(first + index) * HEAD_DIM] : 0.0f;
+        for (int index = 0; index < ROWS; index++) {
+            rows[index] = column[static_cast<size_t>(min(first + index, blocks - 1)) * HEAD_DIM];
         }
         #pragma unroll
-        for (int index = 0; index < BATCH; index++) {
-            if (first + index < blocks) {
-                total = __fadd_rn(total, loaded[index]);
-            }
+        for (int index = 0; index < ROWS; index++) {
+            total = first + index < blocks ? __fadd_rn(total, rows[index]) : total;
         }
     }
-    const float count = static_cast<float>(blocks);
-    const float mean = __fdiv_rn(total, count);
+    const float mean = __fdiv_rn(total, static_cast<float>(blocks));
     float squares = 0.0f;
-    for (int first = 0; first < blocks; first += BATCH) {
-        float loaded[BATCH];
+    for (int first = 0; first < blocks; first += ROWS) {
+        float rows[ROWS];
         #pragma unroll
-        for (int index = 0; index < BATCH; index++) {
-            loaded[index] =
-                first + index < blocks ? column[static_cast<size_t>(first + index) * HEAD_DIM] : 0.0f;
+        for (int index = 0; index < ROWS; index++) {
+            rows[index] = column[static_cast<size_t>(min(first + index, blocks - 1)) * HEAD_DIM];
         }
         #pragma unroll
-        for (int index = 0; index < BATCH; index++) {
+        for (int index = 0; index < ROWS; index++) {
             if (first + index < blocks) {
-                const float centred = __fsub_rn(loaded[index], mean);
+                const float centred = __fsub_rn(rows[index], mean);
                 column[static_cast<size_t>(first + index) * HEAD_DIM] = centred;
                 squares = __fmaf_rn(centred, centred, squares);
             }
         }
     }
     key_mean[head * HEAD_DIM + dimension] = mean;
-    key_variance[head * HEAD_DIM + dimension] = __fdiv_rn(squares, count);
+    key_variance[head * HEAD_DIM + dimension] = __fdiv_rn(squares, static_cast<float>(blocks));
 }
 
-// One CTA takes QUERIES consecutive query blocks of one head. A thread holds one centred block key
-// in registers and scores it against each of the CTA's centroids, which sit in shared memory; then
-// the next key block, 128 further on.
-template <int QUERIES>
-__global__ void __launch_bounds__(THREADS, 3)
+// Shared memory of the routing kernel, after the dynamic [blocks][GROUP] scores.
+struct RouteShared {
+    float4 query_means[GROUP][32];
+    float thresholds[GROUP];
+    float running[GROUP][ROUTE_THREADS]; // each thread's running maxima of the unrouted scores
+    float maxima[ROUTE_WARPS][GROUP];    // [warp][query]: each warp's share of those maxima
+    float sums[ROUTE_WARPS][GROUP];
+};
+
+__global__ void __launch_bounds__(ROUTE_THREADS, 3)
     route_kernel(Mmh3SparseWorkspace workspace, int tokens, int blocks, float tau, float log2_scale,
                  int sink_key_start, int sink_key_end, int sink_query_start, int sink_query_end) {
-    extern __shared__ __align__(16) float weights[]; // [blocks][QUERIES], scores at first
-    uint8_t *routed = reinterpret_cast<uint8_t *>(weights + static_cast<size_t>(QUERIES) * blocks);
-    __shared__ float4 centroids[QUERIES][32];
-    __shared__ float thresholds[QUERIES];
-    __shared__ float tail_maxima[QUERIES];
-    __shared__ float tail_sums[QUERIES];
-    __shared__ float scratch[WARPS];
-    const int first_query = blockIdx.x * QUERIES;
-    const int queries = min(QUERIES, blocks - first_query);
-    const int head = blockIdx.y;
+    // [blocks][GROUP] scores, later weights; then [GROUP][words] masks of routed key blocks.
+    extern __shared__ __align__(16) float scores[];
+    const int words = (blocks + 31) / 32;
+    uint32_t *masks = reinterpret_cast<uint32_t *>(scores + static_cast<size_t>(blocks) * GROUP);
+    __shared__ RouteShared shared;
     const int lane = threadIdx.x % 32;
     const int warp = threadIdx.x / 32;
-    const size_t first_row = static_cast<size_t>(head) * blocks + first_query;
+    const int head = blockIdx.y;
+    const int first_query = blockIdx.x * GROUP;
+    const size_t head_rows = static_cast<size_t>(head) * blocks;
 
-    // The centroids, and per query block the threshold: tau standard deviations of its pooled
-    // scores, from the variance of the block keys along each dimension.
-    const float variance = workspace.key_variance[head * HEAD_DIM + threadIdx.x];
-    for (int query = 0; query < queries; query++) {
-        const float centroid = workspace.centroids[(first_row + query) * HEAD_DIM + threadIdx.x];
-        reinterpret_cast<float *>(&centroids[query][0])[threadIdx.x] = centroid;
-        const float spread =
-            cta_reduce(__fmul_rn(__fmul_rn(centroid, centroid), variance), scratch, false);
-        if (threadIdx.x == 0) {
-            thresholds[query] = __fmul_rn(
-                tau, sqrtf(__fmaf_rn(__fmul_rn(spread, log2_scale), log2_scale, 1e-6f)));
+    // This warp's two query means into shared memory, and their thresholds: tau standard
+    // deviations of a query block's pooled scores, from the variance of the block keys along each
+    // dimension. Lane l holds dimensions l, l + 32, l + 64, l + 96; each group of 32 is added over a
+    // butterfly and the four groups then in order, which is the order the reference's 128 threads
+    // add them in.
+    for (int slot = warp; slot < GROUP; slot += ROUTE_WARPS) {
+        const int own_query = first_query + slot;
+        float groups[4];
+        #pragma unroll
+        for (int group = 0; group < 4; group++) {
+            const int dimension = group * 32 + lane;
+            const float mean =
+                own_query < blocks ? workspace.centroids[(head_rows + own_query) * HEAD_DIM + dimension]
+                                   : 0.0f;
+            reinterpret_cast<float *>(&shared.query_means[slot][0])[dimension] = mean;
+            groups[group] = __fmul_rn(__fmul_rn(mean, mean),
+                                      workspace.key_variance[head * HEAD_DIM + dimension]);
         }
-    }
-    __syncthreads();
-
-    const float *head_keys = workspace.block_keys + static_cast<size_t>(head) * blocks * HEAD_DIM;
-    for (int key_block = threadIdx.x; key_block < blocks; key_block += THREADS) {
-        float2 key[HEAD_DIM / 2];
-        load_row(head_keys + static_cast<size_t>(key_block) * HEAD_DIM, key);
-        #pragma unroll 1
-        for (int query = 0; query < queries; query++) {
-            const int query_block = first_query + query;
-            const float score = __fmul_rn(score_tree(centroids[query], key), log2_scale);
-            weights[static_cast<size_t>(key_block) * QUERIES + query] = score;
-            routed[static_cast<size_t>(query) * blocks + key_block] =
-                score > thresholds[query] || abs(query_block - key_block) <= 1 ||
-                (key_block >= sink_key_start && key_block < sink_key_end) ||
-                (query_block >= sink_query_start && query_block < sink_query_end);
-        }
-    }
-    __syncthreads();
-
-    // The tail of each query block: the key blocks it does not route, as softmax weights against
-    // their maximum, each counted once per token it stands for.
-    for (int query = 0; query < queries; query++) {
-        float *query_weights = weights + query; // QUERIES apart
-        const uint8_t *query_routed = routed + static_cast<size_t>(query) * blocks;
-        float maximum = -FLT_MAX;
-        for (int key_block = threadIdx.x; key_block < blocks; key_block += THREADS) {
-            if (!query_routed[key_block]) {
-                maximum = fmaxf(maximum, query_weights[static_cast<size_t>(key_block) * QUERIES]);
+        #pragma unroll
+        for (int offset = 16; offset > 0; offset /= 2) {
+            #pragma unroll
+            for (int group = 0; group < 4; group++) {
+                groups[group] = __fadd_rn(groups[group],
+                                          __shfl_xor_sync(0xffffffffu, groups[group], offset));
             }
         }
-        maximum = cta_reduce(maximum, scratch, true);
-        float sum = 0.0f;
-        for (int key_block = threadIdx.x; key_block < blocks; key_block += THREADS) {
-            const float weight =
-                query_routed[key_block]
-                    ? 0.0f
-                    : exp2f(query_weights[static_cast<size_t>(key_block) * QUERIES] - maximum);
-            query_weights[static_cast<size_t>(key_block) * QUERIES] = weight;
-            sum = fmaf(weight, static_cast<float>(block_rows(key_block, tokens)), sum);
-        }
-        sum = cta_reduce(sum, scratch, false);
-        if (threadIdx.x == 0) {
-            tail_maxima[query] = maximum;
-            tail_sums[query] = sum;
+        const float spread =
+            __fadd_rn(__fadd_rn(__fadd_rn(groups[0], groups[1]), groups[2]), groups[3]);
+        if (lane == 0) {
+            shared.thresholds[slot] =
+                __fmul_rn(tau, sqrtf(__fmaf_rn(__fmul_rn(spread, log2_scale), log2_scale, 1e-6f)));
         }
     }
     __syncthreads();
 
-    // The weighted values of the tails: thread d sums dimension d of the summed values of the key
-    // blocks, which every query block of the CTA weighs its own way.
-    const float *values =
-        workspace.value_sums + static_cast<size_t>(head) * blocks * HEAD_DIM + threadIdx.x;
-    // A key block's weights for the CTA's query blocks lie side by side, so one or two 16-byte
-    // loads bring all of them, and two query blocks share a packed multiply-add. Each sum still
-    // runs over the key blocks in order.
-    float tails[QUERIES] = {};
-    constexpr int BATCH = 16;
-    for (int first = 0; first < blocks; first += BATCH) {
-        float loaded[BATCH];
-        #pragma unroll
-        for (int index = 0; index < BATCH; index++) {
-            loaded[index] =
-                first + index < blocks ? values[static_cast<size_t>(first + index) * HEAD_DIM] : 0.0f;
+    // A thread to a key block: its centred mean in registers against the eight query means, the
+    // fate of the block for each of them, and the running maxima of what stays in the tails.
+    const float *head_keys = workspace.block_keys + head_rows * HEAD_DIM;
+    // The running maxima live in shared memory: the key's mean takes the registers.
+    #pragma unroll
+    for (int query = 0; query < GROUP; query++) {
+        shared.running[query][threadIdx.x] = -FLT_MAX;
+    }
+    for (int first = 0; first < blocks; first += ROUTE_THREADS) {
+        const int key_block = first + threadIdx.x;
+        const bool present = key_block < blocks;
+        float2 key[HEAD_DIM / 2];
+        if (present) {
+            load_row(head_keys + static_cast<size_t>(key_block) * HEAD_DIM, key);
         }
+        const bool key_sink = key_block >= sink_key_start && key_block < sink_key_end;
+        #pragma unroll 1
+        for (int query = 0; query < GROUP; query++) {
+            const int query_block = first_query + query;
+            bool routed = false;
+            if (present) {
+                const float score =
+                    __fmul_rn(score_tree(shared.query_means[query], key), log2_scale);
+                scores[static_cast<size_t>(key_block) * GROUP + query] = score;
+                routed = score > shared.thresholds[query] || key_sink ||
+                         (key_block >= query_block - 1 && key_block <= query_block + 1) ||
+                         (query_block >= sink_query_start && query_block < sink_query_end);
+                if (!routed) {
+                    shared.running[query][threadIdx.x] =
+                        fmaxf(shared.running[query][threadIdx.x], score);
+                }
+            }
+            // 32 consecutive key blocks of one query block: one word of its mask.
+            const unsigned word = __ballot_sync(0xffffffffu, routed);
+            if (lane == 0 && first + warp * 32 < blocks) {
+                masks[query * words + first / 32 + warp] = word;
+            }
+        }
+    }
+    float maxima[GROUP];
+    #pragma unroll
+    for (int query = 0; query < GROUP; query++) {
+        float maximum = shared.running[query][threadIdx.x];
         #pragma unroll
-        for (int index = 0; index < BATCH; index++) {
-            if (first + index < blocks) {
-                // Routed blocks have weight zero; query blocks past the last one are not stored.
-                const float *block_weights = weights + static_cast<size_t>(first + index) * QUERIES;
-                if constexpr (QUERIES % 4 == 0) {
-                    const float2 value = make_float2(loaded[index], loaded[index]);
+        for (int offset = 16; offset > 0; offset /= 2) {
+            maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, offset));
+        }
+        if (lane == 0) {
+            shared.maxima[warp][query] = maximum;
+        }
+    }
+    __syncthreads();
+    #pragma unroll
+    for (int query = 0; query < GROUP; query++) {
+        float maximum = shared.maxima[0][query];
+        #pragma unroll
+        for (int other = 1; other < ROUTE_WARPS; other++) {
+            maximum = fmaxf(maximum, shared.maxima[other][query]);
+        }
+        maxima[query] = maximum;
+    }
+
+    // The tails: what is not routed, as softmax weights against its maximum, each key block
+    // counted once per token it stands for. The weights replace the scores.
+    float sums[GROUP];
+    #pragma unroll
+    for (int query = 0; query < GROUP; query++) {
+        sums[query] = 0.0f;
+    }
+    for (int key_block = threadIdx.x; key_block < blocks; key_block += ROUTE_THREADS) {
+        const float length = static_cast<float>(tokens_in(key_block, tokens));
+        float *row = scores + static_cast<size_t>(key_block) * GROUP;
+        #pragma unroll
+        for (int query = 0; query < GROUP; query++) {
+            const bool routed = (masks[query * words + key_block / 32] >> (key_block % 32)) & 1u;
+            const float weight = routed ? 0.0f : exp2f(row[query] - maxima[query]);
+            row[query] = weight;
+            sums[query] = fmaf(weight, length, sums[query]);
+        }
+    }
+    #pragma unroll
+    for (int query = 0; query < GROUP; query++) {
+        float sum = sums[query];
+        #pragma unroll
+        for (int offset = 16; offset > 0; offset /= 2) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+        }
+        if (lane == 0) {
+            shared.sums[warp][query] = sum;
+        }
+    }
+    __syncthreads();
+
+    // The weighted values of the tails: thread d sums dimension d of the summed values over the key
+    // blocks, which each of the eight query blocks weighs its own way (a key block's eight weights
+    // lie side by side: two 16-byte loads, and two query blocks to a packed multiply-add). Routed
+    // blocks have weight zero.
+    {
+        const float *values = workspace.value_sums + head_rows * HEAD_DIM + threadIdx.x;
+        float2 tails[GROUP / 2];
+        #pragma unroll
+        for (int pair = 0; pair < GROUP / 2; pair++) {
+            tails[pair] = make_float2(0.0f, 0.0f);
+        }
+        constexpr int ROWS = 16;
+        for (int first = 0; first < blocks; first += ROWS) {
+            float rows[ROWS];
+            #pragma unroll
+            for (int index = 0; index < ROWS; index++) {
+                rows[index] = first + index < blocks
+                                  ? __ldg(values + static_cast<size_t>(first + index) * HEAD_DIM)
+                                  : 0.0f;
+            }
+            #pragma unroll
+            for (int index = 0; index < ROWS; index++) {
+                if (first + index < blocks) {
+                    const float4 *weights = reinterpret_cast<const float4 *>(
+                        scores + static_cast<size_t>(first + index) * GROUP);
+                    const float2 value = make_float2(rows[index], rows[index]);
                     #pragma unroll
-                    for (int four = 0; four < QUERIES / 4; four++) {
-                        const float4 weight = reinterpret_cast<const float4 *>(block_weights)[four];
-                        const float2 low = __ffma2_rn(make_float2(weight.x, weight.y), value,
-                                                      make_float2(tails[four * 4],
-                                                                  tails[four * 4 + 1]));
-                        const float2 high = __ffma2_rn(make_float2(weight.z, weight.w), value,
-                                                       make_float2(tails[four * 4 + 2],
-                                                                   tails[four * 4 + 3]));
-                        tails[four * 4] = low.x;
-                        tails[four * 4 + 1] = low.y;
-                        tails[four * 4 + 2] = high.x;
-                        tails[four * 4 + 3] = high.y;
-                    }
-                } else {
-                    #pragma unroll
-                    for (int query = 0; query < QUERIES; query++) {
-                        tails[query] = fmaf(block_weights[query], loaded[index], tails[query]);
+                    for (int four = 0; four < GROUP / 4; four++) {
+                        const float4 weight = weights[four];
+                        tails[four * 2] =
+                            __ffma2_rn(make_float2(weight.x, weight.y), value, tails[four * 2]);
+                        tails[four * 2 + 1] =
+                            __ffma2_rn(make_float2(weight.z, weight.w), value, tails[four * 2 + 1]);
                     }
                 }
             }
         }
-    }
-    #pragma unroll
-    for (int query = 0; query < QUERIES; query++) {
-        if (query < queries) {
-            workspace.tail_values[(first_row + query) * HEAD_DIM + threadIdx.x] = tails[query];
+        #pragma unroll
+        for (int query = 0; query < GROUP; query++) {
+            if (first_query + query < blocks) {
+                workspace.tail_values[(head_rows + first_query + query) * HEAD_DIM + threadIdx.x] =
+                    query % 2 == 0 ? tails[query / 2].x : tails[query / 2].y;
+            }
         }
     }
 
-    // The routes: ascending key blocks, one warp per query block.
-    for (int query = warp; query < queries; query += WARPS) {
-        const size_t row = first_row + query;
+    // The routes of this warp's query blocks: the set bits of a mask in ascending order, a lane to
+    // a word.
+    for (int slot = warp; slot < GROUP && first_query + slot < blocks; slot += ROUTE_WARPS) {
+        const size_t row = head_rows + first_query + slot;
         uint16_t *route = workspace.routes + row * blocks;
-        const uint8_t *query_routed = routed + static_cast<size_t>(query) * blocks;
-        int count = 0;
-        for (int first = 0; first < blocks; first += 32) {
-            const int key_block = first + lane;
-            const bool flag = key_block < blocks && query_routed[key_block];
-            const unsigned mask = __ballot_sync(0xffffffffu, flag);
-            if (flag) {
-                route[count + __popc(mask & ((1u << lane) - 1u))] = static_cast<uint16_t>(key_block);
+        const uint32_t *mask = masks + slot * words;
+        int written = 0;
+        for (int first = 0; first < words; first += 32) {
+            const int index = first + lane;
+            uint32_t word = index < words ? mask[index] : 0u;
+            // How many key blocks the words before this lane's hold.
+            const int own = __popc(word);
+            int before = own;
+            #pragma unroll
+            for (int offset = 1; offset < 32; offset *= 2) {
+                const int other = __shfl_up_sync(0xffffffffu, before, offset);
+                if (lane >= offset) {
+                    before += other;
+                }
             }
-            count += __popc(mask);
+            const int total = __shfl_sync(0xffffffffu, before, 31);
+            int position = written + before - own;
+            while (word != 0) {
+                const int bit = __ffs(word) - 1;
+                word &= word - 1;
+                route[position++] = static_cast<uint16_t>(index * 32 + bit);
+            }
+            written += total;
         }
         if (lane == 0) {
-            workspace.route_counts[row] = count;
-            workspace.tail_max[row] = tail_maxima[query];
-            workspace.tail_sum[row] = tail_sums[query];
+            float sum = shared.sums[0][slot], maximum = shared.maxima[0][slot];
+            for (int other = 1; other < ROUTE_WARPS; other++) {
+                sum += shared.sums[other][slot];
+                maximum = fmaxf(maximum, shared.maxima[other][slot]);
+            }
+            workspace.route_counts[row] = written;
+            workspace.tail_max[row] = maximum;
+            workspace.tail_sum[row] = sum;
         }
     }
 }
 
-template <int QUERIES>
-int launch_queries(const Mmh3SparseWorkspace &workspace, int tokens, int blocks, int heads,
-                   float tau, float log2_scale, int sink_key_start, int sink_key_end,
-                   int sink_query_start, int sink_query_end, cudaStream_t stream) {
-    // Scores and flags of the CTA's query blocks against every key block.
-    const size_t shared = static_cast<size_t>(QUERIES) * blocks * (sizeof(float) + 1);
+int launch_route(const Mmh3SparseWorkspace &workspace, int tokens, int blocks, int heads, float tau,
+                 float log2_scale, int sink_key_start, int sink_key_end, int sink_query_start,
+                 int sink_query_end, cudaStream_t stream) {
+    // Eight scores and eight mask bits per key block.
+    const size_t shared = static_cast<size_t>(blocks) * GROUP * sizeof(float) +
+                          static_cast<size_t>(GROUP) * ((blocks + 31) / 32) * sizeof(uint32_t);
+    if (shared > 200 * 1024) {
+        return INVALID_VALUE;
+    }
     // The opt-in limit only ever grows, and is per device.
     static std::atomic<size_t> configured[MAX_DEVICES];
     const int device = current_device();
@@ -279,74 +349,49 @@ int launch_queries(const Mmh3SparseWorkspace &workspace, int tokens, int blocks,
         return static_cast<int>(cudaErrorInvalidDevice);
     }
     if (shared > configured[device].load(std::memory_order_relaxed)) {
-        const cudaError_t status =
-            cudaFuncSetAttribute(route_kernel<QUERIES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(shared));
-        if (status != cudaSuccess) {
-            return static_cast<int>(status);
+        const cudaError_t raised = cudaFuncSetAttribute(
+            route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+        if (raised != cudaSuccess) {
+            return static_cast<int>(raised);
         }
         configured[device].store(shared, std::memory_order_relaxed);
     }
-    const dim3 grid((blocks + QUERIES - 1) / QUERIES, heads);
-    route_kernel<QUERIES><<<grid, THREADS, shared, stream>>>(
+    route_kernel<<<dim3((blocks + GROUP - 1) / GROUP, heads), ROUTE_THREADS, shared, stream>>>(
         workspace, tokens, blocks, tau, log2_scale, sink_key_start, sink_key_end, sink_query_start,
         sink_query_end);
     return static_cast<int>(cudaGetLastError());
 }
 
-// As many query blocks per CTA as keep its scores and flags within a third of an SM's shared
-// memory (three CTAs per SM), fewer for very long sequences, down to one.
-int launch_route(const Mmh3SparseWorkspace &workspace, int tokens, int blocks, int heads, float tau,
-                 float log2_scale, int sink_key_start, int sink_key_end, int sink_query_start,
-                 int sink_query_end, cudaStream_t stream) {
-    const size_t row = static_cast<size_t>(blocks) * (sizeof(float) + 1);
-    constexpr size_t SHARE = 66 * 1024, LIMIT = 200 * 1024;
-#define MMH3_ROUTE(QUERIES)                                                                        \
-    launch_queries<QUERIES>(workspace, tokens, blocks, heads, tau, log2_scale, sink_key_start,    \
-                            sink_key_end, sink_query_start, sink_query_end, stream)
-    if (MAX_QUERIES * row <= SHARE) {
-        return MMH3_ROUTE(8);
-    }
-    if (4 * row <= SHARE) {
-        return MMH3_ROUTE(4);
-    }
-    if (2 * row <= SHARE) {
-        return MMH3_ROUTE(2);
-    }
-    if (row <= LIMIT) {
-        return MMH3_ROUTE(1);
-    }
-#undef MMH3_ROUTE
-    return INVALID_VALUE;
-}
+// q . key mean of every token and head, in the units of the exponent: what moves a row's
+// token-level scores into the centred units of the pooled ones. A warp keeps a head's key mean in
+// registers (lane l dimensions 4 l .. 4 l + 3) and walks tokens with it, one 8-byte load a lane.
+constexpr int OFFSET_WARPS = 8;
+constexpr int OFFSET_TOKENS = 64; // tokens to a warp
 
-// One warp per (token, head): q . key mean in the units of the exponent. Lane l chains dimensions
-// l, l + 32, l + 64, l + 96; the lanes meet over a xor butterfly.
-__global__ void __launch_bounds__(256)
-    row_offsets_kernel(const __nv_bfloat16 *__restrict__ query, int tokens, int heads,
-                       int64_t token_stride, int64_t head_stride,
-                       const float *__restrict__ key_mean, float log2_scale,
+__global__ void __launch_bounds__(OFFSET_WARPS * 32)
+    row_offsets_kernel(const __nv_bfloat16 *__restrict__ query, int tokens, int64_t token_stride,
+                       int64_t head_stride, const float *__restrict__ key_mean, float log2_scale,
                        float *__restrict__ row_offsets) {
     const int lane = threadIdx.x % 32;
-    const int64_t item = static_cast<int64_t>(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
-    if (item >= static_cast<int64_t>(tokens) * heads) {
-        return;
-    }
-    const int head = static_cast<int>(item % heads);
-    const int64_t token = item / heads;
-    const __nv_bfloat16 *row = query + token * token_stride + head * head_stride;
-    float partial = 0.0f;
-    #pragma unroll
-    for (int part = 0; part < HEAD_DIM / 32; part++) {
-        partial = __fmaf_rn(__bfloat162float(row[lane + part * 32]),
-                            key_mean[head * HEAD_DIM + lane + part * 32], partial);
-    }
-    #pragma unroll
-    for (int offset = 16; offset > 0; offset /= 2) {
-        partial = __fadd_rn(partial, __shfl_xor_sync(0xffffffffu, partial, offset));
-    }
-    if (lane == 0) {
-        row_offsets[static_cast<size_t>(head) * tokens + token] = __fmul_rn(partial, log2_scale);
+    const int head = blockIdx.y;
+    const int first =
+        (blockIdx.x * OFFSET_WARPS + static_cast<int>(threadIdx.x) / 32) * OFFSET_TOKENS;
+    const float4 mean = reinterpret_cast<const float4 *>(key_mean + head * HEAD_DIM)[lane];
+    const __nv_bfloat16 *column = query + head * head_stride + lane * 4;
+    for (int token = first; token < min(first + OFFSET_TOKENS, tokens); token++) {
+        const uint2 four =
+            __ldg(reinterpret_cast<const uint2 *>(column + static_cast<int64_t>(token) * token_stride));
+        float dot = __uint_as_float(four.x << 16) * mean.x;
+        dot = fmaf(__uint_as_float(four.x & 0xffff0000u), mean.y, dot);
+        dot = fmaf(__uint_as_float(four.y << 16), mean.z, dot);
+        dot = fmaf(__uint_as_float(four.y & 0xffff0000u), mean.w, dot);
+        #pragma unroll
+        for (int offset = 16; offset > 0; offset /= 2) {
+            dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+        }
+        if (lane == 0) {
+            row_offsets[static_cast<size_t>(head) * tokens + token] = dot * log2_scale;
+        }
     }
 }
 
@@ -373,17 +418,18 @@ int launch_sparse_attention(const void *query, const void *key, const void *valu
             return pooled;
         }
     }
-    centre_keys_kernel<<<heads, THREADS, 0, stream>>>(workspace.block_keys, blocks,
-                                                      workspace.key_mean, workspace.key_variance);
+    centre_keys_kernel<<<dim3(HEAD_DIM / 32, heads), 32, 0, stream>>>(
+        workspace.block_keys, blocks, workspace.key_mean, workspace.key_variance);
     const int routed = launch_route(workspace, tokens, blocks, heads, tau, log2_scale, sink_key_start,
                                     sink_key_end, sink_query_start, sink_query_end, stream);
     if (routed != 0) {
         return routed;
     }
-    const int64_t items = static_cast<int64_t>(tokens) * heads;
-    row_offsets_kernel<<<static_cast<unsigned>((items + 7) / 8), 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16 *>(query), tokens, heads, layout.token_stride[QUERY],
-        layout.head_stride[QUERY], workspace.key_mean, log2_scale, workspace.row_offsets);
+    const int per_cta = OFFSET_WARPS * OFFSET_TOKENS;
+    row_offsets_kernel<<<dim3((tokens + per_cta - 1) / per_cta, heads), OFFSET_WARPS * 32, 0,
+                         stream>>>(static_cast<const __nv_bfloat16 *>(query), tokens,
+                                   layout.token_stride[QUERY], layout.head_stride[QUERY],
+                                   workspace.key_mean, log2_scale, workspace.row_offsets);
     const cudaError_t launched = cudaGetLastError();
     if (launched != cudaSuccess) {
         return static_cast<int>(launched);
