@@ -782,13 +782,17 @@ def run_sharded(args) -> None:
     import torch.distributed as dist
 
     from mmh3_b200 import attention, synthetic
-    from mmh3_b200.shard import HostUlyssesPipeline, Shard, UlyssesAttention
+    from mmh3_b200.shard import (HostUlyssesPipeline, OverlappedUlyssesAttention, Shard,
+                                 UlyssesAttention)
 
     rank = int(os.environ["RANK"])
     world = int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    # NCCL's kernels on a high-priority stream: an exchange that runs beside an attention launch
+    # takes the next multiprocessors that launch frees instead of waiting for its last block.
+    options = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local), pg_options=options)
     tokens, heads = VIDEO_TOKENS, HEADS
     scale = synthetic.softmax_scale()
     shard = Shard.even(rank, world, tokens, heads, 1)
@@ -817,12 +821,21 @@ def run_sharded(args) -> None:
     output = torch.zeros((len(own), heads, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
     host_output = torch.empty((len(own), heads, HEAD_DIM), dtype=torch.bfloat16, pin_memory=True)
 
+    # The layer goes through a group of heads at a time (two heads of every rank at least): on
+    # resident inputs so that one group's exchanges hide behind another's attention, end to end
+    # so that the copies do too.
+    groups = max(1, min(4, len(shard.own_heads) // 2))
+    overlapped = OverlappedUlyssesAttention(shard, tokens, heads, dense,
+                                            max(1, min(4, len(shard.own_heads))), "cuda",
+                                            torch.bfloat16, pack=attention.shard_pack,
+                                            unpack=attention.shard_unpack)
+
     def step():
+        overlapped.run(qkv, output)
+
+    def plain_step():
         layer.run(qkv, output)
 
-    # End to end the layer goes through a group of heads at a time (two heads of every rank at
-    # least), so that the copies of one group hide behind the exchange and attention of another.
-    groups = max(1, min(4, len(shard.own_heads) // 2))
     pipeline = HostUlyssesPipeline(shard, tokens, heads, dense, groups,
                                    pack=attention.shard_pack, unpack=attention.shard_unpack)
 
@@ -837,21 +850,27 @@ def run_sharded(args) -> None:
     for _ in range(max(1, args.warmup // 2)):
         end_to_end()
     e2e_ms = time_region(torch, end_to_end, args.steps, barrier=dist.barrier)
+    # The same layer with exchange, attention, exchange one after the other over all heads at once:
+    # what the overlap buys, and the same bits.
+    plain_step()
+    plain = output.clone()
+    plain_ms = time_region(torch, plain_step, max(2, args.steps // 2), barrier=dist.barrier)
     # The pipelined layer must leave what the layer over resident inputs leaves.
     step()
     resident = output.clone()
+    agrees_with_plain = float(torch.equal(resident, plain))
     oracle_error, oracle_rows = sharded_oracle_error(torch, resident, checked_qkv, own, tokens,
                                                      scale)
     end_to_end()
     torch.cuda.synchronize()
-    agrees = float(torch.equal(host_output.cuda(), resident))
+    agrees = float(torch.equal(host_output.cuda(), resident)) * agrees_with_plain
     wires = None if args.skip_gemm else sharded_block(torch, dist, attention, args, shard, layer,
                                                       dense, qkv, output, tokens, heads)
     status = attention.take_status()
-    times = torch.tensor([ms, e2e_ms, float(status), -agrees, oracle_error], dtype=torch.float64,
-                         device="cuda")
+    times = torch.tensor([ms, e2e_ms, float(status), -agrees, oracle_error, plain_ms],
+                         dtype=torch.float64, device="cuda")
     dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, e2e_ms, status, disagrees, oracle_error = times.tolist()
+    ms, e2e_ms, status, disagrees, oracle_error, plain_ms = times.tolist()
     if rank == 0:
         flops = attention_flops(tokens, heads)
         peaks, source = measured_peaks()
@@ -864,6 +883,8 @@ def run_sharded(args) -> None:
             "config": workload_config(world, tokens, heads),
             "kernel_status": int(status),
             "exchange_bytes_per_rank": layer.exchange_bytes(),
+            "head_groups": len(overlapped.cuts),
+            "without_overlap_ms": plain_ms,
             # Rows of every rank's share of the sharded layer's output against the f64 CPU oracle
             # over all keys of the layer: the largest error over all ranks, and the bound.
             "oracle_check": {"max_abs_error": oracle_error, "bound": 2e-2,
@@ -874,8 +895,9 @@ def run_sharded(args) -> None:
                     "d2h_bytes_per_step": host_output.numel() * 2 * world,
                     "head_groups": len(pipeline.cuts),
                     "equals_resident_run": disagrees == -1.0},
-            # per rank and step: N packs, the attention kernel, N unpacks (NCCL's kernels aside)
-            "gpu_launches": args.steps * (2 * world + 1),
+            # per rank, step and group of heads: N packs, the attention kernel, N unpacks (NCCL's
+            # kernels aside)
+            "gpu_launches": args.steps * (2 * world + 1) * len(overlapped.cuts),
             "roofline": {"bound": "tensor", "achieved": value, "peak": peaks["bf16_tflops"] * world,
                          "unit": "TFLOP/s", "frac": value / (peaks["bf16_tflops"] * world),
                          "traffic": DENSE_TRAFFIC_PER_TOKEN * tokens * heads / world,

@@ -121,12 +121,18 @@ class UlyssesAttention:
         return elements * self.send_inputs.element_size()
 
     def run(self, qkv_own: torch.Tensor, output_own: torch.Tensor) -> None:
-        shard = self.shard
-        if shard.is_whole:
+        if self.shard.is_whole:
             self.attention(qkv_own, output_own, self.tokens, self.heads)
             return
+        self.exchange_inputs(qkv_own)
+        self.attend()
+        self.exchange_outputs(output_own)
+
+    def exchange_inputs(self, qkv_own: torch.Tensor) -> None:
+        """Turns "my tokens, every head" into "every token, my heads" in `inputs`: every peer's
+        heads of this rank's rows packed, then the all-to-all."""
         offset = 0
-        for peer, heads in enumerate(shard.heads):
+        for peer, heads in enumerate(self.shard.heads):
             count = self.input_send_splits[peer]
             if count:
                 self.pack(qkv_own, self.send_inputs[offset:offset + count], self.own_tokens, 3,
@@ -134,9 +140,11 @@ class UlyssesAttention:
             offset += count
         dist.all_to_all_single(self.inputs, self.send_inputs, self.input_recv_splits,
                                self.input_send_splits, group=self.group)
+
+    def attend(self) -> None:
+        """The attention of every token on this rank's heads, `inputs` to `attended`."""
         if self.own_heads:
             self.attention(self.inputs, self.attended, self.tokens, self.own_heads)
-        self.exchange_outputs(output_own)
 
     def exchange_outputs(self, output_own: torch.Tensor) -> None:
         """Turns "every token, my heads" in `attended` back into "my tokens, every head"
@@ -152,17 +160,97 @@ class UlyssesAttention:
             offset += count
 
 
-def head_groups(shard: Shard, groups: int) -> list[Shard]:
-    """Cuts every rank's heads into `groups` runs: shard g holds the g-th run of each rank. The
-    layer can then go through a group at a time, every rank busy in every group."""
+def group_sizes(count: int, groups: int, ramped: bool = False) -> list[int]:
+    """`count` heads in `groups` runs, as even as they come. `ramped` makes the first and the last
+    run one head each when there are heads enough, for a pipeline whose first way in and last way
+    out nothing hides."""
+    if ramped and groups >= 3 and count >= groups:
+        return [1] + group_sizes(count - 2, groups - 2) + [1]
+    return [count * (group + 1) // groups - count * group // groups for group in range(groups)]
+
+
+def head_groups(shard: Shard, groups: int, ramped: bool = False) -> list[Shard]:
+    """Cuts every rank's heads into `groups` runs (`group_sizes`): shard g holds the g-th run of
+    each rank. The layer can then go through a group at a time, every rank busy in every group."""
+    sizes = [group_sizes(len(owned), groups, ramped) for owned in shard.heads]
     cuts = []
     for group in range(groups):
-        heads = tuple(range(owned.start + len(owned) * group // groups,
-                            owned.start + len(owned) * (group + 1) // groups)
-                      for owned in shard.heads)
+        heads = tuple(range(owned.start + sum(sizes[peer][:group]),
+                            owned.start + sum(sizes[peer][:group + 1]))
+                      for peer, owned in enumerate(shard.heads))
         if any(len(run) for run in heads):
             cuts.append(Shard(shard.rank, shard.tokens, heads))
     return cuts
+
+
+class OverlappedUlyssesAttention:
+    """`UlyssesAttention` a group of heads at a time (`head_groups`), with the exchanges on a
+    stream of their own: while one group is attended, the next group's q, k and v are packed and
+    exchanged and the last group's output goes back and is unpacked. Only the first group's way in
+    and the last group's way out are left outside the attention kernels. The reference overlaps
+    its exchange with the projection of the rank's own rows on a copy stream the same way
+    (crates/mmh3-cuda/src/dit.rs:1416-1604). Every rank issues its collectives in the same order.
+
+    The groups' attention kernels alternate between the caller's stream and a second one, so that
+    the first blocks of one group fill the multiprocessors the last blocks of the group before
+    leave idle: cutting the heads costs no partial wave. The exchange stream has the higher
+    priority, so its gathers and NCCL's blocks (when the process group was made with
+    `is_high_priority_stream`) take the next multiprocessor an attention block leaves rather than
+    queueing behind the whole launch. On CPU ranks there are no streams and the same steps run one
+    after the other."""
+
+    def __init__(self, shard: Shard, total_tokens: int, heads: int, attention: AttentionFn,
+                 groups: int, device, dtype=torch.bfloat16, pack: PackFn | None = None,
+                 unpack: PackFn | None = None, group=None):
+        self.shard = shard
+        self.cuts = [shard] if shard.is_whole else head_groups(shard, groups, ramped=True)
+        self.layers = [UlyssesAttention(cut, total_tokens, heads, attention, device, dtype, pack,
+                                        unpack, group) for cut in self.cuts]
+        self.overlapped = torch.device(device).type == "cuda" and not shard.is_whole
+        if self.overlapped:
+            self.exchange = torch.cuda.Stream(priority=-1)
+            self.second = torch.cuda.Stream()
+            self.arrived = [torch.cuda.Event() for _ in self.cuts]
+            self.attended = [torch.cuda.Event() for _ in self.cuts]
+            self.finished = torch.cuda.Event()
+
+    def exchange_bytes(self) -> int:
+        return sum(layer.exchange_bytes() for layer in self.layers)
+
+    def run(self, qkv_own: torch.Tensor, output_own: torch.Tensor) -> None:
+        if not self.overlapped:
+            for layer in self.layers:
+                layer.run(qkv_own, output_own)
+            return
+        current = torch.cuda.current_stream()
+        self.exchange.wait_stream(current)
+        self.second.wait_stream(current)
+
+        def way_in(index: int) -> None:
+            with torch.cuda.stream(self.exchange):
+                self.layers[index].exchange_inputs(qkv_own)
+                self.arrived[index].record(self.exchange)
+
+        def way_out(index: int) -> None:
+            with torch.cuda.stream(self.exchange):
+                self.exchange.wait_event(self.attended[index])
+                self.layers[index].exchange_outputs(output_own)
+
+        # The exchange stream: in(0), in(1), out(0), in(2), out(1), ...; the two attention
+        # streams: each group once its rows have arrived.
+        way_in(0)
+        for index, layer in enumerate(self.layers):
+            if index + 1 < len(self.layers):
+                way_in(index + 1)
+            stream = self.second if index % 2 else current
+            with torch.cuda.stream(stream):
+                stream.wait_event(self.arrived[index])
+                layer.attend()
+                self.attended[index].record(stream)
+            way_out(index)
+        self.finished.record(self.exchange)
+        current.wait_event(self.finished)
+        current.wait_stream(self.second)
 
 
 class HostUlyssesPipeline:

@@ -14,8 +14,8 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from mmh3_b200.shard import (ProjectedUlyssesAttention, Shard, UlyssesAttention, head_groups,
-                              own_projection_rows)
+from mmh3_b200.shard import (OverlappedUlyssesAttention, ProjectedUlyssesAttention, Shard,
+                              UlyssesAttention, head_groups, own_projection_rows)
 
 HEAD_DIM = 128
 
@@ -54,7 +54,14 @@ def worker(rank, ranks, port, tokens, heads, results):
         for cut in head_groups(shard, 2):
             UlyssesAttention(cut, tokens, heads, torch_attention, "cpu", torch.float32).run(
                 qkv[own.start:own.stop].contiguous(), grouped)
-        results[rank] = max(error, float((grouped - whole[own.start:own.stop]).abs().max()))
+        error = max(error, float((grouped - whole[own.start:own.stop]).abs().max()))
+        # And through the layer that overlaps the groups' exchanges with their attention on a GPU
+        # (on CPU ranks its steps run in the same order, one after the other).
+        overlapped = torch.zeros_like(output)
+        OverlappedUlyssesAttention(shard, tokens, heads, torch_attention, 2, "cpu",
+                                   torch.float32).run(qkv[own.start:own.stop].contiguous(),
+                                                      overlapped)
+        results[rank] = max(error, float((overlapped - whole[own.start:own.stop]).abs().max()))
     finally:
         dist.destroy_process_group()
 
