@@ -1,17 +1,25 @@
 // The passes over q, k and v that come before the attention: per-head RMSNorm and RoPE, INT8 q and
 // k with one scale per head and block, FP8 V transposed, the |v| maxima, and VSA's pooled tiles.
-// One kernel template covers them all. It is bound by HBM bandwidth: every element of q, k and v
-// is read once and each quantized byte written once.
+// One kernel template covers them all. Every element of q, k and v is read once and each quantized
+// byte written once.
 //
 // The results are bit-identical to the reference's (crates/mmh3-cuda/kernels/dit.cu:98-391,
 // quantized_attention.cu:85-241, vsa_attention.cu:68-91), which fixes the order of every FP32
-// operation: the lane-strided sum of squares with its xor butterfly, the row-ordered sums of the
-// pooled tiles, IEEE divisions by the scales, and round-to-nearest-even conversions.
+// operation: the sum of squares as 32 chains over dimensions l, l + 32, l + 64, l + 96 joined by a
+// butterfly over l, the row-ordered sums of the pooled tiles, IEEE divisions by the scales, and
+// round-to-nearest-even conversions.
 //
-// A CTA of 256 threads owns one block of 64 tokens (or one VSA tile of up to 64) of one head. q, k
-// and v take turns in a 16 KiB tile of shared memory; the rows of the next turn are already in
-// flight in registers while the current one is worked on, and four CTAs share an SM.
+// A CTA of 256 threads owns one block of 64 tokens (or one VSA tile of up to 64) of one head at a
+// time. Four threads share a row; thread c of the four holds dimensions 16 G + 4 c + {0, 1, 2, 3}
+// for G = 0 .. 7 and keeps them in registers from the load to the stores. That choice makes eight
+// of the 32 chains whole in one thread (two shuffle rounds join the four threads, the rest of the
+// butterfly is private), and whenever the rotary pairs are a multiple of 16 it puts both
+// dimensions of every pair, and the pair's cosine and sine for the life of the CTA, in one thread
+// too. Shared memory is then only the weights, the block maximum, the transposition of V and the
+// staging of the pooled sums. The rows of the next turn are in flight in registers while one is
+// worked on.
 #include <cuda_fp8.h>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -22,9 +30,19 @@ namespace {
 constexpr int BLOCK_ROWS = 64;
 constexpr int THREADS = 256;
 constexpr int WARPS = THREADS / 32;
-// A row of 128 BF16 values is 16 chunks of 16 bytes.
-constexpr int CHUNKS_PER_THREAD = BLOCK_ROWS * 16 / THREADS;
+// Threads that share a row, and the groups of four neighbouring dimensions each of them holds.
+constexpr int ROW_THREADS = THREADS / BLOCK_ROWS;
+constexpr int GROUPS = HEAD_DIM / (4 * ROW_THREADS);
 constexpr int HEADS_PER_CTA = 8;
+// Strides in shared memory that keep the threads served together in different banks: a staged row
+// is 128 BF16 values of which a thread touches 8 bytes at a time (16 threads, four rows, at once).
+constexpr int STAGED_STRIDE = HEAD_DIM + 16; // BF16 values
+constexpr int EXCHANGE_STRIDE = HEAD_DIM + 4; // floats
+// Adding 1.5 * 2^23 rounds a float below 2^22 in magnitude to the nearest integer, ties to even,
+// and leaves it in two's complement in the low bits of the sum.
+constexpr float ROUNDING_MAGIC = 12582912.0f;
+// How the rotary embedding finds a dimension's partner.
+enum Rotation { NO_ROTATION = 0, IN_THREAD = 1, THROUGH_SHARED_MEMORY = 2 };
 
 struct InputsParams {
     const __nv_bfloat16 *source[3];
@@ -53,7 +71,7 @@ struct InputsParams {
     // The first and the last of the turns q (0), k (1), v (2) to take.
     int first_part;
     int last_part;
-    // Whether rows can be read in 16-byte chunks.
+    // Whether rows can be read in 8-byte pieces.
     int vector_loads;
     // Heads one CTA walks, sharing the cosines and sines of its block's angles.
     int heads_per_cta;
@@ -81,92 +99,202 @@ struct Divider {
         const uint32_t bits = __float_as_uint(divisor);
         exact = (bits & 0x007fffffu) != 0x007fffffu && divisor >= 1e-24f && divisor <= 1e24f;
     }
-    __device__ __forceinline__ float operator()(float x) const {
-        if (exact) {
-            const float quotient = __fmul_rn(x, reciprocal);
-            const float residual = __fmaf_rn(-quotient, scale, x);
-            return __fmaf_rn(residual, reciprocal, quotient);
+    // The quotient where `exact` holds, and where it does not. A caller with many values asks
+    // `exact` once and runs one of two loops.
+    template <bool QUICK> __device__ __forceinline__ float quotient(float x) const {
+        if (QUICK) {
+            const float estimate = __fmul_rn(x, reciprocal);
+            const float residual = __fmaf_rn(-estimate, scale, x);
+            return __fmaf_rn(residual, reciprocal, estimate);
         }
         return __fdiv_rn(x, scale);
     }
+    // `body(std::true_type)` where the quick quotient is right, `body(std::false_type)` otherwise.
+    template <typename Body> __device__ __forceinline__ void dispatch(const Body &body) const {
+        if (exact) {
+            body(std::true_type());
+        } else {
+            body(std::false_type());
+        }
+    }
 };
 
-// RMSNorm of the row `row` of the tile with `weight`, then the split-half rotary embedding of its
-// first 2 * pairs dimensions from the cosines and sines of the row's angles, written back to the
-// tile in BF16. One warp works on the row; lane l holds dimensions l, l + 32, l + 64 and l + 96,
-// which is what the order of the additions in the sum of squares depends on. Returns the largest
-// magnitude this lane wrote.
-__device__ __forceinline__ float normalize_row(__nv_bfloat16 *row, float *scratch,
-                                               const __nv_bfloat16 *__restrict__ weight,
-                                               const float2 *__restrict__ row_trig, int pairs,
-                                               float epsilon) {
-    const int lane = threadIdx.x % 32;
-    float values[4];
-    float squares = 0.0f;
-    #pragma unroll
-    for (int part = 0; part < 4; part++) {
-        values[part] = __bfloat162float(row[lane + part * 32]);
-        squares = __fmaf_rn(values[part], values[part], squares);
-    }
-    #pragma unroll
-    for (int offset = 16; offset > 0; offset /= 2) {
-        squares += __shfl_xor_sync(0xffffffffu, squares, offset);
-    }
-    const float inverse = rsqrtf(__fmaf_rn(squares, 1.0f / HEAD_DIM, epsilon));
-    #pragma unroll
-    for (int part = 0; part < 4; part++) {
-        values[part] = __fmul_rn(
-            values[part], __fmul_rn(inverse, __bfloat162float(weight[lane + part * 32])));
-    }
-    if (row_trig != nullptr) {
-        #pragma unroll
-        for (int part = 0; part < 4; part++) {
-            scratch[lane + part * 32] = values[part];
-        }
-        __syncwarp();
-        for (int pair = lane; pair < pairs; pair += 32) {
-            const float2 trig = row_trig[pair]; // (cosine, sine)
-            const float first = scratch[pair];
-            const float second = scratch[pair + pairs];
-            scratch[pair] = __fmaf_rn(trig.x, first, -__fmul_rn(trig.y, second));
-            scratch[pair + pairs] = __fmaf_rn(trig.y, first, __fmul_rn(trig.x, second));
-        }
-        __syncwarp();
-        #pragma unroll
-        for (int part = 0; part < 4; part++) {
-            values[part] = scratch[lane + part * 32];
-        }
-        __syncwarp();
-    }
-    float maximum = 0.0f;
-    #pragma unroll
-    for (int part = 0; part < 4; part++) {
-        const __nv_bfloat16 rounded = __float2bfloat16_rn(values[part]);
-        row[lane + part * 32] = rounded;
-        maximum = fmaxf(maximum, fabsf(__bfloat162float(rounded)));
-    }
-    return maximum;
+__device__ __forceinline__ float low_half(uint32_t word) { return __uint_as_float(word << 16); }
+__device__ __forceinline__ float high_half(uint32_t word) {
+    return __uint_as_float(word & 0xffff0000u);
 }
 
-__device__ __forceinline__ float chunk_max(const uint4 &chunk) {
-    const uint32_t words[4] = {chunk.x, chunk.y, chunk.z, chunk.w};
-    float maximum = 0.0f;
-    #pragma unroll
-    for (int word = 0; word < 4; word++) {
-        maximum = fmaxf(maximum, fabsf(__uint_as_float(words[word] << 16)));
-        maximum = fmaxf(maximum, fabsf(__uint_as_float(words[word] & 0xffff0000u)));
-    }
-    return maximum;
+// Two floats rounded to BF16, `low` in the low half.
+__device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
+    uint32_t word;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(word) : "f"(high), "f"(low));
+    return word;
 }
 
-// Dynamic shared memory: the cosines and sines of the block's angles, [rows][pairs] float2, computed
-// once per CTA and used by q and k of every head the CTA takes.
+// Two floats to saturating E4M3, `low` in the low byte of the 16 bits.
+__device__ __forceinline__ uint32_t pack_e4m3(float low, float high) {
+    uint16_t pair;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pair) : "f"(high), "f"(low));
+    return pair;
+}
+
+// The integers nearest to four quotients of magnitude at most 127, as four bytes.
+__device__ __forceinline__ uint32_t pack_int8(float a, float b, float c, float d) {
+    const uint32_t first = __byte_perm(__float_as_uint(__fadd_rn(a, ROUNDING_MAGIC)),
+                                       __float_as_uint(__fadd_rn(b, ROUNDING_MAGIC)), 0x0040);
+    const uint32_t second = __byte_perm(__float_as_uint(__fadd_rn(c, ROUNDING_MAGIC)),
+                                        __float_as_uint(__fadd_rn(d, ROUNDING_MAGIC)), 0x0040);
+    return __byte_perm(first, second, 0x5410);
+}
+
+// The largest magnitude among four BF16 values.
+__device__ __forceinline__ float group_max(const uint2 &group) {
+    return fmaxf(fmaxf(fabsf(low_half(group.x)), fabsf(high_half(group.x))),
+                 fmaxf(fabsf(low_half(group.y)), fabsf(high_half(group.y))));
+}
+
+// A thread's share of a row as floats: values[G][i] is dimension 16 G + 4 c + i, c the thread's
+// place among the four of its row.
+struct RowShare {
+    float values[GROUPS][4];
+
+    __device__ __forceinline__ void unpack(const uint2 (&groups)[GROUPS]) {
+        #pragma unroll
+        for (int group = 0; group < GROUPS; group++) {
+            values[group][0] = low_half(groups[group].x);
+            values[group][1] = high_half(groups[group].x);
+            values[group][2] = low_half(groups[group].y);
+            values[group][3] = high_half(groups[group].y);
+        }
+    }
+
+    // The row's sum of squares, the same bits in all four threads of the row. Chain l of the row
+    // runs over dimensions l, l + 32, l + 64, l + 96; with l = 16 h + 4 c + i its four dimensions
+    // are in groups h, h + 2, h + 4, h + 6 of this thread. The butterfly over l goes 16 (h, in
+    // this thread), 8 and 4 (the two bits of c, across the threads of the row), 2 and 1 (the bits
+    // of i, in this thread), and an addition gives both of its sides the same bits, so every
+    // thread ends with the sum any lane of a 32-lane butterfly would hold.
+    __device__ __forceinline__ float sum_of_squares() const {
+        float sums[4];
+        #pragma unroll
+        for (int index = 0; index < 4; index++) {
+            float chains[2];
+            #pragma unroll
+            for (int half = 0; half < 2; half++) {
+                float squares = 0.0f;
+                #pragma unroll
+                for (int step = 0; step < GROUPS / 2; step++) {
+                    const float value = values[2 * step + half][index];
+                    squares = __fmaf_rn(value, value, squares);
+                }
+                chains[half] = squares;
+            }
+            sums[index] = chains[0] + chains[1];
+        }
+        #pragma unroll
+        for (int offset = ROW_THREADS / 2; offset > 0; offset /= 2) {
+            #pragma unroll
+            for (int index = 0; index < 4; index++) {
+                sums[index] += __shfl_xor_sync(0xffffffffu, sums[index], offset);
+            }
+        }
+        return (sums[0] + sums[2]) + (sums[1] + sums[3]);
+    }
+
+    // The largest magnitude among the values.
+    __device__ __forceinline__ float largest() const {
+        float maxima[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        #pragma unroll
+        for (int group = 0; group < GROUPS; group++) {
+            #pragma unroll
+            for (int index = 0; index < 4; index++) {
+                maxima[index] = fmaxf(maxima[index], fabsf(values[group][index]));
+            }
+        }
+        return fmaxf(fmaxf(maxima[0], maxima[1]), fmaxf(maxima[2], maxima[3]));
+    }
+
+    // The values rounded to BF16.
+    __device__ __forceinline__ void pack(uint2 (&groups)[GROUPS]) const {
+        #pragma unroll
+        for (int group = 0; group < GROUPS; group++) {
+            groups[group] = make_uint2(pack_bf16(values[group][0], values[group][1]),
+                                       pack_bf16(values[group][2], values[group][3]));
+        }
+    }
+};
+
+// The cosines and sines of a thread's pairs where pairs are a multiple of 16: pair 16 G + 4 c + i
+// for the first pairs / 16 values of G.
+struct PairAngles {
+    float cosines[GROUPS / 2][4];
+    float sines[GROUPS / 2][4];
+};
+
+// The split-half rotary embedding where dimension d < pairs = 16 * SIXTEENTHS turns with
+// d + pairs: group G with group G + SIXTEENTHS of the same thread.
+template <int SIXTEENTHS>
+__device__ __forceinline__ void rotate_in_thread(RowShare &share, const PairAngles &angles) {
+    #pragma unroll
+    for (int group = 0; group < SIXTEENTHS; group++) {
+        #pragma unroll
+        for (int index = 0; index < 4; index++) {
+            const float cosine = angles.cosines[group][index];
+            const float sine = angles.sines[group][index];
+            const float first = share.values[group][index];
+            const float second = share.values[group + SIXTEENTHS][index];
+            share.values[group][index] = __fmaf_rn(cosine, first, -__fmul_rn(sine, second));
+            share.values[group + SIXTEENTHS][index] =
+                __fmaf_rn(sine, first, __fmul_rn(cosine, second));
+        }
+    }
+}
+
+// The same for any number of pairs: the four threads of the row leave their values in the row's
+// 128 floats of shared memory, `mine`, and find their partners' there; `cosines` and `sines` are
+// those of the row's pairs.
+__device__ __forceinline__ void rotate_through_shared_memory(RowShare &share, float *mine,
+                                                             const float *cosines,
+                                                             const float *sines, int pairs,
+                                                             int place) {
+    #pragma unroll
+    for (int group = 0; group < GROUPS; group++) {
+        *reinterpret_cast<float4 *>(mine + 16 * group + 4 * place) =
+            make_float4(share.values[group][0], share.values[group][1], share.values[group][2],
+                        share.values[group][3]);
+    }
+    __syncwarp();
+    #pragma unroll
+    for (int group = 0; group < GROUPS; group++) {
+        #pragma unroll
+        for (int index = 0; index < 4; index++) {
+            const int dimension = 16 * group + 4 * place + index;
+            float &value = share.values[group][index];
+            if (dimension < pairs) {
+                value = __fmaf_rn(cosines[dimension], value,
+                                  -__fmul_rn(sines[dimension], mine[dimension + pairs]));
+            } else if (dimension < 2 * pairs) {
+                value = __fmaf_rn(sines[dimension - pairs], mine[dimension - pairs],
+                                  __fmul_rn(cosines[dimension - pairs], value));
+            }
+        }
+    }
+    __syncwarp();
+}
+
+// Dynamic shared memory, only where the rotary pairs are not a multiple of 16: the cosines of the
+// block's angles, [64][pairs], then the sines.
 template <bool NORMALIZE, bool STATS, bool QUANTIZE>
-__global__ void __launch_bounds__(THREADS, 4) inputs_kernel(const InputsParams p) {
-    extern __shared__ __align__(16) float2 trig[];
-    __shared__ __align__(16) __nv_bfloat16 tile[BLOCK_ROWS][HEAD_DIM];
-    __shared__ float scratch[WARPS][HEAD_DIM];
-    __shared__ float maxima[WARPS];
+__global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p) {
+    extern __shared__ __align__(16) float trig[];
+    // The rows as BF16 where V is transposed or sums are pooled. The same memory holds rows of 128
+    // floats for the rotary exchange through shared memory; the two uses take turns, a barrier
+    // between them.
+    __shared__ __align__(16) float exchange[BLOCK_ROWS][EXCHANGE_STRIDE];
+    static_assert(BLOCK_ROWS * STAGED_STRIDE * 2 <= sizeof(exchange), "staged rows fit");
+    __shared__ __align__(16) float weights[2][HEAD_DIM];
+    __shared__ __align__(16) float maxima[2][WARPS];
+    static_assert(WARPS == 8, "the block maximum reads eight warp maxima as two float4");
     const int block = blockIdx.x;
     const int blocks = gridDim.x;
     const int first_head = blockIdx.y * p.heads_per_cta;
@@ -178,94 +306,177 @@ __global__ void __launch_bounds__(THREADS, 4) inputs_kernel(const InputsParams p
                          : min(BLOCK_ROWS, p.tokens - block * BLOCK_ROWS);
     const int lane = threadIdx.x % 32;
     const int warp = threadIdx.x / 32;
-    const bool rotate = NORMALIZE && p.angles != nullptr;
+    const int row = threadIdx.x / ROW_THREADS;
+    const int place = threadIdx.x % ROW_THREADS;
+    const bool row_here = row < rows;
+    const int rotation = !NORMALIZE || p.angles == nullptr || p.pairs == 0 ? NO_ROTATION
+                         : p.pairs % 16 == 0                               ? IN_THREAD
+                                                                           : THROUGH_SHARED_MEMORY;
     const bool values_here =
         QUANTIZE && (p.value_head_maxima != nullptr || p.value_scales_ready != 0);
     const int parts = p.last_part - p.first_part + 1;
     const int items = head_count * parts;
+    auto tile_row = [&](int index) {
+        return reinterpret_cast<__nv_bfloat16 *>(&exchange[0][0]) + index * STAGED_STRIDE;
+    };
+    float *const cosines = trig;
+    float *const sines = trig + BLOCK_ROWS * p.pairs;
 
-    uint4 chunks[CHUNKS_PER_THREAD];
+    // The first group of this thread's row of the CTA's first head, in q, k and v.
+    const auto first_group = [&](int part) {
+        return p.source[part] + (first_token + row) * p.token_stride[part] +
+               first_head * p.head_stride[part] + 4 * place;
+    };
+    const __nv_bfloat16 *const first_groups[3] = {first_group(0), first_group(1), first_group(2)};
+    // The thread's eight groups of its row of turn `item`; zeros past the block's rows.
+    uint2 next[GROUPS];
     auto load = [&](int item) {
         const int part = p.first_part + item % parts;
-        const int head = first_head + item / parts;
-        const __nv_bfloat16 *rows_base =
-            p.source[part] + first_token * p.token_stride[part] + head * p.head_stride[part];
+        const __nv_bfloat16 *source =
+            (part == 0 ? first_groups[0] : part == 1 ? first_groups[1] : first_groups[2]) +
+            (item / parts) * p.head_stride[part];
         #pragma unroll
-        for (int index = 0; index < CHUNKS_PER_THREAD; index++) {
-            const int chunk = threadIdx.x + index * THREADS;
-            if (chunk / 16 < rows) {
-                const __nv_bfloat16 *source =
-                    rows_base + (chunk / 16) * p.token_stride[part] + (chunk % 16) * 8;
+        for (int group = 0; group < GROUPS; group++) {
+            next[group] = make_uint2(0, 0);
+            if (row_here) {
+                const __nv_bfloat16 *from = source + 16 * group;
                 if (p.vector_loads) {
-                    chunks[index] = __ldg(reinterpret_cast<const uint4 *>(source));
+                    next[group] = __ldg(reinterpret_cast<const uint2 *>(from));
                 } else {
-                    uint16_t halves[8];
+                    uint16_t halves[4];
                     #pragma unroll
-                    for (int element = 0; element < 8; element++) {
-                        halves[element] = __ldg(reinterpret_cast<const uint16_t *>(source) + element);
+                    for (int element = 0; element < 4; element++) {
+                        halves[element] = __ldg(reinterpret_cast<const uint16_t *>(from) + element);
                     }
-                    chunks[index] = make_uint4(halves[0] | (uint32_t(halves[1]) << 16),
-                                               halves[2] | (uint32_t(halves[3]) << 16),
-                                               halves[4] | (uint32_t(halves[5]) << 16),
-                                               halves[6] | (uint32_t(halves[7]) << 16));
+                    next[group] = make_uint2(halves[0] | (uint32_t(halves[1]) << 16),
+                                             halves[2] | (uint32_t(halves[3]) << 16));
                 }
             }
         }
     };
 
     load(0);
-    if (rotate) {
-        for (int index = threadIdx.x; index < rows * p.pairs; index += THREADS) {
-            float sine, cosine;
-            sincosf(p.angles[first_token * p.pairs + index], &sine, &cosine);
-            trig[index] = make_float2(cosine, sine);
+    PairAngles angles;
+    if (NORMALIZE) {
+        if (threadIdx.x < HEAD_DIM) {
+            #pragma unroll
+            for (int part = 0; part < 2; part++) {
+                weights[part][threadIdx.x] =
+                    p.weight[part] != nullptr ? __bfloat162float(p.weight[part][threadIdx.x]) : 0.0f;
+            }
         }
+        if (rotation == IN_THREAD) {
+            const float *row_angles = p.angles + (first_token + row) * p.pairs + 4 * place;
+            #pragma unroll
+            for (int group = 0; group < GROUPS / 2; group++) {
+                #pragma unroll
+                for (int index = 0; index < 4; index++) {
+                    float sine = 0.0f, cosine = 0.0f;
+                    if (row_here && 16 * group < p.pairs) {
+                        sincosf(row_angles[16 * group + index], &sine, &cosine);
+                    }
+                    angles.cosines[group][index] = cosine;
+                    angles.sines[group][index] = sine;
+                }
+            }
+        } else if (rotation == THROUGH_SHARED_MEMORY) {
+            for (int index = threadIdx.x; index < rows * p.pairs; index += THREADS) {
+                sincosf(p.angles[first_token * p.pairs + index], &sines[index], &cosines[index]);
+            }
+        }
+        __syncthreads();
     }
     for (int item = 0; item < items; item++) {
         const int part = p.first_part + item % parts;
         const int head = first_head + item / parts;
         const size_t statistic = (static_cast<size_t>(head) * blocks + block) * HEAD_DIM;
-        // The rows go to the tile; the largest magnitude is taken on the way where nothing
-        // changes the rows before it is needed.
-        float maximum = 0.0f;
+        uint2 groups[GROUPS];
         #pragma unroll
-        for (int index = 0; index < CHUNKS_PER_THREAD; index++) {
-            const int chunk = threadIdx.x + index * THREADS;
-            if (chunk / 16 < rows) {
-                *reinterpret_cast<uint4 *>(&tile[chunk / 16][(chunk % 16) * 8]) = chunks[index];
-                if (QUANTIZE && (!NORMALIZE || part == 2)) {
-                    maximum = fmaxf(maximum, chunk_max(chunks[index]));
-                }
-            }
+        for (int group = 0; group < GROUPS; group++) {
+            groups[group] = next[group];
         }
-        __syncthreads();
         if (item + 1 < items) {
             load(item + 1);
         }
+        // Whether the rows of this turn go through shared memory as BF16.
+        const bool staged = STATS || part == 2;
+        const bool needs_maximum = QUANTIZE && (part < 2 || !values_here);
+        float maximum = 0.0f;
+
         if (NORMALIZE && part < 2) {
-            for (int row = warp; row < rows; row += WARPS) {
-                maximum = fmaxf(maximum,
-                                normalize_row(tile[row], scratch[warp], p.weight[part],
-                                              rotate ? trig + row * p.pairs : nullptr, p.pairs,
-                                              p.epsilon));
+            RowShare share;
+            share.unpack(groups);
+            const float squares = share.sum_of_squares();
+            const float inverse = rsqrtf(__fmaf_rn(squares, 1.0f / HEAD_DIM, p.epsilon));
+            #pragma unroll
+            for (int group = 0; group < GROUPS; group++) {
+                const float4 weight =
+                    *reinterpret_cast<const float4 *>(&weights[part][16 * group + 4 * place]);
+                const float factors[4] = {weight.x, weight.y, weight.z, weight.w};
+                #pragma unroll
+                for (int index = 0; index < 4; index++) {
+                    share.values[group][index] = __fmul_rn(
+                        share.values[group][index], __fmul_rn(inverse, factors[index]));
+                }
+            }
+            if (rotation == IN_THREAD) {
+                switch (p.pairs / 16) {
+                case 1: rotate_in_thread<1>(share, angles); break;
+                case 2: rotate_in_thread<2>(share, angles); break;
+                case 3: rotate_in_thread<3>(share, angles); break;
+                default: rotate_in_thread<4>(share, angles); break;
+                }
+            } else if (rotation == THROUGH_SHARED_MEMORY) {
+                rotate_through_shared_memory(share, exchange[row], cosines + row * p.pairs,
+                                             sines + row * p.pairs, p.pairs, place);
+            }
+            // Rounding keeps the order of magnitudes, so the largest rounded magnitude is the
+            // rounded largest magnitude.
+            if (QUANTIZE && row_here) {
+                maximum = __bfloat162float(__float2bfloat16_rn(share.largest()));
+            }
+            share.pack(groups);
+            if (p.normalized[part] != nullptr && row_here) {
+                __nv_bfloat16 *target = p.normalized[part] +
+                                        (first_token + row) * p.token_stride[part] +
+                                        head * p.head_stride[part] + 4 * place;
+                #pragma unroll
+                for (int group = 0; group < GROUPS; group++) {
+                    *reinterpret_cast<uint2 *>(target + 16 * group) = groups[group];
+                }
+            }
+        } else if (needs_maximum) {
+            #pragma unroll
+            for (int group = 0; group < GROUPS; group++) {
+                maximum = fmaxf(maximum, group_max(groups[group]));
             }
         }
-        const bool needs_maximum = QUANTIZE && (part < 2 || !values_here);
+        if (staged) {
+            // The staged rows lie over other warps' exchange rows: those warps must be through
+            // with their rotations, which a barrier of the turn before only tells for V behind a
+            // quantized k.
+            if (rotation == THROUGH_SHARED_MEMORY && !(QUANTIZE && part == 2)) {
+                __syncthreads();
+            }
+            #pragma unroll
+            for (int group = 0; group < GROUPS; group++) {
+                *reinterpret_cast<uint2 *>(tile_row(row) + 16 * group + 4 * place) = groups[group];
+            }
+        }
         if (needs_maximum) {
             maximum = warp_max(maximum);
             if (lane == 0) {
-                maxima[warp] = maximum;
+                maxima[item % 2][warp] = maximum;
             }
         }
-        if (NORMALIZE || needs_maximum) {
+        if (staged || needs_maximum) {
             __syncthreads();
         }
         if (needs_maximum) {
-            maximum = maxima[0];
-            #pragma unroll
-            for (int index = 1; index < WARPS; index++) {
-                maximum = fmaxf(maximum, maxima[index]);
-            }
+            const float4 low = reinterpret_cast<const float4 *>(maxima[item % 2])[0];
+            const float4 high = reinterpret_cast<const float4 *>(maxima[item % 2])[1];
+            maximum = fmaxf(fmaxf(fmaxf(low.x, low.y), fmaxf(low.z, low.w)),
+                            fmaxf(fmaxf(high.x, high.y), fmaxf(high.z, high.w)));
         }
 
         if constexpr (STATS) {
@@ -273,8 +484,8 @@ __global__ void __launch_bounds__(THREADS, 4) inputs_kernel(const InputsParams p
             if (threadIdx.x < HEAD_DIM) {
                 const int dimension = threadIdx.x;
                 float sum = 0.0f;
-                for (int row = 0; row < rows; row++) {
-                    sum += __bfloat162float(tile[row][dimension]);
+                for (int index = 0; index < rows; index++) {
+                    sum += __bfloat162float(tile_row(index)[dimension]);
                 }
                 p.pooled[part][statistic + dimension] = part == 2 ? sum : sum / rows;
             }
@@ -285,8 +496,8 @@ __global__ void __launch_bounds__(THREADS, 4) inputs_kernel(const InputsParams p
                 p.value_maxima[head * blocks + block] = maximum;
             }
             if (values_here) {
-                // FP8 V transposed into 64 columns per block, zero past the block's rows. Each
-                // thread writes one 32-byte sector: 32 rows of one dimension.
+                // FP8 V transposed into 64 columns per block, zero past the block's rows. A thread
+                // takes 16 rows of two neighbouring dimensions and writes 16 bytes of each.
                 float scale;
                 if (p.value_head_maxima != nullptr) {
                     scale = fmaxf(p.value_head_maxima[head] / 448.0f, 1e-30f);
@@ -297,76 +508,69 @@ __global__ void __launch_bounds__(THREADS, 4) inputs_kernel(const InputsParams p
                     scale = p.value_scales[head];
                 }
                 const Divider divide(scale);
-                const int dimension = threadIdx.x % HEAD_DIM;
-                const int first_row = threadIdx.x / HEAD_DIM * 32;
-                uint32_t words[8];
-                #pragma unroll
-                for (int word = 0; word < 8; word++) {
-                    uint32_t packed = 0;
-                    #pragma unroll
-                    for (int byte = 0; byte < 4; byte++) {
-                        const int row = first_row + word * 4 + byte;
-                        const float element =
-                            row < rows ? __bfloat162float(tile[row][dimension]) : 0.0f;
-                        packed |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(
-                                      divide(element), __NV_SATFINITE, __NV_E4M3))
-                                  << (8 * byte);
-                    }
-                    words[word] = packed;
-                }
-                uint4 *destination = reinterpret_cast<uint4 *>(
-                    p.value8 +
-                    (static_cast<int64_t>(head) * HEAD_DIM + dimension) * blocks * BLOCK_ROWS +
-                    static_cast<int64_t>(block) * BLOCK_ROWS + first_row);
-                destination[0] = make_uint4(words[0], words[1], words[2], words[3]);
-                destination[1] = make_uint4(words[4], words[5], words[6], words[7]);
-            }
-        } else {
-            if constexpr (QUANTIZE) {
-                const float scale = fmaxf(maximum / 127.0f, 1e-30f);
-                if (threadIdx.x == 0) {
-                    p.scales[part][head * blocks + block] = scale;
-                }
-                const Divider divide(scale);
-                // A row of 128 INT8 values is 8 chunks of 16 bytes, each from 16 BF16 values.
-                uint8_t *destination =
-                    p.quantized[part] + (first_token * p.heads + head) * HEAD_DIM;
-                for (int chunk = threadIdx.x; chunk < rows * 8; chunk += THREADS) {
-                    const uint4 *source =
-                        reinterpret_cast<const uint4 *>(&tile[chunk / 8][(chunk % 8) * 16]);
-                    const uint4 halves[2] = {source[0], source[1]};
-                    const __nv_bfloat16 *elements =
-                        reinterpret_cast<const __nv_bfloat16 *>(halves);
-                    uint32_t words[4];
+                const int pair = threadIdx.x % (HEAD_DIM / 2);
+                const int first_row = threadIdx.x / (HEAD_DIM / 2) * 16;
+                uint32_t codes[2][4];
+                divide.dispatch([&](auto quick) {
+                    constexpr bool QUICK = decltype(quick)::value;
                     #pragma unroll
                     for (int word = 0; word < 4; word++) {
-                        uint32_t packed = 0;
+                        uint32_t halves[2][2];
                         #pragma unroll
-                        for (int byte = 0; byte < 4; byte++) {
-                            const int8_t value = static_cast<int8_t>(__float2int_rn(
-                                divide(__bfloat162float(elements[word * 4 + byte]))));
-                            packed |= static_cast<uint32_t>(static_cast<uint8_t>(value))
-                                      << (8 * byte);
+                        for (int two = 0; two < 2; two++) {
+                            float elements[2][2]; // [row of the two][dimension of the two]
+                            #pragma unroll
+                            for (int step = 0; step < 2; step++) {
+                                const int index = first_row + word * 4 + two * 2 + step;
+                                const uint32_t both =
+                                    index < rows
+                                        ? reinterpret_cast<const uint32_t *>(tile_row(index))[pair]
+                                        : 0u;
+                                elements[step][0] = divide.quotient<QUICK>(low_half(both));
+                                elements[step][1] = divide.quotient<QUICK>(high_half(both));
+                            }
+                            halves[0][two] = pack_e4m3(elements[0][0], elements[1][0]);
+                            halves[1][two] = pack_e4m3(elements[0][1], elements[1][1]);
                         }
-                        words[word] = packed;
+                        codes[0][word] = __byte_perm(halves[0][0], halves[0][1], 0x5410);
+                        codes[1][word] = __byte_perm(halves[1][0], halves[1][1], 0x5410);
                     }
-                    *reinterpret_cast<uint4 *>(
-                        destination + static_cast<int64_t>(chunk / 8) * p.heads * HEAD_DIM +
-                        (chunk % 8) * 16) = make_uint4(words[0], words[1], words[2], words[3]);
+                });
+                #pragma unroll
+                for (int which = 0; which < 2; which++) {
+                    uint8_t *target = p.value8 +
+                                      (static_cast<int64_t>(head) * HEAD_DIM + 2 * pair + which) *
+                                          blocks * BLOCK_ROWS +
+                                      static_cast<int64_t>(block) * BLOCK_ROWS + first_row;
+                    *reinterpret_cast<uint4 *>(target) = make_uint4(
+                        codes[which][0], codes[which][1], codes[which][2], codes[which][3]);
                 }
             }
-            if (NORMALIZE && p.normalized[part] != nullptr) {
-                __nv_bfloat16 *rows_base = p.normalized[part] +
-                                           first_token * p.token_stride[part] +
-                                           head * p.head_stride[part];
-                for (int chunk = threadIdx.x; chunk < rows * 16; chunk += THREADS) {
-                    *reinterpret_cast<uint4 *>(rows_base + (chunk / 16) * p.token_stride[part] +
-                                               (chunk % 16) * 8) =
-                        *reinterpret_cast<const uint4 *>(&tile[chunk / 16][(chunk % 16) * 8]);
-                }
+        } else if constexpr (QUANTIZE) {
+            const float scale = fmaxf(maximum / 127.0f, 1e-30f);
+            if (threadIdx.x == 0) {
+                p.scales[part][head * blocks + block] = scale;
+            }
+            if (row_here) {
+                const Divider divide(scale);
+                uint8_t *target = p.quantized[part] +
+                                  ((first_token + row) * p.heads + head) * HEAD_DIM + 4 * place;
+                divide.dispatch([&](auto quick) {
+                    constexpr bool QUICK = decltype(quick)::value;
+                    #pragma unroll
+                    for (int group = 0; group < GROUPS; group++) {
+                        *reinterpret_cast<uint32_t *>(target + 16 * group) =
+                            pack_int8(divide.quotient<QUICK>(low_half(groups[group].x)),
+                                      divide.quotient<QUICK>(high_half(groups[group].x)),
+                                      divide.quotient<QUICK>(low_half(groups[group].y)),
+                                      divide.quotient<QUICK>(high_half(groups[group].y)));
+                    }
+                });
             }
         }
-        __syncthreads();
+        if (staged) {
+            __syncthreads();
+        }
     }
 }
 
@@ -399,18 +603,20 @@ bool aligned_rows(const void *base, int64_t token_stride, int64_t head_stride) {
 
 template <bool NORMALIZE, bool STATS, bool QUANTIZE>
 int launch(InputsParams params, int blocks, cudaStream_t stream) {
-    const bool rotate = NORMALIZE && params.angles != nullptr;
+    const bool rotate = NORMALIZE && params.angles != nullptr && params.pairs > 0;
     // With angles a CTA takes several heads so that their sincosf is paid once; the grid still
     // holds several CTAs per SM slot.
     params.heads_per_cta = rotate ? HEADS_PER_CTA : 1;
     const int groups = (params.heads + params.heads_per_cta - 1) / params.heads_per_cta;
-    const size_t shared = rotate ? static_cast<size_t>(BLOCK_ROWS) * params.pairs * sizeof(float2)
-                                 : 0;
-    if (rotate) {
-        // Up to 64 pairs: 32 KiB of cosines and sines beside the 20 KiB of static shared memory.
+    // Only pairs that are not a multiple of 16 need the table of cosines and sines.
+    const size_t shared = rotate && params.pairs % 16 != 0
+                              ? static_cast<size_t>(2) * BLOCK_ROWS * params.pairs * sizeof(float)
+                              : 0;
+    if (shared != 0) {
+        // Up to 63 pairs: 32 KiB of cosines and sines beside the 35 KiB of static shared memory.
         static SharedMemoryOptIn shared_memory;
         const cudaError_t configured = shared_memory.ensure(
-            inputs_kernel<NORMALIZE, STATS, QUANTIZE>, BLOCK_ROWS * (HEAD_DIM / 2) * 8);
+            inputs_kernel<NORMALIZE, STATS, QUANTIZE>, 2 * BLOCK_ROWS * (HEAD_DIM / 2) * 4);
         if (configured != cudaSuccess) {
             return static_cast<int>(configured);
         }

@@ -24,7 +24,7 @@ EPSILON = 1e-6
 SCALE = synthetic.softmax_scale()
 
 
-def make_inputs(oracle, tokens, heads):
+def make_inputs(oracle, tokens, heads, pairs=PAIRS):
     """Blocks of tokens share a direction (attention_inputs.rs:51-98)."""
     inner = heads * 128
     state = tokens * 31 + heads
@@ -35,16 +35,16 @@ def make_inputs(oracle, tokens, heads):
     qkv = directions[(index // (3 * inner) // 64) * 3 * inner + index % (3 * inner)] + noise
     query_weight, state = oracle_lib.lcg(oracle, state, 128, 0.5, 1.5)
     key_weight, state = oracle_lib.lcg(oracle, state, 128, 0.5, 1.5)
-    angles, state = oracle_lib.lcg(oracle, state, tokens * PAIRS, -40.0, 40.0)
+    angles, state = oracle_lib.lcg(oracle, state, tokens * pairs, -40.0, 40.0)
     return (synthetic.to_bf16_bits(qkv.astype(np.float32)).reshape(tokens, 3, heads, 128),
             synthetic.to_bf16_bits(query_weight), synthetic.to_bf16_bits(key_weight), angles)
 
 
-def norm_for(query_weight, key_weight, angles):
+def norm_for(query_weight, key_weight, angles, pairs=PAIRS):
     return attention.HeadNorm(synthetic.bf16_tensor(query_weight, "cuda"),
                               synthetic.bf16_tensor(key_weight, "cuda"),
                               torch.from_numpy(angles).cuda() if angles is not None else None,
-                              PAIRS if angles is not None else 0, EPSILON)
+                              pairs if angles is not None else 0, EPSILON)
 
 
 def valid_value_columns(workspace, lengths):
@@ -143,6 +143,38 @@ def test_norm_and_rope_in_place_is_bit_exact(oracle, reference_kernels, tokens, 
     # v is left alone
     assert torch.equal(ours.view(torch.int16)[:, 2].cpu(),
                        synthetic.bf16_tensor(bits).view(torch.int16)[:, 2])
+
+
+# Multiples of 16 keep both dimensions of a rotary pair in one thread, each with its own unrolled
+# turn; every other count crosses threads through shared memory.
+@pytest.mark.parametrize("pairs", [16, 32, 64, 1, 7, 20, 40, 63])
+@pytest.mark.parametrize("tokens", [65, 200])
+def test_rope_with_other_pair_counts_is_bit_exact(oracle, reference_kernels, tokens, pairs):
+    heads = 3
+    bits, query_weight, key_weight, angles = make_inputs(oracle, tokens, heads, pairs)
+    norm = norm_for(query_weight, key_weight, angles, pairs)
+    ours = synthetic.bf16_tensor(bits, "cuda")
+    theirs = ours.clone()
+    attention.qk_norm_rope(ours, norm, tokens, heads)
+    assert reference_kernels.mmh3_qk_norm_rope(
+        theirs.data_ptr(), norm.query_weight.data_ptr(), norm.key_weight.data_ptr(),
+        norm.angles.data_ptr(), pairs, tokens, heads, heads, EPSILON, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(ours.view(torch.int16), theirs.view(torch.int16))
+    # ... and through the fused preparation, whose INT8 rows come from the rotated values.
+    ours_qkv = synthetic.bf16_tensor(bits, "cuda")
+    theirs_qkv = ours_qkv.clone()
+    ours_space = attention.QuantizedWorkspace(tokens, heads)
+    theirs_space = attention.QuantizedWorkspace(tokens, heads)
+    attention.prepare_inputs(ours_qkv, norm, tokens, heads, quantized=ours_space)
+    raw = theirs_space.raw()
+    assert reference_kernels.mmh3_attention_inputs(
+        theirs_qkv.data_ptr(), norm.query_weight.data_ptr(), norm.key_weight.data_ptr(),
+        norm.angles.data_ptr(), pairs, tokens, heads, EPSILON, None, ctypes.byref(raw), None,
+        None, 0, None, None) == 0
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    assert_workspaces_equal(ours_space, theirs_space, values=False)
 
 
 @pytest.mark.parametrize("tokens", [1, 63, 64, 65, 200, 1000])
