@@ -99,6 +99,9 @@ struct Divider {
         const uint32_t bits = __float_as_uint(divisor);
         exact = (bits & 0x007fffffu) != 0x007fffffu && divisor >= 1e-24f && divisor <= 1e24f;
     }
+    // For a divisor known when compiling, with its reciprocal rounded by the compiler.
+    __device__ __forceinline__ constexpr Divider(float divisor, float rounded_reciprocal)
+        : scale(divisor), reciprocal(rounded_reciprocal), exact(true) {}
     // The quotient where `exact` holds, and where it does not. A caller with many values asks
     // `exact` once and runs one of two loops.
     template <bool QUICK> __device__ __forceinline__ float quotient(float x) const {
@@ -118,6 +121,13 @@ struct Divider {
         }
     }
 };
+
+// maximum / LEVELS as IEEE division gives it wherever the quotient is 1e-30 or more, which is all a
+// scale keeps of it; LEVELS is 127 or 448, whose significands are not all ones.
+template <int LEVELS> __device__ __forceinline__ float scale_for(float maximum) {
+    constexpr Divider divide(static_cast<float>(LEVELS), 1.0f / static_cast<float>(LEVELS));
+    return fmaxf(divide.quotient<true>(maximum), 1e-30f);
+}
 
 __device__ __forceinline__ float low_half(uint32_t word) { return __uint_as_float(word << 16); }
 __device__ __forceinline__ float high_half(uint32_t word) {
@@ -201,17 +211,19 @@ struct RowShare {
         return (sums[0] + sums[2]) + (sums[1] + sums[3]);
     }
 
-    // The largest magnitude among the values.
+    // The largest magnitude among the values, two at a time with the three-input maximum.
     __device__ __forceinline__ float largest() const {
-        float maxima[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        float maxima[2] = {0.0f, 0.0f};
         #pragma unroll
         for (int group = 0; group < GROUPS; group++) {
             #pragma unroll
-            for (int index = 0; index < 4; index++) {
-                maxima[index] = fmaxf(maxima[index], fabsf(values[group][index]));
+            for (int two = 0; two < 2; two++) {
+                asm("max.f32 %0, %0, %1, %2;"
+                    : "+f"(maxima[two])
+                    : "f"(fabsf(values[group][2 * two])), "f"(fabsf(values[group][2 * two + 1])));
             }
         }
-        return fmaxf(fmaxf(maxima[0], maxima[1]), fmaxf(maxima[2], maxima[3]));
+        return fmaxf(maxima[0], maxima[1]);
     }
 
     // The values rounded to BF16.
@@ -284,7 +296,9 @@ __device__ __forceinline__ void rotate_through_shared_memory(RowShare &share, fl
 
 // Dynamic shared memory, only where the rotary pairs are not a multiple of 16: the cosines of the
 // block's angles, [64][pairs], then the sines.
-template <bool NORMALIZE, bool STATS, bool QUANTIZE>
+//
+// SIXTEENTHS is pairs / 16 where the rotary pairs are a multiple of 16, else 0.
+template <bool NORMALIZE, bool STATS, bool QUANTIZE, int SIXTEENTHS>
 __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p) {
     extern __shared__ __align__(16) float trig[];
     // The rows as BF16 where V is transposed or sums are pooled. The same memory holds rows of 128
@@ -309,32 +323,34 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
     const int row = threadIdx.x / ROW_THREADS;
     const int place = threadIdx.x % ROW_THREADS;
     const bool row_here = row < rows;
-    const int rotation = !NORMALIZE || p.angles == nullptr || p.pairs == 0 ? NO_ROTATION
-                         : p.pairs % 16 == 0                               ? IN_THREAD
-                                                                           : THROUGH_SHARED_MEMORY;
+    const int rotation = SIXTEENTHS != 0                                      ? IN_THREAD
+                         : !NORMALIZE || p.angles == nullptr || p.pairs == 0 ? NO_ROTATION
+                                                                             : THROUGH_SHARED_MEMORY;
     const bool values_here =
         QUANTIZE && (p.value_head_maxima != nullptr || p.value_scales_ready != 0);
-    const int parts = p.last_part - p.first_part + 1;
-    const int items = head_count * parts;
+    const int items = head_count * (p.last_part - p.first_part + 1);
     auto tile_row = [&](int index) {
         return reinterpret_cast<__nv_bfloat16 *>(&exchange[0][0]) + index * STAGED_STRIDE;
     };
     float *const cosines = trig;
     float *const sines = trig + BLOCK_ROWS * p.pairs;
 
-    // The first group of this thread's row of the CTA's first head, in q, k and v.
+    // The first group of this thread's row of the CTA's first head, in q, k and v, as an offset
+    // from the tensor's first element.
     const auto first_group = [&](int part) {
-        return p.source[part] + (first_token + row) * p.token_stride[part] +
-               first_head * p.head_stride[part] + 4 * place;
+        return (first_token + row) * p.token_stride[part] + first_head * p.head_stride[part] +
+               4 * place;
     };
-    const __nv_bfloat16 *const first_groups[3] = {first_group(0), first_group(1), first_group(2)};
-    // The thread's eight groups of its row of turn `item`; zeros past the block's rows.
+    const int64_t first_groups[3] = {first_group(0), first_group(1), first_group(2)};
+    const auto pick = [](int part, const auto &of_three) {
+        return part == 0 ? of_three[0] : part == 1 ? of_three[1] : of_three[2];
+    };
+    // The thread's eight groups of its row of one turn (q, k or v of the CTA's head number
+    // `walked`); zeros past the block's rows.
     uint2 next[GROUPS];
-    auto load = [&](int item) {
-        const int part = p.first_part + item % parts;
+    auto load = [&](int part, int walked) {
         const __nv_bfloat16 *source =
-            (part == 0 ? first_groups[0] : part == 1 ? first_groups[1] : first_groups[2]) +
-            (item / parts) * p.head_stride[part];
+            pick(part, p.source) + pick(part, first_groups) + walked * pick(part, p.head_stride);
         #pragma unroll
         for (int group = 0; group < GROUPS; group++) {
             next[group] = make_uint2(0, 0);
@@ -355,7 +371,7 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
         }
     };
 
-    load(0);
+    load(p.first_part, 0);
     PairAngles angles;
     if (NORMALIZE) {
         if (threadIdx.x < HEAD_DIM) {
@@ -365,18 +381,28 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
                     p.weight[part] != nullptr ? __bfloat162float(p.weight[part][threadIdx.x]) : 0.0f;
             }
         }
-        if (rotation == IN_THREAD) {
+        if (SIXTEENTHS != 0) {
             const float *row_angles = p.angles + (first_token + row) * p.pairs + 4 * place;
-            #pragma unroll
-            for (int group = 0; group < GROUPS / 2; group++) {
-                #pragma unroll
-                for (int index = 0; index < 4; index++) {
-                    float sine = 0.0f, cosine = 0.0f;
-                    if (row_here && 16 * group < p.pairs) {
-                        sincosf(row_angles[16 * group + index], &sine, &cosine);
+            #pragma unroll 1
+            for (int group = 0; group < SIXTEENTHS; group++) {
+                float found[2][4] = {};
+                if (row_here) {
+                    #pragma unroll
+                    for (int index = 0; index < 4; index++) {
+                        sincosf(row_angles[16 * group + index], &found[1][index], &found[0][index]);
                     }
-                    angles.cosines[group][index] = cosine;
-                    angles.sines[group][index] = sine;
+                }
+                // The loop is kept a loop for the size of sincosf; its results reach the
+                // registers of their group through the unrolled comparison.
+                #pragma unroll
+                for (int slot = 0; slot < SIXTEENTHS; slot++) {
+                    if (slot == group) {
+                        #pragma unroll
+                        for (int index = 0; index < 4; index++) {
+                            angles.cosines[slot][index] = found[0][index];
+                            angles.sines[slot][index] = found[1][index];
+                        }
+                    }
                 }
             }
         } else if (rotation == THROUGH_SHARED_MEMORY) {
@@ -386,17 +412,26 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
         }
         __syncthreads();
     }
+    // Where this thread's 16 bytes of FP8 V go within a head: the first of its two dimensions,
+    // its 16 rows of the block.
+    const int64_t value_column =
+        static_cast<int64_t>(2 * (threadIdx.x % (HEAD_DIM / 2))) * blocks * BLOCK_ROWS +
+        static_cast<int64_t>(block) * BLOCK_ROWS + threadIdx.x / (HEAD_DIM / 2) * 16;
+    const int64_t quantized_row = ((first_token + row) * p.heads + first_head) * HEAD_DIM + 4 * place;
+    int part = p.first_part;
+    int walked = 0; // heads of the CTA's that are done
     for (int item = 0; item < items; item++) {
-        const int part = p.first_part + item % parts;
-        const int head = first_head + item / parts;
+        const int head = first_head + walked;
         const size_t statistic = (static_cast<size_t>(head) * blocks + block) * HEAD_DIM;
+        const bool last_part = part == p.last_part;
+        const int next_part = last_part ? p.first_part : part + 1;
         uint2 groups[GROUPS];
         #pragma unroll
         for (int group = 0; group < GROUPS; group++) {
             groups[group] = next[group];
         }
         if (item + 1 < items) {
-            load(item + 1);
+            load(next_part, walked + (last_part ? 1 : 0));
         }
         // Whether the rows of this turn go through shared memory as BF16.
         const bool staged = STATS || part == 2;
@@ -419,13 +454,8 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
                         share.values[group][index], __fmul_rn(inverse, factors[index]));
                 }
             }
-            if (rotation == IN_THREAD) {
-                switch (p.pairs / 16) {
-                case 1: rotate_in_thread<1>(share, angles); break;
-                case 2: rotate_in_thread<2>(share, angles); break;
-                case 3: rotate_in_thread<3>(share, angles); break;
-                default: rotate_in_thread<4>(share, angles); break;
-                }
+            if (SIXTEENTHS != 0) {
+                rotate_in_thread<SIXTEENTHS>(share, angles);
             } else if (rotation == THROUGH_SHARED_MEMORY) {
                 rotate_through_shared_memory(share, exchange[row], cosines + row * p.pairs,
                                              sines + row * p.pairs, p.pairs, place);
@@ -437,9 +467,8 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
             }
             share.pack(groups);
             if (p.normalized[part] != nullptr && row_here) {
-                __nv_bfloat16 *target = p.normalized[part] +
-                                        (first_token + row) * p.token_stride[part] +
-                                        head * p.head_stride[part] + 4 * place;
+                __nv_bfloat16 *target = p.normalized[part] + pick(part, first_groups) +
+                                        walked * pick(part, p.head_stride);
                 #pragma unroll
                 for (int group = 0; group < GROUPS; group++) {
                     *reinterpret_cast<uint2 *>(target + 16 * group) = groups[group];
@@ -500,7 +529,7 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
                 // takes 16 rows of two neighbouring dimensions and writes 16 bytes of each.
                 float scale;
                 if (p.value_head_maxima != nullptr) {
-                    scale = fmaxf(p.value_head_maxima[head] / 448.0f, 1e-30f);
+                    scale = scale_for<448>(p.value_head_maxima[head]);
                     if (block == 0 && threadIdx.x == 0) {
                         p.value_scales[head] = scale;
                     }
@@ -521,11 +550,10 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
                             float elements[2][2]; // [row of the two][dimension of the two]
                             #pragma unroll
                             for (int step = 0; step < 2; step++) {
+                                // Rows past the block's were staged as zeros.
                                 const int index = first_row + word * 4 + two * 2 + step;
                                 const uint32_t both =
-                                    index < rows
-                                        ? reinterpret_cast<const uint32_t *>(tile_row(index))[pair]
-                                        : 0u;
+                                    reinterpret_cast<const uint32_t *>(tile_row(index))[pair];
                                 elements[step][0] = divide.quotient<QUICK>(low_half(both));
                                 elements[step][1] = divide.quotient<QUICK>(high_half(both));
                             }
@@ -538,23 +566,21 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
                 });
                 #pragma unroll
                 for (int which = 0; which < 2; which++) {
-                    uint8_t *target = p.value8 +
-                                      (static_cast<int64_t>(head) * HEAD_DIM + 2 * pair + which) *
-                                          blocks * BLOCK_ROWS +
-                                      static_cast<int64_t>(block) * BLOCK_ROWS + first_row;
+                    uint8_t *target = p.value8 + value_column +
+                                      (static_cast<int64_t>(head) * HEAD_DIM + which) *
+                                          blocks * BLOCK_ROWS;
                     *reinterpret_cast<uint4 *>(target) = make_uint4(
                         codes[which][0], codes[which][1], codes[which][2], codes[which][3]);
                 }
             }
         } else if constexpr (QUANTIZE) {
-            const float scale = fmaxf(maximum / 127.0f, 1e-30f);
+            const float scale = scale_for<127>(maximum);
             if (threadIdx.x == 0) {
                 p.scales[part][head * blocks + block] = scale;
             }
             if (row_here) {
                 const Divider divide(scale);
-                uint8_t *target = p.quantized[part] +
-                                  ((first_token + row) * p.heads + head) * HEAD_DIM + 4 * place;
+                uint8_t *target = p.quantized[part] + quantized_row + walked * HEAD_DIM;
                 divide.dispatch([&](auto quick) {
                     constexpr bool QUICK = decltype(quick)::value;
                     #pragma unroll
@@ -571,6 +597,8 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
         if (staged) {
             __syncthreads();
         }
+        part = next_part;
+        walked += last_part ? 1 : 0;
     }
 }
 
@@ -601,29 +629,43 @@ bool aligned_rows(const void *base, int64_t token_stride, int64_t head_stride) {
            head_stride % 8 == 0;
 }
 
+template <bool NORMALIZE, bool STATS, bool QUANTIZE, int SIXTEENTHS>
+int launch_as(const InputsParams &params, int blocks, size_t shared, cudaStream_t stream) {
+    const auto kernel = inputs_kernel<NORMALIZE, STATS, QUANTIZE, SIXTEENTHS>;
+    if (shared != 0) {
+        // Up to 63 pairs: 32 KiB of cosines and sines beside the 35 KiB of static shared memory.
+        static SharedMemoryOptIn shared_memory;
+        const cudaError_t configured =
+            shared_memory.ensure(kernel, 2 * BLOCK_ROWS * (HEAD_DIM / 2) * 4);
+        if (configured != cudaSuccess) {
+            return static_cast<int>(configured);
+        }
+    }
+    const int groups = (params.heads + params.heads_per_cta - 1) / params.heads_per_cta;
+    kernel<<<dim3(blocks, groups), THREADS, shared, stream>>>(params);
+    return static_cast<int>(cudaGetLastError());
+}
+
 template <bool NORMALIZE, bool STATS, bool QUANTIZE>
 int launch(InputsParams params, int blocks, cudaStream_t stream) {
     const bool rotate = NORMALIZE && params.angles != nullptr && params.pairs > 0;
     // With angles a CTA takes several heads so that their sincosf is paid once; the grid still
     // holds several CTAs per SM slot.
     params.heads_per_cta = rotate ? HEADS_PER_CTA : 1;
-    const int groups = (params.heads + params.heads_per_cta - 1) / params.heads_per_cta;
-    // Only pairs that are not a multiple of 16 need the table of cosines and sines.
-    const size_t shared = rotate && params.pairs % 16 != 0
-                              ? static_cast<size_t>(2) * BLOCK_ROWS * params.pairs * sizeof(float)
-                              : 0;
-    if (shared != 0) {
-        // Up to 63 pairs: 32 KiB of cosines and sines beside the 35 KiB of static shared memory.
-        static SharedMemoryOptIn shared_memory;
-        const cudaError_t configured = shared_memory.ensure(
-            inputs_kernel<NORMALIZE, STATS, QUANTIZE>, 2 * BLOCK_ROWS * (HEAD_DIM / 2) * 4);
-        if (configured != cudaSuccess) {
-            return static_cast<int>(configured);
+    if constexpr (NORMALIZE) {
+        if (rotate && params.pairs % 16 == 0) {
+            switch (params.pairs / 16) {
+            case 1: return launch_as<NORMALIZE, STATS, QUANTIZE, 1>(params, blocks, 0, stream);
+            case 2: return launch_as<NORMALIZE, STATS, QUANTIZE, 2>(params, blocks, 0, stream);
+            case 3: return launch_as<NORMALIZE, STATS, QUANTIZE, 3>(params, blocks, 0, stream);
+            default: return launch_as<NORMALIZE, STATS, QUANTIZE, 4>(params, blocks, 0, stream);
+            }
         }
     }
-    inputs_kernel<NORMALIZE, STATS, QUANTIZE>
-        <<<dim3(blocks, groups), THREADS, shared, stream>>>(params);
-    return static_cast<int>(cudaGetLastError());
+    // Only pairs that are not a multiple of 16 need the table of cosines and sines.
+    const size_t shared =
+        rotate ? static_cast<size_t>(2) * BLOCK_ROWS * params.pairs * sizeof(float) : 0;
+    return launch_as<NORMALIZE, STATS, QUANTIZE, 0>(params, blocks, shared, stream);
 }
 
 } // namespace
