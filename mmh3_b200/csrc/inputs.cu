@@ -38,6 +38,9 @@ constexpr int HEADS_PER_CTA = 8;
 // is 128 BF16 values of which a thread touches 8 bytes at a time (16 threads, four rows, at once).
 constexpr int STAGED_STRIDE = HEAD_DIM + 16; // BF16 values
 constexpr int EXCHANGE_STRIDE = HEAD_DIM + 4; // floats
+// INT8 rows on their way out, a warp's eight at a time: 128 bytes of which a thread writes four at
+// a time and later reads 16.
+constexpr int CODES_STRIDE = HEAD_DIM + 16; // bytes
 // Adding 1.5 * 2^23 rounds a float below 2^22 in magnitude to the nearest integer, ties to even,
 // and leaves it in two's complement in the low bits of the sum.
 constexpr float ROUNDING_MAGIC = 12582912.0f;
@@ -307,6 +310,7 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
     __shared__ __align__(16) float exchange[BLOCK_ROWS][EXCHANGE_STRIDE];
     static_assert(BLOCK_ROWS * STAGED_STRIDE * 2 <= sizeof(exchange), "staged rows fit");
     __shared__ __align__(16) float weights[2][HEAD_DIM];
+    __shared__ __align__(16) uint8_t codes[BLOCK_ROWS][CODES_STRIDE];
     __shared__ __align__(16) float maxima[2][WARPS];
     static_assert(WARPS == 8, "the block maximum reads eight warp maxima as two float4");
     const int block = blockIdx.x;
@@ -417,7 +421,7 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
     const int64_t value_column =
         static_cast<int64_t>(2 * (threadIdx.x % (HEAD_DIM / 2))) * blocks * BLOCK_ROWS +
         static_cast<int64_t>(block) * BLOCK_ROWS + threadIdx.x / (HEAD_DIM / 2) * 16;
-    const int64_t quantized_row = ((first_token + row) * p.heads + first_head) * HEAD_DIM + 4 * place;
+    const int64_t quantized_block = (first_token * p.heads + first_head) * HEAD_DIM;
     int part = p.first_part;
     int walked = 0; // heads of the CTA's that are done
     for (int item = 0; item < items; item++) {
@@ -578,21 +582,33 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
             if (threadIdx.x == 0) {
                 p.scales[part][head * blocks + block] = scale;
             }
-            if (row_here) {
-                const Divider divide(scale);
-                uint8_t *target = p.quantized[part] + quantized_row + walked * HEAD_DIM;
-                divide.dispatch([&](auto quick) {
-                    constexpr bool QUICK = decltype(quick)::value;
-                    #pragma unroll
-                    for (int group = 0; group < GROUPS; group++) {
-                        *reinterpret_cast<uint32_t *>(target + 16 * group) =
-                            pack_int8(divide.quotient<QUICK>(low_half(groups[group].x)),
-                                      divide.quotient<QUICK>(high_half(groups[group].x)),
-                                      divide.quotient<QUICK>(low_half(groups[group].y)),
-                                      divide.quotient<QUICK>(high_half(groups[group].y)));
-                    }
-                });
+            // A thread's codes are four bytes in each of eight 16-byte pieces of its row. They
+            // meet the other threads' in shared memory, a warp's eight rows to itself, and leave
+            // as whole 128-byte rows: four rows to a store instead of eight quarter rows.
+            const Divider divide(scale);
+            divide.dispatch([&](auto quick) {
+                constexpr bool QUICK = decltype(quick)::value;
+                #pragma unroll
+                for (int group = 0; group < GROUPS; group++) {
+                    *reinterpret_cast<uint32_t *>(&codes[row][16 * group + 4 * place]) =
+                        pack_int8(divide.quotient<QUICK>(low_half(groups[group].x)),
+                                  divide.quotient<QUICK>(high_half(groups[group].x)),
+                                  divide.quotient<QUICK>(low_half(groups[group].y)),
+                                  divide.quotient<QUICK>(high_half(groups[group].y)));
+                }
+            });
+            __syncwarp();
+            #pragma unroll
+            for (int half = 0; half < 2; half++) {
+                const int leaving = warp * 8 + half * 4 + lane / 8;
+                if (leaving < rows) {
+                    uint8_t *target = p.quantized[part] + quantized_block +
+                                      (static_cast<int64_t>(leaving) * p.heads + walked) * HEAD_DIM;
+                    *reinterpret_cast<uint4 *>(target + 16 * (lane % 8)) =
+                        *reinterpret_cast<const uint4 *>(&codes[leaving][16 * (lane % 8)]);
+                }
             }
+            __syncwarp();
         }
         if (staged) {
             __syncthreads();
