@@ -33,7 +33,7 @@ constexpr int WARPS = THREADS / 32;
 // Threads that share a row, and the groups of four neighbouring dimensions each of them holds.
 constexpr int ROW_THREADS = THREADS / BLOCK_ROWS;
 constexpr int GROUPS = HEAD_DIM / (4 * ROW_THREADS);
-constexpr int HEADS_PER_CTA = 8;
+constexpr int HEADS_PER_CTA = 16;
 // Strides in shared memory that keep the threads served together in different banks: a staged row
 // is 128 BF16 values of which a thread touches 8 bytes at a time (16 threads, four rows, at once).
 constexpr int STAGED_STRIDE = HEAD_DIM + 16; // BF16 values
@@ -80,12 +80,10 @@ struct InputsParams {
     int heads_per_cta;
 };
 
+// The largest of the warp's values, none of them negative or NaN: such floats order as their bits
+// do, and the warp reduces unsigned integers in one instruction.
 __device__ __forceinline__ float warp_max(float value) {
-    #pragma unroll
-    for (int offset = 16; offset > 0; offset /= 2) {
-        value = fmaxf(value, __shfl_xor_sync(0xffffffffu, value, offset));
-    }
-    return value;
+    return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(value)));
 }
 
 // x / scale, rounded to nearest as IEEE division rounds it, for many x and one scale: with
@@ -333,8 +331,12 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
     const bool values_here =
         QUANTIZE && (p.value_head_maxima != nullptr || p.value_scales_ready != 0);
     const int items = head_count * (p.last_part - p.first_part + 1);
-    auto tile_row = [&](int index) {
-        return reinterpret_cast<__nv_bfloat16 *>(&exchange[0][0]) + index * STAGED_STRIDE;
+    // Word `word` (two BF16 values) of staged row `index`. Each run of 16 rows has its words
+    // exchanged in eights, so that the threads that later read the same word of rows 16 apart
+    // find them in different banks.
+    uint32_t *const staged_words = reinterpret_cast<uint32_t *>(&exchange[0][0]);
+    const auto staged_word = [](int index, int word) {
+        return index * (STAGED_STRIDE / 2) + (word ^ (8 * ((index / 16) % 4)));
     };
     float *const cosines = trig;
     float *const sines = trig + BLOCK_ROWS * p.pairs;
@@ -351,8 +353,42 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
     };
     // The thread's eight groups of its row of one turn (q, k or v of the CTA's head number
     // `walked`); zeros past the block's rows.
+    //
+    // A turn that only passes through shared memory (V, and everything where nothing is normalized
+    // or quantized) is loaded as whole rows instead, 16 threads to a row and 16 bytes each, four
+    // times: groups 2 i and 2 i + 1 then hold piece lane % 16 of row 8 warp + 2 i + lane / 16.
+    const auto in_rows = [](int part) { return part == 2 || (!NORMALIZE && !QUANTIZE); };
     uint2 next[GROUPS];
     auto load = [&](int part, int walked) {
+        if (in_rows(part)) {
+            const int64_t token_stride = pick(part, p.token_stride);
+            const __nv_bfloat16 *source = pick(part, p.source) +
+                                          (first_token + 8 * warp + lane / 16) * token_stride +
+                                          (first_head + walked) * pick(part, p.head_stride) +
+                                          8 * (lane % 16);
+            #pragma unroll
+            for (int two = 0; two < GROUPS / 2; two++) {
+                uint4 piece = make_uint4(0, 0, 0, 0);
+                if (8 * warp + 2 * two + lane / 16 < rows) {
+                    const __nv_bfloat16 *from = source + 2 * two * token_stride;
+                    if (p.vector_loads) {
+                        piece = __ldg(reinterpret_cast<const uint4 *>(from));
+                    } else {
+                        uint32_t words[4];
+                        #pragma unroll
+                        for (int word = 0; word < 4; word++) {
+                            const uint16_t *halves = reinterpret_cast<const uint16_t *>(from);
+                            words[word] = __ldg(halves + 2 * word) |
+                                          (uint32_t(__ldg(halves + 2 * word + 1)) << 16);
+                        }
+                        piece = make_uint4(words[0], words[1], words[2], words[3]);
+                    }
+                }
+                next[2 * two] = make_uint2(piece.x, piece.y);
+                next[2 * two + 1] = make_uint2(piece.z, piece.w);
+            }
+            return;
+        }
         const __nv_bfloat16 *source =
             pick(part, p.source) + pick(part, first_groups) + walked * pick(part, p.head_stride);
         #pragma unroll
@@ -418,9 +454,8 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
     }
     // Where this thread's 16 bytes of FP8 V go within a head: the first of its two dimensions,
     // its 16 rows of the block.
-    const int64_t value_column =
-        static_cast<int64_t>(2 * (threadIdx.x % (HEAD_DIM / 2))) * blocks * BLOCK_ROWS +
-        static_cast<int64_t>(block) * BLOCK_ROWS + threadIdx.x / (HEAD_DIM / 2) * 16;
+    const int64_t value_column = static_cast<int64_t>(2 * (8 * warp + lane % 8)) * blocks * BLOCK_ROWS +
+                                 static_cast<int64_t>(block) * BLOCK_ROWS + lane / 8 * 16;
     const int64_t quantized_block = (first_token * p.heads + first_head) * HEAD_DIM;
     int part = p.first_part;
     int walked = 0; // heads of the CTA's that are done
@@ -491,9 +526,21 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
             if (rotation == THROUGH_SHARED_MEMORY && !(QUANTIZE && part == 2)) {
                 __syncthreads();
             }
-            #pragma unroll
-            for (int group = 0; group < GROUPS; group++) {
-                *reinterpret_cast<uint2 *>(tile_row(row) + 16 * group + 4 * place) = groups[group];
+            if (in_rows(part)) {
+                #pragma unroll
+                for (int two = 0; two < GROUPS / 2; two++) {
+                    *reinterpret_cast<uint4 *>(
+                        &staged_words[staged_word(8 * warp + 2 * two + lane / 16,
+                                                  4 * (lane % 16))]) =
+                        make_uint4(groups[2 * two].x, groups[2 * two].y, groups[2 * two + 1].x,
+                                   groups[2 * two + 1].y);
+                }
+            } else {
+                #pragma unroll
+                for (int group = 0; group < GROUPS; group++) {
+                    *reinterpret_cast<uint2 *>(
+                        &staged_words[staged_word(row, 8 * group + 2 * place)]) = groups[group];
+                }
             }
         }
         if (needs_maximum) {
@@ -518,7 +565,8 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
                 const int dimension = threadIdx.x;
                 float sum = 0.0f;
                 for (int index = 0; index < rows; index++) {
-                    sum += __bfloat162float(tile_row(index)[dimension]);
+                    const uint32_t both = staged_words[staged_word(index, dimension / 2)];
+                    sum += dimension % 2 ? high_half(both) : low_half(both);
                 }
                 p.pooled[part][statistic + dimension] = part == 2 ? sum : sum / rows;
             }
@@ -530,7 +578,8 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
             }
             if (values_here) {
                 // FP8 V transposed into 64 columns per block, zero past the block's rows. A thread
-                // takes 16 rows of two neighbouring dimensions and writes 16 bytes of each.
+                // takes 16 rows of two neighbouring dimensions and writes 16 bytes of each; a warp
+                // takes all 64 rows of 16 dimensions, so that its stores fill 64-byte runs.
                 float scale;
                 if (p.value_head_maxima != nullptr) {
                     scale = scale_for<448>(p.value_head_maxima[head]);
@@ -541,9 +590,9 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
                     scale = p.value_scales[head];
                 }
                 const Divider divide(scale);
-                const int pair = threadIdx.x % (HEAD_DIM / 2);
-                const int first_row = threadIdx.x / (HEAD_DIM / 2) * 16;
-                uint32_t codes[2][4];
+                const int pair = 8 * warp + lane % 8;
+                const int first_row = lane / 8 * 16;
+                uint32_t bytes[2][4];
                 divide.dispatch([&](auto quick) {
                     constexpr bool QUICK = decltype(quick)::value;
                     #pragma unroll
@@ -556,16 +605,15 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
                             for (int step = 0; step < 2; step++) {
                                 // Rows past the block's were staged as zeros.
                                 const int index = first_row + word * 4 + two * 2 + step;
-                                const uint32_t both =
-                                    reinterpret_cast<const uint32_t *>(tile_row(index))[pair];
+                                const uint32_t both = staged_words[staged_word(index, pair)];
                                 elements[step][0] = divide.quotient<QUICK>(low_half(both));
                                 elements[step][1] = divide.quotient<QUICK>(high_half(both));
                             }
                             halves[0][two] = pack_e4m3(elements[0][0], elements[1][0]);
                             halves[1][two] = pack_e4m3(elements[0][1], elements[1][1]);
                         }
-                        codes[0][word] = __byte_perm(halves[0][0], halves[0][1], 0x5410);
-                        codes[1][word] = __byte_perm(halves[1][0], halves[1][1], 0x5410);
+                        bytes[0][word] = __byte_perm(halves[0][0], halves[0][1], 0x5410);
+                        bytes[1][word] = __byte_perm(halves[1][0], halves[1][1], 0x5410);
                     }
                 });
                 #pragma unroll
@@ -574,7 +622,7 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
                                       (static_cast<int64_t>(head) * HEAD_DIM + which) *
                                           blocks * BLOCK_ROWS;
                     *reinterpret_cast<uint4 *>(target) = make_uint4(
-                        codes[which][0], codes[which][1], codes[which][2], codes[which][3]);
+                        bytes[which][0], bytes[which][1], bytes[which][2], bytes[which][3]);
                 }
             }
         } else if constexpr (QUANTIZE) {
@@ -665,9 +713,19 @@ int launch_as(const InputsParams &params, int blocks, size_t shared, cudaStream_
 template <bool NORMALIZE, bool STATS, bool QUANTIZE>
 int launch(InputsParams params, int blocks, cudaStream_t stream) {
     const bool rotate = NORMALIZE && params.angles != nullptr && params.pairs > 0;
-    // With angles a CTA takes several heads so that their sincosf is paid once; the grid still
-    // holds several CTAs per SM slot.
-    params.heads_per_cta = rotate ? HEADS_PER_CTA : 1;
+    // With angles a CTA takes several heads so that their sincosf is paid once: as many as leave
+    // the grid a few CTAs for every place on the multiprocessors.
+    params.heads_per_cta = 1;
+    if (rotate) {
+        const int wanted = 4 * 2 * max(multiprocessor_count(), 1);
+        params.heads_per_cta = HEADS_PER_CTA;
+        while (params.heads_per_cta > 1 &&
+               static_cast<int64_t>(blocks) *
+                       ((params.heads + params.heads_per_cta - 1) / params.heads_per_cta) <
+                   wanted) {
+            params.heads_per_cta /= 2;
+        }
+    }
     if constexpr (NORMALIZE) {
         if (rotate && params.pairs % 16 == 0) {
             switch (params.pairs / 16) {
