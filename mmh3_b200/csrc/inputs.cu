@@ -300,7 +300,8 @@ __device__ __forceinline__ void rotate_through_shared_memory(RowShare &share, fl
 //
 // SIXTEENTHS is pairs / 16 where the rotary pairs are a multiple of 16, else 0.
 template <bool NORMALIZE, bool STATS, bool QUANTIZE, int SIXTEENTHS>
-__global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p) {
+__global__ void __launch_bounds__(THREADS, (NORMALIZE || QUANTIZE) ? 2 : 4)
+    inputs_kernel(const InputsParams p) {
     extern __shared__ __align__(16) float trig[];
     // The rows as BF16 where V is transposed or sums are pooled. The same memory holds rows of 128
     // floats for the rotary exchange through shared memory; the two uses take turns, a barrier
@@ -563,10 +564,24 @@ __global__ void __launch_bounds__(THREADS, 2) inputs_kernel(const InputsParams p
             // The sums over the rows in row order, one thread per dimension.
             if (threadIdx.x < HEAD_DIM) {
                 const int dimension = threadIdx.x;
+                // The thread's half of a word as the high half of a float, by one permutation.
+                const uint32_t selector = dimension % 2 ? 0x3244u : 0x1044u;
                 float sum = 0.0f;
-                for (int index = 0; index < rows; index++) {
-                    const uint32_t both = staged_words[staged_word(index, dimension / 2)];
-                    sum += dimension % 2 ? high_half(both) : low_half(both);
+                #pragma unroll
+                for (int run = 0; run < BLOCK_ROWS / 16; run++) {
+                    const uint32_t *words = staged_words + staged_word(16 * run, dimension / 2);
+                    if (16 * run + 16 <= rows) {
+                        #pragma unroll
+                        for (int index = 0; index < 16; index++) {
+                            sum += __uint_as_float(
+                                __byte_perm(words[index * (STAGED_STRIDE / 2)], 0u, selector));
+                        }
+                    } else {
+                        for (int index = 0; 16 * run + index < rows; index++) {
+                            sum += __uint_as_float(
+                                __byte_perm(words[index * (STAGED_STRIDE / 2)], 0u, selector));
+                        }
+                    }
                 }
                 p.pooled[part][statistic + dimension] = part == 2 ? sum : sum / rows;
             }
