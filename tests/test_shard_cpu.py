@@ -15,7 +15,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from mmh3_b200.shard import (OverlappedUlyssesAttention, ProjectedUlyssesAttention, Shard,
-                              UlyssesAttention, head_groups, own_projection_rows)
+                              UlyssesAttention, group_sizes, head_groups, own_projection_rows)
 
 HEAD_DIM = 128
 
@@ -58,7 +58,7 @@ def worker(rank, ranks, port, tokens, heads, results):
         # And through the layer that overlaps the groups' exchanges with their attention on a GPU
         # (on CPU ranks its steps run in the same order, one after the other).
         overlapped = torch.zeros_like(output)
-        OverlappedUlyssesAttention(shard, tokens, heads, torch_attention, 2, "cpu",
+        OverlappedUlyssesAttention(shard, tokens, heads, torch_attention, 4, "cpu",
                                    torch.float32).run(qkv[own.start:own.stop].contiguous(),
                                                       overlapped)
         results[rank] = max(error, float((overlapped - whole[own.start:own.stop]).abs().max()))
@@ -149,6 +149,23 @@ def test_head_groups():
     assert all(cut.tokens == shard.tokens and cut.rank == 1 for cut in cuts)
     # More groups than a rank has heads: its empty runs stay, wholly empty groups go.
     assert len(head_groups(Shard.even(0, 2, 10, 2, 1), 4)) == 1
+
+
+def test_ramped_groups_cover_every_head_once():
+    """The overlapped layer's groups: one head first and last where there are heads enough, every
+    head of every rank in exactly one group, and no group empty on every rank."""
+    assert group_sizes(16, 4, ramped=True) == [1, 7, 7, 1]
+    assert group_sizes(8, 4, ramped=True) == [1, 3, 3, 1]
+    assert group_sizes(4, 4, ramped=True) == [1, 1, 1, 1]
+    assert group_sizes(5, 2, ramped=True) == [2, 3]
+    assert group_sizes(3, 4, ramped=True) == [0, 1, 1, 1]
+    for ranks, heads, groups in ((2, 32, 4), (3, 32, 4), (8, 32, 4), (8, 40, 4), (3, 7, 5), (4, 5, 3)):
+        shard = Shard.even(0, ranks, 1000, heads)
+        cuts = head_groups(shard, groups, ramped=True)
+        for peer in range(ranks):
+            seen = [head for cut in cuts for head in cut.heads[peer]]
+            assert seen == list(shard.heads[peer]), (ranks, heads, groups, peer)
+        assert all(any(len(run) for run in cut.heads) for cut in cuts)
 
 
 def test_even_cuts():
