@@ -821,12 +821,11 @@ def run_sharded(args) -> None:
     output = torch.zeros((len(own), heads, HEAD_DIM), dtype=torch.bfloat16, device="cuda")
     host_output = torch.empty((len(own), heads, HEAD_DIM), dtype=torch.bfloat16, pin_memory=True)
 
-    # The layer goes through a group of heads at a time (two heads of every rank at least): on
-    # resident inputs so that one group's exchanges hide behind another's attention, end to end
-    # so that the copies do too.
-    groups = max(1, min(4, len(shard.own_heads) // 2))
-    overlapped = OverlappedUlyssesAttention(shard, tokens, heads, dense,
-                                            max(1, min(4, len(shard.own_heads))), "cuda",
+    # The layer goes through a group of heads at a time (up to four, the first and the last of one
+    # head of every rank): on resident inputs so that one group's exchanges hide behind another's
+    # attention, end to end so that the copies do too.
+    groups = max(1, min(4, len(shard.own_heads)))
+    overlapped = OverlappedUlyssesAttention(shard, tokens, heads, dense, groups, "cuda",
                                             torch.bfloat16, pack=attention.shard_pack,
                                             unpack=attention.shard_unpack)
 

@@ -156,6 +156,10 @@ class HostPipeline:
     ([tokens, 3, heads, 128] and [tokens, heads, 128]), which a 2D copy describes, and the entry
     point takes a group as a pointer offset with the same strides. The copies go through
     cuda-python's runtime binding; torch owns the buffers and the streams.
+
+    Nothing hides the first group's way in and the last group's way out, so those two groups are
+    one head each; and the groups' kernels alternate between two streams, so that the first
+    blocks of one fill the multiprocessors the last blocks of the one before leave idle.
     """
 
     def __init__(self, tokens: int, heads: int, groups: int = 8):
@@ -163,15 +167,16 @@ class HostPipeline:
 
         self.runtime = runtime
         self.tokens, self.heads = tokens, heads
-        groups = max(1, min(groups, heads))
-        each, extra = divmod(heads, groups)
+        from .shard import group_sizes
+
         self.groups = []
         first = 0
-        for group in range(groups):
-            span = each + (1 if group < extra else 0)
-            self.groups.append((first, span))
-            first += span
+        for span in group_sizes(heads, max(1, min(groups, heads)), ramped=True):
+            if span:
+                self.groups.append((first, span))
+                first += span
         self.copy_in, self.copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+        self.second = torch.cuda.Stream()
         self.arrived = [torch.cuda.Event() for _ in self.groups]
         self.attended = [torch.cuda.Event() for _ in self.groups]
         self.finished = torch.cuda.Event()
@@ -199,6 +204,7 @@ class HostPipeline:
         # What the last call left running on the device buffers comes first.
         self.copy_in.wait_stream(current)
         self.copy_out.wait_stream(current)
+        self.second.wait_stream(current)
         pitch = inner * 2
         for index, (first, span) in enumerate(self.groups):
             offset = first * HEAD_DIM * 2
@@ -206,21 +212,24 @@ class HostPipeline:
                            span * HEAD_DIM * 2, tokens * 3, True, self.copy_in)
             self.arrived[index].record(self.copy_in)
         for index, (first, span) in enumerate(self.groups):
-            current.wait_event(self.arrived[index])
+            stream = self.second if index % 2 else current
+            stream.wait_event(self.arrived[index])
             offset = first * HEAD_DIM
             check(
                 _lib.library().mmh3_attention_bf16(
                     _pointer(qkv, offset), _pointer(qkv, inner + offset),
                     _pointer(qkv, 2 * inner + offset), _pointer(output, offset), tokens, span,
-                    3 * inner, 3 * inner, 3 * inner, inner, scale, _stream()),
+                    3 * inner, 3 * inner, 3 * inner, inner, scale,
+                    ctypes.c_void_p(stream.cuda_stream)),
                 "mmh3_attention_bf16",
             )
-            self.attended[index].record(current)
+            self.attended[index].record(stream)
             self.copy_out.wait_event(self.attended[index])
             self.copy_rows(host_output.data_ptr() + offset * 2, output.data_ptr() + offset * 2,
                            pitch, span * HEAD_DIM * 2, tokens, False, self.copy_out)
         self.finished.record(self.copy_out)
         current.wait_event(self.finished)
+        current.wait_stream(self.second)
 
 
 # -------------------------------------------------------------------------------------------------

@@ -255,10 +255,12 @@ class OverlappedUlyssesAttention:
 
 class HostUlyssesPipeline:
     """`UlyssesAttention` from this rank's rows in pinned host memory to its rows of the output in
-    pinned host memory, a group of heads at a time (`head_groups`): while one group is exchanged
-    and attended, the rows of the next cross the bus and the output of the last goes back, on three
-    streams, as `attention.HostPipeline` does on one GPU. A group's heads are one run per rank, so
-    its rows are that many strided 2D copies each way."""
+    pinned host memory, a group of heads at a time (`head_groups`, the first and the last group one
+    head of every rank): a group's rows cross the bus on one stream, are packed and exchanged on a
+    second (of higher priority, as in `OverlappedUlyssesAttention`), attended on the caller's or a
+    third in turn, exchanged back on the second and copied out on a fourth, so that every stage
+    of one group runs beside other stages of its neighbours. A group's heads are one run per rank,
+    so its rows are that many strided 2D copies each way."""
 
     def __init__(self, shard: Shard, total_tokens: int, heads: int, attention: AttentionFn,
                  groups: int, pack: PackFn | None = None, unpack: PackFn | None = None,
@@ -267,14 +269,17 @@ class HostUlyssesPipeline:
 
         self.shard, self.heads = shard, heads
         self.own_tokens = len(shard.own_tokens)
-        self.cuts = [shard] if shard.is_whole else head_groups(shard, groups)
+        self.cuts = [shard] if shard.is_whole else head_groups(shard, groups, ramped=True)
         self.layers = [UlyssesAttention(cut, total_tokens, heads, attention, "cuda",
                                         torch.bfloat16, pack, unpack, group)
                        for cut in self.cuts]
         # Only its streams and its 2D copy are used.
         self.copies = HostPipeline(total_tokens, heads, groups=1)
+        self.exchange = torch.cuda.Stream(priority=-1)
         self.arrived = [torch.cuda.Event() for _ in self.cuts]
+        self.gathered = [torch.cuda.Event() for _ in self.cuts]
         self.attended = [torch.cuda.Event() for _ in self.cuts]
+        self.returned = [torch.cuda.Event() for _ in self.cuts]
         self.finished = torch.cuda.Event()
 
     def _rows(self, device: torch.Tensor, host: torch.Tensor, cut: Shard, tensors: int,
@@ -293,20 +298,49 @@ class HostUlyssesPipeline:
             host_output: torch.Tensor) -> None:
         """Enqueues everything and returns; the current stream ends up behind the last copy."""
         copy_in, copy_out = self.copies.copy_in, self.copies.copy_out
+        second, exchange = self.copies.second, self.exchange
         current = torch.cuda.current_stream()
-        copy_in.wait_stream(current)
-        copy_out.wait_stream(current)
+        for stream in (copy_in, copy_out, second, exchange):
+            stream.wait_stream(current)
         for index, cut in enumerate(self.cuts):
             self._rows(qkv, host_qkv, cut, 3, True, copy_in)
             self.arrived[index].record(copy_in)
+        if self.shard.is_whole:
+            current.wait_event(self.arrived[0])
+            self.layers[0].run(qkv, output)
+            self.attended[0].record(current)
+            copy_out.wait_event(self.attended[0])
+            self._rows(output, host_output, self.cuts[0], 1, False, copy_out)
+            self.finished.record(copy_out)
+            current.wait_event(self.finished)
+            return
+
+        def way_in(index: int) -> None:
+            with torch.cuda.stream(exchange):
+                exchange.wait_event(self.arrived[index])
+                self.layers[index].exchange_inputs(qkv)
+                self.gathered[index].record(exchange)
+
+        # The exchange stream, the same on every rank: in(0), in(1), out(0), in(2), out(1), ...
+        way_in(0)
         for index, (cut, layer) in enumerate(zip(self.cuts, self.layers)):
-            current.wait_event(self.arrived[index])
-            layer.run(qkv, output)
-            self.attended[index].record(current)
-            copy_out.wait_event(self.attended[index])
+            if index + 1 < len(self.cuts):
+                way_in(index + 1)
+            stream = second if index % 2 else current
+            with torch.cuda.stream(stream):
+                stream.wait_event(self.gathered[index])
+                layer.attend()
+                self.attended[index].record(stream)
+            with torch.cuda.stream(exchange):
+                exchange.wait_event(self.attended[index])
+                layer.exchange_outputs(output)
+                self.returned[index].record(exchange)
+            copy_out.wait_event(self.returned[index])
             self._rows(output, host_output, cut, 1, False, copy_out)
         self.finished.record(copy_out)
         current.wait_event(self.finished)
+        current.wait_stream(second)
+        current.wait_stream(exchange)
 
 
 # project(rows INT8 [count, hidden], scales FP32 [count], qkv [count, 3, own heads, 128]): the

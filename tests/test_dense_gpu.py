@@ -318,8 +318,9 @@ def test_unsupported_combinations_report_an_error():
 
 @pytest.mark.parametrize("groups", [1, 4])
 def test_host_pipeline_equals_one_call(groups):
-    """Pinned host buffers in and out, a group of heads at a time on three streams: the same bits
-    as one call over device buffers, twice in a row over the same buffers."""
+    """Pinned host buffers in and out, a group of heads at a time on four streams (the first and
+    the last group one head each): the same bits as one call over device buffers, twice in a row
+    over the same buffers."""
     tokens, heads = 700, 6
     host_qkv = synthetic.dense_qkv(tokens, heads, seed=21, pinned=True)
     expected = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
@@ -328,7 +329,7 @@ def test_host_pipeline_equals_one_call(groups):
     output = torch.zeros_like(expected)
     host_output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16).pin_memory()
     pipeline = attention.HostPipeline(tokens, heads, groups=groups)
-    assert [span for _, span in pipeline.groups] == ([6] if groups == 1 else [2, 2, 1, 1])
+    assert [span for _, span in pipeline.groups] == ([6] if groups == 1 else [1, 2, 2, 1])
     for _ in range(2):
         host_output.zero_()
         pipeline.run(host_qkv, qkv, output, host_output, SCALE)
