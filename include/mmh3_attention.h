@@ -79,8 +79,10 @@ typedef struct Mmh3VsaWorkspace {
 
 /* Dense softmax(Q K^T * scale) V. element_type 0 is BF16 and 1 is FP16; head_dim 64 or 128.
  * Causal or not, with grouped key/value heads and batches: the DiT's, the text encoder's and the
- * VAE decoder's uses. `scale` must be positive; layouts TMA cannot describe (bases or strides that
- * are not multiples of 16 bytes) return cudaErrorNotSupported.
+ * VAE decoder's uses. `scale` must be positive. Operands TMA cannot describe (bases or strides that
+ * are not multiples of 16 bytes) are first gathered into dense arrays in stream-ordered scratch
+ * (cudaMallocAsync on `stream`, given back with cudaFreeAsync behind the kernel); the result is
+ * the same bits.
  * Replaces crates/mmh3-cuda/kernels/attention.cu:531-536. */
 int mmh3_attention(int element_type, int head_dim, const void *query, const void *key,
                    const void *value, void *output, int tokens, int heads, int batch,

@@ -381,6 +381,35 @@ class VsaWorkspace:
         selected = int(self.route_counts.to(torch.int64).sum().item())
         return selected / (self.heads * self.tiles * self.tiles)
 
+    def route_overlap(self) -> tuple[int, float, float]:
+        """How much neighbouring query tiles share (attention.rs:1005-1048): the pairs (2i, 2i + 1)
+        with any selection, the mean number of tiles the two load between them, and the mean
+        number of distinct tiles, which is what one block over both rows loads. A diagnostic, not
+        a hot path; the token attention's CTAs take exactly these pairs."""
+        tiles, heads = self.tiles, self.heads
+        counts = self.route_counts.view(heads, tiles).to(torch.int64)
+        routes = self.routes.view(heads, tiles, tiles).to(torch.int64) & 0xFFFF
+        entries = torch.arange(tiles, device=routes.device)
+        pairs, separate, merged = 0, 0.0, 0.0
+        even = tiles - tiles % 2
+        for head in range(heads):
+            listed = entries[None, :] < counts[head][:, None]
+            selected = torch.zeros((tiles, tiles + 1), dtype=torch.bool, device=routes.device)
+            # Entries past a row's count, and targets past the last tile, go to a spare column.
+            targets = torch.where(listed & (routes[head] < tiles), routes[head],
+                                  torch.full_like(routes[head], tiles))
+            selected.scatter_(1, targets, True)
+            selected = selected[:even, :tiles]
+            both = counts[head][:even].view(-1, 2).sum(dim=1)
+            some = both > 0
+            pairs += int(some.sum().item())
+            separate += float(both[some].sum().item())
+            merged += float((selected[0::2] | selected[1::2])[some].sum().item())
+        if pairs:
+            separate /= pairs
+            merged /= pairs
+        return pairs, separate, merged
+
     def routes_host(self):
         """Routes [heads, tiles, tiles] as uint16 and counts [heads, tiles], on the host."""
         routes = self.routes.cpu().numpy().view("uint16").reshape(self.heads, self.tiles,

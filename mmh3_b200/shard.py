@@ -17,6 +17,8 @@ onto its own heads.
 from __future__ import annotations
 
 import dataclasses
+import os
+import time
 from typing import Callable
 
 import torch
@@ -63,6 +65,45 @@ class Shard:
     @property
     def is_whole(self) -> bool:
         return self.ranks == 1
+
+
+# The stretches of a shared block in the order it runs them, under the reference's names
+# (crates/mmh3-core/src/shard.rs:455-486).
+STRETCH_NAMES = ("before", "publish", "own projections", "input exchange", "peer projections",
+                 "attention", "output exchange")
+
+
+def profile() -> str:
+    """How a shared step is timed, from MMH3_SHARD_PROFILE (shard.rs:488-502): "sync" waits for
+    the device at the end of every stretch, which gives up the overlap between them and says where
+    the time went; anything else is "off". (The reference's "no-copies" leaves out the copies
+    between the ranks of one process; here a rank is a process.)"""
+    return "sync" if os.environ.get("MMH3_SHARD_PROFILE") == "sync" else "off"
+
+
+class ShardTiming:
+    """Where a profiled shared step went: seconds per stretch (shard.rs:413-452)."""
+
+    def __init__(self, device=None):
+        self.stretches = dict.fromkeys(STRETCH_NAMES, 0.0)
+        self.mark = None
+        self.device = device
+
+    def end(self, stretch: str) -> None:
+        """Ends `stretch` now, the device done with it. The first stretch of a step starts the
+        clock rather than being charged, since it has no end before it."""
+        if self.device is not None and torch.device(self.device).type == "cuda":
+            torch.cuda.synchronize()
+        now = time.perf_counter()
+        if self.mark is not None:
+            self.stretches[stretch] += now - self.mark
+        self.mark = now
+
+    def total(self) -> float:
+        return sum(self.stretches.values())
+
+    def describe_stretches(self) -> str:
+        return ", ".join(f"{name} {spent:.2f} s" for name, spent in self.stretches.items())
 
 
 # attention(qkv [tokens, 3, heads, 128], output [tokens, heads, 128], tokens, heads)
@@ -112,6 +153,8 @@ class UlyssesAttention:
         self.input_recv_splits = [len(peer) * 3 * own_heads * HEAD_DIM for peer in shard.tokens]
         self.output_send_splits = [len(peer) * own_heads * HEAD_DIM for peer in shard.tokens]
         self.output_recv_splits = [own_tokens * len(peer) * HEAD_DIM for peer in shard.heads]
+        # Filled by `run` when MMH3_SHARD_PROFILE=sync.
+        self.timing = ShardTiming(device)
 
     def exchange_bytes(self) -> int:
         """Bytes this rank sends to other ranks per layer."""
@@ -124,11 +167,18 @@ class UlyssesAttention:
         if self.shard.is_whole:
             self.attention(qkv_own, output_own, self.tokens, self.heads)
             return
-        self.exchange_inputs(qkv_own)
+        timing = self.timing if profile() == "sync" else None
+        if timing is not None:
+            timing.end("before")
+        self.exchange_inputs(qkv_own, timing)
         self.attend()
+        if timing is not None:
+            timing.end("attention")
         self.exchange_outputs(output_own)
+        if timing is not None:
+            timing.end("output exchange")
 
-    def exchange_inputs(self, qkv_own: torch.Tensor) -> None:
+    def exchange_inputs(self, qkv_own: torch.Tensor, timing: ShardTiming | None = None) -> None:
         """Turns "my tokens, every head" into "every token, my heads" in `inputs`: every peer's
         heads of this rank's rows packed, then the all-to-all."""
         offset = 0
@@ -138,8 +188,12 @@ class UlyssesAttention:
                 self.pack(qkv_own, self.send_inputs[offset:offset + count], self.own_tokens, 3,
                           self.heads, heads.start, len(heads))
             offset += count
+        if timing is not None:
+            timing.end("publish")
         dist.all_to_all_single(self.inputs, self.send_inputs, self.input_recv_splits,
                                self.input_send_splits, group=self.group)
+        if timing is not None:
+            timing.end("input exchange")
 
     def attend(self) -> None:
         """The attention of every token on this rank's heads, `inputs` to `attended`."""

@@ -310,10 +310,60 @@ def test_unsupported_combinations_report_an_error():
     # more rotary pairs than half a head
     assert library.mmh3_attention_roped(0, 64, *arguments, angles.data_ptr(), 33, 1e-6,
                                         None) == _lib.CUDA_ERROR_INVALID_VALUE
-    # a layout TMA cannot describe: a token stride that is not a multiple of 16 bytes
-    odd = attention.make_layout((3 * 128 + 1,) * 3 + (128,))
-    arguments = arguments[:7] + (ctypes.byref(odd),) + arguments[8:]
-    assert library.mmh3_attention(0, 128, *arguments, None) == _lib.CUDA_ERROR_NOT_SUPPORTED
+
+
+@pytest.mark.parametrize("element_type,head_dim,group,causal",
+                         [(0, 128, 1, 0), (1, 64, 1, 0), (0, 128, 2, 1)])
+def test_layouts_off_the_tma_grid_equal_aligned_ones(element_type, head_dim, group, causal):
+    """Operands whose base or strides are not multiples of 16 bytes: the reference copies them with
+    cp.async instead of TMA and asks for the same bits either way
+    (crates/mmh3-cuda/tests/attention.rs:91-114). Here they are gathered into dense arrays first,
+    and the output must be the bits of the same values in an aligned layout."""
+    tokens, heads = 200, 4
+    kv_heads = heads // group
+    dtype = torch.float16 if element_type else torch.bfloat16
+    generator = torch.Generator(device="cpu").manual_seed(31)
+    query = (torch.rand((tokens, heads, head_dim), generator=generator) * 4 - 2).to(dtype).cuda()
+    key = (torch.rand((tokens, kv_heads, head_dim), generator=generator) * 4 - 2).to(dtype).cuda()
+    value = (torch.rand((tokens, kv_heads, head_dim), generator=generator) * 4 - 2).to(dtype).cuda()
+    library = _lib.library()
+    scale = 1.0 / head_dim ** 0.5
+
+    def run(operands, token_strides, head_strides):
+        output = torch.zeros((tokens, heads, head_dim), dtype=dtype, device="cuda")
+        layout = attention.make_layout(tuple(token_strides) + (heads * head_dim,),
+                                       tuple(head_strides) + (head_dim,),
+                                       heads_per_key_value=group if group > 1 else 0,
+                                       causal=causal)
+        assert library.mmh3_attention(element_type, head_dim, *operands, output.data_ptr(), tokens,
+                                      heads, 1, ctypes.byref(layout), scale, None) == 0
+        torch.cuda.synchronize()
+        assert attention.take_status() == 0
+        return output
+
+    aligned = run([tensor.data_ptr() for tensor in (query, key, value)],
+                  [heads * head_dim, kv_heads * head_dim, kv_heads * head_dim], [head_dim] * 3)
+
+    # The same values two bytes off a 16-byte boundary, with a token stride of an odd number of
+    # elements and heads head_dim + 2 elements apart.
+    def shifted(tensor):
+        count = tensor.shape[1]
+        head_stride = head_dim + 2
+        token_stride = count * head_stride + 1
+        storage = torch.zeros(tokens * token_stride + 16, dtype=dtype, device="cuda")
+        view = torch.as_strided(storage, (tokens, count, head_dim), (token_stride, head_stride, 1), 1)
+        view.copy_(tensor)
+        return storage, storage.data_ptr() + 2, token_stride, head_stride
+
+    storages = [shifted(tensor) for tensor in (query, key, value)]
+    moved = run([entry[1] for entry in storages], [entry[2] for entry in storages],
+                [entry[3] for entry in storages])
+    assert torch.equal(moved.view(torch.int16), aligned.view(torch.int16))
+    # One operand off the grid is enough to take the copy, and the others are left where they are.
+    mixed = run([storages[0][1], key.data_ptr(), value.data_ptr()],
+                [storages[0][2], kv_heads * head_dim, kv_heads * head_dim],
+                [storages[0][3], head_dim, head_dim])
+    assert torch.equal(mixed.view(torch.int16), aligned.view(torch.int16))
 
 
 @pytest.mark.parametrize("groups", [1, 4])

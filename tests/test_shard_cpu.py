@@ -55,6 +55,18 @@ def worker(rank, ranks, port, tokens, heads, results):
             UlyssesAttention(cut, tokens, heads, torch_attention, "cpu", torch.float32).run(
                 qkv[own.start:own.stop].contiguous(), grouped)
         error = max(error, float((grouped - whole[own.start:own.stop]).abs().max()))
+        # A profiled step charges every stretch it has and leaves the result alone
+        # (MMH3_SHARD_PROFILE=sync, crates/mmh3-core/src/shard.rs:413-502).
+        os.environ["MMH3_SHARD_PROFILE"] = "sync"
+        profiled = torch.zeros_like(output)
+        for _ in range(2):
+            layer.run(qkv[own.start:own.stop].contiguous(), profiled)
+        del os.environ["MMH3_SHARD_PROFILE"]
+        spent = layer.timing.stretches
+        assert torch.equal(profiled, output)
+        assert all(spent[name] > 0.0 for name in ("before", "publish", "input exchange",
+                                                  "attention", "output exchange"))
+        assert spent["own projections"] == 0.0 and "attention" in layer.timing.describe_stretches()
         # And through the layer that overlaps the groups' exchanges with their attention on a GPU
         # (on CPU ranks its steps run in the same order, one after the other).
         overlapped = torch.zeros_like(output)

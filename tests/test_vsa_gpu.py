@@ -108,6 +108,19 @@ def test_matches_the_reference(oracle, reference_kernels, heads, sparsity, gated
     # Routing: closed form, CPU oracle, and the reference's kernels.
     assert abs(workspace.selected_fraction() - plan.expected_selected_fraction(kept)) < 1e-9
     routes, counts = workspace.routes_host()
+    # The neighbour-overlap diagnostic against the reference's loops (attention.rs:1023-1047).
+    pairs, separate, merged = 0, 0.0, 0.0
+    for head in range(heads):
+        for tile in range(0, plan.tiles - 1, 2):
+            lists = [routes[head, other, :counts[head, other]] for other in (tile, tile + 1)]
+            if len(lists[0]) + len(lists[1]) == 0:
+                continue
+            pairs += 1
+            separate += len(lists[0]) + len(lists[1])
+            merged += len({int(target) for target in np.concatenate(lists) if target < plan.tiles})
+    found = workspace.route_overlap()
+    assert found[0] == pairs
+    assert abs(found[1] - separate / pairs) < 1e-9 and abs(found[2] - merged / pairs) < 1e-9
     pooled, oracle_route_list, oracle_counts = oracle_routes(oracle, plan, bits, heads, kept)
     for ours, theirs in zip((workspace.pooled_query, workspace.pooled_key, workspace.pooled_value),
                             pooled):
