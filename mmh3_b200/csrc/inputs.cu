@@ -113,6 +113,16 @@ struct Divider {
         }
         return __fdiv_rn(x, scale);
     }
+    // Two quotients at a time, as two independent IEEE operations per packed instruction;
+    // q * (-scale) + x is the same number as -q * scale + x.
+    template <bool QUICK> __device__ __forceinline__ float2 quotients(float2 x) const {
+        if (QUICK) {
+            const float2 estimate = __fmul2_rn(x, make_float2(reciprocal, reciprocal));
+            const float2 residual = __ffma2_rn(estimate, make_float2(-scale, -scale), x);
+            return __ffma2_rn(residual, make_float2(reciprocal, reciprocal), estimate);
+        }
+        return make_float2(__fdiv_rn(x.x, scale), __fdiv_rn(x.y, scale));
+    }
     // `body(std::true_type)` where the quick quotient is right, `body(std::false_type)` otherwise.
     template <typename Body> __device__ __forceinline__ void dispatch(const Body &body) const {
         if (exact) {
@@ -131,6 +141,10 @@ template <int LEVELS> __device__ __forceinline__ float scale_for(float maximum) 
 }
 
 __device__ __forceinline__ float low_half(uint32_t word) { return __uint_as_float(word << 16); }
+// The two BF16 values of a word as floats, the low half first.
+__device__ __forceinline__ float2 both_halves(uint32_t word) {
+    return make_float2(__uint_as_float(word << 16), __uint_as_float(word & 0xffff0000u));
+}
 __device__ __forceinline__ float high_half(uint32_t word) {
     return __uint_as_float(word & 0xffff0000u);
 }
@@ -150,12 +164,12 @@ __device__ __forceinline__ uint32_t pack_e4m3(float low, float high) {
 }
 
 // The integers nearest to four quotients of magnitude at most 127, as four bytes.
-__device__ __forceinline__ uint32_t pack_int8(float a, float b, float c, float d) {
-    const uint32_t first = __byte_perm(__float_as_uint(__fadd_rn(a, ROUNDING_MAGIC)),
-                                       __float_as_uint(__fadd_rn(b, ROUNDING_MAGIC)), 0x0040);
-    const uint32_t second = __byte_perm(__float_as_uint(__fadd_rn(c, ROUNDING_MAGIC)),
-                                        __float_as_uint(__fadd_rn(d, ROUNDING_MAGIC)), 0x0040);
-    return __byte_perm(first, second, 0x5410);
+__device__ __forceinline__ uint32_t pack_int8(float2 low, float2 high) {
+    const float2 magic = make_float2(ROUNDING_MAGIC, ROUNDING_MAGIC);
+    const float2 first = __fadd2_rn(low, magic), second = __fadd2_rn(high, magic);
+    return __byte_perm(
+        __byte_perm(__float_as_uint(first.x), __float_as_uint(first.y), 0x0040),
+        __byte_perm(__float_as_uint(second.x), __float_as_uint(second.y), 0x0040), 0x5410);
 }
 
 // The largest magnitude among four BF16 values.
@@ -164,18 +178,17 @@ __device__ __forceinline__ float group_max(const uint2 &group) {
                  fmaxf(fabsf(low_half(group.y)), fabsf(high_half(group.y))));
 }
 
-// A thread's share of a row as floats: values[G][i] is dimension 16 G + 4 c + i, c the thread's
-// place among the four of its row.
+// A thread's share of a row as floats: values[G][j] holds dimensions 16 G + 4 c + 2 j and the
+// next, c the thread's place among the four of its row. The arithmetic runs on such pairs with
+// the packed FP32 instructions, each half an IEEE operation of its own.
 struct RowShare {
-    float values[GROUPS][4];
+    float2 values[GROUPS][2];
 
     __device__ __forceinline__ void unpack(const uint2 (&groups)[GROUPS]) {
         #pragma unroll
         for (int group = 0; group < GROUPS; group++) {
-            values[group][0] = low_half(groups[group].x);
-            values[group][1] = high_half(groups[group].x);
-            values[group][2] = low_half(groups[group].y);
-            values[group][3] = high_half(groups[group].y);
+            values[group][0] = both_halves(groups[group].x);
+            values[group][1] = both_halves(groups[group].y);
         }
     }
 
@@ -186,30 +199,47 @@ struct RowShare {
     // of i, in this thread), and an addition gives both of its sides the same bits, so every
     // thread ends with the sum any lane of a 32-lane butterfly would hold.
     __device__ __forceinline__ float sum_of_squares() const {
-        float sums[4];
+        float2 sums[2]; // chains i = 0, 1 and i = 2, 3
         #pragma unroll
-        for (int index = 0; index < 4; index++) {
-            float chains[2];
+        for (int two = 0; two < 2; two++) {
+            float2 chains[2];
             #pragma unroll
             for (int half = 0; half < 2; half++) {
-                float squares = 0.0f;
+                float2 squares = make_float2(0.0f, 0.0f);
                 #pragma unroll
                 for (int step = 0; step < GROUPS / 2; step++) {
-                    const float value = values[2 * step + half][index];
-                    squares = __fmaf_rn(value, value, squares);
+                    const float2 value = values[2 * step + half][two];
+                    squares = __ffma2_rn(value, value, squares);
                 }
                 chains[half] = squares;
             }
-            sums[index] = chains[0] + chains[1];
+            sums[two] = __fadd2_rn(chains[0], chains[1]);
         }
         #pragma unroll
         for (int offset = ROW_THREADS / 2; offset > 0; offset /= 2) {
             #pragma unroll
-            for (int index = 0; index < 4; index++) {
-                sums[index] += __shfl_xor_sync(0xffffffffu, sums[index], offset);
+            for (int two = 0; two < 2; two++) {
+                sums[two] = __fadd2_rn(
+                    sums[two], make_float2(__shfl_xor_sync(0xffffffffu, sums[two].x, offset),
+                                           __shfl_xor_sync(0xffffffffu, sums[two].y, offset)));
             }
         }
-        return (sums[0] + sums[2]) + (sums[1] + sums[3]);
+        // Level 2 pairs i with i ^ 2, level 1 what is left.
+        const float2 last = __fadd2_rn(sums[0], sums[1]);
+        return last.x + last.y;
+    }
+
+    // Every value times `inverse` times its weight, the product of those two first.
+    __device__ __forceinline__ void scale(float inverse, const float *weights, int place) {
+        const float2 inverses = make_float2(inverse, inverse);
+        #pragma unroll
+        for (int group = 0; group < GROUPS; group++) {
+            const float4 weight = *reinterpret_cast<const float4 *>(weights + 16 * group + 4 * place);
+            values[group][0] =
+                __fmul2_rn(values[group][0], __fmul2_rn(inverses, make_float2(weight.x, weight.y)));
+            values[group][1] =
+                __fmul2_rn(values[group][1], __fmul2_rn(inverses, make_float2(weight.z, weight.w)));
+        }
     }
 
     // The largest magnitude among the values, two at a time with the three-input maximum.
@@ -221,7 +251,7 @@ struct RowShare {
             for (int two = 0; two < 2; two++) {
                 asm("max.f32 %0, %0, %1, %2;"
                     : "+f"(maxima[two])
-                    : "f"(fabsf(values[group][2 * two])), "f"(fabsf(values[group][2 * two + 1])));
+                    : "f"(fabsf(values[group][two].x)), "f"(fabsf(values[group][two].y)));
             }
         }
         return fmaxf(maxima[0], maxima[1]);
@@ -231,8 +261,8 @@ struct RowShare {
     __device__ __forceinline__ void pack(uint2 (&groups)[GROUPS]) const {
         #pragma unroll
         for (int group = 0; group < GROUPS; group++) {
-            groups[group] = make_uint2(pack_bf16(values[group][0], values[group][1]),
-                                       pack_bf16(values[group][2], values[group][3]));
+            groups[group] = make_uint2(pack_bf16(values[group][0].x, values[group][0].y),
+                                       pack_bf16(values[group][1].x, values[group][1].y));
         }
     }
 };
@@ -240,8 +270,8 @@ struct RowShare {
 // The cosines and sines of a thread's pairs where pairs are a multiple of 16: pair 16 G + 4 c + i
 // for the first pairs / 16 values of G.
 struct PairAngles {
-    float cosines[GROUPS / 2][4];
-    float sines[GROUPS / 2][4];
+    float2 cosines[GROUPS / 2][2];
+    float2 sines[GROUPS / 2][2];
 };
 
 // The split-half rotary embedding where dimension d < pairs = 16 * SIXTEENTHS turns with
@@ -251,14 +281,16 @@ __device__ __forceinline__ void rotate_in_thread(RowShare &share, const PairAngl
     #pragma unroll
     for (int group = 0; group < SIXTEENTHS; group++) {
         #pragma unroll
-        for (int index = 0; index < 4; index++) {
-            const float cosine = angles.cosines[group][index];
-            const float sine = angles.sines[group][index];
-            const float first = share.values[group][index];
-            const float second = share.values[group + SIXTEENTHS][index];
-            share.values[group][index] = __fmaf_rn(cosine, first, -__fmul_rn(sine, second));
-            share.values[group + SIXTEENTHS][index] =
-                __fmaf_rn(sine, first, __fmul_rn(cosine, second));
+        for (int two = 0; two < 2; two++) {
+            const float2 cosine = angles.cosines[group][two];
+            const float2 sine = angles.sines[group][two];
+            const float2 first = share.values[group][two];
+            const float2 second = share.values[group + SIXTEENTHS][two];
+            const float2 crossed = __fmul2_rn(sine, second);
+            share.values[group][two] =
+                __ffma2_rn(cosine, first, make_float2(-crossed.x, -crossed.y));
+            share.values[group + SIXTEENTHS][two] =
+                __ffma2_rn(sine, first, __fmul2_rn(cosine, second));
         }
     }
 }
@@ -273,8 +305,8 @@ __device__ __forceinline__ void rotate_through_shared_memory(RowShare &share, fl
     #pragma unroll
     for (int group = 0; group < GROUPS; group++) {
         *reinterpret_cast<float4 *>(mine + 16 * group + 4 * place) =
-            make_float4(share.values[group][0], share.values[group][1], share.values[group][2],
-                        share.values[group][3]);
+            make_float4(share.values[group][0].x, share.values[group][0].y,
+                        share.values[group][1].x, share.values[group][1].y);
     }
     __syncwarp();
     #pragma unroll
@@ -282,7 +314,8 @@ __device__ __forceinline__ void rotate_through_shared_memory(RowShare &share, fl
         #pragma unroll
         for (int index = 0; index < 4; index++) {
             const int dimension = 16 * group + 4 * place + index;
-            float &value = share.values[group][index];
+            float &value = index % 2 ? share.values[group][index / 2].y
+                                     : share.values[group][index / 2].x;
             if (dimension < pairs) {
                 value = __fmaf_rn(cosines[dimension], value,
                                   -__fmul_rn(sines[dimension], mine[dimension + pairs]));
@@ -439,9 +472,11 @@ __global__ void __launch_bounds__(THREADS, (NORMALIZE || QUANTIZE) ? 2 : 4)
                 for (int slot = 0; slot < SIXTEENTHS; slot++) {
                     if (slot == group) {
                         #pragma unroll
-                        for (int index = 0; index < 4; index++) {
-                            angles.cosines[slot][index] = found[0][index];
-                            angles.sines[slot][index] = found[1][index];
+                        for (int two = 0; two < 2; two++) {
+                            angles.cosines[slot][two] =
+                                make_float2(found[0][2 * two], found[0][2 * two + 1]);
+                            angles.sines[slot][two] =
+                                make_float2(found[1][2 * two], found[1][2 * two + 1]);
                         }
                     }
                 }
@@ -483,17 +518,7 @@ __global__ void __launch_bounds__(THREADS, (NORMALIZE || QUANTIZE) ? 2 : 4)
             share.unpack(groups);
             const float squares = share.sum_of_squares();
             const float inverse = rsqrtf(__fmaf_rn(squares, 1.0f / HEAD_DIM, p.epsilon));
-            #pragma unroll
-            for (int group = 0; group < GROUPS; group++) {
-                const float4 weight =
-                    *reinterpret_cast<const float4 *>(&weights[part][16 * group + 4 * place]);
-                const float factors[4] = {weight.x, weight.y, weight.z, weight.w};
-                #pragma unroll
-                for (int index = 0; index < 4; index++) {
-                    share.values[group][index] = __fmul_rn(
-                        share.values[group][index], __fmul_rn(inverse, factors[index]));
-                }
-            }
+            share.scale(inverse, weights[part], place);
             if (SIXTEENTHS != 0) {
                 rotate_in_thread<SIXTEENTHS>(share, angles);
             } else if (rotation == THROUGH_SHARED_MEMORY) {
@@ -621,8 +646,10 @@ __global__ void __launch_bounds__(THREADS, (NORMALIZE || QUANTIZE) ? 2 : 4)
                                 // Rows past the block's were staged as zeros.
                                 const int index = first_row + word * 4 + two * 2 + step;
                                 const uint32_t both = staged_words[staged_word(index, pair)];
-                                elements[step][0] = divide.quotient<QUICK>(low_half(both));
-                                elements[step][1] = divide.quotient<QUICK>(high_half(both));
+                                const float2 divided =
+                                    divide.quotients<QUICK>(both_halves(both));
+                                elements[step][0] = divided.x;
+                                elements[step][1] = divided.y;
                             }
                             halves[0][two] = pack_e4m3(elements[0][0], elements[1][0]);
                             halves[1][two] = pack_e4m3(elements[0][1], elements[1][1]);
@@ -654,10 +681,8 @@ __global__ void __launch_bounds__(THREADS, (NORMALIZE || QUANTIZE) ? 2 : 4)
                 #pragma unroll
                 for (int group = 0; group < GROUPS; group++) {
                     *reinterpret_cast<uint32_t *>(&codes[row][16 * group + 4 * place]) =
-                        pack_int8(divide.quotient<QUICK>(low_half(groups[group].x)),
-                                  divide.quotient<QUICK>(high_half(groups[group].x)),
-                                  divide.quotient<QUICK>(low_half(groups[group].y)),
-                                  divide.quotient<QUICK>(high_half(groups[group].y)));
+                        pack_int8(divide.quotients<QUICK>(both_halves(groups[group].x)),
+                                  divide.quotients<QUICK>(both_halves(groups[group].y)));
                 }
             });
             __syncwarp();
