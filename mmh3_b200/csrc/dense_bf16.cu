@@ -118,7 +118,10 @@ template <bool HALF, int DIM = 128> struct Element {
 // The maximum may lag the true row maximum by this much (in log2 units) before O is rescaled.
 constexpr float RESCALE_THRESHOLD = 8.0f;
 // Of every four pairs of probabilities, how many take the polynomial exp2 instead of the MUFU.
-constexpr int POLYNOMIAL_PAIRS_OF_4 = 1;
+// One in four costs fewer cycles a block (3,466 against 3,543) and more power: over the twenty
+// launches of a benchmark run the GPU sits at its power cap, where none in four runs at 1,627 MHz
+// instead of 1,582 and is the faster by 0.6 % (2 % in the token attention over routes).
+constexpr int POLYNOMIAL_PAIRS_OF_4 = 0;
 
 struct DenseMaps {
     CUtensorMap query;
@@ -476,9 +479,8 @@ __global__ void __launch_bounds__(THREADS, 1)
                     }
                 }
             }
-            // p = 2^(s * scale - maximum * scale), two elements at a time. One pair in four takes
-            // the polynomial on the FMA pipe: the MUFU alone would need as long for a tile's
-            // exponentials as the tensor pipe needs for its two MMAs.
+            // p = 2^(s * scale - maximum * scale), two elements at a time, on the MUFU (or a share
+            // of the pairs on the FMA pipe's polynomial, see POLYNOMIAL_PAIRS_OF_4).
             const float offset = maximum * scale_log2;
             const float2 scale2 = make_float2(scale_log2, scale_log2);
             const float2 offset2 = make_float2(-offset, -offset);

@@ -56,8 +56,10 @@ constexpr uint32_t TMEM_OUTPUT = 128;
 // scaled by 224 instead of the reference's 448.
 template <bool QUANTIZED> constexpr float RESCALE_LAG = QUANTIZED ? 1.0f : 8.0f;
 constexpr float LOG2_224 = 7.807354922057604f;
-// Of every four pairs of probabilities, how many take the polynomial exp2 instead of the MUFU.
-constexpr int POLYNOMIAL_PAIRS_OF_4 = 1;
+// Of every four pairs of probabilities, how many take the polynomial exp2 instead of the MUFU:
+// none, which at the power cap a layer's worth of launches runs into is 2 % faster than one in
+// four (fewer instructions, a higher clock), as in dense_bf16.cu.
+constexpr int POLYNOMIAL_PAIRS_OF_4 = 0;
 // In the INT8/FP8 form every exponential takes the MUFU, and an integer score s, |s| < 2^22,
 // becomes the float 1.5 * 2^23 + s by adding these bits to it, as in quantized_attention.cu.
 constexpr int32_t MAGIC_BITS = 0x4B400000;
@@ -523,8 +525,7 @@ __global__ void __launch_bounds__(THREADS, 2)
                                        float factor, uint32_t own_p, uint32_t other_p,
                                        bool shared) {
             constexpr bool MASKED = decltype(masked)::value;
-            // p = 2^(factor * score - maximum), times 224 for E4M3; pairs of elements, in BF16
-            // one pair in four on the polynomial.
+            // p = 2^(factor * score - maximum), times 224 for E4M3; pairs of elements.
             // (MAGIC + s) * factor + (offset - MAGIC * factor) = s * factor + offset, the product
             // exact inside the FMA.
             const float offset =
