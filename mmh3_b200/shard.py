@@ -16,6 +16,7 @@ onto its own heads.
 
 from __future__ import annotations
 
+import contextlib
 import dataclasses
 import os
 import time
@@ -71,6 +72,20 @@ class Shard:
 # (crates/mmh3-core/src/shard.rs:455-486).
 STRETCH_NAMES = ("before", "publish", "own projections", "input exchange", "peer projections",
                  "attention", "output exchange")
+
+
+@contextlib.contextmanager
+def stretch_range(name: str, device):
+    """An NVTX range around a stretch of a shared layer on a GPU rank, so that a timeline shows
+    the exchanges beside the attention kernels; nothing on CPU ranks."""
+    marked = torch.device(device).type == "cuda"
+    if marked:
+        torch.cuda.nvtx.range_push("mmh3." + name)
+    try:
+        yield
+    finally:
+        if marked:
+            torch.cuda.nvtx.range_pop()
 
 
 def profile() -> str:
@@ -136,6 +151,7 @@ class UlyssesAttention:
         self.shard, self.tokens, self.heads = shard, total_tokens, heads
         self.attention = attention
         self.group = group
+        self.device = device
         self.pack = pack or _torch_pack
         self.unpack = unpack or _torch_unpack
         own_tokens, own_heads = len(shard.own_tokens), len(shard.own_heads)
@@ -181,37 +197,41 @@ class UlyssesAttention:
     def exchange_inputs(self, qkv_own: torch.Tensor, timing: ShardTiming | None = None) -> None:
         """Turns "my tokens, every head" into "every token, my heads" in `inputs`: every peer's
         heads of this rank's rows packed, then the all-to-all."""
-        offset = 0
-        for peer, heads in enumerate(self.shard.heads):
-            count = self.input_send_splits[peer]
-            if count:
-                self.pack(qkv_own, self.send_inputs[offset:offset + count], self.own_tokens, 3,
-                          self.heads, heads.start, len(heads))
-            offset += count
+        with stretch_range("publish", self.device):
+            offset = 0
+            for peer, heads in enumerate(self.shard.heads):
+                count = self.input_send_splits[peer]
+                if count:
+                    self.pack(qkv_own, self.send_inputs[offset:offset + count], self.own_tokens,
+                              3, self.heads, heads.start, len(heads))
+                offset += count
         if timing is not None:
             timing.end("publish")
-        dist.all_to_all_single(self.inputs, self.send_inputs, self.input_recv_splits,
-                               self.input_send_splits, group=self.group)
+        with stretch_range("input exchange", self.device):
+            dist.all_to_all_single(self.inputs, self.send_inputs, self.input_recv_splits,
+                                   self.input_send_splits, group=self.group)
         if timing is not None:
             timing.end("input exchange")
 
     def attend(self) -> None:
         """The attention of every token on this rank's heads, `inputs` to `attended`."""
         if self.own_heads:
-            self.attention(self.inputs, self.attended, self.tokens, self.own_heads)
+            with stretch_range("attention", self.device):
+                self.attention(self.inputs, self.attended, self.tokens, self.own_heads)
 
     def exchange_outputs(self, output_own: torch.Tensor) -> None:
         """Turns "every token, my heads" in `attended` back into "my tokens, every head"
         (dit.rs:1713-1800)."""
-        dist.all_to_all_single(self.received, self.attended, self.output_recv_splits,
-                               self.output_send_splits, group=self.group)
-        offset = 0
-        for peer, heads in enumerate(self.shard.heads):
-            count = self.output_recv_splits[peer]
-            if count:
-                self.unpack(self.received[offset:offset + count], output_own, self.own_tokens,
-                            self.heads, heads.start, len(heads))
-            offset += count
+        with stretch_range("output exchange", self.device):
+            dist.all_to_all_single(self.received, self.attended, self.output_recv_splits,
+                                   self.output_send_splits, group=self.group)
+            offset = 0
+            for peer, heads in enumerate(self.shard.heads):
+                count = self.output_recv_splits[peer]
+                if count:
+                    self.unpack(self.received[offset:offset + count], output_own,
+                                self.own_tokens, self.heads, heads.start, len(heads))
+                offset += count
 
 
 def group_sizes(count: int, groups: int, ramped: bool = False) -> list[int]:
