@@ -158,20 +158,25 @@ class HostPipeline:
     cuda-python's runtime binding; torch owns the buffers and the streams.
 
     Nothing hides the first group's way in and the last group's way out, so those two groups are
-    one head each; and the groups' kernels alternate between two streams, so that the first
-    blocks of one fill the multiprocessors the last blocks of the one before leave idle.
+    one head each; a group's copy in must fit behind the attention of the group before, and a
+    head's rows cross the bus in about half the time the kernel needs for them, so with
+    `groups = 0` every group is at most twice the one before (1, 2, 4, 8, 16, 1 of 32 heads);
+    and the groups' kernels alternate between two streams, so that the first blocks of one fill
+    the multiprocessors the last blocks of the one before leave idle.
     """
 
-    def __init__(self, tokens: int, heads: int, groups: int = 8):
+    def __init__(self, tokens: int, heads: int, groups: int = 0, growth: float = 2.0):
         from cuda.bindings import runtime
 
         self.runtime = runtime
         self.tokens, self.heads = tokens, heads
-        from .shard import group_sizes
+        from .shard import group_sizes, growing_sizes
 
         self.groups = []
         first = 0
-        for span in group_sizes(heads, max(1, min(groups, heads)), ramped=True):
+        sizes = (growing_sizes(heads, growth) if groups <= 0
+                 else group_sizes(heads, min(groups, heads), ramped=True))
+        for span in sizes:
             if span:
                 self.groups.append((first, span))
                 first += span

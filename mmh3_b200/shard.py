@@ -243,10 +243,33 @@ def group_sizes(count: int, groups: int, ramped: bool = False) -> list[int]:
     return [count * (group + 1) // groups - count * group // groups for group in range(groups)]
 
 
-def head_groups(shard: Shard, groups: int, ramped: bool = False) -> list[Shard]:
-    """Cuts every rank's heads into `groups` runs (`group_sizes`): shard g holds the g-th run of
-    each rank. The layer can then go through a group at a time, every rank busy in every group."""
-    sizes = [group_sizes(len(owned), groups, ramped) for owned in shard.heads]
+def growing_sizes(count: int, growth: float, drain: float = 6.0) -> list[int]:
+    """`count` heads in runs for a pipeline with a stage before the attention (a copy from the
+    host, an exchange) that takes 1 / `growth` of the attention's time per head and a stage after
+    it that takes 1 / `drain`: one head first, whose way in nothing hides; every run at most
+    `growth` times the one before, so that its way in fits behind the attention of the run
+    before; and no run more than `drain` times what follows it, so that its way out fits behind
+    the attention of the runs after it, which ends the list on one head."""
+    sizes, left = [], count
+    while left > 0:
+        room_in = max(1, int(sizes[-1] * growth)) if sizes else 1
+        room_out = max(1, int(drain * left / (1.0 + drain)))
+        sizes.append(left if left == 1 else min(room_in, room_out, left))
+        left -= sizes[-1]
+    return sizes
+
+
+def head_groups(shard: Shard, groups: int, ramped: bool = False,
+                growth: float | None = None) -> list[Shard]:
+    """Cuts every rank's heads into `groups` runs (`group_sizes`), or with `growth` into
+    `growing_sizes` runs: shard g holds the g-th run of each rank. The layer can then go through
+    a group at a time, every rank busy in every group."""
+    if growth is not None:
+        sizes = [growing_sizes(len(owned), growth) for owned in shard.heads]
+        groups = max(len(runs) for runs in sizes)
+        sizes = [runs + [0] * (groups - len(runs)) for runs in sizes]
+    else:
+        sizes = [group_sizes(len(owned), groups, ramped) for owned in shard.heads]
     cuts = []
     for group in range(groups):
         heads = tuple(range(owned.start + sum(sizes[peer][:group]),
@@ -338,12 +361,13 @@ class HostUlyssesPipeline:
 
     def __init__(self, shard: Shard, total_tokens: int, heads: int, attention: AttentionFn,
                  groups: int, pack: PackFn | None = None, unpack: PackFn | None = None,
-                 group=None):
+                 group=None, growth: float | None = None):
         from .attention import HostPipeline
 
         self.shard, self.heads = shard, heads
         self.own_tokens = len(shard.own_tokens)
-        self.cuts = [shard] if shard.is_whole else head_groups(shard, groups, ramped=True)
+        self.cuts = [shard] if shard.is_whole else head_groups(shard, groups, ramped=True,
+                                                               growth=growth)
         self.layers = [UlyssesAttention(cut, total_tokens, heads, attention, "cuda",
                                         torch.bfloat16, pack, unpack, group)
                        for cut in self.cuts]

@@ -366,7 +366,7 @@ def test_layouts_off_the_tma_grid_equal_aligned_ones(element_type, head_dim, gro
     assert torch.equal(mixed.view(torch.int16), aligned.view(torch.int16))
 
 
-@pytest.mark.parametrize("groups", [1, 4])
+@pytest.mark.parametrize("groups", [1, 4, 0])
 def test_host_pipeline_equals_one_call(groups):
     """Pinned host buffers in and out, a group of heads at a time on four streams (the first and
     the last group one head each): the same bits as one call over device buffers, twice in a row
@@ -379,6 +379,7 @@ def test_host_pipeline_equals_one_call(groups):
     output = torch.zeros_like(expected)
     host_output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16).pin_memory()
     pipeline = attention.HostPipeline(tokens, heads, groups=groups)
+    # One group; four, the first and the last of one head; or runs that double and drain.
     assert [span for _, span in pipeline.groups] == ([6] if groups == 1 else [1, 2, 2, 1])
     for _ in range(2):
         host_output.zero_()

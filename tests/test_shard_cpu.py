@@ -15,7 +15,8 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from mmh3_b200.shard import (OverlappedUlyssesAttention, ProjectedUlyssesAttention, Shard,
-                              UlyssesAttention, group_sizes, head_groups, own_projection_rows)
+                              UlyssesAttention, group_sizes, growing_sizes, head_groups,
+                              own_projection_rows)
 
 HEAD_DIM = 128
 
@@ -171,6 +172,14 @@ def test_ramped_groups_cover_every_head_once():
     assert group_sizes(4, 4, ramped=True) == [1, 1, 1, 1]
     assert group_sizes(5, 2, ramped=True) == [2, 3]
     assert group_sizes(3, 4, ramped=True) == [0, 1, 1, 1]
+    assert growing_sizes(32, 2.0) == [1, 2, 4, 8, 14, 2, 1]
+    assert growing_sizes(16, 3.0, 10.0) == [1, 3, 9, 2, 1]
+    assert growing_sizes(4, 1.0) == [1, 1, 1, 1] and growing_sizes(1, 2.0) == [1]
+    for ranks, heads in ((2, 32), (3, 7), (8, 40)):
+        shard = Shard.even(0, ranks, 1000, heads)
+        cuts = head_groups(shard, 0, growth=3.0)
+        for peer in range(ranks):
+            assert [head for cut in cuts for head in cut.heads[peer]] == list(shard.heads[peer])
     for ranks, heads, groups in ((2, 32, 4), (3, 32, 4), (8, 32, 4), (8, 40, 4), (3, 7, 5), (4, 5, 3)):
         shard = Shard.even(0, ranks, 1000, heads)
         cuts = head_groups(shard, groups, ramped=True)
