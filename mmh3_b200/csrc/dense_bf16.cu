@@ -74,7 +74,8 @@ enum Barrier {
     PROBABILITIES_FULL = SCORES_FULL + QUERY_TILES,  // one per query tile
     OUTPUT_FULL = PROBABILITIES_FULL + QUERY_TILES,
     QUERY_READY = OUTPUT_FULL + 1,                   // the query tiles are normalized and rotated
-    BARRIERS = QUERY_READY + 1,
+    PROBABILITIES_HALF = QUERY_READY + 1,            // one per query tile: the first 64 keys' P
+    BARRIERS = PROBABILITIES_HALF + QUERY_TILES,
 };
 static_assert(BARRIERS * 8 + 8 <= 256, "the barriers outgrew their corner of shared memory");
 
@@ -200,6 +201,7 @@ __global__ void __launch_bounds__(THREADS, 1)
         for (int tile = 0; tile < QUERY_TILES; tile++) {
             mbar_init(barrier(SCORES_FULL + tile), 1);
             mbar_init(barrier(PROBABILITIES_FULL + tile), TILE_M);
+            mbar_init(barrier(PROBABILITIES_HALF + tile), TILE_M);
         }
         mbar_init(barrier(OUTPUT_FULL), 1);
         mbar_init(barrier(QUERY_READY), SOFTMAX_WARPS * 32);
@@ -266,10 +268,10 @@ __global__ void __launch_bounds__(THREADS, 1)
                 }
                 tcgen05_commit(barrier(SCORES_FULL + tile));
             };
-            auto accumulate = [&](int tile, uint32_t value_tile, bool first) {
+            auto accumulate = [&](int tile, uint32_t value_tile, bool first, int from, int to) {
                 const uint64_t operand = value_operand(value_tile);
                 #pragma unroll
-                for (int step = 0; step < TILE_N / 16; step++) {
+                for (int step = from; step < to; step++) {
                     // P is BF16, two to a column: 16 keys are 8 columns.
                     mma_f16_ts(tmem + TMEM_OUTPUT + tile * DIM,
                                tmem + TMEM_SCORES + tile * TILE_N + step * 8,
@@ -303,13 +305,23 @@ __global__ void __launch_bounds__(THREADS, 1)
                 const uint32_t key_tile = ring + key_stage * TILE_BYTES;
                 #pragma unroll
                 for (int tile = 0; tile < QUERY_TILES; tile++) {
+                    // The first 64 keys' probabilities are handed over first: their four MMAs
+                    // run while the softmax threads work on the other 64, which takes a quarter
+                    // of O += P V out of the chain softmax -> P V -> S of a tile (62.4 -> 60.8 ms).
+                    alive = mbar_wait(barrier(PROBABILITIES_HALF + tile), block & 1, watchdog,
+                                      STATUS_DENSE | 11);
+                    if (!alive) {
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    accumulate(tile, value_tile, block == 0, 0, TILE_N / 32);
                     alive = mbar_wait(barrier(PROBABILITIES_FULL + tile), block & 1, watchdog,
                                       STATUS_DENSE | 6);
                     if (!alive) {
                         break;
                     }
                     tcgen05_fence_after();
-                    accumulate(tile, value_tile, block == 0);
+                    accumulate(tile, value_tile, false, TILE_N / 32, TILE_N / 16);
                     if (tile == QUERY_TILES - 1) {
                         tcgen05_commit(barrier(RING_EMPTY + value_stage));
                     }
@@ -502,6 +514,11 @@ __global__ void __launch_bounds__(THREADS, 1)
                     packed[pair] = Element<HALF, DIM>::pack(probability.x, probability.y);
                 }
                 tmem_store_32(scores + chunk * 32, packed);
+                if (chunk == 0) {
+                    tmem_wait_store();
+                    tcgen05_fence_before();
+                    mbar_arrive(barrier(PROBABILITIES_HALF + tile));
+                }
             }
             tmem_wait_store();
             tcgen05_fence_before();
