@@ -43,7 +43,7 @@ DENSE_TOKENS = 65536 + 512
 VIDEO_TOKENS = 124992 + 512
 # DRAM bytes per token and head of the dense kernel: 404.7 MB read + 116.2 MB written in the ncu
 # capture of one launch at L = 16,384, H = 32 (q, k, v, output once each would be 1,024 B).
-DENSE_TRAFFIC_PER_TOKEN = 519.3e6 / (16384 * 32)
+DENSE_TRAFFIC_PER_TOKEN = 521.0e6 / (16384 * 32)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -476,7 +476,7 @@ def run_single(args) -> None:
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak, "traffic": DENSE_TRAFFIC_PER_TOKEN * tokens * heads,
                      "traffic_unit": "bytes per launch (dram read + write), scaled in proportion "
-                                     "to L x H from the ncu capture at L=16384, H=32 (519.3 MB "
+                                     "to L x H from the ncu capture at L=16384, H=32 (521.0 MB "
                                      "against 536.9 MB algorithmic)",
                      "algorithmic_bytes": 8.0 * tokens * heads * HEAD_DIM,
                      "peak_source": f"{source} bf16_tflops (burst)",
