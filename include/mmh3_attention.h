@@ -8,9 +8,13 @@
  * - the return value is a cudaError_t as an int, 0 for success; bad arguments give
  *   cudaErrorInvalidValue (1), combinations this library does not implement give
  *   cudaErrorNotSupported (801);
- * - every pointer is caller-owned device memory, the library allocates nothing and never
- *   synchronizes; the kernels of one call are ordered on `stream` (NULL is the legacy default
- *   stream) and the call returns once they are enqueued;
+ * - every pointer is caller-owned device memory and the library never synchronizes; the kernels
+ *   of one call are ordered on `stream` (NULL is the legacy default stream) and the call returns
+ *   once they are enqueued. It allocates nothing, with one exception: BF16 or FP16 operands of the
+ *   dense, VSA and Sol-Attn calls whose base or strides are not multiples of 16 bytes, which TMA
+ *   cannot describe, are first gathered into dense arrays in stream-ordered scratch
+ *   (cudaMallocAsync on `stream`, given back with cudaFreeAsync behind the kernels; the reference
+ *   copies such operands with cp.async inside its kernels). The results are the same bits;
  * - strides are in elements; structs are read during the call only;
  * - any host thread may call, for whatever device is current on it.
  */

@@ -91,6 +91,59 @@ bool encode_tensor_map(CUtensorMap *map, CUtensorMapDataType type, int rank, con
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool tma_aligned(const void *base, int heads, int64_t token_stride, int64_t head_stride) {
+    return reinterpret_cast<uintptr_t>(base) % 16 == 0 && token_stride % 8 == 0 &&
+           (heads == 1 || head_stride % 8 == 0);
+}
+
+namespace {
+
+// An operand copied 16 bits at a time into a dense [tokens][heads][dim] array.
+__global__ void gather_operand_kernel(const uint16_t *__restrict__ source,
+                                      uint16_t *__restrict__ target, int64_t elements, int heads,
+                                      int head_dim, int64_t token_stride, int64_t head_stride) {
+    for (int64_t index = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+         index < elements; index += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int dimension = static_cast<int>(index % head_dim);
+        const int64_t row = index / head_dim;
+        const int head = static_cast<int>(row % heads);
+        const int64_t token = row / heads;
+        target[index] = source[token * token_stride + head * head_stride + dimension];
+    }
+}
+
+} // namespace
+
+StagedOperands::~StagedOperands() {
+    for (void *buffer : buffers) {
+        if (buffer != nullptr) {
+            cudaFreeAsync(buffer, stream);
+        }
+    }
+}
+
+cudaError_t StagedOperands::stage(int slot, const uint16_t *&base, int tokens, int heads,
+                                  int head_dim, int64_t &token_stride, int64_t &head_stride) {
+    if (tma_aligned(base, heads, token_stride, head_stride)) {
+        return cudaSuccess;
+    }
+    const int64_t elements = static_cast<int64_t>(tokens) * heads * head_dim;
+    const cudaError_t allocated = cudaMallocAsync(&buffers[slot], elements * 2, stream);
+    if (allocated != cudaSuccess) {
+        return allocated;
+    }
+    const int64_t wanted = (elements + 255) / 256;
+    const int64_t most = 8 * static_cast<int64_t>(multiprocessor_count() > 0 ? multiprocessor_count() : 1);
+    const int blocks = static_cast<int>(wanted < most ? wanted : most);
+    gather_operand_kernel<<<blocks, 256, 0, stream>>>(base, static_cast<uint16_t *>(buffers[slot]),
+                                                      elements, heads, head_dim, token_stride,
+                                                      head_stride);
+    base = static_cast<const uint16_t *>(buffers[slot]);
+    token_stride = static_cast<int64_t>(heads) * head_dim;
+    head_stride = head_dim;
+    return cudaGetLastError();
+}
+
 } // namespace mmh3
 
 extern "C" int mmh3_b200_take_status(void) {

@@ -73,6 +73,26 @@ struct SharedMemoryOptIn {
     }
 };
 
+// Whether TMA can describe an operand: a base and strides that are multiples of 16 bytes
+// (strides in 16-bit elements).
+bool tma_aligned(const void *base, int heads, int64_t token_stride, int64_t head_stride);
+
+// Dense copies, in stream-ordered scratch that is given back when this goes out of scope, of the
+// 16-bit operands TMA cannot describe (the reference copies such operands with cp.async inside its
+// kernels, crates/mmh3-cuda/kernels/attention.cu:386-418).
+struct StagedOperands {
+    cudaStream_t stream;
+    void *buffers[3] = {nullptr, nullptr, nullptr};
+    explicit StagedOperands(cudaStream_t on) : stream(on) {}
+    StagedOperands(const StagedOperands &) = delete;
+    StagedOperands &operator=(const StagedOperands &) = delete;
+    ~StagedOperands();
+    // Replaces `base` and its strides by a dense [tokens][heads][head_dim] copy when TMA cannot
+    // describe them as they are.
+    cudaError_t stage(int slot, const uint16_t *&base, int tokens, int heads, int head_dim,
+                      int64_t &token_stride, int64_t &head_stride);
+};
+
 // Launchers of the kernels, one per .cu file.
 // dense_bf16.cu: heads of 64 or 128, BF16 or FP16 (`half`), causal or not, grouped key/value heads;
 // non-null `angles` [tokens, pairs] normalize and rotate the query inside the kernel.

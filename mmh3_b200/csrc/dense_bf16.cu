@@ -599,63 +599,6 @@ bool encode_operand(CUtensorMap *map, bool half, int head_dim, const void *base,
         dimensions, strides, box);
 }
 
-// Whether TMA can describe an operand: a base and strides that are multiples of 16 bytes.
-bool tma_aligned(const void *base, int heads, int64_t token_stride, int64_t head_stride) {
-    return reinterpret_cast<uintptr_t>(base) % 16 == 0 && token_stride % 8 == 0 &&
-           (heads == 1 || head_stride % 8 == 0);
-}
-
-// An operand TMA cannot describe, copied 16 bits at a time into a dense [tokens][heads][dim] array
-// that it can (the reference copies such operands with cp.async inside its kernel,
-// crates/mmh3-cuda/kernels/attention.cu:386-418).
-__global__ void gather_operand_kernel(const uint16_t *__restrict__ source,
-                                      uint16_t *__restrict__ target, int64_t elements, int heads,
-                                      int head_dim, int64_t token_stride, int64_t head_stride) {
-    for (int64_t index = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-         index < elements; index += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        const int dimension = static_cast<int>(index % head_dim);
-        const int64_t row = index / head_dim;
-        const int head = static_cast<int>(row % heads);
-        const int64_t token = row / heads;
-        target[index] = source[token * token_stride + head * head_stride + dimension];
-    }
-}
-
-// Stream-ordered scratch that is given back when it goes out of scope.
-struct StagedOperands {
-    cudaStream_t stream;
-    void *buffers[3] = {nullptr, nullptr, nullptr};
-    explicit StagedOperands(cudaStream_t on) : stream(on) {}
-    ~StagedOperands() {
-        for (void *buffer : buffers) {
-            if (buffer != nullptr) {
-                cudaFreeAsync(buffer, stream);
-            }
-        }
-    }
-    // Replaces `base` and its strides by a dense copy when TMA cannot describe them.
-    cudaError_t stage(int slot, const uint16_t *&base, int tokens, int heads, int head_dim,
-                      int64_t &token_stride, int64_t &head_stride) {
-        if (tma_aligned(base, heads, token_stride, head_stride)) {
-            return cudaSuccess;
-        }
-        const int64_t elements = static_cast<int64_t>(tokens) * heads * head_dim;
-        const cudaError_t allocated = cudaMallocAsync(&buffers[slot], elements * 2, stream);
-        if (allocated != cudaSuccess) {
-            return allocated;
-        }
-        const int blocks = static_cast<int>(
-            std::min<int64_t>((elements + 255) / 256, 8 * max(multiprocessor_count(), 1)));
-        gather_operand_kernel<<<blocks, 256, 0, stream>>>(
-            base, static_cast<uint16_t *>(buffers[slot]), elements, heads, head_dim, token_stride,
-            head_stride);
-        base = static_cast<const uint16_t *>(buffers[slot]);
-        token_stride = static_cast<int64_t>(heads) * head_dim;
-        head_stride = head_dim;
-        return cudaGetLastError();
-    }
-};
-
 // The kernel instance for an element type, mask, head dimension and query transform, and its
 // shared memory.
 struct Instance {

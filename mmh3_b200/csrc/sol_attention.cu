@@ -395,6 +395,15 @@ __global__ void __launch_bounds__(OFFSET_WARPS * 32)
     }
 }
 
+int launch_sparse_attention_aligned(const void *query, const void *key, const void *value,
+                                    void *output, int tokens, int heads,
+                                    const Mmh3AttentionLayout &layout, float scale,
+                                    float log2_scale, float tau, int sink_key_start,
+                                    int sink_key_end, int sink_query_start, int sink_query_end,
+                                    const Mmh3SparseWorkspace &workspace,
+                                    const Mmh3QuantizedWorkspace *quantized, int inputs_ready,
+                                    int blocks, cudaStream_t stream);
+
 } // namespace
 
 int launch_sparse_attention(const void *query, const void *key, const void *value, void *output,
@@ -411,6 +420,38 @@ int launch_sparse_attention(const void *query, const void *key, const void *valu
         return NOT_SUPPORTED; // routes are 16-bit block indices
     }
     const float log2_scale = scale * LOG2_E;
+    // Operands off TMA's 16-byte grid are gathered into dense arrays once, for every kernel below
+    // (the row offsets read q eight bytes at a time, the token attention through TMA).
+    StagedOperands staged(stream);
+    Mmh3AttentionLayout dense_layout = layout;
+    const uint16_t *operands[3] = {static_cast<const uint16_t *>(query),
+                                   static_cast<const uint16_t *>(key),
+                                   static_cast<const uint16_t *>(value)};
+    for (int operand = 0; operand < 3; operand++) {
+        const cudaError_t copied =
+            staged.stage(operand, operands[operand], tokens, heads, HEAD_DIM,
+                         dense_layout.token_stride[operand], dense_layout.head_stride[operand]);
+        if (copied != cudaSuccess) {
+            return static_cast<int>(copied);
+        }
+    }
+    return launch_sparse_attention_aligned(operands[QUERY], operands[KEY], operands[VALUE], output,
+                                           tokens, heads, dense_layout, scale, log2_scale, tau,
+                                           sink_key_start, sink_key_end, sink_query_start,
+                                           sink_query_end, workspace, quantized, inputs_ready,
+                                           blocks, stream);
+}
+
+namespace {
+
+int launch_sparse_attention_aligned(const void *query, const void *key, const void *value,
+                                    void *output, int tokens, int heads,
+                                    const Mmh3AttentionLayout &layout, float scale,
+                                    float log2_scale, float tau, int sink_key_start,
+                                    int sink_key_end, int sink_query_start, int sink_query_end,
+                                    const Mmh3SparseWorkspace &workspace,
+                                    const Mmh3QuantizedWorkspace *quantized, int inputs_ready,
+                                    int blocks, cudaStream_t stream) {
     if (!inputs_ready) {
         const int pooled =
             launch_block_statistics(query, key, value, tokens, heads, layout, workspace, stream);
@@ -448,5 +489,7 @@ int launch_sparse_attention(const void *query, const void *key, const void *valu
     return launch_sol_token_attention(query, key, value, output, tokens, heads, layout, scale,
                                       workspace, stream);
 }
+
+} // namespace
 
 } // namespace mmh3

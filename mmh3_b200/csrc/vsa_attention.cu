@@ -789,26 +789,37 @@ bool fill_params(VsaParams &params, void *output, int tokens, const Mmh3Attentio
     return params.status != nullptr;
 }
 
-// BF16 q, k, v as [128, tokens, heads] in boxes of 64 columns x 64 rows.
-bool encode_bf16_maps(VsaMaps &maps, const void *query, const void *key, const void *value,
-                      int tokens, int heads, const Mmh3AttentionLayout &layout) {
-    const void *bases[3] = {query, key, value};
+// BF16 q, k, v as [128, tokens, heads] in boxes of 64 columns x 64 rows. Operands off TMA's
+// 16-byte grid are gathered into dense arrays in `staged` first.
+int encode_bf16_maps(VsaMaps &maps, const void *query, const void *key, const void *value,
+                     int tokens, int heads, const Mmh3AttentionLayout &layout,
+                     StagedOperands &staged) {
+    const uint16_t *bases[3] = {static_cast<const uint16_t *>(query),
+                                static_cast<const uint16_t *>(key),
+                                static_cast<const uint16_t *>(value)};
     CUtensorMap *targets[3] = {&maps.query, &maps.key, &maps.value};
     for (int operand = 0; operand < 3; operand++) {
+        int64_t token_stride = layout.token_stride[operand];
+        int64_t head_stride = layout.head_stride[operand];
+        const cudaError_t copied = staged.stage(operand, bases[operand], tokens, heads, HEAD_DIM,
+                                                token_stride, head_stride);
+        if (copied != cudaSuccess) {
+            return static_cast<int>(copied);
+        }
         const uint64_t dimensions[3] = {HEAD_DIM, static_cast<uint64_t>(tokens),
                                         static_cast<uint64_t>(heads)};
-        uint64_t strides[2] = {static_cast<uint64_t>(layout.token_stride[operand]) * 2,
-                               static_cast<uint64_t>(layout.head_stride[operand]) * 2};
+        uint64_t strides[2] = {static_cast<uint64_t>(token_stride) * 2,
+                               static_cast<uint64_t>(head_stride) * 2};
         if (heads == 1 && strides[1] == 0) {
             strides[1] = strides[0] * static_cast<uint64_t>(tokens);
         }
         const uint32_t box[3] = {64, TILE, 1};
         if (!encode_tensor_map(targets[operand], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
                                bases[operand], dimensions, strides, box)) {
-            return false;
+            return NOT_SUPPORTED;
         }
     }
-    return true;
+    return 0;
 }
 
 } // namespace
@@ -825,8 +836,10 @@ int launch_vsa_attention(const void *query, const void *key, const void *value, 
         return static_cast<int>(cudaErrorInvalidDevice);
     }
     VsaMaps maps;
-    if (!encode_bf16_maps(maps, query, key, value, tokens, heads, layout)) {
-        return NOT_SUPPORTED;
+    StagedOperands staged(stream);
+    const int encoded = encode_bf16_maps(maps, query, key, value, tokens, heads, layout, staged);
+    if (encoded != 0) {
+        return encoded;
     }
     return launch<false>(maps, params, heads, stream);
 }
@@ -849,8 +862,10 @@ int launch_sol_token_attention(const void *query, const void *key, const void *v
     params.tail_values = sparse.tail_values;
     params.row_offsets = sparse.row_offsets;
     VsaMaps maps;
-    if (!encode_bf16_maps(maps, query, key, value, tokens, heads, layout)) {
-        return NOT_SUPPORTED;
+    StagedOperands staged(stream);
+    const int encoded = encode_bf16_maps(maps, query, key, value, tokens, heads, layout, staged);
+    if (encoded != 0) {
+        return encoded;
     }
     return launch<false>(maps, params, heads, stream);
 }

@@ -191,6 +191,37 @@ def test_prepared_inputs_match_separate_passes(oracle, tokens, quantized):
     assert torch.equal(separate[:, :normalized], fused[:, :normalized])
 
 
+@pytest.mark.parametrize("quantized", [False, True])
+def test_a_layout_off_the_tma_grid_gives_the_same_bits(oracle, quantized):
+    """q, k and v two bytes off a 16-byte boundary with an odd token stride: the entry point
+    gathers them into dense arrays first (the reference copies with cp.async instead of TMA,
+    crates/mmh3-cuda/kernels/attention.cu:386-418), and routes, statistics and output must be
+    the bits of the aligned layout."""
+    tokens, heads, tau, sinks = CASES[0]
+    inner = heads * 128
+    qkv = synthetic.bf16_tensor(make_case(oracle, tokens, heads), "cuda")
+    results = []
+    for shifted in (False, True):
+        token_stride = 3 * inner + (1 if shifted else 0)
+        offset = 1 if shifted else 0
+        storage = torch.zeros(tokens * token_stride + 8, dtype=torch.bfloat16, device="cuda")
+        torch.as_strided(storage, (tokens, 3 * inner), (token_stride, 1), offset).copy_(
+            qkv.view(tokens, 3 * inner))
+        layout = attention.make_layout((token_stride,) * 3 + (inner,))
+        output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+        workspace = attention.SparseWorkspace(tokens, heads, quantized=quantized)
+        attention.sparse(storage, output, layout, SCALE, tau, sinks, workspace,
+                         offsets=(offset, offset + inner, offset + 2 * inner, 0))
+        assert attention.take_status() == 0
+        results.append((output, workspace))
+    (aligned, first), (moved, second) = results
+    assert_routes_equal(*first.routes_host(), *second.routes_host())
+    for name in ("centroids", "block_keys", "value_sums", "tail_max", "tail_sum", "tail_values",
+                 "row_offsets"):
+        assert torch.equal(getattr(first, name), getattr(second, name)), name
+    assert torch.equal(aligned.view(torch.int16), moved.view(torch.int16))
+
+
 def test_rejects_what_it_does_not_compute():
     tokens, heads = 128, 1
     qkv = synthetic.dense_qkv(tokens, heads, seed=1).cuda()

@@ -220,6 +220,44 @@ def test_quantized_vsa_matches_the_reference(oracle, reference_kernels, with_val
     assert a @ b / (np.linalg.norm(a) * np.linalg.norm(b)) >= 0.9995
 
 
+def test_a_layout_off_the_tma_grid_gives_the_same_bits(oracle):
+    """q, k and v two bytes off a 16-byte boundary with an odd token stride: the token attention
+    gathers them into dense arrays first (the reference copies with cp.async instead of TMA), and
+    pooled tiles, routes and output must be the bits of the aligned layout."""
+    heads = 2
+    layout = PackedLayout.text_to_video(70, 9, 16, 24, 40)
+    plan, bits, gate_bits = make_case(oracle, layout, heads)
+    tokens, inner = len(layout), heads * 128
+    kept = plan.kept_video_tiles(0.75)
+    qkv = synthetic.bf16_tensor(bits, "cuda")
+    gate = synthetic.bf16_tensor(gate_bits, "cuda")
+    results = []
+    for shifted in (False, True):
+        token_stride = 3 * inner + (1 if shifted else 0)
+        offset = 1 if shifted else 0
+        storage = torch.zeros(tokens * token_stride + 8, dtype=torch.bfloat16, device="cuda")
+        torch.as_strided(storage, (tokens, 3 * inner), (token_stride, 1), offset).copy_(
+            qkv.view(tokens, 3 * inner))
+        vsa_layout = attention.make_layout((token_stride,) * 3 + (inner,))
+        output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+        workspace = attention.VsaWorkspace(plan, tokens, heads)
+        attention.vsa(storage, gate, output, vsa_layout, SCALE, kept, workspace,
+                      offsets=(offset, offset + inner, offset + 2 * inner, 0))
+        assert attention.take_status() == 0
+        results.append((output, workspace))
+    (aligned, first), (moved, second) = results
+    for name in ("pooled_query", "pooled_key", "pooled_value", "route_counts", "coarse"):
+        assert torch.equal(getattr(first, name), getattr(second, name)), name
+    routes, counts = first.routes_host()
+    other_routes, other_counts = second.routes_host()
+    assert np.array_equal(counts, other_counts)
+    for head in range(heads):
+        for tile in range(plan.tiles):
+            count = counts[head, tile]
+            assert np.array_equal(routes[head, tile, :count], other_routes[head, tile, :count])
+    assert torch.equal(aligned.view(torch.int16), moved.view(torch.int16))
+
+
 def test_larger_plan_with_an_odd_tile_count(oracle, reference_kernels):
     """More tiles than one CTA pair, an odd tile count, and routes that differ between neighbours."""
     layout = PackedLayout.text_to_video(130, 9, 32, 48, 0)
