@@ -251,6 +251,9 @@ def run_reference(args) -> None:
                 "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
         "step_is": "a sample of query rows of the layer, not a whole layer",
+        # What `value` times: the reference's CPU path. Its CUDA kernels on the same rows are
+        # under extra.reference_cuda_kernels at N = 1.
+        "reference_class": "cpu",
     }
     if args.gpus == 1 and not args.no_reference_kernels:
         line["extra"] = {"reference_cuda_kernels": reference_kernel_times(tokens, HEADS)}
