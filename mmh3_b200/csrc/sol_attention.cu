@@ -94,6 +94,39 @@ __global__ void __launch_bounds__(32)
     key_variance[head * HEAD_DIM + dimension] = __fdiv_rn(squares, static_cast<float>(blocks));
 }
 
+// The block ranges that are always exact: keys every query attends token by token, queries that
+// attend every key so.
+struct ExactRanges {
+    int first_key, keys_end, first_query, queries_end;
+    __host__ __device__ bool key(int block) const { return block >= first_key && block < keys_end; }
+    __host__ __device__ bool query(int block) const {
+        return block >= first_query && block < queries_end;
+    }
+};
+
+// What the routing kernel is told besides its workspace.
+struct RouteTask {
+    int tokens, blocks;
+    float tau, log2_scale;
+    ExactRanges exact;
+};
+
+// a + the same value of the lanes 16, 8, 4, 2 and 1 away, in that order.
+__device__ __forceinline__ float butterfly_sum(float value) {
+    #pragma unroll
+    for (int reach = 16; reach != 0; reach >>= 1) {
+        value = __fadd_rn(value, __shfl_xor_sync(0xffffffffu, value, reach));
+    }
+    return value;
+}
+__device__ __forceinline__ float butterfly_max(float value) {
+    #pragma unroll
+    for (int reach = 16; reach != 0; reach >>= 1) {
+        value = fmaxf(value, __shfl_xor_sync(0xffffffffu, value, reach));
+    }
+    return value;
+}
+
 // Shared memory of the routing kernel, after the dynamic [blocks][GROUP] scores.
 struct RouteShared {
     float4 query_means[GROUP][32];
@@ -104,8 +137,9 @@ struct RouteShared {
 };
 
 __global__ void __launch_bounds__(ROUTE_THREADS, 3)
-    route_kernel(Mmh3SparseWorkspace workspace, int tokens, int blocks, float tau, float log2_scale,
-                 int sink_key_start, int sink_key_end, int sink_query_start, int sink_query_end) {
+    route_kernel(const Mmh3SparseWorkspace workspace, const RouteTask task) {
+    const int tokens = task.tokens, blocks = task.blocks;
+    const float tau = task.tau, log2_scale = task.log2_scale;
     // [blocks][GROUP] scores, later weights; then [GROUP][words] masks of routed key blocks.
     extern __shared__ __align__(16) float scores[];
     const int words = (blocks + 31) / 32;
@@ -136,12 +170,8 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
                                       workspace.key_variance[head * HEAD_DIM + dimension]);
         }
         #pragma unroll
-        for (int offset = 16; offset > 0; offset /= 2) {
-            #pragma unroll
-            for (int group = 0; group < 4; group++) {
-                groups[group] = __fadd_rn(groups[group],
-                                          __shfl_xor_sync(0xffffffffu, groups[group], offset));
-            }
+        for (int group = 0; group < 4; group++) {
+            groups[group] = butterfly_sum(groups[group]);
         }
         const float spread =
             __fadd_rn(__fadd_rn(__fadd_rn(groups[0], groups[1]), groups[2]), groups[3]);
@@ -167,7 +197,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
         if (present) {
             load_row(head_keys + static_cast<size_t>(key_block) * HEAD_DIM, key);
         }
-        const bool key_sink = key_block >= sink_key_start && key_block < sink_key_end;
+        const bool key_sink = task.exact.key(key_block);
         #pragma unroll 1
         for (int query = 0; query < GROUP; query++) {
             const int query_block = first_query + query;
@@ -178,7 +208,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
                 scores[static_cast<size_t>(key_block) * GROUP + query] = score;
                 routed = score > shared.thresholds[query] || key_sink ||
                          (key_block >= query_block - 1 && key_block <= query_block + 1) ||
-                         (query_block >= sink_query_start && query_block < sink_query_end);
+                         task.exact.query(query_block);
                 if (!routed) {
                     shared.running[query][threadIdx.x] =
                         fmaxf(shared.running[query][threadIdx.x], score);
@@ -194,11 +224,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
     float maxima[GROUP];
     #pragma unroll
     for (int query = 0; query < GROUP; query++) {
-        float maximum = shared.running[query][threadIdx.x];
-        #pragma unroll
-        for (int offset = 16; offset > 0; offset /= 2) {
-            maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, offset));
-        }
+        const float maximum = butterfly_max(shared.running[query][threadIdx.x]);
         if (lane == 0) {
             shared.maxima[warp][query] = maximum;
         }
@@ -234,11 +260,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
     }
     #pragma unroll
     for (int query = 0; query < GROUP; query++) {
-        float sum = sums[query];
-        #pragma unroll
-        for (int offset = 16; offset > 0; offset /= 2) {
-            sum += __shfl_xor_sync(0xffffffffu, sum, offset);
-        }
+        const float sum = butterfly_sum(sums[query]);
         if (lane == 0) {
             shared.sums[warp][query] = sum;
         }
@@ -333,9 +355,9 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
     }
 }
 
-int launch_route(const Mmh3SparseWorkspace &workspace, int tokens, int blocks, int heads, float tau,
-                 float log2_scale, int sink_key_start, int sink_key_end, int sink_query_start,
-                 int sink_query_end, cudaStream_t stream) {
+int launch_route(const Mmh3SparseWorkspace &workspace, const RouteTask &task, int heads,
+                 cudaStream_t stream) {
+    const int blocks = task.blocks;
     // Eight scores and eight mask bits per key block.
     const size_t shared = static_cast<size_t>(blocks) * GROUP * sizeof(float) +
                           static_cast<size_t>(GROUP) * ((blocks + 31) / 32) * sizeof(uint32_t);
@@ -357,8 +379,7 @@ int launch_route(const Mmh3SparseWorkspace &workspace, int tokens, int blocks, i
         configured[device].store(shared, std::memory_order_relaxed);
     }
     route_kernel<<<dim3((blocks + GROUP - 1) / GROUP, heads), ROUTE_THREADS, shared, stream>>>(
-        workspace, tokens, blocks, tau, log2_scale, sink_key_start, sink_key_end, sink_query_start,
-        sink_query_end);
+        workspace, task);
     return static_cast<int>(cudaGetLastError());
 }
 
@@ -385,10 +406,7 @@ __global__ void __launch_bounds__(OFFSET_WARPS * 32)
         dot = fmaf(__uint_as_float(four.x & 0xffff0000u), mean.y, dot);
         dot = fmaf(__uint_as_float(four.y << 16), mean.z, dot);
         dot = fmaf(__uint_as_float(four.y & 0xffff0000u), mean.w, dot);
-        #pragma unroll
-        for (int offset = 16; offset > 0; offset /= 2) {
-            dot += __shfl_xor_sync(0xffffffffu, dot, offset);
-        }
+        dot = butterfly_sum(dot);
         if (lane == 0) {
             row_offsets[static_cast<size_t>(head) * tokens + token] = dot * log2_scale;
         }
@@ -396,13 +414,11 @@ __global__ void __launch_bounds__(OFFSET_WARPS * 32)
 }
 
 int launch_sparse_attention_aligned(const void *query, const void *key, const void *value,
-                                    void *output, int tokens, int heads,
-                                    const Mmh3AttentionLayout &layout, float scale,
-                                    float log2_scale, float tau, int sink_key_start,
-                                    int sink_key_end, int sink_query_start, int sink_query_end,
+                                    void *output, int heads, const Mmh3AttentionLayout &layout,
+                                    float scale, const RouteTask &task,
                                     const Mmh3SparseWorkspace &workspace,
-                                    const Mmh3QuantizedWorkspace *quantized, int inputs_ready,
-                                    int blocks, cudaStream_t stream);
+                                    const Mmh3QuantizedWorkspace *precision, int prepared_inputs,
+                                    cudaStream_t stream);
 
 } // namespace
 
@@ -435,23 +451,25 @@ int launch_sparse_attention(const void *query, const void *key, const void *valu
             return static_cast<int>(copied);
         }
     }
+    const RouteTask task = {tokens, blocks, tau, log2_scale,
+                            {sink_key_start, sink_key_end, sink_query_start, sink_query_end}};
     return launch_sparse_attention_aligned(operands[QUERY], operands[KEY], operands[VALUE], output,
-                                           tokens, heads, dense_layout, scale, log2_scale, tau,
-                                           sink_key_start, sink_key_end, sink_query_start,
-                                           sink_query_end, workspace, quantized, inputs_ready,
-                                           blocks, stream);
+                                           heads, dense_layout, scale, task, workspace, quantized,
+                                           inputs_ready, stream);
 }
 
 namespace {
 
 int launch_sparse_attention_aligned(const void *query, const void *key, const void *value,
-                                    void *output, int tokens, int heads,
-                                    const Mmh3AttentionLayout &layout, float scale,
-                                    float log2_scale, float tau, int sink_key_start,
-                                    int sink_key_end, int sink_query_start, int sink_query_end,
+                                    void *output, int heads, const Mmh3AttentionLayout &layout,
+                                    float scale, const RouteTask &task,
                                     const Mmh3SparseWorkspace &workspace,
-                                    const Mmh3QuantizedWorkspace *quantized, int inputs_ready,
-                                    int blocks, cudaStream_t stream) {
+                                    const Mmh3QuantizedWorkspace *precision, int prepared_inputs,
+                                    cudaStream_t stream) {
+    const int tokens = task.tokens, blocks = task.blocks;
+    const float log2_scale = task.log2_scale;
+    const Mmh3QuantizedWorkspace *const quantized = precision;
+    const int inputs_ready = prepared_inputs;
     if (!inputs_ready) {
         const int pooled =
             launch_block_statistics(query, key, value, tokens, heads, layout, workspace, stream);
@@ -461,10 +479,8 @@ int launch_sparse_attention_aligned(const void *query, const void *key, const vo
     }
     centre_keys_kernel<<<dim3(HEAD_DIM / 32, heads), 32, 0, stream>>>(
         workspace.block_keys, blocks, workspace.key_mean, workspace.key_variance);
-    const int routed = launch_route(workspace, tokens, blocks, heads, tau, log2_scale, sink_key_start,
-                                    sink_key_end, sink_query_start, sink_query_end, stream);
-    if (routed != 0) {
-        return routed;
+    if (const int code = launch_route(workspace, task, heads, stream); code != 0) {
+        return code;
     }
     const int per_cta = OFFSET_WARPS * OFFSET_TOKENS;
     row_offsets_kernel<<<dim3((tokens + per_cta - 1) / per_cta, heads), OFFSET_WARPS * 32, 0,
