@@ -35,6 +35,7 @@
 
 #include "common.cuh"
 #include "pooled_score.cuh"
+#include "sm100.cuh"
 
 namespace mmh3 {
 
@@ -127,7 +128,31 @@ __device__ __forceinline__ float butterfly_max(float value) {
     return value;
 }
 
-// Shared memory of the routing kernel, after the dynamic [blocks][GROUP] scores.
+// 16 bytes from global to shared memory without passing through registers; a thread's copies
+// complete, in order, by the time its wait returns.
+__device__ __forceinline__ void copy_16_bytes_async(float *destination, const float *source) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sm100::smem_u32(destination)),
+                 "l"(source)
+                 : "memory");
+}
+__device__ __forceinline__ void wait_for_own_copies() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// A row of key means staged in shared memory: 128 values and a pad of four, which spreads the 32
+// rows a warp reads at once, 16 bytes a lane, over all the banks.
+constexpr int STAGED_ROW = HEAD_DIM + 4;
+constexpr int STAGED_FLOATS = ROUTE_THREADS * STAGED_ROW;
+// Where the score of key block `key` against the CTA's query block `query` lies: 32 consecutive
+// key blocks of one query side by side (a warp's stores and loads meet no bank twice), and
+// four consecutive key blocks of a query in one 16-byte word.
+__device__ __forceinline__ int score_slot(int key, int query) {
+    return (key / 32) * (32 * GROUP) + query * 32 + key % 32;
+}
+
+// Static shared memory of the routing kernel; the dynamic part holds the scores (a slot for each
+// of `words` * 32 key blocks and GROUP queries), the masks of routed key blocks ([GROUP][words])
+// and the staged key means ([ROUTE_THREADS][STAGED_ROW], later the warps' shares of the tails).
 struct RouteShared {
     float4 query_means[GROUP][32];
     float thresholds[GROUP];
@@ -140,16 +165,32 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
     route_kernel(const Mmh3SparseWorkspace workspace, const RouteTask task) {
     const int tokens = task.tokens, blocks = task.blocks;
     const float tau = task.tau, log2_scale = task.log2_scale;
-    // [blocks][GROUP] scores, later weights; then [GROUP][words] masks of routed key blocks.
     extern __shared__ __align__(16) float scores[];
     const int words = (blocks + 31) / 32;
-    uint32_t *masks = reinterpret_cast<uint32_t *>(scores + static_cast<size_t>(blocks) * GROUP);
+    float *staged = scores + static_cast<size_t>(words) * 32 * GROUP;
+    uint32_t *masks = reinterpret_cast<uint32_t *>(staged + STAGED_FLOATS);
     __shared__ RouteShared shared;
     const int lane = threadIdx.x % 32;
     const int warp = threadIdx.x / 32;
     const int head = blockIdx.y;
     const int first_query = blockIdx.x * GROUP;
     const size_t head_rows = static_cast<size_t>(head) * blocks;
+    const float *head_keys = workspace.block_keys + head_rows * HEAD_DIM;
+
+    // The key means of the 32 key blocks from `first_key` on into this warp's rows of the staging
+    // buffer: a row is 512 contiguous bytes, 16 to a lane.
+    float *own_rows = staged + warp * 32 * STAGED_ROW;
+    const auto stage_keys = [&](int first_key) {
+        #pragma unroll 8
+        for (int row = 0; row < 32; row++) {
+            if (first_key + row < blocks) {
+                copy_16_bytes_async(
+                    own_rows + row * STAGED_ROW + lane * 4,
+                    head_keys + static_cast<size_t>(first_key + row) * HEAD_DIM + lane * 4);
+            }
+        }
+    };
+    stage_keys(warp * 32);
 
     // This warp's two query means into shared memory, and their thresholds: tau standard
     // deviations of a query block's pooled scores, from the variance of the block keys along each
@@ -184,7 +225,9 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
 
     // A thread to a key block: its centred mean in registers against the eight query means, the
     // fate of the block for each of them, and the running maxima of what stays in the tails.
-    const float *head_keys = workspace.block_keys + head_rows * HEAD_DIM;
+    // The means arrive through the staging buffer (a thread reading its own row straight from
+    // global memory would touch 32 cache lines a load), and the next 32 rows are on their way
+    // while these meet the queries.
     // The running maxima live in shared memory: the key's mean takes the registers.
     #pragma unroll
     for (int query = 0; query < GROUP; query++) {
@@ -194,10 +237,21 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
         const int key_block = first + threadIdx.x;
         const bool present = key_block < blocks;
         float2 key[HEAD_DIM / 2];
+        wait_for_own_copies();
+        __syncwarp();
         if (present) {
-            load_row(head_keys + static_cast<size_t>(key_block) * HEAD_DIM, key);
+            const float4 *row = reinterpret_cast<const float4 *>(own_rows + lane * STAGED_ROW);
+            #pragma unroll
+            for (int chunk = 0; chunk < HEAD_DIM / 4; chunk++) {
+                const float4 four = row[chunk];
+                key[chunk * 2] = make_float2(four.x, four.y);
+                key[chunk * 2 + 1] = make_float2(four.z, four.w);
+            }
         }
+        __syncwarp();
+        stage_keys(first + ROUTE_THREADS + warp * 32);
         const bool key_sink = task.exact.key(key_block);
+        float *slots = scores + score_slot(key_block, 0);
         #pragma unroll 1
         for (int query = 0; query < GROUP; query++) {
             const int query_block = first_query + query;
@@ -205,7 +259,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
             if (present) {
                 const float score =
                     __fmul_rn(score_tree(shared.query_means[query], key), log2_scale);
-                scores[static_cast<size_t>(key_block) * GROUP + query] = score;
+                slots[query * 32] = score;
                 routed = score > shared.thresholds[query] || key_sink ||
                          (key_block >= query_block - 1 && key_block <= query_block + 1) ||
                          task.exact.query(query_block);
@@ -241,20 +295,23 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
     }
 
     // The tails: what is not routed, as softmax weights against its maximum, each key block
-    // counted once per token it stands for. The weights replace the scores.
+    // counted once per token it stands for. The weights replace the scores; the slots past the
+    // last key block get weight zero.
     float sums[GROUP];
     #pragma unroll
     for (int query = 0; query < GROUP; query++) {
         sums[query] = 0.0f;
     }
-    for (int key_block = threadIdx.x; key_block < blocks; key_block += ROUTE_THREADS) {
-        const float length = static_cast<float>(tokens_in(key_block, tokens));
-        float *row = scores + static_cast<size_t>(key_block) * GROUP;
+    for (int key_block = threadIdx.x; key_block < words * 32; key_block += ROUTE_THREADS) {
+        const bool present = key_block < blocks;
+        const float length = present ? static_cast<float>(tokens_in(key_block, tokens)) : 0.0f;
+        float *slots = scores + score_slot(key_block, 0);
         #pragma unroll
         for (int query = 0; query < GROUP; query++) {
-            const bool routed = (masks[query * words + key_block / 32] >> (key_block % 32)) & 1u;
-            const float weight = routed ? 0.0f : exp2f(row[query] - maxima[query]);
-            row[query] = weight;
+            const bool routed = (masks[query * words + key_block / 32] >> lane) & 1u;
+            const float weight =
+                routed || !present ? 0.0f : exp2f(slots[query * 32] - maxima[query]);
+            slots[query * 32] = weight;
             sums[query] = fmaf(weight, length, sums[query]);
         }
     }
@@ -267,48 +324,58 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
     }
     __syncthreads();
 
-    // The weighted values of the tails: thread d sums dimension d of the summed values over the key
-    // blocks, which each of the eight query blocks weighs its own way (a key block's eight weights
-    // lie side by side: two 16-byte loads, and two query blocks to a packed multiply-add). Routed
-    // blocks have weight zero.
+    // The weighted values of the tails. A warp takes every fourth group of four key blocks: a lane
+    // loads four dimensions of their summed values (a row is one coalesced 512-byte load) and the
+    // four weights each of the eight query blocks gives them (one 16-byte word a query), and keeps
+    // its four dimensions of the eight sums. Routed blocks have weight zero. The warps' shares
+    // meet in the staging buffer, which the scores are done with.
     {
-        const float *values = workspace.value_sums + head_rows * HEAD_DIM + threadIdx.x;
-        float2 tails[GROUP / 2];
+        const float4 *values =
+            reinterpret_cast<const float4 *>(workspace.value_sums + head_rows * HEAD_DIM) + lane;
+        float2 tails[GROUP][2];
         #pragma unroll
-        for (int pair = 0; pair < GROUP / 2; pair++) {
-            tails[pair] = make_float2(0.0f, 0.0f);
+        for (int query = 0; query < GROUP; query++) {
+            tails[query][0] = tails[query][1] = make_float2(0.0f, 0.0f);
         }
-        constexpr int ROWS = 16;
-        for (int first = 0; first < blocks; first += ROWS) {
-            float rows[ROWS];
+        for (int first = warp * 4; first < blocks; first += ROUTE_WARPS * 4) {
+            float4 rows[4];
             #pragma unroll
-            for (int index = 0; index < ROWS; index++) {
+            for (int index = 0; index < 4; index++) {
                 rows[index] = first + index < blocks
-                                  ? __ldg(values + static_cast<size_t>(first + index) * HEAD_DIM)
-                                  : 0.0f;
+                                  ? __ldg(values + static_cast<size_t>(first + index) * (HEAD_DIM / 4))
+                                  : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
             #pragma unroll
-            for (int index = 0; index < ROWS; index++) {
-                if (first + index < blocks) {
-                    const float4 *weights = reinterpret_cast<const float4 *>(
-                        scores + static_cast<size_t>(first + index) * GROUP);
-                    const float2 value = make_float2(rows[index], rows[index]);
-                    #pragma unroll
-                    for (int four = 0; four < GROUP / 4; four++) {
-                        const float4 weight = weights[four];
-                        tails[four * 2] =
-                            __ffma2_rn(make_float2(weight.x, weight.y), value, tails[four * 2]);
-                        tails[four * 2 + 1] =
-                            __ffma2_rn(make_float2(weight.z, weight.w), value, tails[four * 2 + 1]);
-                    }
+            for (int query = 0; query < GROUP; query++) {
+                const float4 four = *reinterpret_cast<const float4 *>(scores + score_slot(first, query));
+                const float weights[4] = {four.x, four.y, four.z, four.w};
+                #pragma unroll
+                for (int index = 0; index < 4; index++) {
+                    const float2 weight = make_float2(weights[index], weights[index]);
+                    tails[query][0] = __ffma2_rn(
+                        weight, make_float2(rows[index].x, rows[index].y), tails[query][0]);
+                    tails[query][1] = __ffma2_rn(
+                        weight, make_float2(rows[index].z, rows[index].w), tails[query][1]);
                 }
             }
         }
+        float4 *shares = reinterpret_cast<float4 *>(staged);
         #pragma unroll
         for (int query = 0; query < GROUP; query++) {
+            shares[(warp * GROUP + query) * (HEAD_DIM / 4) + lane] = make_float4(
+                tails[query][0].x, tails[query][0].y, tails[query][1].x, tails[query][1].y);
+        }
+        __syncthreads();
+        #pragma unroll
+        for (int query = 0; query < GROUP; query++) {
+            float total = staged[query * HEAD_DIM + threadIdx.x];
+            #pragma unroll
+            for (int other = 1; other < ROUTE_WARPS; other++) {
+                total += staged[(other * GROUP + query) * HEAD_DIM + threadIdx.x];
+            }
             if (first_query + query < blocks) {
                 workspace.tail_values[(head_rows + first_query + query) * HEAD_DIM + threadIdx.x] =
-                    query % 2 == 0 ? tails[query / 2].x : tails[query / 2].y;
+                    total;
             }
         }
     }
@@ -358,9 +425,10 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
 int launch_route(const Mmh3SparseWorkspace &workspace, const RouteTask &task, int heads,
                  cudaStream_t stream) {
     const int blocks = task.blocks;
-    // Eight scores and eight mask bits per key block.
-    const size_t shared = static_cast<size_t>(blocks) * GROUP * sizeof(float) +
-                          static_cast<size_t>(GROUP) * ((blocks + 31) / 32) * sizeof(uint32_t);
+    // Eight scores and eight mask bits per key block, and the staged key means.
+    const size_t words = (blocks + 31) / 32;
+    const size_t shared = words * 32 * GROUP * sizeof(float) + STAGED_FLOATS * sizeof(float) +
+                          GROUP * words * sizeof(uint32_t);
     if (shared > 200 * 1024) {
         return INVALID_VALUE;
     }
