@@ -141,6 +141,9 @@ __device__ __forceinline__ void wait_for_own_copies() {
 
 // A row of key means staged in shared memory: 128 values and a pad of four, which spreads the 32
 // rows a warp reads at once, 16 bytes a lane, over all the banks.
+#ifndef ROUTE_SKIP
+#define ROUTE_SKIP 0
+#endif
 constexpr int STAGED_ROW = HEAD_DIM + 4;
 constexpr int STAGED_FLOATS = ROUTE_THREADS * STAGED_ROW;
 // Where the score of key block `key` against the CTA's query block `query` lies: 32 consecutive
@@ -257,7 +260,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
             const int query_block = first_query + query;
             bool routed = false;
             if (present) {
-                const float score =
+                const float score = ROUTE_SKIP == 3 ? key[query].x :
                     __fmul_rn(score_tree(shared.query_means[query], key), log2_scale);
                 slots[query * 32] = score;
                 routed = score > shared.thresholds[query] || key_sink ||
@@ -302,6 +305,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
     for (int query = 0; query < GROUP; query++) {
         sums[query] = 0.0f;
     }
+    if (ROUTE_SKIP < 2)
     for (int key_block = threadIdx.x; key_block < words * 32; key_block += ROUTE_THREADS) {
         const bool present = key_block < blocks;
         const float length = present ? static_cast<float>(tokens_in(key_block, tokens)) : 0.0f;
@@ -337,26 +341,45 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
         for (int query = 0; query < GROUP; query++) {
             tails[query][0] = tails[query][1] = make_float2(0.0f, 0.0f);
         }
-        for (int first = warp * 4; first < blocks; first += ROUTE_WARPS * 4) {
-            float4 rows[4];
+        // The summed values come from L2, hundreds of cycles away, and two warps a scheduler do
+        // not hide that: the loads run AHEAD groups before their use.
+        constexpr int AHEAD = 4, STRIDE = ROUTE_WARPS * 4;
+        float4 rows[AHEAD][4];
+        const auto load_group = [&](int first, float4 (&into)[4]) {
             #pragma unroll
             for (int index = 0; index < 4; index++) {
-                rows[index] = first + index < blocks
+                into[index] = first + index < blocks
                                   ? __ldg(values + static_cast<size_t>(first + index) * (HEAD_DIM / 4))
                                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             }
+        };
+        #pragma unroll
+        for (int stage = 0; stage < AHEAD; stage++) {
+            load_group(warp * 4 + stage * STRIDE, rows[stage]);
+        }
+        if (ROUTE_SKIP < 1)
+        for (int base = warp * 4; base < blocks; base += AHEAD * STRIDE) {
             #pragma unroll
-            for (int query = 0; query < GROUP; query++) {
-                const float4 four = *reinterpret_cast<const float4 *>(scores + score_slot(first, query));
-                const float weights[4] = {four.x, four.y, four.z, four.w};
-                #pragma unroll
-                for (int index = 0; index < 4; index++) {
-                    const float2 weight = make_float2(weights[index], weights[index]);
-                    tails[query][0] = __ffma2_rn(
-                        weight, make_float2(rows[index].x, rows[index].y), tails[query][0]);
-                    tails[query][1] = __ffma2_rn(
-                        weight, make_float2(rows[index].z, rows[index].w), tails[query][1]);
+            for (int stage = 0; stage < AHEAD; stage++) {
+                const int first = base + stage * STRIDE;
+                if (first < blocks) {
+                    #pragma unroll
+                    for (int query = 0; query < GROUP; query++) {
+                        const float4 four =
+                            *reinterpret_cast<const float4 *>(scores + score_slot(first, query));
+                        const float weights[4] = {four.x, four.y, four.z, four.w};
+                        #pragma unroll
+                        for (int index = 0; index < 4; index++) {
+                            const float2 weight = make_float2(weights[index], weights[index]);
+                            const float4 row = rows[stage][index];
+                            tails[query][0] =
+                                __ffma2_rn(weight, make_float2(row.x, row.y), tails[query][0]);
+                            tails[query][1] =
+                                __ffma2_rn(weight, make_float2(row.z, row.w), tails[query][1]);
+                        }
+                    }
                 }
+                load_group(first + AHEAD * STRIDE, rows[stage]);
             }
         }
         float4 *shares = reinterpret_cast<float4 *>(staged);
