@@ -43,9 +43,10 @@ namespace {
 
 constexpr int BLOCK = 64;
 constexpr int GROUP = 8;                 // query blocks to a CTA
-constexpr int ROUTE_WARPS = 4;           // each looks after two of them
+constexpr int ROUTE_WARPS = 8;           // each looks after one of them
 constexpr int ROUTE_THREADS = ROUTE_WARPS * 32;
-static_assert(ROUTE_THREADS == HEAD_DIM, "the tail values give each thread one dimension");
+constexpr int STEP_KEYS = 16;            // key blocks a warp scores at a time: two to four threads
+constexpr int PASS_KEYS = ROUTE_WARPS * STEP_KEYS;
 
 // Tokens in block `block` of a sequence of `tokens`.
 __device__ __forceinline__ int tokens_in(int block, int tokens) {
@@ -139,32 +140,85 @@ __device__ __forceinline__ void wait_for_own_copies() {
     asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
 }
 
-// A row of key means staged in shared memory: 128 values and a pad of four, which spreads the 32
-// rows a warp reads at once, 16 bytes a lane, over all the banks.
-#ifndef ROUTE_SKIP
-#define ROUTE_SKIP 0
-#endif
+// A row of key means staged in shared memory: 128 values and a pad of four words, and the rows of
+// a warp's 16 key blocks in the order 0, 2, 4, .., 14, 1, 3, .., 15, so that the eight fours of
+// threads, each reading one word of its own row, meet no bank twice.
 constexpr int STAGED_ROW = HEAD_DIM + 4;
-constexpr int STAGED_FLOATS = ROUTE_THREADS * STAGED_ROW;
+constexpr int STAGED_FLOATS = PASS_KEYS * STAGED_ROW;
+__device__ __forceinline__ int staged_row(int key) { return key / 2 + 8 * (key % 2); }
+// A query mean in shared memory: four runs of 32 values, run c holding dimensions c, c + 4,
+// c + 8, ..., each with a pad of four words (four threads read a 16-byte word of their own run each).
+constexpr int QUARTER_ROW = HEAD_DIM / 4 + 4;
 // Where the score of key block `key` against the CTA's query block `query` lies: 32 consecutive
 // key blocks of one query side by side (a warp's stores and loads meet no bank twice), and
 // four consecutive key blocks of a query in one 16-byte word.
 __device__ __forceinline__ int score_slot(int key, int query) {
     return (key / 32) * (32 * GROUP) + query * 32 + key % 32;
 }
+// The 16 bits that `votes` has at lanes 4 i and 4 i + 1, side by side.
+__device__ __forceinline__ uint32_t two_of_every_four(uint32_t votes) {
+    votes &= 0x33333333u;
+    votes = (votes | (votes >> 2)) & 0x0f0f0f0fu;
+    votes = (votes | (votes >> 4)) & 0x00ff00ffu;
+    return (votes | (votes >> 8)) & 0x0000ffffu;
+}
+
+// The pooled scores of two key means against one query mean by four threads, in the FP32 order
+// of pooled_score.cuh: 32 chains l of four fused multiply-adds over dimensions l, l + 32, l + 64,
+// l + 96, then a butterfly over bits 4, 3, 2, 1, 0 of l. Thread c of the four holds the chains
+// l = 4 a + c, a = 0 .. 7, that is dimensions 4 m + c with m = a + 8 k for step k: of a key as the
+// pairs key[i] = (m = 2 i, m = 2 i + 1), of the query as 16-byte words of four consecutive m.
+// Chains a and a + 1 are the halves of packed operations; bits 4, 3, 2 of l are bits 2, 1, 0 of a
+// (two packed additions and the sum of the halves), bits 1 and 0 are c: two exchanges among the
+// four threads, after which each holds both scores.
+__device__ __forceinline__ void score_two_keys(const float4 *__restrict__ query,
+                                               const float2 (&keys)[2][HEAD_DIM / 8],
+                                               float (&scores)[2]) {
+    float2 sums[2][4];
+    #pragma unroll
+    for (int key = 0; key < 2; key++) {
+        #pragma unroll
+        for (int pair = 0; pair < 4; pair++) {
+            sums[key][pair] = make_float2(0.0f, 0.0f);
+        }
+    }
+    #pragma unroll
+    for (int step = 0; step < 4; step++) {
+        #pragma unroll
+        for (int half = 0; half < 2; half++) {
+            const float4 four = query[step * 2 + half];
+            #pragma unroll
+            for (int key = 0; key < 2; key++) {
+                sums[key][half * 2] = __ffma2_rn(make_float2(four.x, four.y),
+                                                 keys[key][half * 2 + step * 4],
+                                                 sums[key][half * 2]);
+                sums[key][half * 2 + 1] = __ffma2_rn(make_float2(four.z, four.w),
+                                                     keys[key][half * 2 + 1 + step * 4],
+                                                     sums[key][half * 2 + 1]);
+            }
+        }
+    }
+    #pragma unroll
+    for (int key = 0; key < 2; key++) {
+        const float2 folded = __fadd2_rn(__fadd2_rn(sums[key][0], sums[key][2]),
+                                         __fadd2_rn(sums[key][1], sums[key][3]));
+        float sum = __fadd_rn(folded.x, folded.y);
+        sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, 2));
+        scores[key] = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, 1));
+    }
+}
 
 // Static shared memory of the routing kernel; the dynamic part holds the scores (a slot for each
-// of `words` * 32 key blocks and GROUP queries), the masks of routed key blocks ([GROUP][words])
-// and the staged key means ([ROUTE_THREADS][STAGED_ROW], later the warps' shares of the tails).
-struct RouteShared {
-    float4 query_means[GROUP][32];
+// of `words` * 32 key blocks and GROUP queries), the staged key means ([PASS_KEYS][STAGED_ROW],
+// later the warps' shares of the tails) and the masks of routed key blocks ([GROUP][words]).
+struct __align__(16) RouteShared {
+    float query_quarters[GROUP][4][QUARTER_ROW];
     float thresholds[GROUP];
-    float running[GROUP][ROUTE_THREADS]; // each thread's running maxima of the unrouted scores
-    float maxima[ROUTE_WARPS][GROUP];    // [warp][query]: each warp's share of those maxima
+    float maxima[ROUTE_WARPS][GROUP]; // [warp][query]: each warp's share of the tails' maxima
     float sums[ROUTE_WARPS][GROUP];
 };
 
-__global__ void __launch_bounds__(ROUTE_THREADS, 3)
+__global__ void __launch_bounds__(ROUTE_THREADS, 2)
     route_kernel(const Mmh3SparseWorkspace workspace, const RouteTask task) {
     const int tokens = task.tokens, blocks = task.blocks;
     const float tau = task.tau, log2_scale = task.log2_scale;
@@ -180,26 +234,25 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
     const size_t head_rows = static_cast<size_t>(head) * blocks;
     const float *head_keys = workspace.block_keys + head_rows * HEAD_DIM;
 
-    // The key means of the 32 key blocks from `first_key` on into this warp's rows of the staging
+    // The key means of the 16 key blocks from `first_key` on into this warp's rows of the staging
     // buffer: a row is 512 contiguous bytes, 16 to a lane.
-    float *own_rows = staged + warp * 32 * STAGED_ROW;
+    float *own_rows = staged + warp * STEP_KEYS * STAGED_ROW;
     const auto stage_keys = [&](int first_key) {
-        #pragma unroll 8
-        for (int row = 0; row < 32; row++) {
+        #pragma unroll
+        for (int row = 0; row < STEP_KEYS; row++) {
             if (first_key + row < blocks) {
                 copy_16_bytes_async(
-                    own_rows + row * STAGED_ROW + lane * 4,
+                    own_rows + staged_row(row) * STAGED_ROW + lane * 4,
                     head_keys + static_cast<size_t>(first_key + row) * HEAD_DIM + lane * 4);
             }
         }
     };
-    stage_keys(warp * 32);
+    stage_keys(warp * STEP_KEYS);
 
-    // This warp's two query means into shared memory, and their thresholds: tau standard
-    // deviations of a query block's pooled scores, from the variance of the block keys along each
-    // dimension. Lane l holds dimensions l, l + 32, l + 64, l + 96; each group of 32 is added over a
-    // butterfly and the four groups then in order, which is the order the reference's 128 threads
-    // add them in.
+    // This warp's query mean into shared memory, and its threshold: tau standard deviations of a
+    // query block's pooled scores, from the variance of the block keys along each dimension. Lane
+    // l holds dimensions l, l + 32, l + 64, l + 96; each group of 32 is added over a butterfly and
+    // the four groups then in order, which is the order the reference's 128 threads add them in.
     for (int slot = warp; slot < GROUP; slot += ROUTE_WARPS) {
         const int own_query = first_query + slot;
         float groups[4];
@@ -209,7 +262,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
             const float mean =
                 own_query < blocks ? workspace.centroids[(head_rows + own_query) * HEAD_DIM + dimension]
                                    : 0.0f;
-            reinterpret_cast<float *>(&shared.query_means[slot][0])[dimension] = mean;
+            shared.query_quarters[slot][dimension % 4][dimension / 4] = mean;
             groups[group] = __fmul_rn(__fmul_rn(mean, mean),
                                       workspace.key_variance[head * HEAD_DIM + dimension]);
         }
@@ -226,62 +279,77 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
     }
     __syncthreads();
 
-    // A thread to a key block: its centred mean in registers against the eight query means, the
-    // fate of the block for each of them, and the running maxima of what stays in the tails.
-    // The means arrive through the staging buffer (a thread reading its own row straight from
-    // global memory would touch 32 cache lines a load), and the next 32 rows are on their way
-    // while these meet the queries.
-    // The running maxima live in shared memory: the key's mean takes the registers.
-    #pragma unroll
-    for (int query = 0; query < GROUP; query++) {
-        shared.running[query][threadIdx.x] = -FLT_MAX;
-    }
-    for (int first = 0; first < blocks; first += ROUTE_THREADS) {
-        const int key_block = first + threadIdx.x;
-        const bool present = key_block < blocks;
-        float2 key[HEAD_DIM / 2];
-        wait_for_own_copies();
-        __syncwarp();
-        if (present) {
-            const float4 *row = reinterpret_cast<const float4 *>(own_rows + lane * STAGED_ROW);
+    // Four threads to two key blocks: thread c of the four holds dimensions c, c + 4, c + 8, ...
+    // of both centred means in registers and meets the same dimensions of the eight query means
+    // in shared memory. The first two of the four then decide a block's fate each for the eight
+    // queries and cast its vote into the bit mask of routed blocks (a warp's votes are 16 key
+    // blocks of one query: half a word). The means arrive through the staging buffer (threads
+    // reading their own rows straight from global memory would touch a cache line each), and
+    // the next 16 rows are on their way while these meet the queries.
+    {
+        const int four = lane / 4, part = lane % 4;
+        uint16_t *half_words = reinterpret_cast<uint16_t *>(masks);
+        for (int first = warp * STEP_KEYS; first < words * 32; first += PASS_KEYS) {
+            float2 keys[2][HEAD_DIM / 8];
+            wait_for_own_copies();
+            __syncwarp();
             #pragma unroll
-            for (int chunk = 0; chunk < HEAD_DIM / 4; chunk++) {
-                const float4 four = row[chunk];
-                key[chunk * 2] = make_float2(four.x, four.y);
-                key[chunk * 2 + 1] = make_float2(four.z, four.w);
-            }
-        }
-        __syncwarp();
-        stage_keys(first + ROUTE_THREADS + warp * 32);
-        const bool key_sink = task.exact.key(key_block);
-        float *slots = scores + score_slot(key_block, 0);
-        #pragma unroll 1
-        for (int query = 0; query < GROUP; query++) {
-            const int query_block = first_query + query;
-            bool routed = false;
-            if (present) {
-                const float score = ROUTE_SKIP == 3 ? key[query].x :
-                    __fmul_rn(score_tree(shared.query_means[query], key), log2_scale);
-                slots[query * 32] = score;
-                routed = score > shared.thresholds[query] || key_sink ||
-                         (key_block >= query_block - 1 && key_block <= query_block + 1) ||
-                         task.exact.query(query_block);
-                if (!routed) {
-                    shared.running[query][threadIdx.x] =
-                        fmaxf(shared.running[query][threadIdx.x], score);
+            for (int key = 0; key < 2; key++) {
+                const float *row = own_rows + staged_row(four * 2 + key) * STAGED_ROW + part;
+                #pragma unroll
+                for (int pair = 0; pair < HEAD_DIM / 8; pair++) {
+                    keys[key][pair] = make_float2(row[pair * 8], row[pair * 8 + 4]);
                 }
             }
-            // 32 consecutive key blocks of one query block: one word of its mask.
-            const unsigned word = __ballot_sync(0xffffffffu, routed);
-            if (lane == 0 && first + warp * 32 < blocks) {
-                masks[query * words + first / 32 + warp] = word;
+            __syncwarp();
+            stage_keys(first + PASS_KEYS);
+            // What this thread decides: the first of the two blocks in thread 0, the second in
+            // thread 1, nothing in the other two.
+            const int key_block = first + four * 2 + part;
+            const bool decides = part < 2 && key_block < blocks;
+            const bool key_sink = task.exact.key(key_block);
+            float *slots = scores + score_slot(key_block, 0);
+            #pragma unroll 1
+            for (int query = 0; query < GROUP; query++) {
+                const int query_block = first_query + query;
+                float both[2];
+                score_two_keys(reinterpret_cast<const float4 *>(shared.query_quarters[query][part]),
+                               keys, both);
+                bool routed = false;
+                if (decides) {
+                    const float score = __fmul_rn(part == 0 ? both[0] : both[1], log2_scale);
+                    slots[query * 32] = score;
+                    routed = score > shared.thresholds[query] || key_sink ||
+                             (key_block >= query_block - 1 && key_block <= query_block + 1) ||
+                             task.exact.query(query_block);
+                }
+                const uint32_t votes = __ballot_sync(0xffffffffu, routed);
+                if (lane == 0) {
+                    half_words[(query * words) * 2 + first / STEP_KEYS] =
+                        static_cast<uint16_t>(two_of_every_four(votes));
+                }
             }
         }
     }
+    __syncthreads();
+
+    // The maxima of what stays in the tails: thread t looks at key blocks t, t + 256, ...
     float maxima[GROUP];
     #pragma unroll
     for (int query = 0; query < GROUP; query++) {
-        const float maximum = butterfly_max(shared.running[query][threadIdx.x]);
+        maxima[query] = -FLT_MAX;
+    }
+    for (int key_block = threadIdx.x; key_block < blocks; key_block += ROUTE_THREADS) {
+        const float *slots = scores + score_slot(key_block, 0);
+        #pragma unroll
+        for (int query = 0; query < GROUP; query++) {
+            const bool routed = (masks[query * words + key_block / 32] >> lane) & 1u;
+            maxima[query] = routed ? maxima[query] : fmaxf(maxima[query], slots[query * 32]);
+        }
+    }
+    #pragma unroll
+    for (int query = 0; query < GROUP; query++) {
+        const float maximum = butterfly_max(maxima[query]);
         if (lane == 0) {
             shared.maxima[warp][query] = maximum;
         }
@@ -305,7 +373,6 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
     for (int query = 0; query < GROUP; query++) {
         sums[query] = 0.0f;
     }
-    if (ROUTE_SKIP < 2)
     for (int key_block = threadIdx.x; key_block < words * 32; key_block += ROUTE_THREADS) {
         const bool present = key_block < blocks;
         const float length = present ? static_cast<float>(tokens_in(key_block, tokens)) : 0.0f;
@@ -328,7 +395,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
     }
     __syncthreads();
 
-    // The weighted values of the tails. A warp takes every fourth group of four key blocks: a lane
+    // The weighted values of the tails. A warp takes every eighth group of four key blocks: a lane
     // loads four dimensions of their summed values (a row is one coalesced 512-byte load) and the
     // four weights each of the eight query blocks gives them (one 16-byte word a query), and keeps
     // its four dimensions of the eight sums. Routed blocks have weight zero. The warps' shares
@@ -341,8 +408,8 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
         for (int query = 0; query < GROUP; query++) {
             tails[query][0] = tails[query][1] = make_float2(0.0f, 0.0f);
         }
-        // The summed values come from L2, hundreds of cycles away, and two warps a scheduler do
-        // not hide that: the loads run AHEAD groups before their use.
+        // The summed values come from L2, hundreds of cycles away, which a few warps a scheduler
+        // do not hide: the loads run AHEAD groups before their use.
         constexpr int AHEAD = 4, STRIDE = ROUTE_WARPS * 4;
         float4 rows[AHEAD][4];
         const auto load_group = [&](int first, float4 (&into)[4]) {
@@ -357,7 +424,6 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
         for (int stage = 0; stage < AHEAD; stage++) {
             load_group(warp * 4 + stage * STRIDE, rows[stage]);
         }
-        if (ROUTE_SKIP < 1)
         for (int base = warp * 4; base < blocks; base += AHEAD * STRIDE) {
             #pragma unroll
             for (int stage = 0; stage < AHEAD; stage++) {
@@ -389,16 +455,15 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
                 tails[query][0].x, tails[query][0].y, tails[query][1].x, tails[query][1].y);
         }
         __syncthreads();
-        #pragma unroll
-        for (int query = 0; query < GROUP; query++) {
-            float total = staged[query * HEAD_DIM + threadIdx.x];
+        for (int item = threadIdx.x; item < GROUP * HEAD_DIM; item += ROUTE_THREADS) {
+            const int query = item / HEAD_DIM;
+            float total = staged[item];
             #pragma unroll
             for (int other = 1; other < ROUTE_WARPS; other++) {
-                total += staged[(other * GROUP + query) * HEAD_DIM + threadIdx.x];
+                total += staged[other * GROUP * HEAD_DIM + item];
             }
             if (first_query + query < blocks) {
-                workspace.tail_values[(head_rows + first_query + query) * HEAD_DIM + threadIdx.x] =
-                    total;
+                workspace.tail_values[(head_rows + first_query) * HEAD_DIM + item] = total;
             }
         }
     }
