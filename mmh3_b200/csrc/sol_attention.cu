@@ -22,13 +22,17 @@
 // order, and a pooled score over the tree of pooled_score.cuh. The tail sums are free to differ in
 // order and do.
 //
-// How the routing kernel is cut: a CTA of four warps takes eight query blocks of a head. A warp
-// owns two query blocks' thresholds, route lists and tail statistics; a thread owns a key block while
-// the scores are taken (the key's mean in its registers, against the eight query means in shared
-// memory), and in that same pass decides the block's fate for all eight queries, keeps the eight
-// running maxima of what is not routed, and casts its vote into the bit mask of routed blocks
-// (a ballot is 32 key blocks of one query: one word of the mask). The route lists are expanded
-// from those words, a lane to a word.
+// How the routing kernel is cut: a CTA of eight warps takes eight query blocks of a head, a warp
+// looking after one block's threshold, route list and tail statistics. While the scores are
+// taken, four threads own two key blocks: the blocks' centred means come through a staging buffer
+// in shared memory (asynchronous 16-byte copies, the next rows in flight while these are used),
+// each of the four threads keeps a quarter of both means in registers and meets the same quarter
+// of the eight query means in shared memory, and two exchanges among the four finish the sums.
+// Two of the four then decide a block's fate each for the eight queries and cast its vote into
+// the bit mask of routed blocks (a ballot is 16 key blocks of one query: half a word of the
+// mask). The maxima of the tails come from the stored scores, the weighted values of the tails
+// a warp to four key blocks with its loads four groups ahead, and the route lists are expanded
+// from the mask words, a lane to a word.
 #include <atomic>
 #include <cfloat>
 #include <cmath>
