@@ -125,6 +125,51 @@ def test_matches_the_reference(oracle, reference_kernels, tokens, heads, tau, si
     assert cosine >= 0.9995
 
 
+@pytest.mark.parametrize("tokens,heads", [(64 * 129 + 5, 2), (64 * 16 + 1, 1), (64 * 271, 1)])
+def test_routes_where_the_passes_over_the_keys_end_raggedly(oracle, reference_kernels, tokens,
+                                                            heads):
+    """The routing kernel walks a head's key blocks 128 to a CTA pass and 16 to a warp, and a word
+    of the mask of routed blocks is two warps' votes: 130 blocks (two in the second pass), 17 (one
+    in the second warp's share), 271 (a last mask word of 15 bits). Routes, counts and the tails'
+    maxima must be the CPU restatement's and the reference kernels' bits, the tails' sums close."""
+    tau, sinks = 1.0, SparseSinks((0, 2), (0, 0))
+    bits = make_case(oracle, tokens, heads)
+    inner = heads * 128
+    qkv = synthetic.bf16_tensor(bits, "cuda")
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    workspace = attention.SparseWorkspace(tokens, heads)
+    layout = attention.qkv_layout(heads)
+    attention.sparse(qkv, output, layout, SCALE, tau, sinks, workspace)
+    assert attention.take_status() == 0
+    work = oracle_lib.sol_route(oracle, bits, tokens, heads, tau, SCALE, flat_sinks(sinks))
+    routes, counts = workspace.routes_host()
+    assert_routes_equal(routes, counts, work["routes"], work["route_counts"])
+    assert bits_equal(workspace.tail_max, work["tail_max"])
+    # The tails are FP32 sums over up to 271 blocks in an order of the kernel's own: held to 1e-6
+    # of the largest sum where the terms cancel, to 1e-4 of the value elsewhere.
+    for name in ("tail_sum", "tail_values"):
+        ours = getattr(workspace, name).cpu().numpy().reshape(work[name].shape)
+        slack = 1e-6 * float(np.abs(work[name]).max())
+        assert np.allclose(ours, work[name], rtol=1e-4, atol=slack), name
+    assert 0.02 < workspace.routed_fraction() < 0.9
+
+    theirs = attention.SparseWorkspace(tokens, heads)
+    reference_output = torch.zeros_like(output)
+    raw = theirs.raw()
+    base = qkv.data_ptr()
+    assert reference_kernels.mmh3_sparse_attention(
+        base, base + 2 * inner, base + 4 * inner, reference_output.data_ptr(), tokens, heads,
+        ctypes.byref(layout), SCALE, tau, *flat_sinks(sinks), ctypes.byref(raw), None, 0,
+        None) == 0
+    torch.cuda.synchronize()
+    assert_routes_equal(routes, counts, *theirs.routes_host())
+    assert torch.equal(workspace.tail_max, theirs.tail_max)
+    assert torch.allclose(workspace.tail_sum, theirs.tail_sum, rtol=1e-4, atol=1e-5)
+    assert torch.allclose(workspace.tail_values, theirs.tail_values, rtol=1e-4,
+                          atol=1e-6 * float(theirs.tail_values.abs().max()))
+    assert torch.max(torch.abs(output.float() - reference_output.float())).item() < 2e-2
+
+
 def test_routing_everything_is_dense_attention():
     """With a threshold no score fails, every block is exact, the tails are empty, and the result
     is the dense kernel's (sparse.rs:240-277 on the GPU)."""
