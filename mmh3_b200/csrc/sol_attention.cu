@@ -293,6 +293,11 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
     {
         const int four = lane / 4, part = lane % 4;
         uint16_t *half_words = reinterpret_cast<uint16_t *>(masks);
+        uint32_t exact_queries = 0;
+        #pragma unroll
+        for (int query = 0; query < GROUP; query++) {
+            exact_queries |= (task.exact.query(first_query + query) ? 1u : 0u) << query;
+        }
         for (int first = warp * STEP_KEYS; first < words * 32; first += PASS_KEYS) {
             float2 keys[2][HEAD_DIM / 8];
             wait_for_own_copies();
@@ -308,30 +313,42 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
             __syncwarp();
             stage_keys(first + PASS_KEYS);
             // What this thread decides: the first of the two blocks in thread 0, the second in
-            // thread 1, nothing in the other two.
+            // thread 1, nothing in the other two. Bit q of `fated` says that the block is exact
+            // for query q whatever its score: a key every query attends so, a neighbour of the
+            // query block, a query block that attends every key so.
             const int key_block = first + four * 2 + part;
             const bool decides = part < 2 && key_block < blocks;
-            const bool key_sink = task.exact.key(key_block);
+            const int ahead = key_block - first_query;
+            const uint32_t fated =
+                task.exact.key(key_block)
+                    ? 0xffu
+                    : (exact_queries |
+                       (ahead >= -1 && ahead <= GROUP ? ((7u << (ahead + 1)) >> 2) & 0xffu : 0u));
             float *slots = scores + score_slot(key_block, 0);
+            uint32_t routed = 0;
             #pragma unroll 1
             for (int query = 0; query < GROUP; query++) {
-                const int query_block = first_query + query;
                 float both[2];
                 score_two_keys(reinterpret_cast<const float4 *>(shared.query_quarters[query][part]),
                                keys, both);
-                bool routed = false;
                 if (decides) {
                     const float score = __fmul_rn(part == 0 ? both[0] : both[1], log2_scale);
                     slots[query * 32] = score;
-                    routed = score > shared.thresholds[query] || key_sink ||
-                             (key_block >= query_block - 1 && key_block <= query_block + 1) ||
-                             task.exact.query(query_block);
+                    routed |= (score > shared.thresholds[query] ? 1u : 0u) << query;
                 }
-                const uint32_t votes = __ballot_sync(0xffffffffu, routed);
-                if (lane == 0) {
-                    half_words[(query * words) * 2 + first / STEP_KEYS] =
-                        static_cast<uint16_t>(two_of_every_four(votes));
-                }
+            }
+            routed = decides ? routed | fated : 0u;
+            // A ballot per query: 16 key blocks' votes, which lane q packs into query q's half
+            // word of the mask.
+            uint32_t votes = 0;
+            #pragma unroll
+            for (int query = 0; query < GROUP; query++) {
+                const uint32_t cast = __ballot_sync(0xffffffffu, (routed >> query) & 1u);
+                votes = lane == query ? cast : votes;
+            }
+            if (lane < GROUP) {
+                half_words[(lane * words) * 2 + first / STEP_KEYS] =
+                    static_cast<uint16_t>(two_of_every_four(votes));
             }
         }
     }
