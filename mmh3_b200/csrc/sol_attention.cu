@@ -46,7 +46,7 @@ namespace mmh3 {
 namespace {
 
 constexpr int BLOCK = 64;
-constexpr int GROUP = 8;                 // query blocks to a CTA
+constexpr int MOST_QUERIES = 8;          // query blocks to a CTA, where their scores fit
 constexpr int ROUTE_WARPS = 8;           // each looks after one of them
 constexpr int ROUTE_THREADS = ROUTE_WARPS * 32;
 constexpr int STEP_KEYS = 16;            // key blocks a warp scores at a time: two to four threads
@@ -156,6 +156,7 @@ constexpr int QUARTER_ROW = HEAD_DIM / 4 + 4;
 // Where the score of key block `key` against the CTA's query block `query` lies: 32 consecutive
 // key blocks of one query side by side (a warp's stores and loads meet no bank twice), and
 // four consecutive key blocks of a query in one 16-byte word.
+template <int GROUP>
 __device__ __forceinline__ int score_slot(int key, int query) {
     return (key / 32) * (32 * GROUP) + query * 32 + key % 32;
 }
@@ -215,6 +216,7 @@ __device__ __forceinline__ void score_two_keys(const float4 *__restrict__ query,
 // Static shared memory of the routing kernel; the dynamic part holds the scores (a slot for each
 // of `words` * 32 key blocks and GROUP queries), the staged key means ([PASS_KEYS][STAGED_ROW],
 // later the warps' shares of the tails) and the masks of routed key blocks ([GROUP][words]).
+template <int GROUP>
 struct __align__(16) RouteShared {
     float query_quarters[GROUP][4][QUARTER_ROW];
     float thresholds[GROUP];
@@ -222,6 +224,7 @@ struct __align__(16) RouteShared {
     float sums[ROUTE_WARPS][GROUP];
 };
 
+template <int GROUP>
 __global__ void __launch_bounds__(ROUTE_THREADS, 2)
     route_kernel(const Mmh3SparseWorkspace workspace, const RouteTask task) {
     const int tokens = task.tokens, blocks = task.blocks;
@@ -230,7 +233,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
     const int words = (blocks + 31) / 32;
     float *staged = scores + static_cast<size_t>(words) * 32 * GROUP;
     uint32_t *masks = reinterpret_cast<uint32_t *>(staged + STAGED_FLOATS);
-    __shared__ RouteShared shared;
+    __shared__ RouteShared<GROUP> shared;
     const int lane = threadIdx.x % 32;
     const int warp = threadIdx.x / 32;
     const int head = blockIdx.y;
@@ -321,10 +324,11 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
             const int ahead = key_block - first_query;
             const uint32_t fated =
                 task.exact.key(key_block)
-                    ? 0xffu
+                    ? (1u << GROUP) - 1u
                     : (exact_queries |
-                       (ahead >= -1 && ahead <= GROUP ? ((7u << (ahead + 1)) >> 2) & 0xffu : 0u));
-            float *slots = scores + score_slot(key_block, 0);
+                       (ahead >= -1 && ahead <= GROUP ? ((7u << (ahead + 1)) >> 2) & ((1u << GROUP) - 1u)
+                                                      : 0u));
+            float *slots = scores + score_slot<GROUP>(key_block, 0);
             uint32_t routed = 0;
             #pragma unroll 1
             for (int query = 0; query < GROUP; query++) {
@@ -361,7 +365,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
         maxima[query] = -FLT_MAX;
     }
     for (int key_block = threadIdx.x; key_block < blocks; key_block += ROUTE_THREADS) {
-        const float *slots = scores + score_slot(key_block, 0);
+        const float *slots = scores + score_slot<GROUP>(key_block, 0);
         #pragma unroll
         for (int query = 0; query < GROUP; query++) {
             const bool routed = (masks[query * words + key_block / 32] >> lane) & 1u;
@@ -397,7 +401,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
     for (int key_block = threadIdx.x; key_block < words * 32; key_block += ROUTE_THREADS) {
         const bool present = key_block < blocks;
         const float length = present ? static_cast<float>(tokens_in(key_block, tokens)) : 0.0f;
-        float *slots = scores + score_slot(key_block, 0);
+        float *slots = scores + score_slot<GROUP>(key_block, 0);
         #pragma unroll
         for (int query = 0; query < GROUP; query++) {
             const bool routed = (masks[query * words + key_block / 32] >> lane) & 1u;
@@ -453,7 +457,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
                     #pragma unroll
                     for (int query = 0; query < GROUP; query++) {
                         const float4 four =
-                            *reinterpret_cast<const float4 *>(scores + score_slot(first, query));
+                            *reinterpret_cast<const float4 *>(scores + score_slot<GROUP>(first, query));
                         const float weights[4] = {four.x, four.y, four.z, four.w};
                         #pragma unroll
                         for (int index = 0; index < 4; index++) {
@@ -531,15 +535,29 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
     }
 }
 
-int launch_route(const Mmh3SparseWorkspace &workspace, const RouteTask &task, int heads,
-                 cudaStream_t stream) {
-    const int blocks = task.blocks;
-    // Eight scores and eight mask bits per key block, and the staged key means.
+// The dynamic shared memory of route_kernel<GROUP>: a score and a mask bit per key block and
+// query, and the staged key means.
+template <int GROUP>
+size_t route_shared_bytes(int blocks) {
     const size_t words = (blocks + 31) / 32;
-    const size_t shared = words * 32 * GROUP * sizeof(float) + STAGED_FLOATS * sizeof(float) +
-                          GROUP * words * sizeof(uint32_t);
-    if (shared > 200 * 1024) {
-        return INVALID_VALUE;
+    return words * 32 * GROUP * sizeof(float) + STAGED_FLOATS * sizeof(float) +
+           GROUP * words * sizeof(uint32_t);
+}
+constexpr size_t MOST_ROUTE_SHARED = 200 * 1024;
+
+// Launches route_kernel with as many query blocks per CTA as their scores leave room for, halving
+// them as the sequence grows, as the reference does (sparse_attention.cu:289-315).
+template <int GROUP>
+int launch_route_with(const Mmh3SparseWorkspace &workspace, const RouteTask &task, int heads,
+                      cudaStream_t stream) {
+    const int blocks = task.blocks;
+    const size_t shared = route_shared_bytes<GROUP>(blocks);
+    if (shared > MOST_ROUTE_SHARED) {
+        if constexpr (GROUP > 1) {
+            return launch_route_with<GROUP / 2>(workspace, task, heads, stream);
+        } else {
+            return INVALID_VALUE;
+        }
     }
     // The opt-in limit only ever grows, and is per device.
     static std::atomic<size_t> configured[MAX_DEVICES];
@@ -548,16 +566,22 @@ int launch_route(const Mmh3SparseWorkspace &workspace, const RouteTask &task, in
         return static_cast<int>(cudaErrorInvalidDevice);
     }
     if (shared > configured[device].load(std::memory_order_relaxed)) {
-        const cudaError_t raised = cudaFuncSetAttribute(
-            route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+        const cudaError_t raised =
+            cudaFuncSetAttribute(route_kernel<GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(shared));
         if (raised != cudaSuccess) {
             return static_cast<int>(raised);
         }
         configured[device].store(shared, std::memory_order_relaxed);
     }
-    route_kernel<<<dim3((blocks + GROUP - 1) / GROUP, heads), ROUTE_THREADS, shared, stream>>>(
+    route_kernel<GROUP><<<dim3((blocks + GROUP - 1) / GROUP, heads), ROUTE_THREADS, shared, stream>>>(
         workspace, task);
     return static_cast<int>(cudaGetLastError());
+}
+
+int launch_route(const Mmh3SparseWorkspace &workspace, const RouteTask &task, int heads,
+                 cudaStream_t stream) {
+    return launch_route_with<MOST_QUERIES>(workspace, task, heads, stream);
 }
 
 // q . key mean of every token and head, in the units of the exponent: what moves a row's

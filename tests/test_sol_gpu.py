@@ -132,8 +132,21 @@ def test_routes_where_the_passes_over_the_keys_end_raggedly(oracle, reference_ke
     of the mask of routed blocks is two warps' votes: 130 blocks (two in the second pass), 17 (one
     in the second warp's share), 271 (a last mask word of 15 bits). Routes, counts and the tails'
     maxima must be the CPU restatement's and the reference kernels' bits, the tails' sums close."""
+    check_routing(oracle, reference_kernels, make_case(oracle, tokens, heads), tokens, heads)
+
+
+def test_routes_of_a_sequence_too_long_for_eight_query_blocks_a_cta(oracle, reference_kernels):
+    """Past 4,000 blocks the scores of eight query blocks no longer fit a CTA's shared memory and
+    the routing kernel takes four to a CTA (the reference halves its own count the same way,
+    sparse_attention.cu:289-315): 4,100 blocks and a partial one, same bits."""
+    tokens, heads = 64 * 4100 + 3, 1
+    qkv = synthetic.dense_qkv(tokens, heads, seed=9)
+    bits = qkv.view(torch.int16).numpy().view(np.uint16).reshape(tokens, 3, heads, 128)
+    check_routing(oracle, reference_kernels, bits, tokens, heads)
+
+
+def check_routing(oracle, reference_kernels, bits, tokens, heads):
     tau, sinks = 1.0, SparseSinks((0, 2), (0, 0))
-    bits = make_case(oracle, tokens, heads)
     inner = heads * 128
     qkv = synthetic.bf16_tensor(bits, "cuda")
     output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
@@ -145,7 +158,7 @@ def test_routes_where_the_passes_over_the_keys_end_raggedly(oracle, reference_ke
     routes, counts = workspace.routes_host()
     assert_routes_equal(routes, counts, work["routes"], work["route_counts"])
     assert bits_equal(workspace.tail_max, work["tail_max"])
-    # The tails are FP32 sums over up to 271 blocks in an order of the kernel's own: held to 1e-6
+    # The tails are FP32 sums over hundreds of blocks in an order of the kernel's own: held to 1e-6
     # of the largest sum where the terms cancel, to 1e-4 of the value elsewhere.
     for name in ("tail_sum", "tail_values"):
         ours = getattr(workspace, name).cpu().numpy().reshape(work[name].shape)
