@@ -168,51 +168,6 @@ __device__ __forceinline__ uint32_t two_of_every_four(uint32_t votes) {
     return (votes | (votes >> 8)) & 0x0000ffffu;
 }
 
-// The pooled scores of two key means against one query mean by four threads, in the FP32 order
-// of pooled_score.cuh: 32 chains l of four fused multiply-adds over dimensions l, l + 32, l + 64,
-// l + 96, then a butterfly over bits 4, 3, 2, 1, 0 of l. Thread c of the four holds the chains
-// l = 4 a + c, a = 0 .. 7, that is dimensions 4 m + c with m = a + 8 k for step k: of a key as the
-// pairs key[i] = (m = 2 i, m = 2 i + 1), of the query as 16-byte words of four consecutive m.
-// Chains a and a + 1 are the halves of packed operations; bits 4, 3, 2 of l are bits 2, 1, 0 of a
-// (two packed additions and the sum of the halves), bits 1 and 0 are c: two exchanges among the
-// four threads, after which each holds both scores.
-__device__ __forceinline__ void score_two_keys(const float4 *__restrict__ query,
-                                               const float2 (&keys)[2][HEAD_DIM / 8],
-                                               float (&scores)[2]) {
-    float2 sums[2][4];
-    #pragma unroll
-    for (int key = 0; key < 2; key++) {
-        #pragma unroll
-        for (int pair = 0; pair < 4; pair++) {
-            sums[key][pair] = make_float2(0.0f, 0.0f);
-        }
-    }
-    #pragma unroll
-    for (int step = 0; step < 4; step++) {
-        #pragma unroll
-        for (int half = 0; half < 2; half++) {
-            const float4 four = query[step * 2 + half];
-            #pragma unroll
-            for (int key = 0; key < 2; key++) {
-                sums[key][half * 2] = __ffma2_rn(make_float2(four.x, four.y),
-                                                 keys[key][half * 2 + step * 4],
-                                                 sums[key][half * 2]);
-                sums[key][half * 2 + 1] = __ffma2_rn(make_float2(four.z, four.w),
-                                                     keys[key][half * 2 + 1 + step * 4],
-                                                     sums[key][half * 2 + 1]);
-            }
-        }
-    }
-    #pragma unroll
-    for (int key = 0; key < 2; key++) {
-        const float2 folded = __fadd2_rn(__fadd2_rn(sums[key][0], sums[key][2]),
-                                         __fadd2_rn(sums[key][1], sums[key][3]));
-        float sum = __fadd_rn(folded.x, folded.y);
-        sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, 2));
-        scores[key] = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, 1));
-    }
-}
-
 // Static shared memory of the routing kernel; the dynamic part holds the scores (a slot for each
 // of `words` * 32 key blocks and GROUP queries), the staged key means ([PASS_KEYS][STAGED_ROW],
 // later the warps' shares of the tails) and the masks of routed key blocks ([GROUP][words]).
