@@ -231,15 +231,27 @@ __global__ void __launch_bounds__(COSINE_THREADS, 1)
 // ---------------------------------------------------------------------------------------------
 // 2. Routes from the cosines.
 
-constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_WARPS = 8;
 constexpr int ROUTE_THREADS = ROUTE_WARPS * 32;
 constexpr int BINS = 512;
+constexpr int LISTED = 1024; // open tiles a warp can list; a row with more is scored whole
 // |approximate - exact| <= BOUND * |q| |k| * scale. Operands cut to TF32 are each off by less
 // than 2^-10 of themselves, so a product by less than 2^-8.99 of its size, and the sum of the 128
 // sizes is at most |q| |k|; the FP32 accumulation, the 16-bit cosine (2^-16) and the rounding of
 // the exact evaluation itself add less than 2^-13 together. 2^-8 leaves a factor of 1.8.
 constexpr float BOUND = 0.00390625f;
-enum Fate : uint8_t { DROPPED = 0, KEPT = 1, OPEN = 2 };
+// A tile's fate once its approximate score is placed: certain tiles carry it in the row of scores
+// itself, as an infinity that any threshold among the open ones sorts the right way.
+constexpr uint32_t KEPT_BITS = 0x7f800000u, DROPPED_BITS = 0xff800000u;
+
+// The open tiles of a row: those listed, or, when the whole row is open, every video tile.
+struct OpenTiles {
+    const uint16_t *list;
+    int first_video_tile;
+    __device__ __forceinline__ int operator[](int index) const {
+        return list != nullptr ? list[index] : first_video_tile + index;
+    }
+};
 
 __device__ __forceinline__ uint32_t order_preserving(float value) {
     const uint32_t bits = __float_as_uint(value);
@@ -263,13 +275,13 @@ __device__ __forceinline__ float warp_sum(float value) {
 template <int BATCH>
 __device__ __forceinline__ void exact_scores(const float (&query)[4],
                                              const float *__restrict__ head_keys,
-                                             const uint16_t *tiles, int count, int lane,
-                                             float scale, float (&scores)[BATCH]) {
+                                             const OpenTiles &tiles, int first, int count,
+                                             int lane, float scale, float (&scores)[BATCH]) {
     float loaded[BATCH][4];
     #pragma unroll
     for (int index = 0; index < BATCH; index++) {
         const float *key =
-            head_keys + static_cast<size_t>(tiles[index < count ? index : 0]) * HEAD_DIM + lane;
+            head_keys + static_cast<size_t>(tiles[first + (index < count ? index : 0)]) * HEAD_DIM + lane;
         #pragma unroll
         for (int part = 0; part < 4; part++) {
             loaded[index][part] = __ldg(key + part * 32);
@@ -301,7 +313,7 @@ __device__ __forceinline__ void exact_scores(const float (&query)[4],
 // Among the `count` tiles listed in `list`, whose exact scores are in `values`: the order-preserving
 // bits of the `wanted`-th largest score, and how many of the tiles equal to it belong to the
 // `wanted` largest. One byte of the bits at a time from the top; `bins` is 256 counters.
-__device__ __forceinline__ void select_among(const uint16_t *list, int count, const float *values,
+__device__ __forceinline__ void select_among(const OpenTiles &list, int count, const float *values,
                                              int wanted, int *bins, int lane, uint32_t &threshold,
                                              int &ties) {
     uint32_t settled = 0;
@@ -361,21 +373,20 @@ __device__ __forceinline__ void select_among(const uint16_t *list, int count, co
     }
 }
 
-__global__ void __launch_bounds__(ROUTE_THREADS, 3)
+__global__ void __launch_bounds__(ROUTE_THREADS, 2)
     route_kernel(Mmh3VsaWorkspace workspace, int tiles, int prefix_tiles, int kept, float scale) {
-    // [tiles] key norms, then per warp: [tiles] scores, [BINS] counters, [tiles] tile numbers,
-    // [tiles] fates.
+    // [tiles] key norms, then per warp: [tiles] scores, [BINS] counters, [LISTED] tile numbers.
     extern __shared__ __align__(16) uint8_t route_memory[];
     const int lane = threadIdx.x % 32;
     const int warp = threadIdx.x / 32;
     const int head = blockIdx.y;
     const int padded = (tiles + 3) & ~3;
     float *key_norms = reinterpret_cast<float *>(route_memory);
-    uint8_t *mine = route_memory + padded * 4 + static_cast<size_t>(warp) * (padded * 7 + BINS * 4);
+    uint8_t *mine = route_memory + padded * 4 +
+                    static_cast<size_t>(warp) * (padded * 4 + BINS * 4 + LISTED * 2);
     float *values = reinterpret_cast<float *>(mine);
     int *bins = reinterpret_cast<int *>(mine + padded * 4);
     uint16_t *list = reinterpret_cast<uint16_t *>(mine + padded * 4 + BINS * 4);
-    uint8_t *fates = mine + padded * 6 + BINS * 4;
     __shared__ float warp_maxima[ROUTE_WARPS];
 
     const float *head_keys = workspace.pooled_key + static_cast<size_t>(head) * tiles * HEAD_DIM;
@@ -420,7 +431,11 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
         warp_maxima[warp] = largest;
     }
     __syncthreads();
-    largest = fmaxf(fmaxf(warp_maxima[0], warp_maxima[1]), fmaxf(warp_maxima[2], warp_maxima[3]));
+    largest = warp_maxima[0];
+    #pragma unroll
+    for (int other = 1; other < ROUTE_WARPS; other++) {
+        largest = fmaxf(largest, warp_maxima[other]);
+    }
 
     // The CTAs of a head share its query tiles round robin, a warp to a tile.
     for (int query_tile = blockIdx.x * ROUTE_WARPS + warp; query_tile < tiles;
@@ -514,29 +529,32 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
             __syncwarp();
         }
 
-        // Every tile's fate, and the open ones listed in ascending order. Everything is open when
-        // the scores could not be binned or the counts do not add up.
+        // Every tile's fate, and the open ones listed in ascending order: a certain tile's score
+        // gives way to the infinity that stands for its fate. Everything is open when the scores
+        // could not be binned, the counts do not add up or the list overflows.
         int certain = 0, listed = 0;
         for (int first = prefix_tiles; first < tiles; first += 32) {
             const int tile = first + lane;
-            uint8_t fate = DROPPED;
+            bool kept_for_certain = false, open = false;
             if (tile < tiles) {
                 const float value = binned ? values[tile] : 0.0f;
-                fate = value > keep_above ? KEPT : (value < drop_below ? DROPPED : OPEN);
-                fates[tile] = fate;
+                kept_for_certain = value > keep_above;
+                open = !kept_for_certain && !(value < drop_below);
+                if (!open) {
+                    values[tile] = __uint_as_float(kept_for_certain ? KEPT_BITS : DROPPED_BITS);
+                }
             }
-            certain += __popc(__ballot_sync(0xffffffffu, fate == KEPT));
-            const unsigned open_mask = __ballot_sync(0xffffffffu, tile < tiles && fate == OPEN);
-            if (tile < tiles && fate == OPEN) {
-                list[listed + __popc(open_mask & ((1u << lane) - 1))] = static_cast<uint16_t>(tile);
+            certain += __popc(__ballot_sync(0xffffffffu, kept_for_certain));
+            const unsigned open_mask = __ballot_sync(0xffffffffu, open);
+            const int slot = listed + __popc(open_mask & ((1u << lane) - 1));
+            if (open && slot < LISTED) {
+                list[slot] = static_cast<uint16_t>(tile);
             }
             listed += __popc(open_mask);
         }
-        if (kept - certain < 1 || kept - certain > listed) {
-            for (int tile = prefix_tiles + lane; tile < tiles; tile += 32) {
-                fates[tile] = OPEN;
-                list[tile - prefix_tiles] = static_cast<uint16_t>(tile);
-            }
+        OpenTiles open_tiles = {list, prefix_tiles};
+        if (kept - certain < 1 || kept - certain > listed || listed > LISTED) {
+            open_tiles.list = nullptr;
             certain = 0;
             listed = video_tiles;
         }
@@ -546,18 +564,19 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
         constexpr int BATCH = 8;
         for (int first = 0; first < listed; first += BATCH) {
             float scores[BATCH];
-            exact_scores<BATCH>(query, head_keys, list + first, listed - first, lane, scale, scores);
+            exact_scores<BATCH>(query, head_keys, open_tiles, first, listed - first, lane, scale,
+                                scores);
             #pragma unroll
             for (int index = 0; index < BATCH; index++) {
                 if (lane == index && first + index < listed) {
-                    values[list[first + index]] = scores[index];
+                    values[open_tiles[first + index]] = scores[index];
                 }
             }
         }
         __syncwarp();
         uint32_t threshold;
         int ties;
-        select_among(list, listed, values, kept - certain, bins, lane, threshold, ties);
+        select_among(open_tiles, listed, values, kept - certain, bins, lane, threshold, ties);
 
         // The prefix tiles, the certain ones, and of the open ones those above the threshold and
         // the first `ties` at it. The list lands on the cosines it was computed from, which are
@@ -568,14 +587,9 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 3)
             bool keep = tile < tiles && tile < prefix_tiles;
             bool tie = false;
             if (tile < tiles && tile >= prefix_tiles) {
-                const uint8_t fate = fates[tile];
-                if (fate == OPEN) {
-                    const uint32_t bits = order_preserving(values[tile]);
-                    keep = bits > threshold;
-                    tie = bits == threshold;
-                } else {
-                    keep = fate == KEPT;
-                }
+                const uint32_t bits = order_preserving(values[tile]);
+                keep = bits > threshold;
+                tie = bits == threshold;
             }
             const unsigned tie_mask = __ballot_sync(0xffffffffu, tie);
             if (tie && ties_seen + __popc(tie_mask & ((1u << lane) - 1)) < ties) {
@@ -691,7 +705,7 @@ __global__ void __launch_bounds__(COARSE_WARPS * 32)
 
 size_t route_shared_bytes(int tiles) {
     const size_t padded = (static_cast<size_t>(tiles) + 3) & ~static_cast<size_t>(3);
-    return padded * 4 + ROUTE_WARPS * (padded * 7 + BINS * 4);
+    return padded * 4 + ROUTE_WARPS * (padded * 4 + BINS * 4 + LISTED * 2);
 }
 
 } // namespace
@@ -749,8 +763,8 @@ int launch_select(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int p
         configured[device].store(shared, std::memory_order_relaxed);
     }
     // Every CTA computes its head's key norms once, so there are only as many CTAs as the device
-    // holds at a time (three to an SM), shared out evenly over the heads.
-    const int resident = 3 * multiprocessor_count();
+    // holds at a time (two to an SM), shared out evenly over the heads.
+    const int resident = 2 * multiprocessor_count();
     const int per_head = std::max(1, std::min((tiles + ROUTE_WARPS - 1) / ROUTE_WARPS, resident / heads));
     route_kernel<<<dim3(per_head, heads), ROUTE_THREADS, shared, stream>>>(
         workspace, tiles, prefix_tiles, kept, scale);
