@@ -287,3 +287,38 @@ def test_larger_plan_with_an_odd_tile_count(oracle, reference_kernels):
     b = reference_output.float().cpu().numpy().astype(np.float64).ravel()
     assert np.max(np.abs(a - b)) < 0.05
     assert a @ b / (np.linalg.norm(a) * np.linalg.norm(b)) >= 0.9995
+
+
+def test_a_row_of_equal_scores_longer_than_the_list_of_open_tiles(reference_kernels):
+    """Every key row the same, so every video tile of a row scores alike and none is certain: the
+    route kernel lists at most 1,024 open tiles and takes a row with more (here all 2,016) whole.
+    The routes must still be the reference kernels': the first `kept` video tiles, ties going to
+    the lower index (vsa.rs:341-357 on the GPU, at the benchmark's plan)."""
+    layout, plan = synthetic.video_plan()
+    tokens, heads = len(layout), 1
+    inner = heads * 128
+    kept = plan.kept_video_tiles(0.875)
+    generator = torch.Generator().manual_seed(21)
+    rows = torch.randn((tokens, 3, heads, 128), generator=generator)
+    rows[:, 1] = torch.randn((1, heads, 128), generator=generator)
+    qkv = rows.to(torch.bfloat16).cuda()
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    reference_output = torch.zeros_like(output)
+    workspace = attention.VsaWorkspace(plan, tokens, heads)
+    theirs = attention.VsaWorkspace(plan, tokens, heads)
+    vsa_layout = attention.qkv_layout(heads)
+    attention.vsa(qkv, None, output, vsa_layout, SCALE, kept, workspace)
+    raw = theirs.raw()
+    base = qkv.data_ptr()
+    assert reference_kernels.mmh3_vsa_attention(
+        base, base + 2 * inner, base + 4 * inner, None, inner, reference_output.data_ptr(), tokens,
+        heads, ctypes.byref(vsa_layout), SCALE, plan.tiles, plan.prefix_tiles, kept,
+        ctypes.byref(raw), None, 0, None) == 0
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    routes, counts = workspace.routes_host()
+    assert_routes_equal(routes, counts, *theirs.routes_host())
+    assert (counts[:, plan.prefix_tiles:] == plan.prefix_tiles + kept).all()
+    a = output.float().cpu().numpy().astype(np.float64).ravel()
+    b = reference_output.float().cpu().numpy().astype(np.float64).ravel()
+    assert np.max(np.abs(a - b)) < 0.05
