@@ -47,10 +47,13 @@ constexpr int PANEL = 128;                     // query tiles and key tiles to a
 constexpr int PANEL_SLAB = PANEL * 128;        // 128 rows of 32 floats
 constexpr int PANEL_SLABS = HEAD_DIM / 32;
 constexpr int PANEL_BYTES = PANEL_SLABS * PANEL_SLAB;
-constexpr int COSINE_THREADS = 160;            // four warps own the TMEM lanes, the fifth loads and issues
-constexpr int COSINE_SMEM_NORMS = 2 * PANEL_BYTES;
-constexpr int COSINE_SMEM_BARRIERS = COSINE_SMEM_NORMS + PANEL * 4;
-constexpr int COSINE_SMEM_BYTES = COSINE_SMEM_BARRIERS + 64 + 1024;
+constexpr int COSINE_STAGES = 2;               // key panels and accumulators in flight
+constexpr int COSINE_STORING_WARPS = 8;        // two to a quarter of the TMEM lanes, 64 columns each
+constexpr int COSINE_THREADS = (COSINE_STORING_WARPS + 1) * 32; // the ninth warp loads and issues
+constexpr int COSINE_SMEM_KEYS = PANEL_BYTES;
+constexpr int COSINE_SMEM_NORMS = (1 + COSINE_STAGES) * PANEL_BYTES;
+constexpr int COSINE_SMEM_BARRIERS = COSINE_SMEM_NORMS + COSINE_STAGES * PANEL * 4;
+constexpr int COSINE_SMEM_BYTES = COSINE_SMEM_BARRIERS + 128 + 1024;
 constexpr float COSINE_ONE = 32767.0f;
 constexpr uint32_t FORMAT_TF32 = 2;            // kind::tf32
 constexpr uint32_t COSINE_MMA =
@@ -91,16 +94,28 @@ __device__ __forceinline__ float panel_row_square(const uint8_t *panel, int row)
     return sum;
 }
 
+// A CTA keeps one panel of 128 query means and walks the key panels blockIdx.x, blockIdx.x +
+// gridDim.x, ...: the ninth warp's first lane loads them into a ring of two and issues each
+// panel's 16 MMAs into one of two accumulators, and the eight storing warps take a panel's norms
+// and store the finished accumulator's cosines while the next panel's MMAs run.
 __global__ void __launch_bounds__(COSINE_THREADS, 1)
     cosine_kernel(const __grid_constant__ CosineMaps maps, uint16_t *__restrict__ table, int tiles,
                   unsigned int *status) {
     extern __shared__ uint8_t shared_memory[];
     const uint32_t base = (smem_u32(shared_memory) + 1023u) & ~1023u;
     uint8_t *aligned = shared_memory + (base - smem_u32(shared_memory));
-    const uint32_t loaded = base + COSINE_SMEM_BARRIERS, multiplied = loaded + 8;
+    // Barriers: the query panel; per stage the key panel loaded and free again, its norms written,
+    // the accumulator full and read out.
+    const uint32_t barriers = base + COSINE_SMEM_BARRIERS;
+    const uint32_t query_loaded = barriers;
+    const auto key_loaded = [&](int stage) { return barriers + 8 + stage * 8; };
+    const auto key_free = [&](int stage) { return barriers + 8 + (COSINE_STAGES + stage) * 8; };
+    const auto norms_written = [&](int stage) { return barriers + 8 + (2 * COSINE_STAGES + stage) * 8; };
+    const auto multiplied = [&](int stage) { return barriers + 8 + (3 * COSINE_STAGES + stage) * 8; };
+    const auto read_out = [&](int stage) { return barriers + 8 + (4 * COSINE_STAGES + stage) * 8; };
     float *inverse_key_norms = reinterpret_cast<float *>(aligned + COSINE_SMEM_NORMS);
-    volatile uint32_t *tmem_slot =
-        reinterpret_cast<volatile uint32_t *>(aligned + COSINE_SMEM_BARRIERS + 16);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(
+        aligned + COSINE_SMEM_BARRIERS + 8 + 5 * COSINE_STAGES * 8);
     volatile uint32_t *abort_flag = tmem_slot + 1;
     const Watchdog watchdog = {abort_flag, status};
     if (*reinterpret_cast<volatile unsigned int *>(status) != 0) {
@@ -108,74 +123,136 @@ __global__ void __launch_bounds__(COSINE_THREADS, 1)
     }
     const int warp = threadIdx.x / 32;
     const int lane = threadIdx.x % 32;
-    const int first_key = blockIdx.x * PANEL;
     const int first_query = blockIdx.y * PANEL;
     const int head = blockIdx.z;
+    const int panels = (tiles + PANEL - 1) / PANEL;
+    // The key panels of this CTA: blockIdx.x + turn * gridDim.x.
+    const int turns = (panels - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                      static_cast<int>(gridDim.x);
 
     if (threadIdx.x == 0) {
-        mbar_init(loaded, 1);
-        mbar_init(multiplied, 1);
+        mbar_init(query_loaded, 1);
+        for (int stage = 0; stage < COSINE_STAGES; stage++) {
+            mbar_init(key_loaded(stage), 1);
+            mbar_init(key_free(stage), 1 + COSINE_STORING_WARPS / 2); // the MMAs and the norms' readers
+            mbar_init(norms_written(stage), COSINE_STORING_WARPS / 2);
+            mbar_init(multiplied(stage), 1);
+            mbar_init(read_out(stage), COSINE_STORING_WARPS);
+        }
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async();
     }
-    if (warp == 4) {
-        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), PANEL);
+    if (warp == COSINE_STORING_WARPS) {
+        tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), COSINE_STAGES * PANEL);
     }
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == 4) {
+    if (warp == COSINE_STORING_WARPS) {
         if (lane == 0) {
-            mbar_expect_tx(loaded, 2 * PANEL_BYTES);
+            const auto load_keys = [&](int turn) {
+                const int stage = turn % COSINE_STAGES;
+                const int first_key = (static_cast<int>(blockIdx.x) + turn * static_cast<int>(gridDim.x)) * PANEL;
+                mbar_expect_tx(key_loaded(stage), PANEL_BYTES);
+                for (int slab = 0; slab < PANEL_SLABS; slab++) {
+                    tma_load_3d(base + COSINE_SMEM_KEYS + stage * PANEL_BYTES + slab * PANEL_SLAB,
+                                &maps.key, key_loaded(stage), slab * 32, first_key, head);
+                }
+            };
+            mbar_expect_tx(query_loaded, PANEL_BYTES);
             for (int slab = 0; slab < PANEL_SLABS; slab++) {
-                tma_load_3d(base + slab * PANEL_SLAB, &maps.query, loaded, slab * 32, first_query,
-                            head);
-                tma_load_3d(base + PANEL_BYTES + slab * PANEL_SLAB, &maps.key, loaded, slab * 32,
-                            first_key, head);
+                tma_load_3d(base + slab * PANEL_SLAB, &maps.query, query_loaded, slab * 32,
+                            first_query, head);
             }
-            if (mbar_wait(loaded, 0, watchdog, STATUS_SELECT | 1)) {
+            for (int turn = 0; turn < min(turns, COSINE_STAGES); turn++) {
+                load_keys(turn);
+            }
+            bool alive = mbar_wait(query_loaded, 0, watchdog, STATUS_SELECT | 1);
+            for (int turn = 0; alive && turn < turns; turn++) {
+                const int stage = turn % COSINE_STAGES;
+                const uint32_t parity = (turn / COSINE_STAGES) & 1;
+                alive = mbar_wait(key_loaded(stage), parity, watchdog, STATUS_SELECT | 2) &&
+                        mbar_wait(read_out(stage), parity ^ 1, watchdog, STATUS_SELECT | 4);
+                if (!alive) {
+                    break;
+                }
                 tcgen05_fence_after();
                 // Eight floats, 32 bytes, to an MMA: four steps to a slab of 32 dimensions.
+                const uint32_t keys = base + COSINE_SMEM_KEYS + stage * PANEL_BYTES;
                 #pragma unroll
                 for (int step = 0; step < HEAD_DIM / 8; step++) {
                     const uint32_t offset = (step / 4) * PANEL_SLAB + (step % 4) * 32;
-                    mma_tf32(tmem, smem_descriptor(base + offset, 16, 1024),
-                             smem_descriptor(base + PANEL_BYTES + offset, 16, 1024), step > 0);
+                    mma_tf32(tmem + stage * PANEL, smem_descriptor(base + offset, 16, 1024),
+                             smem_descriptor(keys + offset, 16, 1024), step > 0);
                 }
-                tcgen05_commit(multiplied);
+                tcgen05_commit(multiplied(stage));
+                tcgen05_commit(key_free(stage));
+                // The panel after this one goes where the panel before this one was, once the
+                // MMAs and the norms are done with that.
+                if (turn >= 1 && turn + 1 < turns) {
+                    const int refilled = (turn + 1) % COSINE_STAGES;
+                    const uint32_t emptied = ((turn + 1) / COSINE_STAGES - 1) & 1;
+                    alive = mbar_wait(key_free(refilled), emptied, watchdog, STATUS_SELECT | 5);
+                    if (alive) {
+                        load_keys(turn + 1);
+                    }
+                }
             }
         }
     } else {
-        // Thread r: the norm of query row r and of key row r while the MMAs run, then row r of the
-        // products.
-        const int row = warp * 32 + lane;
-        bool alive = __all_sync(0xffffffffu, mbar_wait(loaded, 0, watchdog, STATUS_SELECT | 2));
+        // Thread r of the first four warps: the norm of key row r of every panel; every thread: the
+        // norm of its query row and half of that row of the products.
+        const int row = (warp % 4) * 32 + lane;
+        const int half = warp / 4;
+        bool alive = __all_sync(0xffffffffu, mbar_wait(query_loaded, 0, watchdog, STATUS_SELECT | 2));
         float inverse_query_norm = 0.0f;
         if (alive) {
             const float query_square = panel_row_square(aligned, row);
-            const float key_square = panel_row_square(aligned + PANEL_BYTES, row);
             inverse_query_norm = query_square > 0.0f ? rsqrtf(query_square) : 0.0f;
-            inverse_key_norms[row] = key_square > 0.0f ? rsqrtf(key_square) : 0.0f;
         }
-        // The four warps that own the rows, not the one that loads.
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        alive = alive &&
-                __all_sync(0xffffffffu, mbar_wait(multiplied, 0, watchdog, STATUS_SELECT | 3));
-        if (alive) {
+        const int query_tile = first_query + row;
+        const uint32_t lane_base = static_cast<uint32_t>((warp % 4) * 32) << 16;
+        // Whole 16-byte groups of a row can be stored as such when every row starts on one.
+        const bool vector_stores = tiles % 8 == 0 && reinterpret_cast<uintptr_t>(table) % 16 == 0;
+        for (int turn = 0; alive && turn < turns; turn++) {
+            const int stage = turn % COSINE_STAGES;
+            const uint32_t parity = (turn / COSINE_STAGES) & 1;
+            const int first_key = (static_cast<int>(blockIdx.x) + turn * static_cast<int>(gridDim.x)) * PANEL;
+            float *norms = inverse_key_norms + stage * PANEL;
+            if (half == 0) {
+                // The norms of this stage's last panel have been read by every warp once its
+                // accumulator is read out.
+                alive = __all_sync(0xffffffffu,
+                                   mbar_wait(key_loaded(stage), parity, watchdog, STATUS_SELECT | 6) &&
+                                       mbar_wait(read_out(stage), parity ^ 1, watchdog,
+                                                 STATUS_SELECT | 7));
+                if (!alive) {
+                    break;
+                }
+                const float key_square =
+                    panel_row_square(aligned + COSINE_SMEM_KEYS + stage * PANEL_BYTES, row);
+                norms[row] = key_square > 0.0f ? rsqrtf(key_square) : 0.0f;
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(norms_written(stage));
+                    mbar_arrive(key_free(stage));
+                }
+            }
+            alive = __all_sync(0xffffffffu,
+                               mbar_wait(norms_written(stage), parity, watchdog, STATUS_SELECT | 8) &&
+                                   mbar_wait(multiplied(stage), parity, watchdog, STATUS_SELECT | 3));
+            if (!alive) {
+                break;
+            }
             tcgen05_fence_after();
-            const int query_tile = first_query + row;
-            const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-            uint16_t *slots = table + (static_cast<size_t>(head) * tiles + query_tile) * tiles +
-                              first_key;
-            // Whole 16-byte groups of a row can be stored as such when every row starts on one.
-            const bool vector_stores = tiles % 8 == 0 && reinterpret_cast<uintptr_t>(table) % 16 == 0;
+            uint16_t *slots = table + (static_cast<size_t>(head) * tiles + query_tile) * tiles + first_key;
             #pragma unroll
-            for (int chunk = 0; chunk < PANEL / 32; chunk++) {
+            for (int chunk = half * 2; chunk < half * 2 + 2; chunk++) {
                 uint32_t values[32];
-                tmem_load_32(tmem + lane_base + chunk * 32, values);
+                tmem_load_32(tmem + lane_base + stage * PANEL + chunk * 32, values);
                 tmem_wait_load();
                 uint32_t packed[16];
                 #pragma unroll
@@ -185,7 +262,7 @@ __global__ void __launch_bounds__(COSINE_THREADS, 1)
                     for (int side = 0; side < 2; side++) {
                         const int column = chunk * 32 + pair * 2 + side;
                         const float cosine = __uint_as_float(values[pair * 2 + side]) *
-                                             inverse_query_norm * inverse_key_norms[column];
+                                             inverse_query_norm * norms[column];
                         fractions[side] =
                             __float2int_rn(fminf(fmaxf(cosine, -1.0f), 1.0f) * COSINE_ONE);
                     }
@@ -213,18 +290,24 @@ __global__ void __launch_bounds__(COSINE_THREADS, 1)
                     }
                 }
             }
+            // This warp is done with the accumulator and with the stage's norms.
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(read_out(stage));
+            }
         }
     }
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == COSINE_STORING_WARPS) {
         if (*abort_flag != 0) {
             for (int spin = 0; spin < 64; spin++) {
                 __nanosleep(1000);
             }
         }
         tcgen05_fence_after();
-        tmem_dealloc(tmem, PANEL);
+        tmem_dealloc(tmem, COSINE_STAGES * PANEL);
     }
 }
 
@@ -740,8 +823,13 @@ int launch_select(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int p
                                dimensions, strides, box)) {
             return NOT_SUPPORTED;
         }
+        // A CTA walks a share of the key panels of its query panel: as few shares as fill the
+        // device four times over, so that the last round of CTAs costs little.
         const int panels = (tiles + PANEL - 1) / PANEL;
-        cosine_kernel<<<dim3(panels, panels, heads), COSINE_THREADS, COSINE_SMEM_BYTES, stream>>>(
+        const int wanted = 4 * multiprocessor_count();
+        const int shares =
+            std::max(1, std::min(panels, (wanted + panels * heads - 1) / (panels * heads)));
+        cosine_kernel<<<dim3(shares, panels, heads), COSINE_THREADS, COSINE_SMEM_BYTES, stream>>>(
             maps, workspace.routes, tiles, status);
         const cudaError_t launched = cudaGetLastError();
         if (launched != cudaSuccess) {
