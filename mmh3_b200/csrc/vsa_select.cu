@@ -349,20 +349,23 @@ __device__ __forceinline__ float warp_sum(float value) {
     return value;
 }
 
-// The pooled scores of BATCH tiles in the reference's FP32 order, by a whole warp: lane l holds
+// The pooled scores of eight tiles in the reference's FP32 order, by a whole warp: lane l holds
 // dimensions l, l + 32, l + 64, l + 96 of the query and reads the same of each key (coalesced
-// loads, all BATCH tiles' in flight together: a route's open tiles are scattered over a head's
+// loads, all eight tiles' in flight together: a route's open tiles are scattered over a head's
 // megabyte of means, and one tile at a time would wait for L2 a hundred times a row), chains four
-// fused multiply-adds from zero, and the xor butterfly from bit 4 down to bit 0 adds the 32 chains
-// in the reference's tree (an addition commutes, so every lane ends with the same bits).
-template <int BATCH>
-__device__ __forceinline__ void exact_scores(const float (&query)[4],
-                                             const float *__restrict__ head_keys,
-                                             const OpenTiles &tiles, int first, int count,
-                                             int lane, float scale, float (&scores)[BATCH]) {
-    float loaded[BATCH][4];
+// fused multiply-adds from zero, and a xor butterfly from bit 4 down to bit 0 adds the 32 chains
+// in the reference's tree. The butterfly narrows as it goes: at bit 4 a lane keeps four of the
+// eight tiles' sums and hands the other four to its partner, at bit 3 two, at bit 2 one, so that
+// each sum is still the one the full butterfly leaves in that lane (an addition commutes) at 9
+// exchanges instead of 40. Lane l ends with the score of tile (l / 4) % 8 of the eight.
+constexpr int EXACT_BATCH = 8;
+__device__ __forceinline__ float exact_scores(const float (&query)[4],
+                                              const float *__restrict__ head_keys,
+                                              const OpenTiles &tiles, int first, int count,
+                                              int lane, float scale) {
+    float loaded[EXACT_BATCH][4];
     #pragma unroll
-    for (int index = 0; index < BATCH; index++) {
+    for (int index = 0; index < EXACT_BATCH; index++) {
         const float *key =
             head_keys + static_cast<size_t>(tiles[first + (index < count ? index : 0)]) * HEAD_DIM + lane;
         #pragma unroll
@@ -370,27 +373,35 @@ __device__ __forceinline__ void exact_scores(const float (&query)[4],
             loaded[index][part] = __ldg(key + part * 32);
         }
     }
+    float eight[8];
     #pragma unroll
-    for (int index = 0; index < BATCH; index++) {
+    for (int index = 0; index < EXACT_BATCH; index++) {
         float chain = 0.0f;
         #pragma unroll
         for (int part = 0; part < 4; part++) {
             chain = __fmaf_rn(query[part], loaded[index][part], chain);
         }
-        scores[index] = chain;
+        eight[index] = chain;
+    }
+    const bool upper_four = lane & 16, upper_two = lane & 8, upper_one = lane & 4;
+    float four[4], two[2];
+    #pragma unroll
+    for (int index = 0; index < 4; index++) {
+        const float kept = upper_four ? eight[4 + index] : eight[index];
+        const float handed = upper_four ? eight[index] : eight[4 + index];
+        four[index] = __fadd_rn(kept, __shfl_xor_sync(0xffffffffu, handed, 16));
     }
     #pragma unroll
-    for (int offset = 16; offset > 0; offset /= 2) {
-        #pragma unroll
-        for (int index = 0; index < BATCH; index++) {
-            scores[index] =
-                __fadd_rn(scores[index], __shfl_xor_sync(0xffffffffu, scores[index], offset));
-        }
+    for (int index = 0; index < 2; index++) {
+        const float kept = upper_two ? four[2 + index] : four[index];
+        const float handed = upper_two ? four[index] : four[2 + index];
+        two[index] = __fadd_rn(kept, __shfl_xor_sync(0xffffffffu, handed, 8));
     }
-    #pragma unroll
-    for (int index = 0; index < BATCH; index++) {
-        scores[index] = __fmul_rn(scores[index], scale);
-    }
+    float score = __fadd_rn(upper_one ? two[1] : two[0],
+                            __shfl_xor_sync(0xffffffffu, upper_one ? two[0] : two[1], 4));
+    score = __fadd_rn(score, __shfl_xor_sync(0xffffffffu, score, 2));
+    score = __fadd_rn(score, __shfl_xor_sync(0xffffffffu, score, 1));
+    return __fmul_rn(score, scale);
 }
 
 // Among the `count` tiles listed in `list`, whose exact scores are in `values`: the order-preserving
@@ -643,17 +654,14 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
         }
         __syncwarp();
 
-        // The open tiles scored exactly, eight at a time.
-        constexpr int BATCH = 8;
-        for (int first = 0; first < listed; first += BATCH) {
-            float scores[BATCH];
-            exact_scores<BATCH>(query, head_keys, open_tiles, first, listed - first, lane, scale,
-                                scores);
-            #pragma unroll
-            for (int index = 0; index < BATCH; index++) {
-                if (lane == index && first + index < listed) {
-                    values[open_tiles[first + index]] = scores[index];
-                }
+        // The open tiles scored exactly, eight at a time; the first of the four lanes that end
+        // with a tile's score puts it in the tile's place.
+        for (int first = 0; first < listed; first += EXACT_BATCH) {
+            const float score =
+                exact_scores(query, head_keys, open_tiles, first, listed - first, lane, scale);
+            const int index = first + lane / 4;
+            if (lane % 4 == 0 && index < listed) {
+                values[open_tiles[index]] = score;
             }
         }
         __syncwarp();
