@@ -14,8 +14,9 @@
 //
 // 1. `cosine_kernel`: all pairs on the tensor cores. tcgen05.mma kind::tf32 over the FP32 tile
 //    means (TMA into swizzled shared memory, accumulators in tensor memory) gives every score to
-//    about 2^-9 of |q| |k|. The epilogue divides by the two norms and stores the cosine as a
-//    signed 16-bit fraction in the very slot of the route table the pair owns (the table is
+//    about 2^-9 of |q| |k|. A CTA keeps a panel of query means and walks key panels through a ring
+//    of two with two accumulators. The epilogue divides by the two norms and stores the cosine as
+//    a signed 16-bit fraction in the very slot of the route table the pair owns (the table is
 //    [heads][tiles][tiles] uint16, one slot a pair), so no other scratch is needed.
 // 2. `route_kernel`: a warp per query tile. It rebuilds the approximate scores from its row of
 //    cosines, finds the bin of a 512-bin histogram that holds the kept-th largest, and from the
@@ -24,8 +25,8 @@
 //    are scored again, exactly, in the reference's FP32 order, a lane to a chain; a radix select
 //    over their order-preserving bit patterns finds the threshold among them and how many ties at
 //    it are kept; and one ballot pass over the row emits the ascending list. If the counts ever
-//    fail to add up (they cannot while the bound holds), the row is redone with every tile scored
-//    exactly.
+//    fail to add up (they cannot while the bound holds) or the open tiles outgrow their list, the
+//    row is redone with every tile scored exactly.
 // 3. `coarse_kernel`, only for gated layers: a warp per query tile walks the tiles 32 at a time
 //    with an online softmax in FP32 (this output is held to a tolerance, not to bits).
 #include <algorithm>
