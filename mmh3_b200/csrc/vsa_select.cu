@@ -214,6 +214,7 @@ __global__ void __launch_bounds__(COSINE_THREADS, 1)
             const float query_square = panel_row_square(aligned, row);
             inverse_query_norm = query_square > 0.0f ? rsqrtf(query_square) : 0.0f;
         }
+        const float query_factor = inverse_query_norm * COSINE_ONE;
         const int query_tile = first_query + row;
         const uint32_t lane_base = static_cast<uint32_t>((warp % 4) * 32) << 16;
         // Whole 16-byte groups of a row can be stored as such when every row starts on one.
@@ -255,20 +256,26 @@ __global__ void __launch_bounds__(COSINE_THREADS, 1)
                 uint32_t values[32];
                 tmem_load_32(tmem + lane_base + stage * PANEL + chunk * 32, values);
                 tmem_wait_load();
+                // product / (|q| |k|) * 32767, rounded, the two of a pair saturated into 16 bits
+                // each by one instruction (a cosine is within a rounding of +-1 already).
                 uint32_t packed[16];
                 #pragma unroll
-                for (int pair = 0; pair < 16; pair++) {
-                    int fractions[2];
+                for (int four = 0; four < 8; four++) {
+                    const float4 key_norms =
+                        *reinterpret_cast<const float4 *>(norms + chunk * 32 + four * 4);
+                    const float inverse[4] = {key_norms.x, key_norms.y, key_norms.z, key_norms.w};
+                    int fractions[4];
                     #pragma unroll
-                    for (int side = 0; side < 2; side++) {
-                        const int column = chunk * 32 + pair * 2 + side;
-                        const float cosine = __uint_as_float(values[pair * 2 + side]) *
-                                             inverse_query_norm * norms[column];
-                        fractions[side] =
-                            __float2int_rn(fminf(fmaxf(cosine, -1.0f), 1.0f) * COSINE_ONE);
+                    for (int index = 0; index < 4; index++) {
+                        fractions[index] = __float2int_rn(__uint_as_float(values[four * 4 + index]) *
+                                                          query_factor * inverse[index]);
                     }
-                    packed[pair] = (static_cast<uint32_t>(fractions[0]) & 0xffffu) |
-                                   (static_cast<uint32_t>(fractions[1]) << 16);
+                    #pragma unroll
+                    for (int pair = 0; pair < 2; pair++) {
+                        asm("cvt.pack.sat.s16.s32 %0, %1, %2;"
+                            : "=r"(packed[four * 2 + pair])
+                            : "r"(fractions[pair * 2 + 1]), "r"(fractions[pair * 2]));
+                    }
                 }
                 if (query_tile < tiles) {
                     const int column = first_key + chunk * 32;
