@@ -634,6 +634,10 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
         // Every tile's fate, and the open ones listed in ascending order: a certain tile's score
         // gives way to the infinity that stands for its fate. Everything is open when the scores
         // could not be binned, the counts do not add up or the list overflows.
+        // A bit per video tile says that it is kept: 32 consecutive tiles to a word, in the upper
+        // half of the counters, which the binning is done with.
+        uint32_t *kept_words = reinterpret_cast<uint32_t *>(bins + BINS / 2);
+        const int words = (video_tiles + 31) / 32;
         int certain = 0, listed = 0;
         for (int first = prefix_tiles; first < tiles; first += 32) {
             const int tile = first + lane;
@@ -646,7 +650,11 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
                     values[tile] = __uint_as_float(kept_for_certain ? KEPT_BITS : DROPPED_BITS);
                 }
             }
-            certain += __popc(__ballot_sync(0xffffffffu, kept_for_certain));
+            const unsigned kept_mask = __ballot_sync(0xffffffffu, kept_for_certain);
+            if (lane == 0) {
+                kept_words[(first - prefix_tiles) / 32] = kept_mask;
+            }
+            certain += __popc(kept_mask);
             const unsigned open_mask = __ballot_sync(0xffffffffu, open);
             const int slot = listed + __popc(open_mask & ((1u << lane) - 1));
             if (open && slot < LISTED) {
@@ -659,6 +667,9 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
             open_tiles.list = nullptr;
             certain = 0;
             listed = video_tiles;
+            for (int word = lane; word < words; word += 32) {
+                kept_words[word] = 0;
+            }
         }
         __syncwarp();
 
@@ -677,15 +688,15 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
         int ties;
         select_among(open_tiles, listed, values, kept - certain, bins, lane, threshold, ties);
 
-        // The prefix tiles, the certain ones, and of the open ones those above the threshold and
-        // the first `ties` at it. The list lands on the cosines it was computed from, which are
-        // all read by now.
-        int count = 0, ties_seen = 0;
-        for (int first = 0; first < tiles; first += 32) {
-            const int tile = first + lane;
-            bool keep = tile < tiles && tile < prefix_tiles;
-            bool tie = false;
-            if (tile < tiles && tile >= prefix_tiles) {
+        // Of the open tiles those above the threshold and the first `ties` at it join the kept
+        // ones: the list is in ascending order, so ties go to the lower index.
+        int ties_seen = 0;
+        for (int first = 0; first < listed; first += 32) {
+            const int index = first + lane;
+            int tile = prefix_tiles;
+            bool keep = false, tie = false;
+            if (index < listed) {
+                tile = open_tiles[index];
                 const uint32_t bits = order_preserving(values[tile]);
                 keep = bits > threshold;
                 tie = bits == threshold;
@@ -695,11 +706,38 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
                 keep = true;
             }
             ties_seen += __popc(tie_mask);
-            const unsigned keep_mask = __ballot_sync(0xffffffffu, keep);
             if (keep) {
-                route[count + __popc(keep_mask & ((1u << lane) - 1))] = static_cast<uint16_t>(tile);
+                atomicOr(&kept_words[(tile - prefix_tiles) / 32], 1u << ((tile - prefix_tiles) % 32));
             }
-            count += __popc(keep_mask);
+        }
+        __syncwarp();
+
+        // The route: the prefix tiles, then the set bits in ascending order, a lane to a word. The
+        // list lands on the cosines it was computed from, which are all read by now.
+        for (int tile = lane; tile < prefix_tiles; tile += 32) {
+            route[tile] = static_cast<uint16_t>(tile);
+        }
+        int count = prefix_tiles;
+        for (int first = 0; first < words; first += 32) {
+            const int index = first + lane;
+            uint32_t word = index < words ? kept_words[index] : 0u;
+            const int own = __popc(word);
+            int before = own;
+            #pragma unroll
+            for (int offset = 1; offset < 32; offset *= 2) {
+                const int other = __shfl_up_sync(0xffffffffu, before, offset);
+                if (lane >= offset) {
+                    before += other;
+                }
+            }
+            const int total = __shfl_sync(0xffffffffu, before, 31);
+            int position = count + before - own;
+            while (word != 0) {
+                const int bit = __ffs(word) - 1;
+                word &= word - 1;
+                route[position++] = static_cast<uint16_t>(prefix_tiles + index * 32 + bit);
+            }
+            count += total;
         }
         if (lane == 0) {
             workspace.route_counts[row] = count;
@@ -813,8 +851,8 @@ int launch_select(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int p
                   int kept, float scale, int coarse, cudaStream_t stream) {
     // The route kernel keeps a row of scores per warp in shared memory.
     const size_t shared = route_shared_bytes(tiles);
-    if (shared > 200 * 1024) {
-        return INVALID_VALUE;
+    if (shared > 200 * 1024 || tiles > 32 * (BINS / 2)) {
+        return INVALID_VALUE; // the second: a bit per tile in half of a warp's counters
     }
     unsigned int *status = status_pointer();
     if (status == nullptr) {
