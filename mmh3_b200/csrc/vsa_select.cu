@@ -366,22 +366,27 @@ __device__ __forceinline__ float warp_sum(float value) {
 // eight tiles' sums and hands the other four to its partner, at bit 3 two, at bit 2 one, so that
 // each sum is still the one the full butterfly leaves in that lane (an addition commutes) at 9
 // exchanges instead of 40. Lane l ends with the score of tile (l / 4) % 8 of the eight.
+// In three steps, so that the next eight tiles' loads can go between the second and the third.
 constexpr int EXACT_BATCH = 8;
-__device__ __forceinline__ float exact_scores(const float (&query)[4],
-                                              const float *__restrict__ head_keys,
-                                              const OpenTiles &tiles, int first, int count,
-                                              int lane, float scale) {
-    float loaded[EXACT_BATCH][4];
+// Lane l's dimensions l, l + 32, l + 64, l + 96 of the key means of the tiles first .. first + 7
+// of `tiles` (the last one again past `count`).
+__device__ __forceinline__ void load_open_keys(const float *__restrict__ head_keys,
+                                               const OpenTiles &tiles, int first, int count,
+                                               int lane, float (&loaded)[EXACT_BATCH][4]) {
     #pragma unroll
     for (int index = 0; index < EXACT_BATCH; index++) {
-        const float *key =
-            head_keys + static_cast<size_t>(tiles[first + (index < count ? index : 0)]) * HEAD_DIM + lane;
+        const int listed = min(first + index, count - 1);
+        const float *key = head_keys + static_cast<size_t>(tiles[listed]) * HEAD_DIM + lane;
         #pragma unroll
         for (int part = 0; part < 4; part++) {
             loaded[index][part] = __ldg(key + part * 32);
         }
     }
-    float eight[8];
+}
+// This lane's chains of the eight tiles.
+__device__ __forceinline__ void chain_sums(const float (&query)[4],
+                                           const float (&loaded)[EXACT_BATCH][4],
+                                           float (&eight)[EXACT_BATCH]) {
     #pragma unroll
     for (int index = 0; index < EXACT_BATCH; index++) {
         float chain = 0.0f;
@@ -391,6 +396,10 @@ __device__ __forceinline__ float exact_scores(const float (&query)[4],
         }
         eight[index] = chain;
     }
+}
+// The narrowing butterfly over the eight tiles' chains: the score of tile (lane / 4) % 8.
+__device__ __forceinline__ float narrowed_score(const float (&eight)[EXACT_BATCH], int lane,
+                                                float scale) {
     const bool upper_four = lane & 16, upper_two = lane & 8, upper_one = lane & 4;
     float four[4], two[2];
     #pragma unroll
@@ -675,12 +684,23 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
 
         // The open tiles scored exactly, eight at a time; the first of the four lanes that end
         // with a tile's score puts it in the tile's place.
-        for (int first = 0; first < listed; first += EXACT_BATCH) {
-            const float score =
-                exact_scores(query, head_keys, open_tiles, first, listed - first, lane, scale);
-            const int index = first + lane / 4;
-            if (lane % 4 == 0 && index < listed) {
-                values[open_tiles[index]] = score;
+        // The next eight tiles' loads go out as soon as these eight's chains are summed, ahead of
+        // the butterfly.
+        if (listed > 0) {
+            float loaded[EXACT_BATCH][4];
+            load_open_keys(head_keys, open_tiles, 0, listed, lane, loaded);
+            for (int first = 0; first < listed; first += EXACT_BATCH) {
+                float eight[EXACT_BATCH];
+                chain_sums(query, loaded, eight);
+                const int index = first + lane / 4;
+                const int own_tile = open_tiles[min(index, listed - 1)];
+                if (first + EXACT_BATCH < listed) {
+                    load_open_keys(head_keys, open_tiles, first + EXACT_BATCH, listed, lane, loaded);
+                }
+                const float score = narrowed_score(eight, lane, scale);
+                if (lane % 4 == 0 && index < listed) {
+                    values[own_tile] = score;
+                }
             }
         }
         __syncwarp();
