@@ -24,7 +24,7 @@
 //    above that bin), "certainly dropped" (more than 2 B below) and the few in between. Only those
 //    are scored again, exactly, in the reference's FP32 order, a lane to a chain; a radix select
 //    over their order-preserving bit patterns finds the threshold among them and how many ties at
-//    it are kept; and one ballot pass over the row emits the ascending list. If the counts ever
+//    it are kept; and the ascending list is written from a bit per kept tile. If the counts ever
 //    fail to add up (they cannot while the bound holds) or the open tiles outgrow their list, the
 //    row is redone with every tile scored exactly.
 // 3. `coarse_kernel`, only for gated layers: a warp per query tile walks the tiles 32 at a time
