@@ -56,4 +56,29 @@ __device__ __forceinline__ void score_two_keys(const float4 *__restrict__ query,
     }
 }
 
+// The xor butterfly from bit 4 down to bit 0 over eight values a lane at once, narrowing as it
+// goes: at bit 4 a lane keeps four of the eight sums and hands its partner the other four, at bit
+// 3 two, at bit 2 one, so that each sum is the one the full butterfly leaves in that lane (an
+// addition commutes) at 9 exchanges instead of 40. Lane l ends with sum (l / 4) % 8 of the eight.
+__device__ __forceinline__ float narrowed_sum(const float (&eight)[8], int lane) {
+    const bool upper_four = lane & 16, upper_two = lane & 8, upper_one = lane & 4;
+    float four[4], two[2];
+    #pragma unroll
+    for (int index = 0; index < 4; index++) {
+        const float kept = upper_four ? eight[4 + index] : eight[index];
+        const float handed = upper_four ? eight[index] : eight[4 + index];
+        four[index] = __fadd_rn(kept, __shfl_xor_sync(0xffffffffu, handed, 16));
+    }
+    #pragma unroll
+    for (int index = 0; index < 2; index++) {
+        const float kept = upper_two ? four[2 + index] : four[index];
+        const float handed = upper_two ? four[index] : four[2 + index];
+        two[index] = __fadd_rn(kept, __shfl_xor_sync(0xffffffffu, handed, 8));
+    }
+    float sum = __fadd_rn(upper_one ? two[1] : two[0],
+                          __shfl_xor_sync(0xffffffffu, upper_one ? two[0] : two[1], 4));
+    sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, 2));
+    return __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, 1));
+}
+
 } // namespace mmh3

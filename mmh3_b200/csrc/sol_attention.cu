@@ -555,16 +555,29 @@ __global__ void __launch_bounds__(OFFSET_WARPS * 32)
         (blockIdx.x * OFFSET_WARPS + static_cast<int>(threadIdx.x) / 32) * OFFSET_TOKENS;
     const float4 mean = reinterpret_cast<const float4 *>(key_mean + head * HEAD_DIM)[lane];
     const __nv_bfloat16 *column = query + head * head_stride + lane * 4;
-    for (int token = first; token < min(first + OFFSET_TOKENS, tokens); token++) {
-        const uint2 four =
-            __ldg(reinterpret_cast<const uint2 *>(column + static_cast<int64_t>(token) * token_stride));
-        float dot = __uint_as_float(four.x << 16) * mean.x;
-        dot = fmaf(__uint_as_float(four.x & 0xffff0000u), mean.y, dot);
-        dot = fmaf(__uint_as_float(four.y << 16), mean.z, dot);
-        dot = fmaf(__uint_as_float(four.y & 0xffff0000u), mean.w, dot);
-        dot = butterfly_sum(dot);
-        if (lane == 0) {
-            row_offsets[static_cast<size_t>(head) * tokens + token] = dot * log2_scale;
+    // Eight tokens at a time: their loads in flight together, and one narrowing butterfly for the
+    // eight sums (lane l ends with the sum of token (l / 4) % 8).
+    const int end = min(first + OFFSET_TOKENS, tokens);
+    for (int token = first; token < end; token += 8) {
+        uint2 loaded[8];
+        #pragma unroll
+        for (int index = 0; index < 8; index++) {
+            loaded[index] = __ldg(reinterpret_cast<const uint2 *>(
+                column + static_cast<int64_t>(min(token + index, end - 1)) * token_stride));
+        }
+        float dots[8];
+        #pragma unroll
+        for (int index = 0; index < 8; index++) {
+            const uint2 four = loaded[index];
+            float dot = __uint_as_float(four.x << 16) * mean.x;
+            dot = fmaf(__uint_as_float(four.x & 0xffff0000u), mean.y, dot);
+            dot = fmaf(__uint_as_float(four.y << 16), mean.z, dot);
+            dots[index] = fmaf(__uint_as_float(four.y & 0xffff0000u), mean.w, dot);
+        }
+        const float dot = narrowed_sum(dots, lane);
+        const int own = token + lane / 4;
+        if (lane % 4 == 0 && own < end) {
+            row_offsets[static_cast<size_t>(head) * tokens + own] = dot * log2_scale;
         }
     }
 }

@@ -33,6 +33,7 @@
 #include <cfloat>
 
 #include "common.cuh"
+#include "pooled_score.cuh"
 #include "sm100.cuh"
 
 namespace mmh3 {
@@ -400,25 +401,7 @@ __device__ __forceinline__ void chain_sums(const float (&query)[4],
 // The narrowing butterfly over the eight tiles' chains: the score of tile (lane / 4) % 8.
 __device__ __forceinline__ float narrowed_score(const float (&eight)[EXACT_BATCH], int lane,
                                                 float scale) {
-    const bool upper_four = lane & 16, upper_two = lane & 8, upper_one = lane & 4;
-    float four[4], two[2];
-    #pragma unroll
-    for (int index = 0; index < 4; index++) {
-        const float kept = upper_four ? eight[4 + index] : eight[index];
-        const float handed = upper_four ? eight[index] : eight[4 + index];
-        four[index] = __fadd_rn(kept, __shfl_xor_sync(0xffffffffu, handed, 16));
-    }
-    #pragma unroll
-    for (int index = 0; index < 2; index++) {
-        const float kept = upper_two ? four[2 + index] : four[index];
-        const float handed = upper_two ? four[index] : four[2 + index];
-        two[index] = __fadd_rn(kept, __shfl_xor_sync(0xffffffffu, handed, 8));
-    }
-    float score = __fadd_rn(upper_one ? two[1] : two[0],
-                            __shfl_xor_sync(0xffffffffu, upper_one ? two[0] : two[1], 4));
-    score = __fadd_rn(score, __shfl_xor_sync(0xffffffffu, score, 2));
-    score = __fadd_rn(score, __shfl_xor_sync(0xffffffffu, score, 1));
-    return __fmul_rn(score, scale);
+    return __fmul_rn(narrowed_sum(eight, lane), scale);
 }
 
 // Among the `count` tiles listed in `list`, whose exact scores are in `values`: the order-preserving
