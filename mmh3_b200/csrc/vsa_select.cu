@@ -753,94 +753,230 @@ __global__ void __launch_bounds__(ROUTE_THREADS, 2)
 // 3. The coarse output of a gated layer: softmax over all tiles of the pooled scores, times the
 // tiles' mean values (the workspace holds their sums).
 
-constexpr int COARSE_WARPS = 4;
-constexpr int COARSE_CHUNK = 32;   // tiles staged at a time
-constexpr int COARSE_PITCH = HEAD_DIM + 4;
+constexpr int COARSE_WARPS = 8;
+constexpr int COARSE_QUERIES = 8;                      // query tiles to a warp
+constexpr int COARSE_KEYS = 32 / COARSE_QUERIES;       // key tiles to a butterfly
+constexpr int COARSE_CHUNK = 32;    // key tiles staged at a time, twice over
+constexpr int COARSE_STAGE = 2 * COARSE_CHUNK * HEAD_DIM; // floats: the chunk's key means, its value sums
 
-__global__ void __launch_bounds__(COARSE_WARPS * 32)
+// 16 bytes from global to shared memory without passing through registers; a thread's copies
+// complete, in order, by the time its wait returns.
+__device__ __forceinline__ void copy_16_bytes_async(float *destination, const float *source) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(destination)),
+                 "l"(source)
+                 : "memory");
+}
+__device__ __forceinline__ void wait_for_own_copies() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// The sums over the 32 lanes of 32 values a lane, one sum to a lane: a xor butterfly that halves
+// what a lane holds at every step (16 + 8 + 4 + 2 + 1 exchanges). Lane l ends with the sum of
+// value l: at the step over lane bit b a lane keeps the values whose own bit b equals the lane's.
+template <int HALF>
+__device__ __forceinline__ void halve_to_own_lanes(float (&values)[32], int lane) {
+    const bool upper = lane & HALF;
+    #pragma unroll
+    for (int index = 0; index < HALF; index++) {
+        const float kept = upper ? values[HALF + index] : values[index];
+        const float handed = upper ? values[index] : values[HALF + index];
+        values[index] = kept + __shfl_xor_sync(0xffffffffu, handed, HALF);
+    }
+}
+__device__ __forceinline__ float sum_to_own_lane(float (&values)[32], int lane) {
+    halve_to_own_lanes<16>(values, lane);
+    halve_to_own_lanes<8>(values, lane);
+    halve_to_own_lanes<4>(values, lane);
+    halve_to_own_lanes<2>(values, lane);
+    halve_to_own_lanes<1>(values, lane);
+    return values[0];
+}
+
+// A CTA of eight warps takes 64 query tiles of a head, a warp eight of them, and walks the head's
+// tiles 32 at a time through two stages of shared memory (asynchronous copies, the next chunk on
+// its way while this one is used). Scores: lane l keeps dimensions 4 l .. 4 l + 3 of its warp's
+// eight query means in registers (times scale and log2 e), reads the same dimensions of a key
+// mean, and the 32 partial products of eight queries with four keys go through one halving
+// butterfly, which leaves lane l the score of query l / 4 against key l % 4 of the four. Softmax:
+// online, a lane over its query's eight scores of the chunk and the four lanes of a query
+// together. Values: the weights (over the tiles' lengths: the workspace holds sums, not means) go
+// through shared memory, eight queries' side by side, and a lane accumulates its four dimensions
+// of the eight outputs.
+__global__ void __launch_bounds__(COARSE_WARPS * 32, 2)
     coarse_kernel(Mmh3VsaWorkspace workspace, int tiles, float scale) {
-    __shared__ __align__(16) float keys[COARSE_CHUNK][COARSE_PITCH];
-    __shared__ __align__(16) float means[COARSE_CHUNK][COARSE_PITCH];
-    __shared__ __align__(16) float queries[COARSE_WARPS][HEAD_DIM];
+    extern __shared__ __align__(16) float coarse_memory[];
+    // Two stages, then per warp [COARSE_CHUNK][COARSE_QUERIES] weights and [COARSE_QUERIES]
+    // corrections, then [tiles] inverse lengths.
+    float *stages = coarse_memory;
     const int lane = threadIdx.x % 32;
     const int warp = threadIdx.x / 32;
+    float *weights = coarse_memory + 2 * COARSE_STAGE +
+                     warp * (COARSE_CHUNK + 1) * COARSE_QUERIES;
+    float *corrections = weights + COARSE_CHUNK * COARSE_QUERIES;
+    float *inverse_lengths =
+        coarse_memory + 2 * COARSE_STAGE + COARSE_WARPS * (COARSE_CHUNK + 1) * COARSE_QUERIES;
     const int head = blockIdx.y;
-    const int query_tile = blockIdx.x * COARSE_WARPS + warp;
-    const bool active = query_tile < tiles;
     const size_t head_rows = static_cast<size_t>(head) * tiles;
-    if (active) {
-        for (int part = 0; part < 4; part++) {
-            queries[warp][lane + part * 32] =
-                workspace.pooled_query[(head_rows + query_tile) * HEAD_DIM + lane + part * 32];
-        }
-    }
-    float maximum = -FLT_MAX, sum = 0.0f;
-    float outputs[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int first = 0; first < tiles; first += COARSE_CHUNK) {
-        __syncthreads();
-        // The chunk's key means, and its value sums divided by the tile lengths.
-        for (int index = threadIdx.x; index < COARSE_CHUNK * (HEAD_DIM / 4); index += COARSE_WARPS * 32) {
-            const int tile = first + index / (HEAD_DIM / 4), four = index % (HEAD_DIM / 4);
-            float4 key = make_float4(0.0f, 0.0f, 0.0f, 0.0f), mean = key;
-            if (tile < tiles) {
-                key = __ldg(reinterpret_cast<const float4 *>(workspace.pooled_key +
-                                                             (head_rows + tile) * HEAD_DIM) + four);
-                mean = __ldg(reinterpret_cast<const float4 *>(workspace.pooled_value +
-                                                              (head_rows + tile) * HEAD_DIM) + four);
-                const float inverse = 1.0f / static_cast<float>(workspace.tile_lengths[tile]);
-                mean = make_float4(mean.x * inverse, mean.y * inverse, mean.z * inverse,
-                                   mean.w * inverse);
-            }
-            *reinterpret_cast<float4 *>(&keys[index / (HEAD_DIM / 4)][four * 4]) = key;
-            *reinterpret_cast<float4 *>(&means[index / (HEAD_DIM / 4)][four * 4]) = mean;
-        }
-        __syncthreads();
-        if (!active) {
-            continue;
-        }
-        // Lane l scores tile first + l.
-        float score = 0.0f;
-        #pragma unroll 8
-        for (int four = 0; four < HEAD_DIM / 4; four++) {
-            const float4 key = *reinterpret_cast<const float4 *>(&keys[lane][four * 4]);
-            const float4 query = *reinterpret_cast<const float4 *>(&queries[warp][four * 4]);
-            score = fmaf(key.x, query.x, score);
-            score = fmaf(key.y, query.y, score);
-            score = fmaf(key.z, query.z, score);
-            score = fmaf(key.w, query.w, score);
-        }
-        score = first + lane < tiles ? score * scale : -FLT_MAX;
-        float chunk_maximum = score;
+    const int first_query = (blockIdx.x * COARSE_WARPS + warp) * COARSE_QUERIES;
+    const float *head_keys = workspace.pooled_key + head_rows * HEAD_DIM;
+    const float *head_values = workspace.pooled_value + head_rows * HEAD_DIM;
+
+    // A chunk's rows are contiguous in both arrays: 2 * 32 * 32 16-byte pieces, eight to a thread.
+    const auto stage_chunk = [&](int chunk) {
+        float *stage = stages + (chunk % 2) * COARSE_STAGE;
+        const int first = chunk * COARSE_CHUNK;
         #pragma unroll
-        for (int offset = 16; offset > 0; offset /= 2) {
-            chunk_maximum = fmaxf(chunk_maximum, __shfl_xor_sync(0xffffffffu, chunk_maximum, offset));
+        for (int turn = 0; turn < 2 * COARSE_CHUNK * (HEAD_DIM / 4) / (COARSE_WARPS * 32); turn++) {
+            const int piece = turn * COARSE_WARPS * 32 + static_cast<int>(threadIdx.x);
+            const int row = (piece / (HEAD_DIM / 4)) % COARSE_CHUNK;
+            const bool values = piece >= COARSE_CHUNK * (HEAD_DIM / 4);
+            if (first + row < tiles) {
+                copy_16_bytes_async(stage + piece * 4,
+                                    (values ? head_values : head_keys) +
+                                        static_cast<size_t>(first + row) * HEAD_DIM +
+                                        (piece % (HEAD_DIM / 4)) * 4);
+            } else {
+                // Past the last tile: zeros, which a weight of zero leaves zero.
+                *reinterpret_cast<float4 *>(stage + piece * 4) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+        }
+    };
+    stage_chunk(0);
+    for (int tile = threadIdx.x; tile < tiles; tile += COARSE_WARPS * 32) {
+        inverse_lengths[tile] = 1.0f / static_cast<float>(workspace.tile_lengths[tile]);
+    }
+    float4 queries[COARSE_QUERIES];
+    const float factor = scale * LOG2_E;
+    #pragma unroll
+    for (int query = 0; query < COARSE_QUERIES; query++) {
+        float4 four = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (first_query + query < tiles) {
+            four = __ldg(reinterpret_cast<const float4 *>(
+                             workspace.pooled_query + (head_rows + first_query + query) * HEAD_DIM) +
+                         lane);
+        }
+        queries[query] = make_float4(four.x * factor, four.y * factor, four.z * factor, four.w * factor);
+    }
+    // This lane's query (lane / 4) and its keys of a chunk (lane % 4 of every four).
+    float maximum = -FLT_MAX, sum = 0.0f;
+    float4 outputs[COARSE_QUERIES];
+    #pragma unroll
+    for (int query = 0; query < COARSE_QUERIES; query++) {
+        outputs[query] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    const int chunks = (tiles + COARSE_CHUNK - 1) / COARSE_CHUNK;
+    for (int chunk = 0; chunk < chunks; chunk++) {
+        wait_for_own_copies();
+        __syncthreads();
+        if (chunk + 1 < chunks) {
+            stage_chunk(chunk + 1);
+        }
+        const float4 *keys = reinterpret_cast<const float4 *>(stages + (chunk % 2) * COARSE_STAGE);
+        const float4 *values = keys + COARSE_CHUNK * (HEAD_DIM / 4);
+        const int first = chunk * COARSE_CHUNK;
+
+        float scores[COARSE_CHUNK / COARSE_KEYS];
+        #pragma unroll
+        for (int group = 0; group < COARSE_CHUNK / COARSE_KEYS; group++) {
+            float partial[32];
+            #pragma unroll
+            for (int key = 0; key < COARSE_KEYS; key++) {
+                const float4 four = keys[(group * COARSE_KEYS + key) * (HEAD_DIM / 4) + lane];
+                #pragma unroll
+                for (int query = 0; query < COARSE_QUERIES; query++) {
+                    partial[query * COARSE_KEYS + key] =
+                        fmaf(queries[query].w, four.w,
+                             fmaf(queries[query].z, four.z,
+                                  fmaf(queries[query].y, four.y, queries[query].x * four.x)));
+                }
+            }
+            const float score = sum_to_own_lane(partial, lane);
+            scores[group] =
+                first + group * COARSE_KEYS + lane % COARSE_KEYS < tiles ? score : -FLT_MAX;
+        }
+        // The chunk's maximum for this lane's query, over the lane's eight keys and the four lanes.
+        float chunk_maximum = scores[0];
+        #pragma unroll
+        for (int group = 1; group < COARSE_CHUNK / COARSE_KEYS; group++) {
+            chunk_maximum = fmaxf(chunk_maximum, scores[group]);
+        }
+        #pragma unroll
+        for (int reach = 1; reach < COARSE_KEYS; reach *= 2) {
+            chunk_maximum = fmaxf(chunk_maximum, __shfl_xor_sync(0xffffffffu, chunk_maximum, reach));
         }
         const float raised = fmaxf(maximum, chunk_maximum);
-        const float correction = expf(maximum - raised);
+        const float correction = exp2f(maximum - raised);
         maximum = raised;
-        const float weight = first + lane < tiles ? expf(score - maximum) : 0.0f;
-        sum = sum * correction + warp_sum(weight);
+        float chunk_sum = 0.0f;
         #pragma unroll
-        for (int part = 0; part < 4; part++) {
-            outputs[part] *= correction;
+        for (int group = 0; group < COARSE_CHUNK / COARSE_KEYS; group++) {
+            const int key = group * COARSE_KEYS + lane % COARSE_KEYS;
+            const float weight = first + key < tiles ? exp2f(scores[group] - maximum) : 0.0f;
+            chunk_sum += weight;
+            weights[key * COARSE_QUERIES + lane / COARSE_KEYS] =
+                weight * inverse_lengths[min(first + key, tiles - 1)];
         }
-        // Lane l accumulates dimensions l, l + 32, l + 64, l + 96.
-        #pragma unroll 8
-        for (int tile = 0; tile < COARSE_CHUNK; tile++) {
-            const float shared_weight = __shfl_sync(0xffffffffu, weight, tile);
+        #pragma unroll
+        for (int reach = 1; reach < COARSE_KEYS; reach *= 2) {
+            chunk_sum += __shfl_xor_sync(0xffffffffu, chunk_sum, reach);
+        }
+        sum = sum * correction + chunk_sum;
+        if (lane % COARSE_KEYS == 0) {
+            corrections[lane / COARSE_KEYS] = correction;
+        }
+        __syncwarp();
+        {
+            float all[COARSE_QUERIES];
             #pragma unroll
-            for (int part = 0; part < 4; part++) {
-                outputs[part] = fmaf(shared_weight, means[tile][lane + part * 32], outputs[part]);
+            for (int four = 0; four < COARSE_QUERIES / 4; four++) {
+                const float4 loaded = *reinterpret_cast<const float4 *>(corrections + four * 4);
+                all[four * 4] = loaded.x, all[four * 4 + 1] = loaded.y;
+                all[four * 4 + 2] = loaded.z, all[four * 4 + 3] = loaded.w;
+            }
+            #pragma unroll
+            for (int query = 0; query < COARSE_QUERIES; query++) {
+                outputs[query].x *= all[query];
+                outputs[query].y *= all[query];
+                outputs[query].z *= all[query];
+                outputs[query].w *= all[query];
             }
         }
+        #pragma unroll 4
+        for (int key = 0; key < COARSE_CHUNK; key++) {
+            const float4 four = values[key * (HEAD_DIM / 4) + lane];
+            float all[COARSE_QUERIES];
+            #pragma unroll
+            for (int four = 0; four < COARSE_QUERIES / 4; four++) {
+                const float4 loaded =
+                    *reinterpret_cast<const float4 *>(weights + key * COARSE_QUERIES + four * 4);
+                all[four * 4] = loaded.x, all[four * 4 + 1] = loaded.y;
+                all[four * 4 + 2] = loaded.z, all[four * 4 + 3] = loaded.w;
+            }
+            #pragma unroll
+            for (int query = 0; query < COARSE_QUERIES; query++) {
+                outputs[query].x = fmaf(all[query], four.x, outputs[query].x);
+                outputs[query].y = fmaf(all[query], four.y, outputs[query].y);
+                outputs[query].z = fmaf(all[query], four.z, outputs[query].z);
+                outputs[query].w = fmaf(all[query], four.w, outputs[query].w);
+            }
+        }
+        __syncwarp();
     }
-    if (active) {
-        const float inverse = 1.0f / sum;
-        for (int part = 0; part < 4; part++) {
-            workspace.coarse[(head_rows + query_tile) * HEAD_DIM + lane + part * 32] =
-                outputs[part] * inverse;
+    #pragma unroll
+    for (int query = 0; query < COARSE_QUERIES; query++) {
+        const float inverse = 1.0f / __shfl_sync(0xffffffffu, sum, query * COARSE_KEYS);
+        if (first_query + query < tiles) {
+            reinterpret_cast<float4 *>(workspace.coarse +
+                                       (head_rows + first_query + query) * HEAD_DIM)[lane] =
+                make_float4(outputs[query].x * inverse, outputs[query].y * inverse,
+                            outputs[query].z * inverse, outputs[query].w * inverse);
         }
     }
+}
+
+size_t coarse_shared_bytes(int tiles) {
+    return sizeof(float) * (2 * COARSE_STAGE + COARSE_WARPS * (COARSE_CHUNK + 1) * COARSE_QUERIES +
+                            static_cast<size_t>(tiles));
 }
 
 size_t route_shared_bytes(int tiles) {
@@ -917,7 +1053,22 @@ int launch_select(const Mmh3VsaWorkspace &workspace, int tiles, int heads, int p
     if (launched != cudaSuccess || !coarse) {
         return static_cast<int>(launched);
     }
-    coarse_kernel<<<dim3((tiles + COARSE_WARPS - 1) / COARSE_WARPS, heads), COARSE_WARPS * 32, 0,
+    const size_t coarse_shared = coarse_shared_bytes(tiles);
+    if (coarse_shared > 200 * 1024) {
+        return INVALID_VALUE;
+    }
+    static std::atomic<size_t> coarse_configured[MAX_DEVICES];
+    if (coarse_shared > coarse_configured[device].load(std::memory_order_relaxed)) {
+        const cudaError_t raised =
+            cudaFuncSetAttribute(coarse_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(coarse_shared));
+        if (raised != cudaSuccess) {
+            return static_cast<int>(raised);
+        }
+        coarse_configured[device].store(coarse_shared, std::memory_order_relaxed);
+    }
+    const int per_cta = COARSE_WARPS * COARSE_QUERIES;
+    coarse_kernel<<<dim3((tiles + per_cta - 1) / per_cta, heads), COARSE_WARPS * 32, coarse_shared,
                     stream>>>(workspace, tiles, scale);
     return static_cast<int>(cudaGetLastError());
 }
