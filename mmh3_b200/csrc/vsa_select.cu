@@ -27,8 +27,9 @@
 //    it are kept; and the ascending list is written from a bit per kept tile. If the counts ever
 //    fail to add up (they cannot while the bound holds) or the open tiles outgrow their list, the
 //    row is redone with every tile scored exactly.
-// 3. `coarse_kernel`, only for gated layers: a warp per query tile walks the tiles 32 at a time
-//    with an online softmax in FP32 (this output is held to a tolerance, not to bits).
+// 3. `coarse_kernel`, only for gated layers: eight query tiles to a warp in registers, the tiles
+//    32 at a time through shared memory, an online softmax in FP32 (this output is held to a
+//    tolerance, not to bits).
 #include <algorithm>
 #include <cfloat>
 
