@@ -652,19 +652,6 @@ def run_sol(torch, attention, qkv, output, tokens, heads, scale, steps) -> dict:
         entries = ((routes[head].to(torch.int64) & 0xFFFF) * mask).clamp_(0, blocks - 1)
         routed_keys[head] = (lengths[entries] * mask).sum(dim=1)
     sparse_flops = float((routed_keys * lengths[None, :]).sum().item()) * 4.0 * HEAD_DIM
-    # The same layer with the gate of the coarse branch, as VSA-trained checkpoints run it: the
-    # selection also leaves softmax(pooled scores) . mean values, which the token attention adds
-    # to its rows times the gate.
-    gate = torch.randn((tokens, heads * HEAD_DIM), dtype=torch.bfloat16, device="cuda",
-                       generator=torch.Generator(device="cuda").manual_seed(4))
-
-    def whole_gated():
-        attention.vsa(qkv, gate, output, vsa_layout, scale, kept, workspace)
-
-    whole_gated()
-    gated_ms = time_region(torch, whole_gated, steps)
-    gated_kernels = kernel_times(torch, whole_gated)
-    del gate
     return {
         "workload": f"Sol-Attn L={tokens}, H={heads}, tau 1.3, 8 prefix blocks exact",
         "ms": ms, "sparse_flops": sparse_flops, "sparse_tflops": sparse_flops / ms / 1e9,
