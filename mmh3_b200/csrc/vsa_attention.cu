@@ -118,6 +118,7 @@ struct VsaParams {
     int tiles;
     float scale_log2;
     int vector_stores;
+    int vector_gates; // gate rows start on 16 bytes
     unsigned int *status;
 };
 
@@ -698,18 +699,50 @@ __global__ void __launch_bounds__(THREADS, 2)
                         results[index] = __uint_as_float(values[index]) * inverse;
                     }
                     if (gated) {
+                        // 32 gates (eight to a 16-byte load where the rows allow it) times the
+                        // tile's 32 coarse values.
+                        float gates[32];
+                        if (p.vector_gates) {
+                            #pragma unroll
+                            for (int part = 0; part < 4; part++) {
+                                const uint4 eight =
+                                    __ldg(reinterpret_cast<const uint4 *>(gate_row + chunk * 32) + part);
+                                const uint32_t words[4] = {eight.x, eight.y, eight.z, eight.w};
+                                #pragma unroll
+                                for (int word = 0; word < 4; word++) {
+                                    gates[part * 8 + word * 2] = __uint_as_float(words[word] << 16);
+                                    gates[part * 8 + word * 2 + 1] =
+                                        __uint_as_float(words[word] & 0xffff0000u);
+                                }
+                            }
+                        } else {
+                            #pragma unroll
+                            for (int index = 0; index < 32; index++) {
+                                gates[index] = __bfloat162float(gate_row[chunk * 32 + index]);
+                            }
+                        }
                         #pragma unroll
-                        for (int index = 0; index < 32; index++) {
-                            results[index] =
-                                fmaf(__bfloat162float(gate_row[chunk * 32 + index]),
-                                     __ldg(coarse + chunk * 32 + index), results[index]);
+                        for (int part = 0; part < 8; part++) {
+                            const float4 four =
+                                __ldg(reinterpret_cast<const float4 *>(coarse + chunk * 32) + part);
+                            results[part * 4] = fmaf(gates[part * 4], four.x, results[part * 4]);
+                            results[part * 4 + 1] =
+                                fmaf(gates[part * 4 + 1], four.y, results[part * 4 + 1]);
+                            results[part * 4 + 2] =
+                                fmaf(gates[part * 4 + 2], four.z, results[part * 4 + 2]);
+                            results[part * 4 + 3] =
+                                fmaf(gates[part * 4 + 3], four.w, results[part * 4 + 3]);
                         }
                     }
                     if (tailed) {
                         #pragma unroll
-                        for (int index = 0; index < 32; index++) {
-                            results[index] = fmaf(__ldg(tail_values + chunk * 32 + index),
-                                                  tail_weight, results[index]);
+                        for (int part = 0; part < 8; part++) {
+                            const float4 four = __ldg(
+                                reinterpret_cast<const float4 *>(tail_values + chunk * 32) + part);
+                            results[part * 4] = fmaf(four.x, tail_weight, results[part * 4]);
+                            results[part * 4 + 1] = fmaf(four.y, tail_weight, results[part * 4 + 1]);
+                            results[part * 4 + 2] = fmaf(four.z, tail_weight, results[part * 4 + 2]);
+                            results[part * 4 + 3] = fmaf(four.w, tail_weight, results[part * 4 + 3]);
                         }
                     }
                     uint32_t packed[16];
@@ -782,6 +815,8 @@ bool fill_params(VsaParams &params, void *output, int tokens, const Mmh3Attentio
     params.tokens = tokens;
     params.tiles = tiles;
     params.scale_log2 = scale * LOG2_E;
+    params.vector_gates = gate != nullptr && reinterpret_cast<uintptr_t>(gate) % 16 == 0 &&
+                          gate_stride % 8 == 0;
     params.vector_stores = reinterpret_cast<uintptr_t>(output) % 16 == 0 &&
                            layout.token_stride[OUTPUT] % 8 == 0 &&
                            layout.head_stride[OUTPUT] % 8 == 0;
