@@ -217,6 +217,42 @@ def test_video_sparse_attention_at_the_benchmark_size(reference_kernels, video_c
            milliseconds(reference_call))
 
 
+def test_gated_video_sparse_attention_at_the_benchmark_size(reference_kernels, video_case):
+    """The same layer with the gate of the coarse branch: the coarse output of all 2,024 x 32 query
+    tiles to 1e-4 of the reference kernel's, the routes its bits, the gated output close."""
+    plan, tokens, kept, qkv = video_case
+    generator = torch.Generator(device="cuda").manual_seed(5)
+    gate = torch.randn((tokens, INNER), generator=generator, device="cuda").bfloat16()
+    ours = torch.zeros((tokens, HEADS, 128), dtype=torch.bfloat16, device="cuda")
+    theirs = torch.zeros_like(ours)
+    workspace = attention.VsaWorkspace(plan, tokens, HEADS)
+    other = attention.VsaWorkspace(plan, tokens, HEADS)
+    vsa_layout = attention.qkv_layout(HEADS)
+    attention.vsa(qkv, gate, ours, vsa_layout, SCALE, kept, workspace)
+    raw = other.raw()
+    base = qkv.data_ptr()
+    def reference_call():
+        assert reference_kernels.mmh3_vsa_attention(
+            base, base + 2 * INNER, base + 4 * INNER, gate.data_ptr(), INNER, theirs.data_ptr(),
+            tokens, HEADS, ctypes.byref(vsa_layout), SCALE, plan.tiles, plan.prefix_tiles, kept,
+            ctypes.byref(raw), None, 0, None) == 0
+
+    reference_call()
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    assert torch.equal(workspace.route_counts, other.route_counts)
+    valid = (torch.arange(plan.tiles, device="cuda")[None, :] <
+             workspace.route_counts.view(-1, 1))
+    assert torch.equal(workspace.routes.view(-1, plan.tiles)[valid],
+                       other.routes.view(-1, plan.tiles)[valid])
+    assert torch.allclose(workspace.coarse, other.coarse, rtol=1e-4, atol=1e-5)
+    assert cosine(ours, theirs) >= 0.9995
+    assert torch.max(torch.abs(ours.float() - theirs.float())).item() <= 2e-2
+    report("gated VSA, L=125,504, H=32, 252 of 2,016 video tiles kept",
+           milliseconds(lambda: attention.vsa(qkv, gate, ours, vsa_layout, SCALE, kept, workspace)),
+           milliseconds(reference_call))
+
+
 def test_quantized_video_sparse_attention_at_the_benchmark_size(reference_kernels, video_case):
     """The INT8/FP8 form of the same layer, as the DiT calls it with inputs_ready = 2: both
     libraries prepare their own copy of the rows (norm, INT8 q/k, FP8 V, pooled tiles), select and
