@@ -591,6 +591,16 @@ __global__ void __launch_bounds__(THREADS, 2)
         for (int step = 0; step < steps; step++) {
             int tiles_now[2];
             const StepKind kind = next_step(step, cursors, tiles_now);
+            // What the step's key tiles bring (their lengths, and their scales in INT8) is read
+            // while the scores are still being taken.
+            const int first_tile = tiles_now[0], second_tile = tiles_now[1];
+            const int first_valid = first_tile >= 0 ? tile_length(first_tile) : 0;
+            const int second_valid = second_tile >= 0 ? tile_length(second_tile) : 0;
+            float first_factor = query_factor, second_factor = query_factor;
+            if constexpr (QUANTIZED) {
+                first_factor *= first_tile >= 0 ? __ldg(head_key_scales + first_tile) : 0.0f;
+                second_factor *= second_tile >= 0 ? __ldg(head_key_scales + second_tile) : 0.0f;
+            }
             alive = mbar_wait(barrier(S::SCORES_FULL), step & 1, watchdog, STATUS_VSA | 7);
             alive = __all_sync(0xffffffffu, alive);
             if (!alive) {
@@ -608,13 +618,9 @@ __global__ void __launch_bounds__(THREADS, 2)
                 const bool probability_phase = kind != BOTH_BOTH || pass >= 2;
                 const int slot = kind == OWN ? half : pass % 2;
                 const bool shared = kind != OWN;
-                const int key_tile = tiles_now[slot];
-                const bool active = key_tile >= 0;
-                const int valid = active ? tile_length(key_tile) : 0;
-                float factor = query_factor;
-                if constexpr (QUANTIZED) {
-                    factor *= active ? __ldg(head_key_scales + key_tile) : 0.0f;
-                }
+                const bool active = (slot == 0 ? first_tile : second_tile) >= 0;
+                const int valid = slot == 0 ? first_valid : second_valid;
+                const float factor = slot == 0 ? first_factor : second_factor;
                 const uint32_t scores = score_columns + slot * TILE;
                 const uint32_t own_p = score_columns + slot * P_COLUMNS;
                 const uint32_t other_p = score_columns + (1 - half) * P_COLUMNS;
