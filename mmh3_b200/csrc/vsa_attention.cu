@@ -48,6 +48,9 @@ constexpr int THREADS = (SOFTMAX_WARPS + 2) * 32;
 // key tiles both lists hold are walked once for both query tiles; longer sequences pair the lists
 // entry by entry only.
 constexpr int MAX_BITMAP_TILES = 16384;
+// Route lists of up to this many tiles are sorted into the schedule's lists once per CTA; longer
+// ones are walked entry by entry as the steps come.
+constexpr int TABLE_ENTRIES = 1024;
 constexpr uint32_t TMEM_COLUMNS = 256;
 constexpr uint32_t TMEM_SCORES = 0;
 constexpr uint32_t TMEM_OUTPUT = 128;
@@ -74,7 +77,9 @@ template <bool QUANTIZED> struct Shape {
     static constexpr int SMEM_BARRIERS = SMEM_RING + STAGES * TILE_BYTES;
     // After the barriers: one bit per tile for each of the CTA's two route lists.
     static constexpr int SMEM_BITMAPS = SMEM_BARRIERS + 256;
-    static constexpr int SMEM_BYTES = SMEM_BITMAPS + 2 * (MAX_BITMAP_TILES / 8) + 1024;
+    // Then the schedule's three lists of tiles (common, only in list 0, only in list 1).
+    static constexpr int SMEM_TABLES = SMEM_BITMAPS + 2 * (MAX_BITMAP_TILES / 8);
+    static constexpr int SMEM_BYTES = SMEM_TABLES + 3 * TABLE_ENTRIES * 2 + 1024;
     static constexpr int QUERY_FULL = 0;
     static constexpr int RING_FULL = 1;
     static constexpr int RING_EMPTY = RING_FULL + STAGES;
@@ -195,6 +200,39 @@ __global__ void __launch_bounds__(THREADS, 2)
         __syncthreads();
     }
     const int common = compared ? common_tiles : 0;
+    // The schedule's lists, in ascending order as the route lists are: the tiles both lists hold,
+    // and each list's own. A warp to a list, 32 entries at a time; every role then reads a step's
+    // tiles from shared memory instead of walking the route lists in global memory against the
+    // bitmaps as the steps come.
+    uint16_t *tables = reinterpret_cast<uint16_t *>(aligned + S::SMEM_TABLES);
+    const bool tabled = compared && counts[0] <= TABLE_ENTRIES && counts[1] <= TABLE_ENTRIES;
+    if (tabled) {
+        if (warp < 3) {
+            const int half = warp == 2 ? 1 : 0;
+            const bool want_common = warp == 0;
+            uint16_t *table = tables + warp * TABLE_ENTRIES;
+            int written = 0;
+            const int entries = half ? counts[1] : counts[0];
+            const uint16_t *list = half ? lists[1] : lists[0];
+            for (int first = 0; first < entries; first += 32) {
+                const int entry = first + lane;
+                int tile = 0;
+                bool keep = false;
+                if (entry < entries) {
+                    tile = list[entry];
+                    const bool in_other =
+                        (bitmaps[(1 - half) * BITMAP_WORDS + tile / 32] >> (tile % 32)) & 1u;
+                    keep = in_other == want_common;
+                }
+                const unsigned kept = __ballot_sync(0xffffffffu, keep);
+                if (keep) {
+                    table[written + __popc(kept & ((1u << lane) - 1))] = static_cast<uint16_t>(tile);
+                }
+                written += __popc(kept);
+            }
+        }
+        __syncthreads();
+    }
     // The schedule every role walks. First the `common` tiles, two to a step (both query tiles
     // against both key tiles: a full 128 x 128 block of S), then the odd one left over alone (a
     // 128 x 64 block), then the remaining entries of the two lists paired in order, each query
@@ -218,6 +256,17 @@ __global__ void __launch_bounds__(THREADS, 2)
     // (the next entries that list 1 also holds); BOTH_ONE fills only tiles[0].
     auto next_step = [&](int step, Cursors &cursors, int (&tiles)[2]) {
         const StepKind kind = step_kind(step);
+        if (tabled) {
+            if (kind == OWN) {
+                const int index = step - double_steps - single_steps;
+                tiles[0] = index < counts[0] - common ? tables[TABLE_ENTRIES + index] : -1;
+                tiles[1] = index < counts[1] - common ? tables[2 * TABLE_ENTRIES + index] : -1;
+            } else {
+                tiles[0] = tables[2 * step];
+                tiles[1] = kind == BOTH_BOTH ? tables[2 * step + 1] : -1;
+            }
+            return kind;
+        }
         if (kind != OWN) {
             int entry = cursors.at[0];
             for (int slot = 0; slot < (kind == BOTH_BOTH ? 2 : 1); slot++) {
@@ -441,7 +490,12 @@ __global__ void __launch_bounds__(THREADS, 2)
         // Softmax: this thread owns row `row` of the pair, which is row `row % 64` of tile `half`.
         const int row = warp * 32 + lane;
         const int half = row / TILE;
-        const int count = counts[half];
+        // This thread's tile of the two, picked once: indexing the pairs with `half` would put
+        // them in local memory.
+        const int count = half ? counts[1] : counts[0];
+        const bool own_exists = half ? exists[1] : exists[0];
+        const int own_query_tile = half ? query_tiles[1] : query_tiles[0];
+        const size_t own_route_row = half ? route_rows[1] : route_rows[0];
         const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
         // The 64 columns of S that hold this tile's keys, and where its P goes: BF16 P packs two
         // keys to a column (own keys in 32 columns), E4M3 P four (16 columns).
@@ -453,7 +507,7 @@ __global__ void __launch_bounds__(THREADS, 2)
         float query_factor = p.scale_log2;
         const float *head_key_scales = nullptr;
         if constexpr (QUANTIZED) {
-            query_factor *= exists[half] ? p.query_scales[route_rows[half]] : 0.0f;
+            query_factor *= own_exists ? p.query_scales[own_route_row] : 0.0f;
             head_key_scales = p.key_scales + static_cast<size_t>(head) * p.tiles;
         }
         float maximum = -INFINITY;
@@ -658,8 +712,8 @@ __global__ void __launch_bounds__(THREADS, 2)
             tcgen05_fence_after();
             const int tile_row = row % TILE;
             const bool stored =
-                exists[half] && tile_row < tile_length(query_tiles[half]) && count > 0;
-            const int64_t token = stored ? tile_start(query_tiles[half]) + tile_row : 0;
+                own_exists && tile_row < tile_length(own_query_tile) && count > 0;
+            const int64_t token = stored ? tile_start(own_query_tile) + tile_row : 0;
             const float sum = (sums[0].x + sums[0].y) + (sums[1].x + sums[1].y);
             float value_scale = 1.0f;
             if constexpr (QUANTIZED) {
@@ -670,19 +724,19 @@ __global__ void __launch_bounds__(THREADS, 2)
             // sum arrives as a softmax state (maximum, sum of weights, weighted values) in the
             // units of the centred scores, which this row's scores reach by its offset.
             const bool tailed = p.tail_max != nullptr;
-            const float *tail_values = tailed ? p.tail_values + route_rows[half] * HEAD_DIM : nullptr;
+            const float *tail_values = tailed ? p.tail_values + own_route_row * HEAD_DIM : nullptr;
             float tail_weight = 0.0f;
             if (tailed && stored) {
                 const float centred =
                     maximum - p.row_offsets[static_cast<size_t>(head) * p.tokens + token];
-                const float tail_maximum = p.tail_max[route_rows[half]];
+                const float tail_maximum = p.tail_max[own_route_row];
                 const float merged = fmaxf(centred, tail_maximum);
                 const float routed_weight = exp2f(centred - merged);
                 // E4M3 probabilities, and with them the sum and O, carry a factor of 224.
                 constexpr float CARRIED = QUANTIZED ? 224.0f : 1.0f;
                 tail_weight = CARRIED * exp2f(tail_maximum - merged);
                 const float total =
-                    1.0f / (sum * routed_weight + p.tail_sum[route_rows[half]] * tail_weight);
+                    1.0f / (sum * routed_weight + p.tail_sum[own_route_row] * tail_weight);
                 tail_weight *= total;
                 inverse = value_scale * routed_weight * total;
             }
@@ -692,7 +746,7 @@ __global__ void __launch_bounds__(THREADS, 2)
             const __nv_bfloat16 *gate_row =
                 gated ? p.gate + token * p.gate_stride + static_cast<int64_t>(head) * HEAD_DIM
                       : nullptr;
-            const float *coarse = gated ? p.coarse + route_rows[half] * HEAD_DIM : nullptr;
+            const float *coarse = gated ? p.coarse + own_route_row * HEAD_DIM : nullptr;
             #pragma unroll
             for (int chunk = 0; chunk < 4; chunk++) {
                 uint32_t values[32];
