@@ -322,3 +322,34 @@ def test_a_row_of_equal_scores_longer_than_the_list_of_open_tiles(reference_kern
     a = output.float().cpu().numpy().astype(np.float64).ravel()
     b = reference_output.float().cpu().numpy().astype(np.float64).ravel()
     assert np.max(np.abs(a - b)) < 0.05
+
+
+def test_route_lists_longer_than_the_schedule_tables(reference_kernels):
+    """With 70 % of the benchmark plan's 2,016 video tiles kept a route list holds over 1,400
+    tiles, more than the token attention sorts into shared memory once per CTA: it then walks the
+    lists entry by entry as the steps come. Routes and output against the reference's kernels."""
+    layout, plan = synthetic.video_plan()
+    tokens, heads = len(layout), 1
+    inner = heads * 128
+    kept = plan.kept_video_tiles(0.3)
+    assert kept > 1024
+    qkv = synthetic.video_qkv_device(layout, plan, heads, seed=13)
+    output = torch.zeros((tokens, heads, 128), dtype=torch.bfloat16, device="cuda")
+    reference_output = torch.zeros_like(output)
+    workspace = attention.VsaWorkspace(plan, tokens, heads)
+    theirs = attention.VsaWorkspace(plan, tokens, heads)
+    vsa_layout = attention.qkv_layout(heads)
+    attention.vsa(qkv, None, output, vsa_layout, SCALE, kept, workspace)
+    raw = theirs.raw()
+    base = qkv.data_ptr()
+    assert reference_kernels.mmh3_vsa_attention(
+        base, base + 2 * inner, base + 4 * inner, None, inner, reference_output.data_ptr(), tokens,
+        heads, ctypes.byref(vsa_layout), SCALE, plan.tiles, plan.prefix_tiles, kept,
+        ctypes.byref(raw), None, 0, None) == 0
+    torch.cuda.synchronize()
+    assert attention.take_status() == 0
+    assert_routes_equal(*workspace.routes_host(), *theirs.routes_host())
+    a = output.float().cpu().numpy().astype(np.float64).ravel()
+    b = reference_output.float().cpu().numpy().astype(np.float64).ravel()
+    assert np.max(np.abs(a - b)) < 0.05
+    assert a @ b / (np.linalg.norm(a) * np.linalg.norm(b)) >= 0.9995
